@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the Granite 4.2 8B layer-glue kernels on B200.
+
+Workload (the box-scale sweep the headline metric is quoted on): 65536 token rows, sharded
+by rows over the N GPUs of one node, each shard running the full 40-layer glue sequence
+(per layer: residual add + RMSNorm -> FP8, RoPE + int8 paged KV write, residual add +
+RMSNorm -> FP8, SwiGLU -> FP8; then the final norm) on seeded random bf16 activations of
+Granite 8B shape. No collective on the data path; NCCL only carries the timing reduction.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+prints ONE JSON line (rank 0). `value` is whole-job tokens/s with inputs resident in HBM;
+`roofline` is the dominant op's algorithmic bytes over its CUDA-event time; `e2e` is the same
+sequence through the host-buffer C-ABI entry point (host<->device copies inside the timed
+region); `cpu_baseline` is the reference's CPU formulation on this box's cores.
+`--impl reference` times only that CPU formulation and prints the reference arm's line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOTAL_TOKENS = 65536
+METRIC = "layer_glue_tokens_per_s"
+UNIT = "tokens/s"
+WORKLOAD = ("box-scale sweep: 65536 tokens row-sharded, 40-layer glue sequence "
+            "(2x add+RMSNorm->FP8, RoPE+int8 paged KV, SwiGLU->FP8 per layer, final norm), "
+            "Granite 8B shapes H4096/I12800/32q/8kv/d128")
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, MEASURED_PEAKS.json absent)"
+
+
+# ------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.lines, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()  # the exact process started above
+        sm, smax, reasons = [], None, set()
+        for ts, line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                clock, cmax = float(f[1]), float(f[2])
+            except ValueError:
+                continue
+            smax = cmax
+            if t0 - 0.05 <= ts <= t1 + 0.15:
+                sm.append(clock)
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                      "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        if not sm:  # region shorter than one sample: take what there is
+            sm = [float(l.split(",")[1]) for _, l in self.lines[-3:] if len(l.split(",")) > 2] or [0.0]
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------- CPU arm
+def np_f32_to_bf16(a):
+    import numpy as np
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
+class CpuGlue:
+    """The same layer sequence on the host cores, through the oracle library (the reference's
+    own compiled host code when oracle/_ref is present, else the C port). Rows are split over
+    threads; the per-tensor FP8 amax is the max of the threads' maxima."""
+
+    def __init__(self, rows: int, layers: int, threads: int):
+        import numpy as np
+        from oracle import g4_oracle
+        self.np, self.g4 = np, g4_oracle
+        self.kind = "reference" if g4_oracle.available("reference") else "port"
+        self.lib = g4_oracle.load(self.kind)
+        self.rows, self.layers, self.threads = rows, layers, max(1, min(threads, rows))
+        rng = np.random.default_rng(0)
+
+        def randn(*shape):
+            return np_f32_to_bf16(rng.standard_normal(shape, dtype=np.float32))
+        H, I, self.Hq, self.Hk, self.d = 4096, 12800, 32, 8, 128
+        self.buf = {"y_attn": randn(rows, H), "y_mlp": randn(rows, H), "qkv": randn(rows, 6144),
+                    "gate": randn(rows, I), "up": randn(rows, I)}
+        self.h0 = randn(rows, H)
+        self.w = np_f32_to_bf16(1.0 + 0.02 * rng.standard_normal((2, H), dtype=np.float32))
+        self.cos, self.sin = self.lib.rope_tables(1e7, 128, rows)
+        self.pos = np.arange(rows, dtype=np.int32)
+        self.caches = (np.zeros((8, rows, 128), np.int8), np.zeros((8, rows, 128), np.int8),
+                       np.zeros((8, rows), np.float32), np.zeros((8, rows), np.float32))
+
+    def _quant(self, x):
+        lib, par = self.lib, self.g4.parallel_rows
+        amax = max(par(lambda lo, hi: lib.amax_bf16(x[lo:hi]), self.rows, self.threads))
+        scale = lib.fp8_scale_from_amax(amax)
+        par(lambda lo, hi: lib.quant_fp8_with_scale(x[lo:hi], scale), self.rows, self.threads)
+
+    def step(self):
+        lib, par, b = self.lib, self.g4.parallel_rows, self.buf
+        h = self.h0
+        for _ in range(self.layers):
+            for y, w in ((b["y_attn"], self.w[0]), (b["y_mlp"], self.w[1])):
+                parts = par(lambda lo, hi: lib.add_rmsnorm(y[lo:hi], h[lo:hi], w, 1e-5, 0.22), self.rows,
+                            self.threads)
+                h = self.np.concatenate([p[0] for p in parts])
+                self._quant(self.np.concatenate([p[1] for p in parts]))
+                if y is b["y_attn"]:
+                    par(lambda lo, hi: lib.rope_kv_int8(b["qkv"][lo:hi], self.cos, self.sin, self.pos[lo:hi],
+                                                        self.pos[lo:hi], self.Hq, self.Hk, self.d, self.rows, 0,
+                                                        self.caches), self.rows, self.threads)
+            act = self.np.concatenate(par(lambda lo, hi: lib.swiglu(b["gate"][lo:hi], b["up"][lo:hi]),
+                                          self.rows, self.threads))
+            self._quant(act)
+        par(lambda lo, hi: lib.add_rmsnorm(h[lo:hi], None, self.w[0], 1e-5, 1.0, want_h=False), self.rows,
+            self.threads)
+
+
+def cpu_tokens_per_s(rows: int, layers: int, threads: int, steps: int, warmup: int):
+    cpu = CpuGlue(rows, layers, threads)
+    for _ in range(warmup):
+        cpu.step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu.step()
+    dt = time.perf_counter() - t0
+    # tokens/s of the full 40-layer sequence: a step of `layers` layers stands for layers/40 of it
+    tokens_per_s = rows * steps / dt * (layers / 40.0)
+    return tokens_per_s, dt, cpu
+
+
+def host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference_arm(args, rank: int, world: int):
+    if rank != 0:
+        return
+    threads = host_threads()
+    rows = int(os.environ.get("G4_BENCH_CPU_ROWS", "256"))
+    tps, dt, cpu = cpu_tokens_per_s(rows, 40, threads, args.steps, args.warmup)
+    sample = (f"{rows} of the 65536 token rows through all 40 layers + final norm per step, rows split "
+              f"over {cpu.threads} threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cpu.threads, "kind": cpu.kind,
+                         "sample": sample},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------- GPU arm
+def run_gpu_arm(args, rank: int, local_rank: int, world: int):
+    import torch
+    import torch.distributed as dist
+    import granite4_b200  # noqa: F401
+    from granite4_b200 import capi, glue
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU (there is no CPU fallback for the kernels)")
+    capi.lib()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    shapes = glue.GraniteShapes()
+    if TOTAL_TOKENS % world:
+        raise SystemExit("the GPU count must divide 65536")
+    rows = int(os.environ.get("G4_BENCH_ROWS", TOTAL_TOKENS // world))  # override only for profiling
+    total_tokens = rows * world
+    seq = glue.GlueSequence(rows, shapes, device=device, seed=rank, sets=2)
+    seq.reset()
+    stream = torch.cuda.current_stream(device)
+
+    def sync_all():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        seq.run()
+    sync_all()
+
+    # ---- timed region: K steps, CUDA events on the launching stream ---------------------
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    op_events = {"add_rmsnorm_fp8": [], "rope_kv_int8": [], "swiglu_fp8": [], "final_norm": []}
+    seq.launches = 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    wall0 = time.time()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        timed_step(seq, op_events, stream)
+    ev1.record(stream)
+    sync_all()
+    wall1 = time.time()
+    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
+    ms = ev0.elapsed_time(ev1)
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = t.item()
+    status = capi.lib().device_status()
+
+    if rank == 0:
+        peak, peak_src = load_peaks()
+        bpr = glue.bytes_per_row(shapes)
+        ops = {}
+        for name, evs in op_events.items():
+            dur = [a.elapsed_time(b) for a, b in evs]
+            per_row = bpr["add_rmsnorm_fp8" if name == "add_rmsnorm_fp8" else name]
+            mean_ms = statistics.mean(dur)
+            ops[name] = {"launches": len(dur), "mean_us": mean_ms * 1e3,
+                         "share": sum(dur) / (ms if ms > 0 else 1.0),
+                         "achieved_gbs": per_row * rows / (mean_ms * 1e-3) / 1e9,
+                         "frac": per_row * rows / (mean_ms * 1e-3) / 1e9 / peak,
+                         "bytes_per_row": per_row}
+        dominant = max(ops, key=lambda k: ops[k]["share"])
+        tokens_per_s = total_tokens * args.steps / (ms_max * 1e-3)
+        line = {
+            "metric": METRIC, "value": tokens_per_s, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_max / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "rows_per_gpu": rows, "total_tokens": total_tokens,
+                       "layers": shapes.layers, "parallelism": f"rows/{world}",
+                       "l2": "inputs larger than L2: two rotated input sets, >= 1.1 GB touched per layer",
+                       "bytes_per_token": glue.bytes_per_token(shapes)},
+            "roofline": {"bound": "hbm", "kernel": dominant, "achieved": ops[dominant]["achieved_gbs"],
+                         "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                         "frac": ops[dominant]["frac"], "traffic": None,
+                         "algorithmic_bytes_per_launch": ops[dominant]["bytes_per_row"] * rows},
+            "sequence_roofline": {"achieved": glue.bytes_per_token(shapes) * total_tokens * args.steps /
+                                  (ms_max * 1e-3) / 1e9 / world, "unit": "GB/s per GPU",
+                                  "frac": glue.bytes_per_token(shapes) * total_tokens * args.steps /
+                                  (ms_max * 1e-3) / 1e9 / world / peak},
+            "ops": ops,
+            "clocks": clocks,
+            "gpu_launches": seq.launches,
+            "device_status": status,
+        }
+        # CPU baseline on this box's cores (rank 0, N = 1 only), bounded sample
+        if world == 1 and not args.no_cpu:
+            threads = host_threads()
+            c_rows = int(os.environ.get("G4_BENCH_CPU_ROWS", "256"))
+            tps, dt, cpu = cpu_tokens_per_s(c_rows, 40, threads, 3, 1)
+            line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": cpu.threads, "kind": cpu.kind,
+                                    "sample": f"{c_rows} token rows through all 40 layers + final norm, "
+                                              f"3 steps after 1 warm-up, {dt:.1f} s"}
+        line["e2e"] = None
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def timed_step(seq, op_events, stream):
+    """GlueSequence.run() with an event pair around every op (for the per-op durations)."""
+    import torch
+    from granite4_b200 import glue, kernels as k
+    s = seq.shapes
+
+    def timed(name, fn):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        rc = fn()
+        b.record(stream)
+        if rc != 0:
+            raise RuntimeError(f"{name} returned {rc}")
+        op_events[name].append((a, b))
+
+    for layer in range(seq.layers):
+        buf = seq.sets[layer % len(seq.sets)]
+        timed("add_rmsnorm_fp8", lambda: k.add_rmsnorm_fp8(
+            buf["y_attn"], seq.h, seq.w[layer, 0], s.eps, s.residual_multiplier, h_out=seq.h,
+            n_fp8=seq.n_fp8, scale_amax=seq.scales[layer, 0]))
+        timed("rope_kv_int8", lambda: k.rope_kv_int8_paged(
+            buf["qkv"], seq.tables.cos, seq.tables.sin, seq.pos_rows, seq.kv_rows, s.q_heads, s.kv_heads,
+            s.head_dim, seq.pool_rows, seq.max_pos, 0, seq.q_rot, seq.cache_k[layer], seq.cache_v[layer],
+            seq.k_scale[layer], seq.v_scale[layer]))
+        timed("add_rmsnorm_fp8", lambda: k.add_rmsnorm_fp8(
+            buf["y_mlp"], seq.h, seq.w[layer, 1], s.eps, s.residual_multiplier, h_out=seq.h,
+            n_fp8=seq.n_fp8, scale_amax=seq.scales[layer, 1]))
+        timed("swiglu_fp8", lambda: k.swiglu_fp8(buf["gate"], buf["up"], act_fp8=seq.act_fp8,
+                                                 scale_amax=seq.scales[layer, 2]))
+        seq.launches += glue.KERNELS_PER_LAYER
+    timed("final_norm", lambda: k.rmsnorm(seq.h, seq.w_final, s.eps, seq.rows, s.hidden, seq.out))
+    seq.launches += glue.KERNELS_FINAL
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world == 1 and args.gpus > 1:
+        raise SystemExit(f"--gpus {args.gpus} needs one process per GPU: launch with "
+                         f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {args.gpus} "
+                         f"--master-addr 127.0.0.1 --master-port <port> bench.py --gpus {args.gpus} ...")
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+    else:
+        run_gpu_arm(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,410 @@
+// RoPE on Q/K with the rotated K and the raw V quantised into the int8 paged KV
+// cache; RoPE table build; the plain RoPE and int8 append primitives.
+//
+// Formulation (reference: prefill kernel engine/src/prefill_gemm.cu:356-428,
+// decode / verify kernel engine/src/forward_gpu.cu:598-665, scalar math
+// engine/src/device_math.cuh:105-134, host twins engine/src/kernel_math.h:71-86,
+// :191-219):
+//   tables  cos/sin(pos * theta^(-2i/d)) in double, stored f32 [max_pos][d/2]
+//   rotate  (a, b) = (x[i], x[i + d/2]): lo = a c - b s, hi = b c + a s (f32)
+//   q_rot   = bf16(rotated q)
+//   K row   k' = rotated k (f32 in the prefill form, rounded to bf16 in the
+//           decode form); amax = max |k'|, s = amax / 127,
+//           code = clamp(round_half_away(k' / s), +-127); V the same on raw v
+//   paging  code row (hkv * stride + kv_row) * d, scale (hkv * stride + kv_row);
+//           kv_row = d_pt[pos] (16-token pages: page_id * 16 + pos % 16)
+//
+// Kernel layout (d = 128): eight lanes own one head. Lane j holds columns
+// [8j, 8j+8) and [64+8j, 64+8j+8), i.e. both halves of its eight rotation
+// pairs, so the rotation needs no exchange and the row amax is three xor
+// shuffles. A 128-thread CTA covers 16 heads of one token row; loads are 128-bit
+// (a warp reads four whole heads = 1 KB), q_rot stores are 128-bit, code stores
+// are two 8-byte pieces per lane that together fill the head's 128-byte cache
+// row. The cos/sin row of the token (512 B) is read through the read-only path
+// by every head group and stays in L1.
+//
+// Algorithmic bytes per token row (Hq 32, Hk 8): q 8192 + k 2048 + v 2048 +
+// cos/sin 512 + ids 8 read; q_rot 8192 + codes 2048 + scales 64 written =
+// 23 108 B.
+#include "g4_host.h"
+#include "g4_math.cuh"
+
+#include "../../include/granite4_b200.h"
+#include "../../include/granite4_b200.hpp"
+
+#include <cstdlib>
+#include <vector>
+
+namespace g4 {
+namespace {
+
+enum RowMode { kRunOfPositions = 0, kPerRowArrays = 1, kDescriptor = 2 };
+
+struct RopeKvParams {
+  const uint16_t* q;  // row pitch pitch_q elements; NULL when there is no q
+  const uint16_t* k;
+  const uint16_t* v;
+  long long pitch_q, pitch_k, pitch_v;
+  const float* cos_tbl;
+  const float* sin_tbl;
+  uint16_t* q_rot;  // [rows][Hq * 128]
+  int8_t* cache_k;
+  int8_t* cache_v;
+  float* k_scale;
+  float* v_scale;
+  // where row r sits
+  int mode;
+  int base_pos;
+  const int* pos_rows;
+  const int* kv_rows;
+  const int* d_pt;
+  const granite4_multi_rows* mr;
+  int max_pos;  // bound for pos_rows (kPerRowArrays)
+  int rows, Hq, Hk;
+  long long stride;
+  int groups;       // 16-head groups per row
+  int rotate_k;     // 0: K rows are appended as they are (plain append)
+  int k_from_bf16;  // quantise the bf16-rounded rotated K
+};
+
+constexpr int kD = 128;
+constexpr int kHeadsPerCta = 16;
+
+__device__ __forceinline__ void unpack8(uint4 u, float (&v)[8]) {
+  v[0] = bf16_lo(u.x), v[1] = bf16_hi(u.x), v[2] = bf16_lo(u.y), v[3] = bf16_hi(u.y);
+  v[4] = bf16_lo(u.z), v[5] = bf16_hi(u.z), v[6] = bf16_lo(u.w), v[7] = bf16_hi(u.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(v[0], v[1]);
+  u.y = pack_bf16x2(v[2], v[3]);
+  u.z = pack_bf16x2(v[4], v[5]);
+  u.w = pack_bf16x2(v[6], v[7]);
+  return u;
+}
+
+__global__ void __launch_bounds__(kHeadsPerCta * 8) rope_kv_int8_kernel(const RopeKvParams p) {
+  const int r = blockIdx.x / p.groups;
+  const int head = (blockIdx.x % p.groups) * kHeadsPerCta + (threadIdx.x >> 3);
+  const int j = threadIdx.x & 7;
+  const int heads_total = p.Hq + 2 * p.Hk;
+
+  int pos, kv_row;
+  if (p.mode == kRunOfPositions) {
+    pos = p.base_pos + r;
+    kv_row = p.d_pt != nullptr ? __ldg(p.d_pt + pos) : pos;
+  } else if (p.mode == kPerRowArrays) {
+    pos = __ldg(p.pos_rows + r);
+    kv_row = __ldg(p.kv_rows + r);
+    // a bad index skips the row instead of touching memory outside the pool
+    if (pos < 0 || pos >= p.max_pos || kv_row < 0 || kv_row >= p.stride) return;
+  } else {
+    pos = p.mr->pos[r];
+    const int slot = p.mr->tree ? p.mr->slot[r] : pos;
+    kv_row = p.mr->pt[r][slot];
+  }
+  // Whole 8-lane groups leave together, so the shuffles below stay converged
+  // within the groups that remain (the mask names only their own lanes).
+  if (head >= heads_total) return;
+
+  const bool is_q = head < p.Hq;
+  const bool is_k = !is_q && head < p.Hq + p.Hk;
+  const uint16_t* src;
+  if (is_q) src = p.q + static_cast<size_t>(r) * p.pitch_q + static_cast<size_t>(head) * kD;
+  else if (is_k) src = p.k + static_cast<size_t>(r) * p.pitch_k + static_cast<size_t>(head - p.Hq) * kD;
+  else src = p.v + static_cast<size_t>(r) * p.pitch_v + static_cast<size_t>(head - p.Hq - p.Hk) * kD;
+
+  float lo[8], hi[8];
+  unpack8(ld_stream(reinterpret_cast<const uint4*>(src) + j), lo);
+  unpack8(ld_stream(reinterpret_cast<const uint4*>(src) + 8 + j), hi);
+
+  if (is_q || (is_k && p.rotate_k)) {
+    const float4* cp = reinterpret_cast<const float4*>(p.cos_tbl + static_cast<size_t>(pos) * (kD / 2)) + 2 * j;
+    const float4* sp = reinterpret_cast<const float4*>(p.sin_tbl + static_cast<size_t>(pos) * (kD / 2)) + 2 * j;
+    const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float a, b;
+      rope_pair(lo[e], hi[e], c[e], s[e], a, b);
+      lo[e] = a, hi[e] = b;
+    }
+  }
+  if (is_q) {
+    uint4* dst = reinterpret_cast<uint4*>(p.q_rot + (static_cast<size_t>(r) * p.Hq + head) * kD);
+    st_stream(dst + j, pack8(lo));
+    st_stream(dst + 8 + j, pack8(hi));
+    return;
+  }
+  if (is_k && p.rotate_k && p.k_from_bf16) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) lo[e] = round_bf16(lo[e]), hi[e] = round_bf16(hi[e]);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fmaxf(fabsf(lo[e]), fabsf(hi[e])));
+  // the 8 lanes of this head: lanes [g*8, g*8+8) of the warp
+  const unsigned gmask = 0xffu << (threadIdx.x & 24);
+  amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 4));
+  const float sc = kv8_scale(amax);
+  const int hkv = is_k ? head - p.Hq : head - p.Hq - p.Hk;
+  const size_t srow = static_cast<size_t>(hkv) * p.stride + kv_row;
+  int8_t* cache = (is_k ? p.cache_k : p.cache_v) + srow * kD;
+  if (j == 0) (is_k ? p.k_scale : p.v_scale)[srow] = sc;
+  uint2 cl, ch;
+  cl.x = pack_i8x4(kv8_quant(lo[0], sc), kv8_quant(lo[1], sc), kv8_quant(lo[2], sc), kv8_quant(lo[3], sc));
+  cl.y = pack_i8x4(kv8_quant(lo[4], sc), kv8_quant(lo[5], sc), kv8_quant(lo[6], sc), kv8_quant(lo[7], sc));
+  ch.x = pack_i8x4(kv8_quant(hi[0], sc), kv8_quant(hi[1], sc), kv8_quant(hi[2], sc), kv8_quant(hi[3], sc));
+  ch.y = pack_i8x4(kv8_quant(hi[4], sc), kv8_quant(hi[5], sc), kv8_quant(hi[6], sc), kv8_quant(hi[7], sc));
+  st_stream(reinterpret_cast<uint2*>(cache) + j, cl);
+  st_stream(reinterpret_cast<uint2*>(cache) + 8 + j, ch);
+}
+
+// Plain RoPE of [rows][d] with table row = row index; any even d. One thread
+// per rotation pair (a test primitive in the reference, kept for its callers).
+__global__ void __launch_bounds__(256)
+    rope_rows_kernel(const uint16_t* x, const float* cos_tbl, const float* sin_tbl, int rows, int d,
+                     uint16_t* out) {
+  const int half = d / 2;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(rows) * half) return;
+  const long long row = idx / half;
+  const int i = static_cast<int>(idx % half);
+  const float a = bf16_to_f32(x[row * d + i]), b = bf16_to_f32(x[row * d + i + half]);
+  float lo, hi;
+  rope_pair(a, b, cos_tbl[row * half + i], sin_tbl[row * half + i], lo, hi);
+  out[row * d + i] = static_cast<uint16_t>(f32_to_bf16_bits(lo));
+  out[row * d + i + half] = static_cast<uint16_t>(f32_to_bf16_bits(hi));
+}
+
+// int8 append of bf16 K/V rows for head dims other than 128: one CTA of d
+// threads per (kv head, row), shared-memory amax.
+__global__ void __launch_bounds__(1024)
+    kv_append_int8_generic_kernel(const uint16_t* src_k, const uint16_t* src_v, int8_t* cache_k,
+                                  int8_t* cache_v, float* k_scale, float* v_scale, int base_pos,
+                                  int stride, int Hk, int d, const int* d_pt) {
+  const int hkv = blockIdx.x, r = blockIdx.y, i = threadIdx.x;
+  const int pos = base_pos + r;
+  const int row = d_pt != nullptr ? d_pt[pos] : pos;
+  const bool act = i < d;  // the CTA is d rounded up to whole warps
+  const size_t src = (static_cast<size_t>(r) * Hk + hkv) * d + i;
+  const float x = act ? bf16_to_f32(src_k[src]) : 0.0f, y = act ? bf16_to_f32(src_v[src]) : 0.0f;
+  float ax = warp_max(fabsf(x)), ay = warp_max(fabsf(y));
+  __shared__ float wmax[2][32];
+  if ((i & 31) == 0) wmax[0][i >> 5] = ax, wmax[1][i >> 5] = ay;
+  __syncthreads();
+  float mk = 0.0f, mv = 0.0f;
+  for (int w = 0; w < (d + 31) / 32; ++w) mk = fmaxf(mk, wmax[0][w]), mv = fmaxf(mv, wmax[1][w]);
+  const float sk = kv8_scale(mk), sv = kv8_scale(mv);
+  const size_t srow = static_cast<size_t>(hkv) * stride + row;
+  if (i == 0) k_scale[srow] = sk, v_scale[srow] = sv;
+  if (!act) return;
+  cache_k[srow * d + i] = static_cast<int8_t>(kv8_quant(x, sk));
+  cache_v[srow * d + i] = static_cast<int8_t>(kv8_quant(y, sv));
+}
+
+int launch_rope_kv(const char* fn, RopeKvParams& p) {
+  const int heads_total = p.Hq + 2 * p.Hk;
+  p.groups = (heads_total + kHeadsPerCta - 1) / kHeadsPerCta;
+  const long long ctas = static_cast<long long>(p.rows) * p.groups;
+  if (ctas > INT_MAX) return fail(fn, "too many rows");
+  rope_kv_int8_kernel<<<static_cast<unsigned>(ctas), kHeadsPerCta * 8, 0, current_stream()>>>(p);
+  G4_LAUNCH_CHECK(fn);
+  return 0;
+}
+
+}  // namespace
+}  // namespace g4
+
+extern "C" {
+
+int granite4_rope_tables_build(double theta, int head_dim, int max_pos, float** d_cos,
+                               float** d_sin) {
+  const char* fn = "granite4_rope_tables_build";
+  if (d_cos == nullptr || d_sin == nullptr || !std::isfinite(theta) || theta <= 0.0 ||
+      head_dim <= 0 || (head_dim & 1) != 0 || head_dim > 256 || max_pos <= 0)
+    return g4::fail(fn, "invalid arguments");
+  *d_cos = nullptr;
+  *d_sin = nullptr;
+  const int half = head_dim / 2;
+  const size_t n = static_cast<size_t>(max_pos) * half;
+  std::vector<float> h_cos(n), h_sin(n);
+  // engine/src/kernel_math.h:191-206: everything in double, stored as f32.
+  for (int i = 0; i < half; ++i) {
+    const double inv_freq = 1.0 / std::pow(theta, 2.0 * static_cast<double>(i) / head_dim);
+    for (int pos = 0; pos < max_pos; ++pos) {
+      const double angle = static_cast<double>(pos) * inv_freq;
+      h_cos[static_cast<size_t>(pos) * half + i] = static_cast<float>(std::cos(angle));
+      h_sin[static_cast<size_t>(pos) * half + i] = static_cast<float>(std::sin(angle));
+    }
+  }
+  float *c = nullptr, *s = nullptr;
+  if (cudaMalloc(&c, n * sizeof(float)) != cudaSuccess) return g4::fail(fn, "cudaMalloc failed");
+  if (cudaMalloc(&s, n * sizeof(float)) != cudaSuccess) {
+    cudaFree(c);
+    return g4::fail(fn, "cudaMalloc failed");
+  }
+  if (cudaMemcpy(c, h_cos.data(), n * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess ||
+      cudaMemcpy(s, h_sin.data(), n * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) {
+    cudaFree(c);
+    cudaFree(s);
+    return g4::fail(fn, "upload failed");
+  }
+  *d_cos = c;
+  *d_sin = s;
+  return 0;
+}
+
+int granite4_kernel_rope(const uint16_t* d_x, const float* d_cos, const float* d_sin, int rows,
+                         int head_dim, uint16_t* d_out) {
+  const char* fn = "granite4_kernel_rope";
+  if (d_x == nullptr || d_cos == nullptr || d_sin == nullptr || d_out == nullptr || rows <= 0 ||
+      head_dim <= 0 || (head_dim & 1) != 0 || static_cast<long long>(rows) * head_dim > INT_MAX ||
+      head_dim > 256)
+    return g4::fail(fn, "invalid arguments");
+  const long long pairs = static_cast<long long>(rows) * (head_dim / 2);
+  g4::rope_rows_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, g4::current_stream()>>>(
+      d_x, d_cos, d_sin, rows, head_dim, d_out);
+  G4_LAUNCH_CHECK(fn);
+  return 0;
+}
+
+int granite4_kernel_kv_append_int8_batched(const uint16_t* d_src_k, const uint16_t* d_src_v,
+                                           int8_t* d_cache_k, int8_t* d_cache_v,
+                                           float* d_cache_k_scale, float* d_cache_v_scale,
+                                           int base_pos, int rows, int stride, int Hk, int d,
+                                           const int* d_pt) {
+  const char* fn = "granite4_kernel_kv_append_int8_batched";
+  if (d_src_k == nullptr || d_src_v == nullptr || d_cache_k == nullptr || d_cache_v == nullptr ||
+      d_cache_k_scale == nullptr || d_cache_v_scale == nullptr || base_pos < 0 || rows <= 0 ||
+      rows > GRANITE4_MAX_VERIFY_ROWS || Hk <= 0 || d <= 0 || d > 1024 ||
+      base_pos > INT_MAX - rows || stride < base_pos + rows ||
+      static_cast<long long>(Hk) * d > INT_MAX || stride > INT_MAX / (Hk > 1 ? Hk : 1))
+    return g4::fail(fn, "invalid arguments");
+  const bool fast = d == g4::kD && g4::aligned16(d_src_k) && g4::aligned16(d_src_v) &&
+                    g4::aligned16(d_cache_k) && g4::aligned16(d_cache_v);
+  if (!fast) {
+    g4::kv_append_int8_generic_kernel<<<dim3(Hk, rows), (d + 31) / 32 * 32, 0,
+                                        g4::current_stream()>>>(
+        d_src_k, d_src_v, d_cache_k, d_cache_v, d_cache_k_scale, d_cache_v_scale, base_pos, stride,
+        Hk, d, d_pt);
+    G4_LAUNCH_CHECK(fn);
+    return 0;
+  }
+  g4::RopeKvParams p{};
+  p.q = nullptr, p.k = d_src_k, p.v = d_src_v;
+  p.pitch_k = p.pitch_v = static_cast<long long>(Hk) * d;
+  p.cache_k = d_cache_k, p.cache_v = d_cache_v, p.k_scale = d_cache_k_scale,
+  p.v_scale = d_cache_v_scale;
+  p.mode = g4::kRunOfPositions, p.base_pos = base_pos, p.d_pt = d_pt;
+  p.rows = rows, p.Hq = 0, p.Hk = Hk, p.stride = stride, p.rotate_k = 0, p.k_from_bf16 = 0;
+  return g4::launch_rope_kv(fn, p);
+}
+
+int granite4_prefill_rope_split_append_int8(const uint16_t* qkv, const float* cos_tbl,
+                                            const float* sin_tbl, int base_pos, int rows, int Hq,
+                                            int Hk, int d, int stride, uint16_t* q_rot,
+                                            int8_t* cache_k, int8_t* cache_v,
+                                            float* cache_k_scale, float* cache_v_scale,
+                                            const int* d_pt) {
+  const char* fn = "prefill_rope_split_append_int8";
+  // engine/src/prefill_gemm.cu:1335-1340 (qkv / table pointers are checked too here)
+  if (rows <= 0 || rows > 65535 || base_pos < 0 || stride < base_pos + rows || d != g4::kD ||
+      Hq <= 0 || Hk <= 0 || q_rot == nullptr || cache_k == nullptr || cache_v == nullptr ||
+      cache_k_scale == nullptr || cache_v_scale == nullptr || qkv == nullptr ||
+      cos_tbl == nullptr || sin_tbl == nullptr)
+    return g4::fail(fn, "invalid arguments");
+  if (!g4::aligned16(qkv) || !g4::aligned16(q_rot) || !g4::aligned16(cache_k) ||
+      !g4::aligned16(cache_v) || !g4::aligned16(cos_tbl) || !g4::aligned16(sin_tbl))
+    return g4::fail(fn, "pointers must be 16-byte aligned");
+  g4::RopeKvParams p{};
+  const long long pitch = static_cast<long long>(Hq + 2 * Hk) * d;
+  p.q = qkv, p.k = qkv + static_cast<size_t>(Hq) * d, p.v = qkv + static_cast<size_t>(Hq + Hk) * d;
+  p.pitch_q = p.pitch_k = p.pitch_v = pitch;
+  p.cos_tbl = cos_tbl, p.sin_tbl = sin_tbl, p.q_rot = q_rot;
+  p.cache_k = cache_k, p.cache_v = cache_v, p.k_scale = cache_k_scale, p.v_scale = cache_v_scale;
+  p.mode = g4::kRunOfPositions, p.base_pos = base_pos, p.d_pt = d_pt;
+  p.rows = rows, p.Hq = Hq, p.Hk = Hk, p.stride = stride, p.rotate_k = 1, p.k_from_bf16 = 0;
+  return g4::launch_rope_kv(fn, p);
+}
+
+int granite4_gpu_multi_rope_append(const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                                   const float* cos_tbl, const float* sin_tbl,
+                                   const granite4_multi_rows* d_rows, int rows, int Hq, int Hk,
+                                   int d, int bits, void* cache_k, void* cache_v, float* k_scale,
+                                   float* v_scale, int stride, uint16_t* q_rot) {
+  const char* fn = "gpu_multi_rope_append";
+  // engine/src/forward_gpu.cu:3911 (-1 also tells the caller to take its unfused path)
+  if (d_rows == nullptr || rows < 1 || rows > GRANITE4_MAX_VERIFY_ROWS) return -1;
+  if (bits != 8 || d != g4::kD) return -1;  // other cache formats are not built here
+  if (q == nullptr || k == nullptr || v == nullptr || cos_tbl == nullptr || sin_tbl == nullptr ||
+      cache_k == nullptr || cache_v == nullptr || k_scale == nullptr || v_scale == nullptr ||
+      q_rot == nullptr || Hq <= 0 || Hk <= 0 || stride <= 0)
+    return g4::fail(fn, "invalid arguments");
+  g4::RopeKvParams p{};
+  p.q = q, p.k = k, p.v = v;
+  p.pitch_q = static_cast<long long>(Hq) * d, p.pitch_k = p.pitch_v = static_cast<long long>(Hk) * d;
+  p.cos_tbl = cos_tbl, p.sin_tbl = sin_tbl, p.q_rot = q_rot;
+  p.cache_k = static_cast<int8_t*>(cache_k), p.cache_v = static_cast<int8_t*>(cache_v);
+  p.k_scale = k_scale, p.v_scale = v_scale;
+  p.mode = g4::kDescriptor, p.mr = d_rows;
+  p.rows = rows, p.Hq = Hq, p.Hk = Hk, p.stride = stride, p.rotate_k = 1, p.k_from_bf16 = 1;
+  return g4::launch_rope_kv(fn, p);
+}
+
+int granite4_kernel_rope_kv_int8_paged(const uint16_t* d_qkv, const float* d_cos,
+                                       const float* d_sin, const int* d_pos_rows,
+                                       const int* d_kv_rows, int rows, int Hq, int Hk, int d,
+                                       int stride, int max_pos, int k_from_bf16,
+                                       uint16_t* d_q_rot, int8_t* d_cache_k, int8_t* d_cache_v,
+                                       float* d_k_scale, float* d_v_scale) {
+  const char* fn = "granite4_kernel_rope_kv_int8_paged";
+  if (d_qkv == nullptr || d_cos == nullptr || d_sin == nullptr || d_pos_rows == nullptr ||
+      d_kv_rows == nullptr || rows <= 0 || Hq <= 0 || Hk <= 0 || d != g4::kD || stride <= 0 ||
+      max_pos <= 0 || d_q_rot == nullptr || d_cache_k == nullptr || d_cache_v == nullptr ||
+      d_k_scale == nullptr || d_v_scale == nullptr)
+    return g4::fail(fn, "invalid arguments");
+  if (!g4::aligned16(d_qkv) || !g4::aligned16(d_q_rot) || !g4::aligned16(d_cache_k) ||
+      !g4::aligned16(d_cache_v) || !g4::aligned16(d_cos) || !g4::aligned16(d_sin))
+    return g4::fail(fn, "pointers must be 16-byte aligned");
+  g4::RopeKvParams p{};
+  const long long pitch = static_cast<long long>(Hq + 2 * Hk) * d;
+  p.q = d_qkv, p.k = d_qkv + static_cast<size_t>(Hq) * d,
+  p.v = d_qkv + static_cast<size_t>(Hq + Hk) * d;
+  p.pitch_q = p.pitch_k = p.pitch_v = pitch;
+  p.cos_tbl = d_cos, p.sin_tbl = d_sin, p.q_rot = d_q_rot;
+  p.cache_k = d_cache_k, p.cache_v = d_cache_v, p.k_scale = d_k_scale, p.v_scale = d_v_scale;
+  p.mode = g4::kPerRowArrays, p.pos_rows = d_pos_rows, p.kv_rows = d_kv_rows, p.max_pos = max_pos;
+  p.rows = rows, p.Hq = Hq, p.Hk = Hk, p.stride = stride, p.rotate_k = 1,
+  p.k_from_bf16 = k_from_bf16 != 0;
+  return g4::launch_rope_kv(fn, p);
+}
+
+}  // extern "C"
+
+namespace granite4 {
+
+int prefill_rope_split_append_int8(const std::uint16_t* qkv, const float* cos_tbl,
+                                   const float* sin_tbl, int base_pos, int rows, int Hq, int Hk,
+                                   int d, int stride, std::uint16_t* q_rot, std::int8_t* cache_k,
+                                   std::int8_t* cache_v, float* cache_k_scale,
+                                   float* cache_v_scale, const int* d_pt) {
+  return granite4_prefill_rope_split_append_int8(qkv, cos_tbl, sin_tbl, base_pos, rows, Hq, Hk, d,
+                                                 stride, q_rot, cache_k, cache_v, cache_k_scale,
+                                                 cache_v_scale, d_pt);
+}
+
+int gpu_multi_rope_append(const std::uint16_t* q, const std::uint16_t* k, const std::uint16_t* v,
+                          const float* cos_tbl, const float* sin_tbl, const GpuMultiRows* d_rows,
+                          int rows, int Hq, int Hk, int d, int bits, void* cache_k, void* cache_v,
+                          float* k_scale, float* v_scale, int stride, std::uint16_t* q_rot) {
+  return granite4_gpu_multi_rope_append(q, k, v, cos_tbl, sin_tbl,
+                                        reinterpret_cast<const granite4_multi_rows*>(d_rows), rows,
+                                        Hq, Hk, d, bits, cache_k, cache_v, k_scale, v_scale, stride,
+                                        q_rot);
+}
+
+}  // namespace granite4

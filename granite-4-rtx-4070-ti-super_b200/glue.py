@@ -1,0 +1,157 @@
+"""The per-layer glue sequence of the Granite 4.2 8B forward over a shard of token rows.
+
+This is the order in which the reference's prefill path calls the glue kernels
+(``engine/src/forward_gpu.cu:2751-2863``), with the GEMMs and the attention between them
+left out: their outputs are inputs here.
+
+    embed (once)                                               a1
+    per layer:  h += rm * y_attn ; n1 = norm(h) -> FP8          a2   (y_attn: O-projection output)
+                RoPE(q, k) + int8 paged KV write from qkv       a3   (qkv: QKV GEMM output)
+                h += rm * y_mlp  ; n2 = norm(h) -> FP8          a2   (y_mlp: down-projection output)
+                act = SwiGLU(gate, up) -> FP8                   a4   (gate/up GEMM output)
+    final norm of h -> bf16                                    a5
+
+Rows are independent (the per-tensor FP8 scale is per launch, i.e. per shard), so several
+GPUs each run this on their own rows with nothing exchanged.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import kernels
+
+
+@dataclass(frozen=True)
+class GraniteShapes:
+    """engine/src/model_config.h:18-25 (sizes), :35-42 (scalars; the multipliers are runtime
+    arguments there and default to 1.0 - the values here are the benchmark configuration's)."""
+    hidden: int = 4096
+    intermediate: int = 12800
+    q_heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    layers: int = 40
+    vocab: int = 100352
+    eps: float = 1e-5
+    residual_multiplier: float = 0.22
+    embedding_multiplier: float = 12.0
+    rope_theta: float = 1e7
+
+    @property
+    def qkv_width(self) -> int:
+        return (self.q_heads + 2 * self.kv_heads) * self.head_dim
+
+
+# algorithmic bytes per token row of each kernel: every input read once, every output written
+# once, per-launch tables and weights not counted
+def bytes_per_row(s: GraniteShapes) -> dict:
+    H, I, d = s.hidden, s.intermediate, s.head_dim
+    q, kv = s.q_heads * d, s.kv_heads * d
+    return {
+        "embed": 4 + 2 * H + 2 * H,
+        "add_rmsnorm_fp8": 2 * H + 2 * H + 2 * H + H,
+        "rope_kv_int8": 2 * q + 2 * kv + 2 * kv + 2 * 4 * (d // 2) + 4 + 2 * q + 2 * kv + 2 * 4 * s.kv_heads,
+        "swiglu_fp8": 2 * I + 2 * I + I,
+        "final_norm": 2 * H + 2 * H,
+    }
+
+
+def bytes_per_token(s: GraniteShapes) -> int:
+    b = bytes_per_row(s)
+    return s.layers * (2 * b["add_rmsnorm_fp8"] + b["rope_kv_int8"] + b["swiglu_fp8"]) + b["final_norm"]
+
+
+# kernels (not memsets) the sequence launches per layer and at the end
+KERNELS_PER_LAYER = 2 * 2 + 1 + 2
+KERNELS_FINAL = 1
+
+
+class GlueSequence:
+    """Device buffers for `rows` token rows and the calls that run the sequence over them.
+
+    Inputs that stand for GEMM / attention outputs are filled with seeded N(0, 1) bf16 values;
+    `sets` independent copies are rotated layer by layer so that no kernel finds its inputs in
+    L2 from the previous layer even at small row counts.
+    """
+
+    def __init__(self, rows: int, shapes: GraniteShapes = GraniteShapes(), device="cuda",
+                 seed: int = 0, sets: int = 2, layers: int | None = None, pool_rows: int | None = None,
+                 max_pos: int | None = None):
+        s = self.shapes = shapes
+        self.rows, self.device = rows, torch.device(device)
+        self.layers = s.layers if layers is None else layers
+        self.pool_rows = rows if pool_rows is None else pool_rows
+        self.max_pos = max(rows, 1) if max_pos is None else max_pos
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        bf = torch.bfloat16
+
+        def randn(*shape):
+            return torch.randn(*shape, generator=g, device=self.device, dtype=torch.float32).to(bf)
+
+        self.sets = []
+        for _ in range(sets):
+            self.sets.append({
+                "y_attn": randn(rows, s.hidden), "y_mlp": randn(rows, s.hidden),
+                "qkv": randn(rows, s.qkv_width),
+                "gate": randn(rows, s.intermediate), "up": randn(rows, s.intermediate),
+            })
+        self.h0 = randn(rows, s.hidden)  # stands for the embedding output
+        self.h = torch.empty_like(self.h0)
+        # norm weights ~ N(1, 0.02): [layers][2][hidden] + final
+        self.w = (1.0 + 0.02 * torch.randn(self.layers, 2, s.hidden, generator=g, device=self.device)).to(bf)
+        self.w_final = (1.0 + 0.02 * torch.randn(s.hidden, generator=g, device=self.device)).to(bf)
+        self.n_fp8 = torch.empty(rows, s.hidden, dtype=torch.uint8, device=self.device)
+        self.q_rot = torch.empty(rows, s.q_heads * s.head_dim, dtype=bf, device=self.device)
+        self.act_fp8 = torch.empty(rows, s.intermediate, dtype=torch.uint8, device=self.device)
+        self.out = torch.empty(rows, s.hidden, dtype=bf, device=self.device)
+        self.scales = torch.zeros(self.layers, 3, 2, dtype=torch.float32, device=self.device)
+        # int8 paged pool per layer: codes [L][Hk][pool_rows][d], scales [L][Hk][pool_rows]
+        self.cache_k = torch.zeros(self.layers, s.kv_heads, self.pool_rows, s.head_dim, dtype=torch.int8,
+                                   device=self.device)
+        self.cache_v = torch.zeros_like(self.cache_k)
+        self.k_scale = torch.zeros(self.layers, s.kv_heads, self.pool_rows, dtype=torch.float32,
+                                   device=self.device)
+        self.v_scale = torch.zeros_like(self.k_scale)
+        self.tables = kernels.RopeTables(s.rope_theta, s.head_dim, self.max_pos, self.device)
+        # identity placement unless set_rows() says otherwise
+        self.pos_rows = torch.arange(rows, dtype=torch.int32, device=self.device) % self.max_pos
+        self.kv_rows = torch.arange(rows, dtype=torch.int32, device=self.device) % self.pool_rows
+        self.launches = 0
+
+    def set_rows(self, pos_rows, kv_rows):
+        self.pos_rows = torch.as_tensor(pos_rows, dtype=torch.int32).to(self.device)
+        self.kv_rows = torch.as_tensor(kv_rows, dtype=torch.int32).to(self.device)
+
+    def reset(self):
+        self.h.copy_(self.h0)
+
+    def _check(self, rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what} returned {rc}")
+
+    def run_layer(self, layer: int):
+        s, k = self.shapes, kernels
+        buf = self.sets[layer % len(self.sets)]
+        self._check(k.add_rmsnorm_fp8(buf["y_attn"], self.h, self.w[layer, 0], s.eps, s.residual_multiplier,
+                                      h_out=self.h, n_fp8=self.n_fp8, scale_amax=self.scales[layer, 0]),
+                    "add_rmsnorm_fp8")
+        self._check(k.rope_kv_int8_paged(buf["qkv"], self.tables.cos, self.tables.sin, self.pos_rows,
+                                         self.kv_rows, s.q_heads, s.kv_heads, s.head_dim, self.pool_rows,
+                                         self.max_pos, 0, self.q_rot, self.cache_k[layer], self.cache_v[layer],
+                                         self.k_scale[layer], self.v_scale[layer]), "rope_kv_int8_paged")
+        self._check(k.add_rmsnorm_fp8(buf["y_mlp"], self.h, self.w[layer, 1], s.eps, s.residual_multiplier,
+                                      h_out=self.h, n_fp8=self.n_fp8, scale_amax=self.scales[layer, 1]),
+                    "add_rmsnorm_fp8")
+        self._check(k.swiglu_fp8(buf["gate"], buf["up"], act_fp8=self.act_fp8,
+                                 scale_amax=self.scales[layer, 2]), "swiglu_fp8")
+        self.launches += KERNELS_PER_LAYER
+
+    def run(self):
+        """One step: all layers, then the final norm. Enqueues only; does not synchronise."""
+        for layer in range(self.layers):
+            self.run_layer(layer)
+        self._check(kernels.rmsnorm(self.h, self.w_final, self.shapes.eps, self.rows, self.shapes.hidden,
+                                    self.out), "rmsnorm")
+        self.launches += KERNELS_FINAL

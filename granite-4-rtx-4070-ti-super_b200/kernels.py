@@ -1,0 +1,205 @@
+"""Host-side mirror of the reference engine's launch interface for the layer glue kernels.
+
+Same names, argument order and return convention (0 / -1) as the reference's launchers
+(``engine/src/prefill_gemm.h``, ``engine/src/kernels_phase2.cu``, ``engine/src/forward_gpu_api.h``),
+over PyTorch CUDA tensors: torch only provides device memory and the stream, every
+computation happens in the library's own kernels. bf16 tensors may be passed as
+``torch.bfloat16`` or as ``torch.uint16``/``int16`` bit patterns; FP8 outputs are ``uint8``.
+
+Each call launches on torch's current stream of the tensor's device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import capi
+
+_BF16_OK = (torch.bfloat16, torch.uint16, torch.int16)
+
+
+def _p(t, *dtypes):
+    """Device pointer of a contiguous CUDA tensor (None passes through)."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("expected a CUDA tensor: these kernels have no CPU path")
+    if not t.is_contiguous():
+        raise ValueError("expected a contiguous tensor")
+    if dtypes and t.dtype not in dtypes:
+        raise TypeError(f"unexpected dtype {t.dtype}, wanted one of {dtypes}")
+    return t.data_ptr()
+
+
+def _enter(t):
+    """Select the tensor's device and torch's current stream on it for the launch."""
+    lib = capi.lib()
+    torch.cuda.set_device(t.device)
+    lib.granite4_b200_set_stream(torch.cuda.current_stream(t.device).cuda_stream)
+    return lib
+
+
+# ---- a1 ---------------------------------------------------------------------------------
+def prefill_embed_rows(d_tokens, start, rows, emb, mult, out):
+    """engine/src/prefill_gemm.h:42-43. out[r] = bf16(mult * emb[d_tokens[start + r]])."""
+    lib = _enter(emb)
+    return lib.granite4_prefill_embed_rows(_p(d_tokens, torch.int32), start, rows, _p(emb, *_BF16_OK),
+                                           mult, _p(out, *_BF16_OK), emb.shape[-1])
+
+
+def embed_gather(d_tokens, emb, mult, out):
+    """granite4_kernel_embed_gather: no 65535-row limit, out-of-vocabulary ids give zero rows."""
+    lib = _enter(emb)
+    return lib.granite4_kernel_embed_gather(_p(d_tokens, torch.int32), d_tokens.numel(),
+                                            _p(emb, *_BF16_OK), emb.shape[0], mult,
+                                            _p(out, *_BF16_OK), emb.shape[1])
+
+
+# ---- a2 / a5 ------------------------------------------------------------------------------
+def rmsnorm(d_x, d_w, eps, rows, cols, d_out, batched=False):
+    """engine/src/kernels_phase2.cu:910-936 (granite4_kernel_rmsnorm[_batched])."""
+    lib = _enter(d_x)
+    fn = lib.granite4_kernel_rmsnorm_batched if batched else lib.granite4_kernel_rmsnorm
+    return fn(_p(d_x, *_BF16_OK), _p(d_w, *_BF16_OK), eps, rows, cols, _p(d_out, *_BF16_OK))
+
+
+def add_rmsnorm_fp8(y, res, w, eps, resid_mult, h_out=None, n_bf16=None, n_fp8=None,
+                    scale_amax=None):
+    """granite4_kernel_add_rmsnorm_fp8. y / res: bf16 or float32 [rows][cols]; res may be None.
+    scale_amax: float32[2] receiving {scale, amax} when n_fp8 is given."""
+    lib = _enter(y)
+    rows, cols = y.shape
+    return lib.granite4_kernel_add_rmsnorm_fp8(
+        _p(y), int(y.dtype == torch.float32), _p(res), int(res is not None and res.dtype == torch.float32),
+        _p(w, *_BF16_OK), eps, resid_mult, rows, cols, _p(h_out, *_BF16_OK), _p(n_bf16, *_BF16_OK),
+        _p(n_fp8, torch.uint8), _p(scale_amax, torch.float32))
+
+
+def fp8_quant(x, codes, scale_amax):
+    """granite4_kernel_fp8_quant: per-tensor e4m3 of a bf16 tensor."""
+    lib = _enter(x)
+    return lib.granite4_kernel_fp8_quant(_p(x, *_BF16_OK), x.numel(), _p(codes, torch.uint8),
+                                         _p(scale_amax, torch.float32))
+
+
+# ---- a3 -----------------------------------------------------------------------------------
+class _DevArray:
+    """Zero-copy view of raw device memory for torch.as_tensor (CUDA array interface)."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False),
+                                         "version": 2}
+
+
+class RopeTables:
+    """Device cos/sin tables built by granite4_rope_tables_build, which allocates them with
+    cudaMalloc as the reference's does. `cos` / `sin` are float32 [max_pos][head_dim/2] views
+    of that memory; close() (or collection) frees it through granite4_b200_free."""
+
+    def __init__(self, theta, head_dim, max_pos, device=None):
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        torch.cuda.set_device(device)
+        self._lib = capi.lib()
+        c, s = C.c_void_p(), C.c_void_p()
+        rc = self._lib.granite4_rope_tables_build(theta, head_dim, max_pos, C.byref(c), C.byref(s))
+        if rc != 0:
+            raise RuntimeError("granite4_rope_tables_build failed")
+        self.device, self.max_pos, self.half = device, max_pos, head_dim // 2
+        self.cos_ptr, self.sin_ptr = c.value, s.value
+        shape = (max_pos, self.half)
+        self.cos = torch.as_tensor(_DevArray(self.cos_ptr, shape, "<f4"), device=device)
+        self.sin = torch.as_tensor(_DevArray(self.sin_ptr, shape, "<f4"), device=device)
+
+    def close(self):
+        if getattr(self, "cos_ptr", None):
+            self.cos = self.sin = None
+            self._lib.granite4_b200_free(self.cos_ptr)
+            self._lib.granite4_b200_free(self.sin_ptr)
+            self.cos_ptr = self.sin_ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _tbl(t):
+    return t if isinstance(t, int) else _p(t, torch.float32)
+
+
+def rope(d_x, d_cos, d_sin, rows, head_dim, d_out):
+    """engine/src/kernels_phase2.cu:938-951 (granite4_kernel_rope)."""
+    lib = _enter(d_x)
+    return lib.granite4_kernel_rope(_p(d_x, *_BF16_OK), _tbl(d_cos), _tbl(d_sin), rows, head_dim,
+                                    _p(d_out, *_BF16_OK))
+
+
+def kv_append_int8_batched(d_src_k, d_src_v, d_cache_k, d_cache_v, d_cache_k_scale,
+                           d_cache_v_scale, base_pos, rows, stride, Hk, d, d_pt=None):
+    """engine/src/kernels_phase2.cu:1107-1131."""
+    lib = _enter(d_src_k)
+    return lib.granite4_kernel_kv_append_int8_batched(
+        _p(d_src_k, *_BF16_OK), _p(d_src_v, *_BF16_OK), _p(d_cache_k, torch.int8),
+        _p(d_cache_v, torch.int8), _p(d_cache_k_scale, torch.float32),
+        _p(d_cache_v_scale, torch.float32), base_pos, rows, stride, Hk, d, _p(d_pt, torch.int32))
+
+
+def prefill_rope_split_append_int8(qkv, cos_tbl, sin_tbl, base_pos, rows, Hq, Hk, d, stride, q_rot,
+                                   cache_k, cache_v, cache_k_scale, cache_v_scale, d_pt=None):
+    """engine/src/prefill_gemm.h:58-64."""
+    lib = _enter(qkv)
+    return lib.granite4_prefill_rope_split_append_int8(
+        _p(qkv, *_BF16_OK), _tbl(cos_tbl), _tbl(sin_tbl), base_pos, rows, Hq, Hk, d, stride,
+        _p(q_rot, *_BF16_OK), _p(cache_k, torch.int8), _p(cache_v, torch.int8),
+        _p(cache_k_scale, torch.float32), _p(cache_v_scale, torch.float32), _p(d_pt, torch.int32))
+
+
+def gpu_multi_rope_append(q, k, v, cos_tbl, sin_tbl, d_rows, rows, Hq, Hk, d, bits, cache_k, cache_v,
+                          k_scale, v_scale, stride, q_rot):
+    """engine/src/forward_gpu_api.h:224-227. d_rows: uint8 CUDA tensor holding a MultiRows."""
+    lib = _enter(q)
+    return lib.granite4_gpu_multi_rope_append(
+        _p(q, *_BF16_OK), _p(k, *_BF16_OK), _p(v, *_BF16_OK), _tbl(cos_tbl), _tbl(sin_tbl), _p(d_rows),
+        rows, Hq, Hk, d, bits, _p(cache_k), _p(cache_v), _p(k_scale, torch.float32),
+        _p(v_scale, torch.float32), stride, _p(q_rot, *_BF16_OK))
+
+
+def multi_rows_to_device(desc: capi.MultiRows, device):
+    """Upload a MultiRows descriptor; returns a uint8 CUDA tensor to pass as d_rows."""
+    raw = bytes(desc)
+    return torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
+
+
+def rope_kv_int8_paged(qkv, cos_tbl, sin_tbl, pos_rows, kv_rows, Hq, Hk, d, stride, max_pos,
+                       k_from_bf16, q_rot, cache_k, cache_v, k_scale, v_scale):
+    """granite4_kernel_rope_kv_int8_paged: per-row RoPE positions and pool rows."""
+    lib = _enter(qkv)
+    return lib.granite4_kernel_rope_kv_int8_paged(
+        _p(qkv, *_BF16_OK), _tbl(cos_tbl), _tbl(sin_tbl), _p(pos_rows, torch.int32),
+        _p(kv_rows, torch.int32), qkv.shape[0], Hq, Hk, d, stride, max_pos, int(k_from_bf16),
+        _p(q_rot, *_BF16_OK), _p(cache_k, torch.int8), _p(cache_v, torch.int8),
+        _p(k_scale, torch.float32), _p(v_scale, torch.float32))
+
+
+# ---- a4 -----------------------------------------------------------------------------------
+def prefill_silu_mul(gu, I, rows, act):
+    """engine/src/prefill_gemm.h:105: gu float32 [rows][2 I] -> act bf16 [rows][I]."""
+    lib = _enter(gu)
+    return lib.granite4_prefill_silu_mul(_p(gu, torch.float32), I, rows, _p(act, *_BF16_OK))
+
+
+def swiglu_fp8(gate, up, act_bf16=None, act_fp8=None, scale_amax=None, ld=None):
+    """granite4_kernel_swiglu_fp8. gate / up: [rows][I] bf16 or float32; they may be column
+    views of one [rows][2 I] buffer (pass ld = 2 I; contiguity is then not checked)."""
+    lib = capi.lib()
+    torch.cuda.set_device(gate.device)
+    lib.granite4_b200_set_stream(torch.cuda.current_stream(gate.device).cuda_stream)
+    rows, I = gate.shape
+    if ld is None:
+        ld = gate.stride(0)
+    return lib.granite4_kernel_swiglu_fp8(gate.data_ptr(), up.data_ptr(),
+                                          int(gate.dtype == torch.float32), ld, rows, I,
+                                          _p(act_bf16, *_BF16_OK), _p(act_fp8, torch.uint8),
+                                          _p(scale_amax, torch.float32))

@@ -1,0 +1,227 @@
+/* C ABI of libgranite4_b200.so: the Granite 4.2 8B per-layer glue kernels for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Conventions, identical to the reference engine's launchers
+ * (engine/src/kernels_phase2.cu:822-836): every pointer named d_* is
+ * caller-owned device memory on the current device; a launcher validates its
+ * arguments, enqueues its kernels on the calling thread's stream (see
+ * granite4_b200_set_stream) and returns without synchronising; it returns 0 on
+ * success and -1 on invalid arguments or a launch error, with one diagnostic
+ * line on stderr. Nothing here allocates unless its comment says so. bf16
+ * tensors are passed as uint16_t bit patterns, FP8 e4m3 as uint8_t.
+ *
+ * "Kept" entry points have the reference's name, argument list and error
+ * behaviour, so the reference's forward pass and tests link against this
+ * library unchanged; the citation is the reference definition each replaces.
+ * "Added" entry points cover fusions the reference does not have (its FP8
+ * activation path is future work, docs/phases.md:714-715); they follow the same
+ * conventions.
+ */
+#ifndef GRANITE4_B200_H
+#define GRANITE4_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------ */
+/* Library status (kept: engine/src/capi.h:18-66, engine/src/capi.cc:44-75)  */
+/* ------------------------------------------------------------------------ */
+typedef enum {
+  granite4_status_ok = 0,
+  granite4_unimplemented = 1,
+  granite4_no_device = 2,
+  granite4_unavailable = 3,
+} granite4_status_code;
+
+typedef struct {
+  const char* model_id;
+  long num_layers;
+  long hidden_size;
+  long intermediate_size;
+  long num_attention_heads;
+  long num_key_value_heads;
+  long head_dim;
+  long vocab_size;
+  long max_context_length;
+  const char* gpu_target; /* "sm_100a" here; the reference reports "sm_89" */
+} granite4_model_info;
+
+typedef struct {
+  granite4_status_code status;
+  int cuda_device_present;
+  const char* status_text;
+  const char* message; /* e.g. "device is sm_90, engine targets sm_100a" */
+} granite4_status_info;
+
+/* engine/src/capi.cc:44-58. NULL-tolerant, static strings, no allocation. */
+void granite4_get_model_info(granite4_model_info* out);
+/* engine/src/capi.cc:60-75 with the arch check of :17-36 retargeted to 10.0. */
+void granite4_status(granite4_status_info* out);
+
+/* ------------------------------------------------------------------------ */
+/* Stream selection (added)                                                  */
+/* ------------------------------------------------------------------------ */
+/* Launch stream for the calling host thread, as a cudaStream_t. The default
+ * (and the meaning of NULL) is the per-thread default stream the reference
+ * build uses (engine/CMakeLists.txt:43-48). Always returns 0. */
+int granite4_b200_set_stream(void* cuda_stream);
+/* Reads the library's device status word on the current device into *out
+ * (blocking device-to-host copy). 0 means no kernel has reported a problem;
+ * bit 0: the embedding kernel gave up waiting for a bulk copy, bits 1-3: the
+ * same for the norm, SwiGLU and RoPE kernels. A set bit means the outputs of
+ * that launch are incomplete. Returns 0, or -1 if the word cannot be read. */
+int granite4_b200_device_status(unsigned int* out);
+/* cudaFree() for hosts that do not link the CUDA runtime themselves (ctypes,
+ * cgo): releases a buffer granite4_rope_tables_build returned. 0 / -1. */
+int granite4_b200_free(void* d_ptr);
+
+/* ------------------------------------------------------------------------ */
+/* a1. Embedding gather x embedding_multiplier                               */
+/* ------------------------------------------------------------------------ */
+/* Kept: granite4::prefill_embed_rows, engine/src/prefill_gemm.h:42-43,
+ * engine/src/prefill_gemm.cu:1300-1309.
+ * out[r][:] = bf16(mult * emb[d_tokens[start + r]][:]), r in [0, rows).
+ * -1 when rows <= 0, rows > 65535 or H <= 0 (the reference's limits). */
+int granite4_prefill_embed_rows(const int32_t* d_tokens, int start, int rows, const uint16_t* emb,
+                                float mult, uint16_t* out, int H);
+/* Added: the same gather without the 65535-row limit and with the vocabulary
+ * size known: a row whose id is outside [0, vocab) is written as zeros instead
+ * of reading out of bounds. */
+int granite4_kernel_embed_gather(const int32_t* d_tokens, long long rows, const uint16_t* d_emb,
+                                 int vocab, float mult, uint16_t* d_out, int H);
+
+/* ------------------------------------------------------------------------ */
+/* a2 / a5. Residual add + RMSNorm, bf16 and FP8 outputs                     */
+/* ------------------------------------------------------------------------ */
+/* Kept: engine/src/kernels_phase2.cu:910-920.
+ * d_out[r][c] = bf16(x * r * w), r = 1 / sqrt(mean(x^2) + eps); -1 on NULL
+ * pointers, non-finite or non-positive eps, rows or cols <= 0, or
+ * rows * cols > INT_MAX. */
+int granite4_kernel_rmsnorm(const uint16_t* d_x, const uint16_t* d_w, float eps, int rows, int cols,
+                            uint16_t* d_out);
+/* Kept: engine/src/kernels_phase2.cu:922-936 (additionally rows <= 16). */
+int granite4_kernel_rmsnorm_batched(const uint16_t* d_x, const uint16_t* d_w, float eps, int rows,
+                                    int cols, uint16_t* d_out);
+/* Added: the residual add the reference does in its GEMM epilogues
+ * (engine/src/prefill_gemm.cu:81-88, engine/src/forward_gpu.cu:988-995) fused
+ * with the norm that follows it (engine/src/kernels_phase2.cu:51-132) and with a
+ * per-tensor FP8 e4m3 quantisation of the normed output (the reference's weight
+ * quantiser rule, engine/src/checkpoint_main.cc:118-122, :702-723):
+ *   h = bf16(res + resid_mult * y)         (d_res == NULL: h = bf16(y))
+ *   n = bf16(h * r * w)
+ *   amax = max |n| over all rows, scale = float(amax / 448),
+ *   code = e4m3(n / scale)                 (scale == 0: e4m3(n))
+ * d_y is bf16 (y_is_f32 == 0) or f32; d_res likewise. Outputs, each optional:
+ * d_h_out [rows][cols] bf16 (may alias d_res), d_n_bf16, d_n_fp8.
+ * d_scale_amax: float[2] = {scale, amax}, required when d_n_fp8 is given.
+ * cols must be a multiple of 8, at most 32768, and every row 16-byte aligned.
+ * With d_n_fp8 this enqueues a 8-byte memset and two kernels (the scale depends
+ * on every row, so the codes are written by a second sweep). */
+int granite4_kernel_add_rmsnorm_fp8(const void* d_y, int y_is_f32, const void* d_res,
+                                    int res_is_f32, const uint16_t* d_w, float eps,
+                                    float resid_mult, int rows, int cols, uint16_t* d_h_out,
+                                    uint16_t* d_n_bf16, uint8_t* d_n_fp8, float* d_scale_amax);
+/* Added: per-tensor FP8 quantisation of a bf16 tensor of n elements (n % 8 ==
+ * 0) with the same rule; d_scale_amax as above. */
+int granite4_kernel_fp8_quant(const uint16_t* d_x, long long n, uint8_t* d_codes,
+                              float* d_scale_amax);
+
+/* ------------------------------------------------------------------------ */
+/* a3. RoPE on Q/K + int8 paged KV write                                     */
+/* ------------------------------------------------------------------------ */
+/* Kept: engine/src/kernels_phase2.cu:868-908. Builds the [max_pos][head_dim/2]
+ * f32 cos and sin tables in double on the host and uploads them. ALLOCATES two
+ * device buffers with cudaMalloc; the caller cudaFree()s them. Synchronous. */
+int granite4_rope_tables_build(double theta, int head_dim, int max_pos, float** d_cos,
+                               float** d_sin);
+/* Kept: engine/src/kernels_phase2.cu:938-951. Row r of [rows][head_dim] is
+ * rotated with table row r. */
+int granite4_kernel_rope(const uint16_t* d_x, const float* d_cos, const float* d_sin, int rows,
+                         int head_dim, uint16_t* d_out);
+/* Kept: engine/src/kernels_phase2.cu:1107-1131. Quantise bf16 K/V rows
+ * [rows][Hk][d] to int8 + per-(row, head) f32 scale and store them at pool rows
+ * d_pt[base_pos + r] (d_pt == NULL: base_pos + r). rows <= 16. */
+int granite4_kernel_kv_append_int8_batched(const uint16_t* d_src_k, const uint16_t* d_src_v,
+                                           int8_t* d_cache_k, int8_t* d_cache_v,
+                                           float* d_cache_k_scale, float* d_cache_v_scale,
+                                           int base_pos, int rows, int stride, int Hk, int d,
+                                           const int* d_pt);
+/* Kept: granite4::prefill_rope_split_append_int8, engine/src/prefill_gemm.h:58-64,
+ * engine/src/prefill_gemm.cu:1328-1346. Token-major qkv [rows][(Hq+2Hk) d] at
+ * positions base_pos + r: RoPE(q) -> q_rot bf16; RoPE(k) (kept in f32) and raw
+ * v quantised per (row, kv head) into the [Hk][stride][d] int8 caches with
+ * [Hk][stride] f32 scales at pool row d_pt[pos] (NULL: pos). d must be 128,
+ * rows <= 65535, stride >= base_pos + rows. */
+int granite4_prefill_rope_split_append_int8(const uint16_t* qkv, const float* cos_tbl,
+                                            const float* sin_tbl, int base_pos, int rows, int Hq,
+                                            int Hk, int d, int stride, uint16_t* q_rot,
+                                            int8_t* cache_k, int8_t* cache_v,
+                                            float* cache_k_scale, float* cache_v_scale,
+                                            const int* d_pt);
+/* Device row descriptor of a multi-session step; layout of
+ * granite4::GpuMultiRows, engine/src/forward_gpu_api.h:162-182. */
+#define GRANITE4_MAX_VERIFY_ROWS 16
+#define GRANITE4_MAX_TREE_DEPTH 8
+typedef struct granite4_multi_rows {
+  int n;
+  int pos[GRANITE4_MAX_VERIFY_ROWS];
+  const int* pt[GRANITE4_MAX_VERIFY_ROWS];
+  int32_t* tok[GRANITE4_MAX_VERIFY_ROWS];
+  int grp[GRANITE4_MAX_VERIFY_ROWS];
+  int tree;
+  int slot[GRANITE4_MAX_VERIFY_ROWS];
+  int tbase[GRANITE4_MAX_VERIFY_ROWS];
+  int tail[GRANITE4_MAX_VERIFY_ROWS][GRANITE4_MAX_TREE_DEPTH];
+} granite4_multi_rows;
+/* Kept: granite4::gpu_multi_rope_append, engine/src/forward_gpu_api.h:219-229,
+ * engine/src/forward_gpu.cu:598-665, :3907-3914. Decode / verify form: separate
+ * q [rows][Hq d], k, v [rows][Hk d]; row r's RoPE position is d_rows->pos[r] and
+ * its pool row d_rows->pt[r][slot] (slot = pos, or d_rows->slot[r] for tree
+ * rows). K is rounded to bf16 after the rotation and then quantised. Only
+ * bits == 8 and d == 128 are built here; anything else returns -1, which the
+ * reference's callers treat as "use the unfused path". rows <= 16. */
+int granite4_gpu_multi_rope_append(const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                                   const float* cos_tbl, const float* sin_tbl,
+                                   const granite4_multi_rows* d_rows, int rows, int Hq, int Hk,
+                                   int d, int bits, void* cache_k, void* cache_v, float* k_scale,
+                                   float* v_scale, int stride, uint16_t* q_rot);
+/* Added: the prefill form with per-row positions and pool rows, for batches
+ * whose rows are not one consecutive run of positions (several sequences,
+ * offsets, permuted page tables). d_pos_rows[r] in [0, max_pos) indexes the
+ * RoPE tables; d_kv_rows[r] in [0, stride) is the pool row (page_id * 16 + pos %
+ * 16 under 16-token pages, engine/src/kv_pool.cc:285-298); rows with an index
+ * outside those ranges are skipped. k_from_bf16 selects the decode kernels'
+ * rounding of K (1) or the prefill kernel's (0). d must be 128. */
+int granite4_kernel_rope_kv_int8_paged(const uint16_t* d_qkv, const float* d_cos,
+                                       const float* d_sin, const int* d_pos_rows,
+                                       const int* d_kv_rows, int rows, int Hq, int Hk, int d,
+                                       int stride, int max_pos, int k_from_bf16,
+                                       uint16_t* d_q_rot, int8_t* d_cache_k, int8_t* d_cache_v,
+                                       float* d_k_scale, float* d_v_scale);
+
+/* ------------------------------------------------------------------------ */
+/* a4. SwiGLU, bf16 and FP8 outputs                                          */
+/* ------------------------------------------------------------------------ */
+/* Kept: granite4::prefill_silu_mul, engine/src/prefill_gemm.h:105,
+ * engine/src/prefill_gemm.cu:1468-1474. gu is f32 [rows][2 I] (gate columns
+ * first); act[r][i] = bf16(silu(gu[r][i]) * gu[r][I + i]). */
+int granite4_prefill_silu_mul(const float* gu, int I, int rows, uint16_t* act);
+/* Added: SwiGLU on bf16 (in_is_f32 == 0) or f32 gate / up rows of pitch ld
+ * elements, with optional bf16 output and optional per-tensor FP8 output:
+ *   a = bf16(silu(g) * u), amax = max |a|, scale = float(amax / 448),
+ *   code = e4m3(a / scale).
+ * d_scale_amax: float[2] = {scale, amax}, required with d_act_fp8. I must be
+ * a multiple of 8, rows 16-byte aligned. With d_act_fp8 this enqueues an 8-byte
+ * memset and two kernels. */
+int granite4_kernel_swiglu_fp8(const void* d_gate, const void* d_up, int in_is_f32, long long ld,
+                               int rows, int I, uint16_t* d_act_bf16, uint8_t* d_act_fp8,
+                               float* d_scale_amax);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRANITE4_B200_H */
