@@ -215,7 +215,10 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         raise SystemExit("the GPU count must divide 65536")
     rows = int(os.environ.get("G4_BENCH_ROWS", TOTAL_TOKENS // world))  # override only for profiling
     total_tokens = rows * world
-    seq = glue.GlueSequence(rows, shapes, device=device, seed=rank, sets=2)
+    prof_layers = os.environ.get("G4_BENCH_LAYERS")  # fewer layers: only for short profiler captures
+    workspace = os.environ.get("G4_BENCH_WORKSPACE", "1") != "0"  # 0: the scratch-free second sweeps
+    seq = glue.GlueSequence(rows, shapes, device=device, seed=rank, sets=2,
+                            layers=int(prof_layers) if prof_layers else None, workspace=workspace)
     seq.reset()
     stream = torch.cuda.current_stream(device)
 
@@ -274,7 +277,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_max / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows_per_gpu": rows, "total_tokens": total_tokens,
-                       "layers": shapes.layers, "parallelism": f"rows/{world}",
+                       "layers": seq.layers, "parallelism": f"rows/{world}",
+                       "fp8_sweep_scratch": workspace,
                        "l2": "inputs larger than L2: two rotated input sets, >= 1.1 GB touched per layer",
                        "bytes_per_token": glue.bytes_per_token(shapes)},
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": ops[dominant]["achieved_gbs"],
@@ -308,35 +312,16 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
 def timed_step(seq, op_events, stream):
     """GlueSequence.run() with an event pair around every op (for the per-op durations)."""
     import torch
-    from granite4_b200 import glue, kernels as k
-    s = seq.shapes
 
-    def timed(name, fn):
+    def timed(name, thunk):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
-        rc = fn()
+        rc = thunk()
         b.record(stream)
-        if rc != 0:
-            raise RuntimeError(f"{name} returned {rc}")
         op_events[name].append((a, b))
+        return rc
 
-    for layer in range(seq.layers):
-        buf = seq.sets[layer % len(seq.sets)]
-        timed("add_rmsnorm_fp8", lambda: k.add_rmsnorm_fp8(
-            buf["y_attn"], seq.h, seq.w[layer, 0], s.eps, s.residual_multiplier, h_out=seq.h,
-            n_fp8=seq.n_fp8, scale_amax=seq.scales[layer, 0]))
-        timed("rope_kv_int8", lambda: k.rope_kv_int8_paged(
-            buf["qkv"], seq.tables.cos, seq.tables.sin, seq.pos_rows, seq.kv_rows, s.q_heads, s.kv_heads,
-            s.head_dim, seq.pool_rows, seq.max_pos, 0, seq.q_rot, seq.cache_k[layer], seq.cache_v[layer],
-            seq.k_scale[layer], seq.v_scale[layer]))
-        timed("add_rmsnorm_fp8", lambda: k.add_rmsnorm_fp8(
-            buf["y_mlp"], seq.h, seq.w[layer, 1], s.eps, s.residual_multiplier, h_out=seq.h,
-            n_fp8=seq.n_fp8, scale_amax=seq.scales[layer, 1]))
-        timed("swiglu_fp8", lambda: k.swiglu_fp8(buf["gate"], buf["up"], act_fp8=seq.act_fp8,
-                                                 scale_amax=seq.scales[layer, 2]))
-        seq.launches += glue.KERNELS_PER_LAYER
-    timed("final_norm", lambda: k.rmsnorm(seq.h, seq.w_final, s.eps, seq.rows, s.hidden, seq.out))
-    seq.launches += glue.KERNELS_FINAL
+    seq.run(wrap=timed)
 
 
 def main():

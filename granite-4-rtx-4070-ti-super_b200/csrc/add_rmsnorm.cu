@@ -11,22 +11,26 @@
 //   code = e4m3_rne(n / scale)
 //
 // Data layout: rows are contiguous, cols % 8 == 0, every row 16-byte aligned.
-// One CTA owns one row; a thread owns V chunks of 8 elements (one 128-bit load
-// each for bf16, two for f32), strided by the CTA width so a warp reads 512
-// contiguous bytes per load. The row stays in registers between the reduction
-// and the normalise step, so each input byte is read once per sweep.
 //
-// The FP8 scale depends on every row, so FP8 output takes two sweeps: the
-// stats sweep writes h (and n as bf16 if asked) and folds max |n| into
-// d_scale_amax[1] with an integer atomicMax; the encode sweep re-reads the
-// bf16 hidden state (8 KB per row instead of the 16 KB of y and res), repeats
-// the same reduction in the same order (so n is bit-identical) and writes the
-// codes. The encode sweep walks the rows backwards: the rows the stats sweep
-// wrote last are the ones most likely still in L2.
+// Stats sweep (add_rmsnorm_kernel): one CTA owns one row; a thread owns V chunks
+// of 8 elements (one 128-bit load each for bf16, two for f32), strided by the
+// CTA width so a warp reads 512 contiguous bytes per load. The row stays in
+// registers between the reduction and the normalise step, so each input byte is
+// read once. It writes h, optionally n as bf16 and the row's r, and folds
+// max |n| into d_scale_amax[1] with an integer atomicMax.
+//
+// The FP8 scale depends on every row, so the codes come from a second sweep:
+//   * with r saved per row (d_rstd given): norm_encode_kernel streams the bf16
+//     hidden state once more (8 KB per row, not the 16 KB of y and res),
+//     recomputes n = bf16(h r w) elementwise and writes the codes;
+//   * without it, the row kernel runs again in encode mode and repeats the
+//     reduction in the same order, so n is bit-identical either way.
+// The second sweep walks the rows backwards: the rows the first sweep wrote
+// last are the ones most likely still in L2.
 //
 // Algorithmic bytes per row at cols = 4096, bf16 y and res, h + FP8 out:
-// 8192 + 8192 read, 8192 + 4096 written = 28 672; the encode sweep adds a
-// second 8192-byte read of h.
+// 8192 + 8192 read, 8192 + 4096 written = 28 672; the second sweep adds another
+// 8192-byte read of h.
 #include "g4_host.h"
 #include "g4_math.cuh"
 
@@ -46,12 +50,14 @@ struct NormParams {
   uint16_t* n_bf16;
   uint8_t* n_fp8;
   float* scale_amax;  // [0] scale, [1] amax
+  float* rstd;        // [rows] or NULL
   float eps;
   float rm;
   int rows;
   int cols8;  // cols / 8
   int cols;
   int reverse;  // walk rows from the last to the first
+  double inv_cols;  // 1 / cols when cols is a power of two (the scaling is then exact), else 0
 };
 
 enum { kStats = 0, kEncode = 1 };
@@ -65,9 +71,7 @@ __device__ __forceinline__ void load_chunk(const void* base, size_t chunk, float
     v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
     v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
   } else {
-    const uint4 u = ld_stream(reinterpret_cast<const uint4*>(base) + chunk);
-    v[0] = bf16_lo(u.x), v[1] = bf16_hi(u.x), v[2] = bf16_lo(u.y), v[3] = bf16_hi(u.y);
-    v[4] = bf16_lo(u.z), v[5] = bf16_hi(u.z), v[6] = bf16_lo(u.w), v[7] = bf16_hi(u.w);
+    unpack8(ld_stream(reinterpret_cast<const uint4*>(base) + chunk), v);
   }
 }
 
@@ -112,96 +116,128 @@ __global__ void __launch_bounds__(max_threads_for(V))
       }
     }
   }
-  uint4 hb[V];
+  // the norm reads the bf16-rounded hidden state, as the reference's separate norm kernel does
 #pragma unroll
   for (int j = 0; j < V; ++j) {
-    hb[j].x = pack_bf16x2(h[j][0], h[j][1]);
-    hb[j].y = pack_bf16x2(h[j][2], h[j][3]);
-    hb[j].z = pack_bf16x2(h[j][4], h[j][5]);
-    hb[j].w = pack_bf16x2(h[j][6], h[j][7]);
-    h[j][0] = bf16_lo(hb[j].x), h[j][1] = bf16_hi(hb[j].x);
-    h[j][2] = bf16_lo(hb[j].y), h[j][3] = bf16_hi(hb[j].y);
-    h[j][4] = bf16_lo(hb[j].z), h[j][5] = bf16_hi(hb[j].z);
-    h[j][6] = bf16_lo(hb[j].w), h[j][7] = bf16_hi(hb[j].w);
-  }
-  if (PHASE == kStats && p.h_out != nullptr) {
-    uint4* dst = reinterpret_cast<uint4*>(p.h_out) + row_chunk0;
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
+    const uint4 hb = pack8(h[j]);
+    unpack8(hb, h[j]);
+    if (PHASE == kStats && p.h_out != nullptr) {
       const int c = t + j * T;
-      if (c < p.cols8) dst[c] = hb[j];  // default policy: the encode sweep re-reads it
+      // default cache policy: the second sweep re-reads it
+      if (c < p.cols8) reinterpret_cast<uint4*>(p.h_out)[row_chunk0 + c] = hb;
     }
   }
 
   // ---- sum of squares in double, fixed order ----------------------------------
-  // Each square of a bf16 value is exact in f32; the double sum then carries
-  // ~29 spare bits, so float(sum / cols) equals the host's sequential double
-  // sum except when the quotient lies within ~1e-13 relative of a float
-  // rounding boundary.
+  // A bf16 value converts to double exactly and its square is exact there; the
+  // double sum then carries ~29 spare bits, so float(sum / cols) equals the
+  // host's sequential double sum except when the quotient lies within ~1e-13
+  // relative of a float rounding boundary.
   double acc = 0.0;
 #pragma unroll
   for (int j = 0; j < V; ++j)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc += static_cast<double>(__fmul_rn(h[j][e], h[j][e]));
+    for (int e = 0; e < 8; ++e) {
+      const double d = static_cast<double>(h[j][e]);
+      acc = fma(d, d, acc);
+    }
   acc = warp_sum(acc);
   __shared__ double s_part[32];
-  __shared__ float s_amax[32];
+  __shared__ uint32_t s_amax[32];
   const int warp = t >> 5, lane = t & 31, nwarps = T >> 5;
   if (lane == 0) s_part[warp] = acc;
   __syncthreads();
   double total = 0.0;
   for (int i = 0; i < nwarps; ++i) total += s_part[i];
-  const float ms = static_cast<float>(total / static_cast<double>(p.cols));
+  const float ms = static_cast<float>(p.inv_cols != 0.0 ? total * p.inv_cols
+                                                         : total / static_cast<double>(p.cols));
   const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, p.eps)));
+  if (PHASE == kStats && p.rstd != nullptr && t == 0) p.rstd[row] = r;
 
   // ---- normalise -----------------------------------------------------------------
-  float scale = 0.0f;
-  if (PHASE == kEncode) scale = fp8_scale_from_amax(__ldcg(p.scale_amax + 1));
-  float amax = 0.0f;
+  Fp8Scale fs{};
+  if (PHASE == kEncode) fs = fp8_scale_from_amax(__ldcg(p.scale_amax + 1));
+  uint32_t amax = 0u;
 #pragma unroll
   for (int j = 0; j < V; ++j) {
     const int c = t + j * T;
     if (c < p.cols8) {
-      const uint4 wu = __ldg(reinterpret_cast<const uint4*>(p.w) + c);
-      float wv[8] = {bf16_lo(wu.x), bf16_hi(wu.x), bf16_lo(wu.y), bf16_hi(wu.y),
-                     bf16_lo(wu.z), bf16_hi(wu.z), bf16_lo(wu.w), bf16_hi(wu.w)};
-      float n[8];
+      float wv[8], n[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.w) + c), wv);
 #pragma unroll
       for (int e = 0; e < 8; ++e) n[e] = __fmul_rn(__fmul_rn(h[j][e], r), wv[e]);
-      uint4 nb;
-      nb.x = pack_bf16x2(n[0], n[1]);
-      nb.y = pack_bf16x2(n[2], n[3]);
-      nb.z = pack_bf16x2(n[4], n[5]);
-      nb.w = pack_bf16x2(n[6], n[7]);
+      const uint4 nb = pack8(n);
       if (PHASE == kStats) {
         if (p.n_bf16 != nullptr) {
           uint4* dst = reinterpret_cast<uint4*>(p.n_bf16) + row_chunk0 + c;
           if (p.n_fp8 != nullptr) *dst = nb; else st_stream(dst, nb);
         }
-        // |bf16| as bits: clear the two sign bits and take the integer max.
-        const uint32_t m0 = nb.x & 0x7fff7fffu, m1 = nb.y & 0x7fff7fffu;
-        const uint32_t m2 = nb.z & 0x7fff7fffu, m3 = nb.w & 0x7fff7fffu;
-        amax = fmaxf(amax, fmaxf(fmaxf(bf16_lo(m0), bf16_hi(m0)), fmaxf(bf16_lo(m1), bf16_hi(m1))));
-        amax = fmaxf(amax, fmaxf(fmaxf(bf16_lo(m2), bf16_hi(m2)), fmaxf(bf16_lo(m3), bf16_hi(m3))));
+        amax = amax_acc(amax, nb);
       } else {
-        uint2 codes;
-        codes.x = fp8x4_quant(bf16_lo(nb.x), bf16_hi(nb.x), bf16_lo(nb.y), bf16_hi(nb.y), scale);
-        codes.y = fp8x4_quant(bf16_lo(nb.z), bf16_hi(nb.z), bf16_lo(nb.w), bf16_hi(nb.w), scale);
-        st_stream(reinterpret_cast<uint2*>(p.n_fp8) + row_chunk0 + c, codes);
+        st_stream(reinterpret_cast<uint2*>(p.n_fp8) + row_chunk0 + c, fp8x8_quant(nb, fs));
       }
     }
   }
   if (PHASE == kStats && p.scale_amax != nullptr) {
-    amax = warp_max(amax);
+    amax = amax_warp(amax);
     if (lane == 0) s_amax[warp] = amax;
     __syncthreads();
     if (t == 0) {
-      float m = 0.0f;
-      for (int i = 0; i < nwarps; ++i) m = fmaxf(m, s_amax[i]);
-      atomic_amax(p.scale_amax + 1, m);
+      uint32_t m = 0u;
+      for (int i = 0; i < nwarps; ++i) m = max_u16x2(m, s_amax[i]);
+      atomic_amax(p.scale_amax + 1, amax_value(m));
     }
   }
-  if (PHASE == kEncode && blockIdx.x == 0 && t == 0) p.scale_amax[0] = scale;
+  if (PHASE == kEncode && blockIdx.x == 0 && t == 0) p.scale_amax[0] = fs.scale;
+}
+
+// Second sweep with r known per row: a plain streaming pass. A CTA takes kRowsPerCta
+// consecutive rows; a thread takes the chunks t, t + T, ... of each, so every
+// thread has kRowsPerCta * ceil(cols8 / T) independent 128-bit loads to issue
+// before it needs any of them.
+constexpr int kRowsPerCta = 4;
+constexpr int kEncodeThreads = 256;
+constexpr int kEncodeMaxIter = 2;  // cols8 <= 512 per pass of the unrolled body
+
+__global__ void __launch_bounds__(kEncodeThreads) norm_encode_kernel(const NormParams p) {
+  const int t = threadIdx.x;
+  const int tiles = (p.rows + kRowsPerCta - 1) / kRowsPerCta;
+  const int tile = p.reverse ? tiles - 1 - static_cast<int>(blockIdx.x) : blockIdx.x;
+  const int row0 = tile * kRowsPerCta;
+  const Fp8Scale fs = fp8_scale_from_amax(__ldcg(p.scale_amax + 1));
+  if (blockIdx.x == 0 && t == 0) p.scale_amax[0] = fs.scale;
+  const uint4* h = reinterpret_cast<const uint4*>(p.h_out);
+  uint2* out = reinterpret_cast<uint2*>(p.n_fp8);
+  for (int c0 = 0; c0 < p.cols8; c0 += kEncodeThreads * kEncodeMaxIter) {
+    uint4 hv[kRowsPerCta][kEncodeMaxIter];
+    uint4 wv[kEncodeMaxIter];
+#pragma unroll
+    for (int k = 0; k < kEncodeMaxIter; ++k) {
+      const int c = c0 + k * kEncodeThreads + t;
+      if (c < p.cols8) {
+        wv[k] = __ldg(reinterpret_cast<const uint4*>(p.w) + c);
+#pragma unroll
+        for (int j = 0; j < kRowsPerCta; ++j)
+          if (row0 + j < p.rows) hv[j][k] = ld_stream(h + static_cast<size_t>(row0 + j) * p.cols8 + c);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kRowsPerCta; ++j) {
+      if (row0 + j >= p.rows) continue;
+      const float r = __ldg(p.rstd + row0 + j);
+#pragma unroll
+      for (int k = 0; k < kEncodeMaxIter; ++k) {
+        const int c = c0 + k * kEncodeThreads + t;
+        if (c >= p.cols8) continue;
+        float hf[8], wf[8], n[8];
+        unpack8(hv[j][k], hf);
+        unpack8(wv[k], wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) n[e] = __fmul_rn(__fmul_rn(hf[e], r), wf[e]);
+        st_stream(out + static_cast<size_t>(row0 + j) * p.cols8 + c, fp8x8_quant(pack8(n), fs));
+      }
+    }
+  }
 }
 
 // Any cols, any alignment: one CTA per row, scalar accesses, the row re-read
@@ -212,8 +248,8 @@ __global__ void __launch_bounds__(256)
   const size_t base = static_cast<size_t>(blockIdx.x) * cols;
   double acc = 0.0;
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    const float v = bf16_to_f32(x[base + c]);
-    acc += static_cast<double>(__fmul_rn(v, v));
+    const double v = static_cast<double>(bf16_to_f32(x[base + c]));
+    acc = fma(v, v, acc);
   }
   acc = warp_sum(acc);
   __shared__ double s_part[8];
@@ -231,40 +267,45 @@ __global__ void __launch_bounds__(256)
 }
 
 // Elementwise per-tensor FP8 of a bf16 tensor: amax sweep, then encode sweep.
+constexpr int kQuantUnroll = 4;
 __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* x, long long n8, float* scale_amax) {
-  float amax = 0.0f;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const uint4 u = __ldg(x + i);
-    const uint32_t m0 = u.x & 0x7fff7fffu, m1 = u.y & 0x7fff7fffu, m2 = u.z & 0x7fff7fffu,
-                   m3 = u.w & 0x7fff7fffu;
-    amax = fmaxf(amax, fmaxf(fmaxf(bf16_lo(m0), bf16_hi(m0)), fmaxf(bf16_lo(m1), bf16_hi(m1))));
-    amax = fmaxf(amax, fmaxf(fmaxf(bf16_lo(m2), bf16_hi(m2)), fmaxf(bf16_lo(m3), bf16_hi(m3))));
+  uint32_t amax = 0u;
+  const long long base = static_cast<long long>(blockIdx.x) * (256 * kQuantUnroll) + threadIdx.x;
+  uint4 v[kQuantUnroll];
+#pragma unroll
+  for (int k = 0; k < kQuantUnroll; ++k) {
+    const long long i = base + k * 256;
+    v[k] = i < n8 ? __ldg(x + i) : make_uint4(0, 0, 0, 0);
   }
-  amax = warp_max(amax);
-  __shared__ float s[8];
+#pragma unroll
+  for (int k = 0; k < kQuantUnroll; ++k) amax = amax_acc(amax, v[k]);
+  amax = amax_warp(amax);
+  __shared__ uint32_t s[8];
   if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = amax;
   __syncthreads();
   if (threadIdx.x == 0) {
-    float m = 0.0f;
-    for (int i = 0; i < 8; ++i) m = fmaxf(m, s[i]);
-    atomic_amax(scale_amax + 1, m);
+    uint32_t m = 0u;
+    for (int i = 0; i < 8; ++i) m = max_u16x2(m, s[i]);
+    atomic_amax(scale_amax + 1, amax_value(m));
   }
 }
 
 __global__ void __launch_bounds__(256)
     encode_bf16_kernel(const uint4* x, long long n8, uint2* codes, float* scale_amax) {
-  const float scale = fp8_scale_from_amax(__ldcg(scale_amax + 1));
-  if (blockIdx.x == 0 && threadIdx.x == 0) scale_amax[0] = scale;
+  const Fp8Scale fs = fp8_scale_from_amax(__ldcg(scale_amax + 1));
+  if (blockIdx.x == 0 && threadIdx.x == 0) scale_amax[0] = fs.scale;
   // last element first: the tail of the tensor is what the amax sweep left in L2
-  for (long long k = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; k < n8;
-       k += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long i = n8 - 1 - k;
-    const uint4 u = ld_stream(x + i);
-    uint2 c;
-    c.x = fp8x4_quant(bf16_lo(u.x), bf16_hi(u.x), bf16_lo(u.y), bf16_hi(u.y), scale);
-    c.y = fp8x4_quant(bf16_lo(u.z), bf16_hi(u.z), bf16_lo(u.w), bf16_hi(u.w), scale);
-    st_stream(codes + i, c);
+  const long long base = static_cast<long long>(blockIdx.x) * (256 * kQuantUnroll) + threadIdx.x;
+  uint4 v[kQuantUnroll];
+#pragma unroll
+  for (int k = 0; k < kQuantUnroll; ++k) {
+    const long long i = n8 - 1 - (base + k * 256);
+    if (i >= 0) v[k] = ld_stream(x + i);
+  }
+#pragma unroll
+  for (int k = 0; k < kQuantUnroll; ++k) {
+    const long long i = n8 - 1 - (base + k * 256);
+    if (i >= 0) st_stream(codes + i, fp8x8_quant(v[k], fs));
   }
 }
 
@@ -310,18 +351,22 @@ void launch_phase(const NormParams& p, bool y_f32, bool res_f32, cudaStream_t st
   }
 }
 
+long long quant_grid(long long n8) { return (n8 + 256 * kQuantUnroll - 1) / (256 * kQuantUnroll); }
+
 }  // namespace
 
 // Shared by the kept rmsnorm entry points and the fused one.
 int add_rmsnorm_launch(const char* fn, const void* d_y, int y_is_f32, const void* d_res,
                        int res_is_f32, const uint16_t* d_w, float eps, float rm, int rows, int cols,
                        uint16_t* d_h_out, uint16_t* d_n_bf16, uint8_t* d_n_fp8,
-                       float* d_scale_amax) {
+                       float* d_scale_amax, float* d_rstd) {
   cudaStream_t st = current_stream();
   NormParams p{};
   p.y = d_y, p.res = d_res, p.w = d_w, p.h_out = d_h_out, p.n_bf16 = d_n_bf16, p.n_fp8 = d_n_fp8;
   p.scale_amax = d_n_fp8 != nullptr ? d_scale_amax : nullptr;
+  p.rstd = d_rstd;
   p.eps = eps, p.rm = rm, p.rows = rows, p.cols = cols, p.cols8 = cols / 8, p.reverse = 0;
+  p.inv_cols = (cols & (cols - 1)) == 0 ? 1.0 / static_cast<double>(cols) : 0.0;
   if (d_n_fp8 != nullptr)
     G4_CUDA_TRY(fn, cudaMemsetAsync(d_scale_amax, 0, 2 * sizeof(float), st));
   launch_phase<kStats>(p, y_is_f32 != 0, res_is_f32 != 0, st);
@@ -330,9 +375,13 @@ int add_rmsnorm_launch(const char* fn, const void* d_y, int y_is_f32, const void
     if (d_n_bf16 != nullptr) {
       // n already sits in memory as bf16: encode it elementwise.
       const long long n8 = static_cast<long long>(rows) * (cols / 8);
-      const int grid = static_cast<int>(std::min<long long>((n8 + 255) / 256, sm_count() * 16LL));
-      encode_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(d_n_bf16), n8,
-                                               reinterpret_cast<uint2*>(d_n_fp8), d_scale_amax);
+      encode_bf16_kernel<<<static_cast<unsigned>(quant_grid(n8)), 256, 0, st>>>(
+          reinterpret_cast<const uint4*>(d_n_bf16), n8, reinterpret_cast<uint2*>(d_n_fp8),
+          d_scale_amax);
+    } else if (d_h_out != nullptr && d_rstd != nullptr) {
+      NormParams q = p;
+      q.reverse = 1;
+      norm_encode_kernel<<<(rows + kRowsPerCta - 1) / kRowsPerCta, kEncodeThreads, 0, st>>>(q);
     } else {
       NormParams q = p;
       q.reverse = 1;
@@ -363,7 +412,7 @@ int rmsnorm_entry(const char* fn, const uint16_t* d_x, const uint16_t* d_w, floa
     return 0;
   }
   return add_rmsnorm_launch(fn, d_x, 0, nullptr, 0, d_w, eps, 1.0f, rows, cols, nullptr, d_out,
-                            nullptr, nullptr);
+                            nullptr, nullptr, nullptr);
 }
 
 }  // namespace g4
@@ -384,7 +433,8 @@ int granite4_kernel_rmsnorm_batched(const uint16_t* d_x, const uint16_t* d_w, fl
 int granite4_kernel_add_rmsnorm_fp8(const void* d_y, int y_is_f32, const void* d_res,
                                     int res_is_f32, const uint16_t* d_w, float eps,
                                     float resid_mult, int rows, int cols, uint16_t* d_h_out,
-                                    uint16_t* d_n_bf16, uint8_t* d_n_fp8, float* d_scale_amax) {
+                                    uint16_t* d_n_bf16, uint8_t* d_n_fp8, float* d_scale_amax,
+                                    float* d_rstd) {
   const char* fn = "granite4_kernel_add_rmsnorm_fp8";
   if (d_y == nullptr || d_w == nullptr || !std::isfinite(eps) || eps <= 0.0f ||
       !std::isfinite(resid_mult) || rows <= 0 || cols <= 0 ||
@@ -400,7 +450,7 @@ int granite4_kernel_add_rmsnorm_fp8(const void* d_y, int y_is_f32, const void* d
       !g4::aligned16(d_h_out) || !g4::aligned16(d_n_bf16) || !g4::aligned16(d_n_fp8))
     return g4::fail(fn, "pointers must be 16-byte aligned");
   return g4::add_rmsnorm_launch(fn, d_y, y_is_f32, d_res, res_is_f32, d_w, eps, resid_mult, rows,
-                                cols, d_h_out, d_n_bf16, d_n_fp8, d_scale_amax);
+                                cols, d_h_out, d_n_bf16, d_n_fp8, d_scale_amax, d_rstd);
 }
 
 int granite4_kernel_fp8_quant(const uint16_t* d_x, long long n, uint8_t* d_codes,
@@ -411,12 +461,14 @@ int granite4_kernel_fp8_quant(const uint16_t* d_x, long long n, uint8_t* d_codes
     return g4::fail(fn, "invalid arguments");
   cudaStream_t st = g4::current_stream();
   const long long n8 = n / 8;
-  const int grid = static_cast<int>(std::min<long long>((n8 + 255) / 256, g4::sm_count() * 16LL));
+  const long long grid = g4::quant_grid(n8);
+  if (grid > INT_MAX) return g4::fail(fn, "tensor too large");
   G4_CUDA_TRY(fn, cudaMemsetAsync(d_scale_amax, 0, 2 * sizeof(float), st));
-  g4::amax_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(d_x), n8, d_scale_amax);
+  g4::amax_bf16_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(
+      reinterpret_cast<const uint4*>(d_x), n8, d_scale_amax);
   G4_LAUNCH_CHECK(fn);
-  g4::encode_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(d_x), n8,
-                                               reinterpret_cast<uint2*>(d_codes), d_scale_amax);
+  g4::encode_bf16_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(
+      reinterpret_cast<const uint4*>(d_x), n8, reinterpret_cast<uint2*>(d_codes), d_scale_amax);
   G4_LAUNCH_CHECK(fn);
   return 0;
 }

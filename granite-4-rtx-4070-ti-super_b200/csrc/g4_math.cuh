@@ -1,11 +1,18 @@
 // Device scalar math of the Granite glue kernels (sm_100a).
 //
 // Every rounding point is spelled with an explicit round-to-nearest intrinsic
-// (__fmul_rn / __fadd_rn / __fdiv_rn / __fsqrt_rn): the compiler may not fuse
-// a multiply into a following add, so results equal the reference's host fp32
-// formulation (engine/src/kernel_math.h, compiled without FMA) bit for bit
-// wherever that formulation has no transcendental. All kernels here are
-// HBM-bound, so the extra instructions are free.
+// (__fmul_rn / __fadd_rn / ...): the compiler may not fuse a multiply into a
+// following add, so results equal the reference's host fp32 formulation
+// (engine/src/kernel_math.h, compiled without FMA) bit for bit wherever that
+// formulation has no transcendental.
+//
+// These kernels move 3-6 bytes per element, which at HBM speed leaves an SM
+// only 10-20 issue slots per element. The quantisers therefore have a short
+// common path (a multiply by the reciprocal of the scale and a hardware
+// conversion) and an exact path (IEEE division and the rounding rule spelled
+// out) that is taken only by the few elements whose quotient lies so close to a
+// rounding boundary that the short path could pick the other side. The results
+// are those of the exact path everywhere.
 #pragma once
 
 #include <cuda_fp8.h>
@@ -22,18 +29,63 @@ __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w 
 __device__ __forceinline__ float bf16_to_f32(uint16_t b) {
   return __uint_as_float(static_cast<uint32_t>(b) << 16);
 }
+// The reference's integer form (add 0x7fff + lsb, shift). Kept for scalar
+// fallback kernels.
 __device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
   uint32_t u = __float_as_uint(f);
   u += 0x7fffu + ((u >> 16) & 1u);
   return u >> 16;
 }
-// (lo, hi) -> packed pair, lo in the low half.
+// (lo, hi) -> packed pair, lo in the low half: one conversion instruction for
+// two elements. It rounds to nearest even exactly as the integer form does for
+// every finite input and for infinities (NaN payloads may differ).
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
 }
 // Round a float to the nearest bf16 and return it as a float.
 __device__ __forceinline__ float round_bf16(float f) {
-  return __uint_as_float(f32_to_bf16_bits(f) << 16);
+  return __uint_as_float(pack_bf16x2(0.0f, f) & 0xffff0000u);
+}
+
+__device__ __forceinline__ void unpack8(uint4 u, float (&v)[8]) {
+  v[0] = bf16_lo(u.x), v[1] = bf16_hi(u.x), v[2] = bf16_lo(u.y), v[3] = bf16_hi(u.y);
+  v[4] = bf16_lo(u.z), v[5] = bf16_hi(u.z), v[6] = bf16_lo(u.w), v[7] = bf16_hi(u.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(v[0], v[1]);
+  u.y = pack_bf16x2(v[2], v[3]);
+  u.z = pack_bf16x2(v[4], v[5]);
+  u.w = pack_bf16x2(v[6], v[7]);
+  return u;
+}
+
+// ---- running max |x| over packed bf16 pairs -----------------------------------
+// Clearing the two sign bits leaves magnitudes whose bit patterns order like
+// unsigned 16-bit integers, so the running maximum is one AND and one packed
+// integer max per two elements.
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t amax_acc(uint32_t acc, uint32_t bf16_pair) {
+  return max_u16x2(acc, bf16_pair & 0x7fff7fffu);
+}
+__device__ __forceinline__ uint32_t amax_acc(uint32_t acc, uint4 v) {
+  return amax_acc(amax_acc(amax_acc(amax_acc(acc, v.x), v.y), v.z), v.w);
+}
+__device__ __forceinline__ uint32_t amax_warp(uint32_t acc) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc = max_u16x2(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+  return acc;
+}
+// Larger half of the packed accumulator, as a float.
+__device__ __forceinline__ float amax_value(uint32_t acc) {
+  const uint32_t lo = acc & 0xffffu, hi = acc >> 16;
+  return __uint_as_float((lo > hi ? lo : hi) << 16);
 }
 
 // ---- FP8 e4m3, per-tensor scale --------------------------------------------
@@ -41,66 +93,89 @@ __device__ __forceinline__ float round_bf16(float f) {
 // engine/src/fp8_convert.cc:47-122): scale = float(amax / 448) with the
 // division in double; code = RNE_e4m3(double(v) / double(scale)) in exact
 // arithmetic, |q| >= 464 clipping to +-448; scale == 0 -> encode v itself.
-__device__ __forceinline__ float fp8_scale_from_amax(float amax) {
-  return static_cast<float>(static_cast<double>(amax) / 448.0);
+// v is always a bf16 value here, so the double quotient the reference forms
+// rounds to e4m3 exactly as the true quotient v / scale does.
+//
+// The quantiser is exact and branch-free, five instructions per element plus
+// half a conversion:
+//  1. 1 / scale, nudged up by less than 2^-38 relative, is split into a 16-bit
+//     head and a 24-bit tail. A bf16 value has 8 significant bits, so v * head is
+//     exact in f32, and one FMA rounding TOWARD ZERO adds v * tail: q is the
+//     true quotient v / scale truncated to 24 bits. (The nudge keeps the product
+//     from falling a hair below an exactly representable quotient. It cannot
+//     carry the product past an e4m3 midpoint: v has 8 significant bits and
+//     scale 24, so a quotient that is not exactly a midpoint is at least 2^-29
+//     relative away from it.)
+//  2. rem = fma(-q, scale, v) is the exact remainder, zero iff q is the true
+//     quotient.
+//  3. If it is not, the last mantissa bit of q is set: q is now the true quotient
+//     rounded TO ODD. A value rounded to odd at 24 bits rounds to nearest even at
+//     any precision two or more bits shorter exactly as the unrounded value does,
+//     so the hardware e4m3 conversion that follows returns the reference's code
+//     for every input: true ties go to even, near-ties (about one bf16 mantissa
+//     pattern in 128 is a would-be tie that the rounding of the scale itself
+//     moved off the midpoint) go to the side the double quotient is on, and the
+//     e4m3 subnormal range and the saturation need no special case.
+struct Fp8Scale {
+  float scale;   // 0 when the tensor is all zeros
+  float div;     // divisor used for the remainder: scale, or 1 when scale == 0
+  float inv_hi;  // head of 1 / div: low 8 mantissa bits clear
+  float inv_lo;  // tail, rounded up
+};
+__device__ __forceinline__ Fp8Scale fp8_scale_from_amax(float amax) {
+  Fp8Scale s;
+  s.scale = static_cast<float>(static_cast<double>(amax) / 448.0);
+  s.div = s.scale > 0.0f ? s.scale : 1.0f;
+  const double inv = (1.0 / static_cast<double>(s.div)) * (1.0 + 0x1p-45);
+  s.inv_hi = __uint_as_float(__float_as_uint(__double2float_rz(inv)) & 0xffffff00u);
+  s.inv_lo = __double2float_ru(inv - static_cast<double>(s.inv_hi));
+  return s;
 }
 
-// The quotient handed to the hardware e4m3 conversion. The f32 quotient of two
-// floats is the correctly rounded true quotient; rounding it a second time to
-// e4m3 differs from rounding the true quotient only when the f32 quotient sits
-// exactly on an e4m3 midpoint that the true quotient is not on. The exact
-// remainder sign (one FMA) says which side the true quotient is on, and the
-// quotient is moved one f32 ulp that way, off the midpoint. True ties (zero
-// remainder) are left for the conversion's round-half-even, as the reference
-// does. v is a bf16 value, so the double quotient the reference forms rounds to
-// e4m3 exactly as the true quotient does.
-__device__ __forceinline__ float fp8_scaled(float v, float scale) {
-  float q = __fdiv_rn(v, scale);
-  const uint32_t qb = __float_as_uint(q);
-  const uint32_t mag = qb & 0x7fffffffu;
-  bool tie;
-  if (mag >= 0x3c800000u) {  // |q| >= 2^-6: 3 mantissa bits survive
-    tie = (mag & 0x000fffffu) == 0x00080000u;
-  } else {  // fixed step 2^-9
-    const float y = __uint_as_float(mag) * 512.0f;
-    tie = (y - floorf(y)) == 0.5f;
-  }
-  if (tie) {
-    const float rem = __fmaf_rn(-q, scale, v);  // sign of (true quotient - q), scale > 0
-    if (rem != 0.0f) {
-      const bool up = rem > 0.0f;
-      const bool neg = (qb >> 31) != 0u;
-      q = __uint_as_float(up != neg ? qb + 1u : qb - 1u);
-    }
-  }
-  return q;
-}
-
-// Two scaled values -> two e4m3 codes (lo in the low byte). cvt.rn.satfinite:
-// round to nearest even, everything above 448 (incl. inf) saturates to 448,
-// NaN -> 0x7F, the sign of zero is kept.
+// Two floats -> two e4m3 codes (lo in the low byte). cvt.rn.satfinite: round to
+// nearest even, everything above 448 (incl. inf) saturates to 448, NaN -> 0x7F,
+// the sign of zero is kept.
 __device__ __forceinline__ uint32_t fp8x2_encode(float lo, float hi) {
   return static_cast<uint32_t>(
       __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
 }
-__device__ __forceinline__ uint32_t fp8x2_quant(float lo, float hi, float scale) {
-  if (scale > 0.0f) {
-    lo = fp8_scaled(lo, scale);
-    hi = fp8_scaled(hi, scale);
-  }
-  return fp8x2_encode(lo, hi);
+
+// v / scale rounded to odd (see above); v is a bf16-valued float.
+__device__ __forceinline__ float fp8_quotient_odd(float v, const Fp8Scale s) {
+  const float q = __fmaf_rz(v, s.inv_lo, __fmul_rn(v, s.inv_hi));
+  const float rem = __fmaf_rn(-q, s.div, v);
+  uint32_t qb = __float_as_uint(q);
+  if (rem != 0.0f) qb |= 1u;
+  return __uint_as_float(qb);
 }
-// Four values -> four codes in one 32-bit word (element 0 in the low byte).
-__device__ __forceinline__ uint32_t fp8x4_quant(float a, float b, float c, float d, float scale) {
-  return fp8x2_quant(a, b, scale) | (fp8x2_quant(c, d, scale) << 16);
+
+// Eight packed bf16 values -> eight codes (element 0 in the low byte of .x).
+__device__ __forceinline__ uint2 fp8x8_quant(uint4 p, const Fp8Scale s) {
+  float v[8];
+  unpack8(p, v);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = fp8_quotient_odd(v[e], s);
+  uint2 c;
+  c.x = fp8x2_encode(v[0], v[1]) | (fp8x2_encode(v[2], v[3]) << 16);
+  c.y = fp8x2_encode(v[4], v[5]) | (fp8x2_encode(v[6], v[7]) << 16);
+  return c;
 }
 
 // ---- int8 KV rows (Q8_0) ----------------------------------------------------
 // Reference: engine/src/device_math.cuh:105-134, engine/src/kernel_math.h:71-86.
 // s = amax / 127 (IEEE division), code = clamp(round_half_away(x / s), +-127),
 // s == 0 -> 0.
-__device__ __forceinline__ float kv8_scale(float amax) { return __fdiv_rn(amax, 127.0f); }
-__device__ __forceinline__ int kv8_quant(float x, float s) {
+struct Kv8Scale {
+  float s;
+  float inv;  // 1 / s, or 0 when s == 0 (every code is then 0)
+};
+__device__ __forceinline__ Kv8Scale kv8_scale(float amax) {
+  Kv8Scale k;
+  k.s = __fdiv_rn(amax, 127.0f);
+  k.inv = k.s != 0.0f ? __fdiv_rn(1.0f, k.s) : 0.0f;
+  return k;
+}
+static __device__ __noinline__ int kv8_quant_exact(float x, float s) {
   if (s == 0.0f) return 0;
   const float q = __fdiv_rn(x, s);
   float t = truncf(q);
@@ -109,9 +184,23 @@ __device__ __forceinline__ int kv8_quant(float x, float s) {
   t = fminf(fmaxf(t, -127.0f), 127.0f);
   return static_cast<int>(t);
 }
+// Short path: x * inv is within 2e-5 of the true quotient (|q| <= 127), so its
+// nearest integer is the right code unless the fraction is that close to one
+// half; those elements take the exact path. |x| <= amax keeps |q| <= 127 + 2e-5,
+// which rounds into range without a clamp. The magic constant 1.5 * 2^23 makes
+// the f32 add itself round to the nearest integer and leaves it in the low bits.
+__device__ __forceinline__ int kv8_quant(float x, const Kv8Scale k) {
+  const float q = __fmul_rn(x, k.inv);
+  const float t = __fadd_rn(q, 12582912.0f);
+  const float d = __fsub_rn(q, __fsub_rn(t, 12582912.0f));
+  int code = static_cast<int>(__float_as_uint(t)) - 0x4b400000;
+  // written so that a NaN (an overflowed 1 / s for a subnormal s) also goes the exact way
+  if (!(fabsf(d) <= 0.4999f)) code = kv8_quant_exact(x, k.s);
+  return code;
+}
 __device__ __forceinline__ uint32_t pack_i8x4(int a, int b, int c, int d) {
   return (static_cast<uint32_t>(a) & 0xffu) | ((static_cast<uint32_t>(b) & 0xffu) << 8) |
-         ((static_cast<uint32_t>(c) & 0xffu) << 16) | ((static_cast<uint32_t>(d) & 0xffu) << 24);
+         ((static_cast<uint32_t>(c) & 0xffu) << 16) | (static_cast<uint32_t>(d) << 24);
 }
 
 // ---- RoPE, Llama half split -------------------------------------------------
@@ -124,16 +213,27 @@ __device__ __forceinline__ void rope_pair(float a, float b, float c, float s, fl
 
 // ---- SwiGLU -----------------------------------------------------------------
 // Reference: engine/src/kernel_math.h:239, :571-584: silu(g) * u with
-// silu(g) = g / (1 + expf(-g)); expf is the accurate library routine.
+// silu(g) = g / (1 + expf(-g)), rounded to bf16 by the caller.
+// exp and the reciprocal use the SFU approximations (ex2.approx, rcp.approx):
+// the f32 result is within a few f32 ulp of the host's, which the bf16 rounding
+// that follows hides except for roughly one element in several thousand, where
+// the bf16 result is the neighbouring value (the stated tolerance is 1 bf16
+// ulp; the reference's own device kernels are tested to the same bound against
+// this host formula). For g < -87.3 the reciprocal underflows to zero and the
+// result is -0 where the host gives a number of magnitude < 1e-36.
 __device__ __forceinline__ float swiglu(float g, float u) {
-  const float sg = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
-  return __fmul_rn(sg, u);
+  float e, r;
+  const float t = __fmul_rn(g, -1.4426950408889634f);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+  const float d = __fadd_rn(1.0f, e);
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+  return __fmul_rn(__fmul_rn(g, r), u);
 }
 
 // ---- memory helpers -----------------------------------------------------------
 // Read-once / write-once data goes through the streaming cache policy so it
-// does not push reusable lines (norm weights, RoPE tables, the hidden state a
-// second phase re-reads) out of L2.
+// does not push reusable lines (norm weights, RoPE tables, data a second sweep
+// re-reads) out of L2.
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }

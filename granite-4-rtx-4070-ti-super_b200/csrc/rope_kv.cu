@@ -70,97 +70,113 @@ struct RopeKvParams {
 constexpr int kD = 128;
 constexpr int kHeadsPerCta = 16;
 
-__device__ __forceinline__ void unpack8(uint4 u, float (&v)[8]) {
-  v[0] = bf16_lo(u.x), v[1] = bf16_hi(u.x), v[2] = bf16_lo(u.y), v[3] = bf16_hi(u.y);
-  v[4] = bf16_lo(u.z), v[5] = bf16_hi(u.z), v[6] = bf16_lo(u.w), v[7] = bf16_hi(u.w);
-}
-__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
-  uint4 u;
-  u.x = pack_bf16x2(v[0], v[1]);
-  u.y = pack_bf16x2(v[2], v[3]);
-  u.z = pack_bf16x2(v[4], v[5]);
-  u.w = pack_bf16x2(v[6], v[7]);
-  return u;
-}
+// Rows one CTA walks through. All the loads of the kRows rows (activations,
+// then table rows) are issued before the first is used, which is what hides the
+// memory latency here: the per-row work is too short for occupancy alone to do it.
+constexpr int kRows = 2;
 
 __global__ void __launch_bounds__(kHeadsPerCta * 8) rope_kv_int8_kernel(const RopeKvParams p) {
-  const int r = blockIdx.x / p.groups;
+  const int r0 = (blockIdx.x / p.groups) * kRows;
   const int head = (blockIdx.x % p.groups) * kHeadsPerCta + (threadIdx.x >> 3);
   const int j = threadIdx.x & 7;
   const int heads_total = p.Hq + 2 * p.Hk;
-
-  int pos, kv_row;
-  if (p.mode == kRunOfPositions) {
-    pos = p.base_pos + r;
-    kv_row = p.d_pt != nullptr ? __ldg(p.d_pt + pos) : pos;
-  } else if (p.mode == kPerRowArrays) {
-    pos = __ldg(p.pos_rows + r);
-    kv_row = __ldg(p.kv_rows + r);
-    // a bad index skips the row instead of touching memory outside the pool
-    if (pos < 0 || pos >= p.max_pos || kv_row < 0 || kv_row >= p.stride) return;
-  } else {
-    pos = p.mr->pos[r];
-    const int slot = p.mr->tree ? p.mr->slot[r] : pos;
-    kv_row = p.mr->pt[r][slot];
-  }
   // Whole 8-lane groups leave together, so the shuffles below stay converged
   // within the groups that remain (the mask names only their own lanes).
   if (head >= heads_total) return;
-
   const bool is_q = head < p.Hq;
   const bool is_k = !is_q && head < p.Hq + p.Hk;
-  const uint16_t* src;
-  if (is_q) src = p.q + static_cast<size_t>(r) * p.pitch_q + static_cast<size_t>(head) * kD;
-  else if (is_k) src = p.k + static_cast<size_t>(r) * p.pitch_k + static_cast<size_t>(head - p.Hq) * kD;
-  else src = p.v + static_cast<size_t>(r) * p.pitch_v + static_cast<size_t>(head - p.Hq - p.Hk) * kD;
+  const bool rotate = is_q || (is_k && p.rotate_k);
 
-  float lo[8], hi[8];
-  unpack8(ld_stream(reinterpret_cast<const uint4*>(src) + j), lo);
-  unpack8(ld_stream(reinterpret_cast<const uint4*>(src) + 8 + j), hi);
-
-  if (is_q || (is_k && p.rotate_k)) {
-    const float4* cp = reinterpret_cast<const float4*>(p.cos_tbl + static_cast<size_t>(pos) * (kD / 2)) + 2 * j;
-    const float4* sp = reinterpret_cast<const float4*>(p.sin_tbl + static_cast<size_t>(pos) * (kD / 2)) + 2 * j;
-    const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
-    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-    const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  int pos[kRows], kv_row[kRows];
+  bool ok[kRows];
+  uint4 xlo[kRows], xhi[kRows];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float a, b;
-      rope_pair(lo[e], hi[e], c[e], s[e], a, b);
-      lo[e] = a, hi[e] = b;
+  for (int i = 0; i < kRows; ++i) {
+    const int r = r0 + i;
+    ok[i] = r < p.rows;
+    pos[i] = kv_row[i] = 0;
+    if (!ok[i]) continue;
+    if (p.mode == kRunOfPositions) {
+      pos[i] = p.base_pos + r;
+      kv_row[i] = p.d_pt != nullptr ? __ldg(p.d_pt + pos[i]) : pos[i];
+    } else if (p.mode == kPerRowArrays) {
+      pos[i] = __ldg(p.pos_rows + r);
+      kv_row[i] = __ldg(p.kv_rows + r);
+    } else {
+      pos[i] = p.mr->pos[r];
+      const int slot = p.mr->tree ? p.mr->slot[r] : pos[i];
+      kv_row[i] = p.mr->pt[r][slot];
+    }
+    const uint16_t* src;
+    if (is_q) src = p.q + static_cast<size_t>(r) * p.pitch_q + static_cast<size_t>(head) * kD;
+    else if (is_k) src = p.k + static_cast<size_t>(r) * p.pitch_k + static_cast<size_t>(head - p.Hq) * kD;
+    else src = p.v + static_cast<size_t>(r) * p.pitch_v + static_cast<size_t>(head - p.Hq - p.Hk) * kD;
+    xlo[i] = ld_stream(reinterpret_cast<const uint4*>(src) + j);
+    xhi[i] = ld_stream(reinterpret_cast<const uint4*>(src) + 8 + j);
+  }
+  if (p.mode == kPerRowArrays) {
+    // a bad index skips the row instead of touching memory outside the tables or the pool
+#pragma unroll
+    for (int i = 0; i < kRows; ++i)
+      if (pos[i] < 0 || pos[i] >= p.max_pos || kv_row[i] < 0 || kv_row[i] >= p.stride) ok[i] = false;
+  }
+  float4 c0[kRows], c1[kRows], s0[kRows], s1[kRows];
+  if (rotate) {
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      if (!ok[i]) continue;
+      const float4* cp = reinterpret_cast<const float4*>(p.cos_tbl + static_cast<size_t>(pos[i]) * (kD / 2)) + 2 * j;
+      const float4* sp = reinterpret_cast<const float4*>(p.sin_tbl + static_cast<size_t>(pos[i]) * (kD / 2)) + 2 * j;
+      c0[i] = __ldg(cp), c1[i] = __ldg(cp + 1), s0[i] = __ldg(sp), s1[i] = __ldg(sp + 1);
     }
   }
-  if (is_q) {
-    uint4* dst = reinterpret_cast<uint4*>(p.q_rot + (static_cast<size_t>(r) * p.Hq + head) * kD);
-    st_stream(dst + j, pack8(lo));
-    st_stream(dst + 8 + j, pack8(hi));
-    return;
-  }
-  if (is_k && p.rotate_k && p.k_from_bf16) {
+  const unsigned gmask = 0xffu << (threadIdx.x & 24);  // the 8 lanes of this head
 #pragma unroll
-    for (int e = 0; e < 8; ++e) lo[e] = round_bf16(lo[e]), hi[e] = round_bf16(hi[e]);
-  }
-  float amax = 0.0f;
+  for (int i = 0; i < kRows; ++i) {
+    if (!ok[i]) continue;  // uniform over the CTA: every thread works on the same rows
+    const int r = r0 + i;
+    float lo[8], hi[8];
+    unpack8(xlo[i], lo);
+    unpack8(xhi[i], hi);
+    if (rotate) {
+      const float c[8] = {c0[i].x, c0[i].y, c0[i].z, c0[i].w, c1[i].x, c1[i].y, c1[i].z, c1[i].w};
+      const float s[8] = {s0[i].x, s0[i].y, s0[i].z, s0[i].w, s1[i].x, s1[i].y, s1[i].z, s1[i].w};
 #pragma unroll
-  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fmaxf(fabsf(lo[e]), fabsf(hi[e])));
-  // the 8 lanes of this head: lanes [g*8, g*8+8) of the warp
-  const unsigned gmask = 0xffu << (threadIdx.x & 24);
-  amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
-  amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 4));
-  const float sc = kv8_scale(amax);
-  const int hkv = is_k ? head - p.Hq : head - p.Hq - p.Hk;
-  const size_t srow = static_cast<size_t>(hkv) * p.stride + kv_row;
-  int8_t* cache = (is_k ? p.cache_k : p.cache_v) + srow * kD;
-  if (j == 0) (is_k ? p.k_scale : p.v_scale)[srow] = sc;
-  uint2 cl, ch;
-  cl.x = pack_i8x4(kv8_quant(lo[0], sc), kv8_quant(lo[1], sc), kv8_quant(lo[2], sc), kv8_quant(lo[3], sc));
-  cl.y = pack_i8x4(kv8_quant(lo[4], sc), kv8_quant(lo[5], sc), kv8_quant(lo[6], sc), kv8_quant(lo[7], sc));
-  ch.x = pack_i8x4(kv8_quant(hi[0], sc), kv8_quant(hi[1], sc), kv8_quant(hi[2], sc), kv8_quant(hi[3], sc));
-  ch.y = pack_i8x4(kv8_quant(hi[4], sc), kv8_quant(hi[5], sc), kv8_quant(hi[6], sc), kv8_quant(hi[7], sc));
-  st_stream(reinterpret_cast<uint2*>(cache) + j, cl);
-  st_stream(reinterpret_cast<uint2*>(cache) + 8 + j, ch);
+      for (int e = 0; e < 8; ++e) {
+        float a, b;
+        rope_pair(lo[e], hi[e], c[e], s[e], a, b);
+        lo[e] = a, hi[e] = b;
+      }
+    }
+    if (is_q) {
+      uint4* dst = reinterpret_cast<uint4*>(p.q_rot + (static_cast<size_t>(r) * p.Hq + head) * kD);
+      st_stream(dst + j, pack8(lo));
+      st_stream(dst + 8 + j, pack8(hi));
+      continue;
+    }
+    if (is_k && p.rotate_k && p.k_from_bf16) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) lo[e] = round_bf16(lo[e]), hi[e] = round_bf16(hi[e]);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fmaxf(fabsf(lo[e]), fabsf(hi[e])));
+    amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 4));
+    const Kv8Scale sc = kv8_scale(amax);
+    const int hkv = is_k ? head - p.Hq : head - p.Hq - p.Hk;
+    const size_t srow = static_cast<size_t>(hkv) * p.stride + kv_row[i];
+    int8_t* cache = (is_k ? p.cache_k : p.cache_v) + srow * kD;
+    if (j == 0) (is_k ? p.k_scale : p.v_scale)[srow] = sc.s;
+    uint2 cl, ch;
+    cl.x = pack_i8x4(kv8_quant(lo[0], sc), kv8_quant(lo[1], sc), kv8_quant(lo[2], sc), kv8_quant(lo[3], sc));
+    cl.y = pack_i8x4(kv8_quant(lo[4], sc), kv8_quant(lo[5], sc), kv8_quant(lo[6], sc), kv8_quant(lo[7], sc));
+    ch.x = pack_i8x4(kv8_quant(hi[0], sc), kv8_quant(hi[1], sc), kv8_quant(hi[2], sc), kv8_quant(hi[3], sc));
+    ch.y = pack_i8x4(kv8_quant(hi[4], sc), kv8_quant(hi[5], sc), kv8_quant(hi[6], sc), kv8_quant(hi[7], sc));
+    st_stream(reinterpret_cast<uint2*>(cache) + j, cl);
+    st_stream(reinterpret_cast<uint2*>(cache) + 8 + j, ch);
+  }
 }
 
 // Plain RoPE of [rows][d] with table row = row index; any even d. One thread
@@ -198,18 +214,18 @@ __global__ void __launch_bounds__(1024)
   __syncthreads();
   float mk = 0.0f, mv = 0.0f;
   for (int w = 0; w < (d + 31) / 32; ++w) mk = fmaxf(mk, wmax[0][w]), mv = fmaxf(mv, wmax[1][w]);
-  const float sk = kv8_scale(mk), sv = kv8_scale(mv);
+  const float sk = kv8_scale(mk).s, sv = kv8_scale(mv).s;
   const size_t srow = static_cast<size_t>(hkv) * stride + row;
   if (i == 0) k_scale[srow] = sk, v_scale[srow] = sv;
   if (!act) return;
-  cache_k[srow * d + i] = static_cast<int8_t>(kv8_quant(x, sk));
-  cache_v[srow * d + i] = static_cast<int8_t>(kv8_quant(y, sv));
+  cache_k[srow * d + i] = static_cast<int8_t>(kv8_quant_exact(x, sk));
+  cache_v[srow * d + i] = static_cast<int8_t>(kv8_quant_exact(y, sv));
 }
 
 int launch_rope_kv(const char* fn, RopeKvParams& p) {
   const int heads_total = p.Hq + 2 * p.Hk;
   p.groups = (heads_total + kHeadsPerCta - 1) / kHeadsPerCta;
-  const long long ctas = static_cast<long long>(p.rows) * p.groups;
+  const long long ctas = static_cast<long long>((p.rows + kRows - 1) / kRows) * p.groups;
   if (ctas > INT_MAX) return fail(fn, "too many rows");
   rope_kv_int8_kernel<<<static_cast<unsigned>(ctas), kHeadsPerCta * 8, 0, current_stream()>>>(p);
   G4_LAUNCH_CHECK(fn);

@@ -14,14 +14,18 @@
 // reads 512 contiguous bytes per load instruction and has 2 * kUnroll 128-bit
 // loads in flight per thread.
 //
-// FP8 needs two sweeps because the scale depends on every element: the amax
-// sweep computes a and max |a| (and writes a as bf16 when asked); the encode
-// sweep recomputes a from gate/up (or reads the bf16 copy when one was written)
-// and writes the codes, walking the items backwards so that it starts on the
-// part of the input the first sweep left in L2.
+// FP8 needs two sweeps because the scale depends on every element. The first
+// computes a and max |a|. If the caller passes a bf16 buffer for a (as an
+// output it wants, or purely as workspace) the first sweep stores a there and
+// the second sweep is a light bf16 -> e4m3 pass over it; without one the second
+// sweep recomputes a from gate and up. Both move the same number of bytes
+// (115 200 per row at I = 12800), but the first evaluates the exponential once,
+// and at HBM speed an SM has only ~15 issue slots per element, which the
+// exponential, the reciprocal and the quantiser together overrun. The second
+// sweep walks the items backwards so that it starts on what the first left in L2.
 //
 // Algorithmic bytes per row at I = 12800, bf16 in, FP8 out: 2 * 25 600 read +
-// 12 800 written = 64 000; the encode sweep adds a second 51 200-byte read.
+// 12 800 written = 64 000.
 #include "g4_host.h"
 #include "g4_math.cuh"
 
@@ -41,7 +45,7 @@ struct SwigluParams {
   float* scale_amax;   // [0] scale, [1] amax
   long long ld;        // input row pitch, elements
   long long items;     // rows * I / 8
-  int ipr;             // items per row = I / 8
+  unsigned ipr;        // items per row = I / 8
   int contiguous;      // ld == I: item index is the element offset / 8
 };
 
@@ -49,106 +53,118 @@ enum { kAmax = 0, kEncode = 1, kPlain = 2 };
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
-template <bool F32>
-__device__ __forceinline__ void load8(const void* base, long long elem_off, float (&v)[8]) {
-  if (F32) {
-    const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem_off);
-    const float4 a = ld_stream(p), b = ld_stream(p + 1);
-    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-  } else {
-    const uint4 u =
-        ld_stream(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + elem_off));
-    v[0] = bf16_lo(u.x), v[1] = bf16_hi(u.x), v[2] = bf16_lo(u.y), v[3] = bf16_hi(u.y);
-    v[4] = bf16_lo(u.z), v[5] = bf16_hi(u.z), v[6] = bf16_lo(u.w), v[7] = bf16_hi(u.w);
-  }
+__device__ __forceinline__ long long item_offset(const SwigluParams& p, long long it) {
+  if (p.contiguous) return it * 8;
+  // items < 2^32 is checked by the launcher, so a 32-bit division does
+  const unsigned row = static_cast<unsigned>(it) / p.ipr;
+  return static_cast<long long>(row) * p.ld + static_cast<long long>(static_cast<unsigned>(it) - row * p.ipr) * 8;
 }
 
-// MODE kPlain: bf16 out only. kAmax: amax (+ optional bf16 out). kEncode: codes.
+// gate / up item -> 8 activations, packed bf16
+template <bool F32>
+__device__ __forceinline__ uint4 swiglu8(const void* gate, const void* up, long long off) {
+  float g[8], u[8], a[8];
+  if (F32) {
+    const float4* gp = reinterpret_cast<const float4*>(static_cast<const float*>(gate) + off);
+    const float4* up4 = reinterpret_cast<const float4*>(static_cast<const float*>(up) + off);
+    const float4 g0 = ld_stream(gp), g1 = ld_stream(gp + 1), u0 = ld_stream(up4), u1 = ld_stream(up4 + 1);
+    g[0] = g0.x, g[1] = g0.y, g[2] = g0.z, g[3] = g0.w, g[4] = g1.x, g[5] = g1.y, g[6] = g1.z, g[7] = g1.w;
+    u[0] = u0.x, u[1] = u0.y, u[2] = u0.z, u[3] = u0.w, u[4] = u1.x, u[5] = u1.y, u[6] = u1.z, u[7] = u1.w;
+  } else {
+    unpack8(ld_stream(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(gate) + off)), g);
+    unpack8(ld_stream(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(up) + off)), u);
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) a[e] = swiglu(g[e], u[e]);
+  return pack8(a);
+}
+
+// MODE kPlain: bf16 out only. kAmax: amax (+ bf16 out when a buffer is given).
+// kEncode: codes, from the bf16 buffer (FROM_BF16) or recomputed.
 template <bool F32, int MODE, bool FROM_BF16>
 __global__ void __launch_bounds__(kThreads) swiglu_kernel(const SwigluParams p) {
-  const long long tile0 = static_cast<long long>(blockIdx.x) * (kThreads * kUnroll);
-  float scale = 0.0f;
+  const long long tile0 = static_cast<long long>(blockIdx.x) * (kThreads * kUnroll) + threadIdx.x;
+  Fp8Scale fs{};
   if (MODE == kEncode) {
-    scale = fp8_scale_from_amax(__ldcg(p.scale_amax + 1));
-    if (blockIdx.x == 0 && threadIdx.x == 0) p.scale_amax[0] = scale;
+    fs = fp8_scale_from_amax(__ldcg(p.scale_amax + 1));
+    if (blockIdx.x == 0 && threadIdx.x == 0) p.scale_amax[0] = fs.scale;
   }
   long long item[kUnroll];
-  bool ok[kUnroll];
-  uint4 a_bits[kUnroll];
-  float g[kUnroll][8], u[kUnroll][8];
+  uint4 a[kUnroll];
+  uint4 graw[kUnroll], uraw[kUnroll];  // bf16 inputs: every load is issued before any math
 #pragma unroll
   for (int k = 0; k < kUnroll; ++k) {
-    long long it = tile0 + k * kThreads + threadIdx.x;
-    ok[k] = it < p.items;
+    long long it = tile0 + k * kThreads;
+    if (it >= p.items) {
+      item[k] = -1;
+      a[k] = graw[k] = uraw[k] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
     if (MODE == kEncode) it = p.items - 1 - it;  // backwards
     item[k] = it;
-    if (ok[k]) {
-      if (FROM_BF16) {
-        a_bits[k] = ld_stream(reinterpret_cast<const uint4*>(p.act_bf16) + it);
-      } else {
-        long long off;
-        if (p.contiguous) {
-          off = it * 8;
-        } else {
-          const long long row = it / p.ipr;
-          off = row * p.ld + (it - row * p.ipr) * 8;
-        }
-        load8<F32>(p.gate, off, g[k]);
-        load8<F32>(p.up, off, u[k]);
-      }
+    if (FROM_BF16) {
+      a[k] = ld_stream(reinterpret_cast<const uint4*>(p.act_bf16) + it);
+    } else if (F32) {
+      a[k] = swiglu8<true>(p.gate, p.up, item_offset(p, it));
+    } else {
+      const long long off = item_offset(p, it);
+      graw[k] = ld_stream(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.gate) + off));
+      uraw[k] = ld_stream(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.up) + off));
     }
   }
-  float amax = 0.0f;
+  if (!FROM_BF16 && !F32) {
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) {
+      float g[8], u[8], v[8];
+      unpack8(graw[k], g);
+      unpack8(uraw[k], u);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = swiglu(g[e], u[e]);
+      a[k] = pack8(v);
+    }
+  }
+  uint32_t amax = 0u;
 #pragma unroll
   for (int k = 0; k < kUnroll; ++k) {
-    if (!ok[k]) continue;
-    if (!FROM_BF16) {
-      float a[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) a[e] = swiglu(g[k][e], u[k][e]);
-      a_bits[k].x = pack_bf16x2(a[0], a[1]);
-      a_bits[k].y = pack_bf16x2(a[2], a[3]);
-      a_bits[k].z = pack_bf16x2(a[4], a[5]);
-      a_bits[k].w = pack_bf16x2(a[6], a[7]);
-    }
-    const uint4 ab = a_bits[k];
-    if (MODE != kEncode) {
+    if (item[k] < 0) continue;
+    if (MODE == kEncode) {
+      st_stream(reinterpret_cast<uint2*>(p.act_fp8) + item[k], fp8x8_quant(a[k], fs));
+    } else {
       if (p.act_bf16 != nullptr) {
         uint4* dst = reinterpret_cast<uint4*>(p.act_bf16) + item[k];
-        if (MODE == kAmax) *dst = ab; else st_stream(dst, ab);
+        if (MODE == kAmax) *dst = a[k]; else st_stream(dst, a[k]);  // kAmax: re-read by the encode sweep
       }
-      if (MODE == kAmax) {
-        const uint32_t m0 = ab.x & 0x7fff7fffu, m1 = ab.y & 0x7fff7fffu, m2 = ab.z & 0x7fff7fffu,
-                       m3 = ab.w & 0x7fff7fffu;
-        amax = fmaxf(amax, fmaxf(fmaxf(bf16_lo(m0), bf16_hi(m0)), fmaxf(bf16_lo(m1), bf16_hi(m1))));
-        amax = fmaxf(amax, fmaxf(fmaxf(bf16_lo(m2), bf16_hi(m2)), fmaxf(bf16_lo(m3), bf16_hi(m3))));
-      }
-    } else {
-      uint2 c;
-      c.x = fp8x4_quant(bf16_lo(ab.x), bf16_hi(ab.x), bf16_lo(ab.y), bf16_hi(ab.y), scale);
-      c.y = fp8x4_quant(bf16_lo(ab.z), bf16_hi(ab.z), bf16_lo(ab.w), bf16_hi(ab.w), scale);
-      st_stream(reinterpret_cast<uint2*>(p.act_fp8) + item[k], c);
+      if (MODE == kAmax) amax = amax_acc(amax, a[k]);
     }
   }
   if (MODE == kAmax) {
-    amax = warp_max(amax);
-    __shared__ float s[kThreads / 32];
+    amax = amax_warp(amax);
+    __shared__ uint32_t s[kThreads / 32];
     if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = amax;
     __syncthreads();
     if (threadIdx.x == 0) {
-      float m = 0.0f;
+      uint32_t m = 0u;
 #pragma unroll
-      for (int i = 0; i < kThreads / 32; ++i) m = fmaxf(m, s[i]);
-      atomic_amax(p.scale_amax + 1, m);
+      for (int i = 0; i < kThreads / 32; ++i) m = max_u16x2(m, s[i]);
+      atomic_amax(p.scale_amax + 1, amax_value(m));
     }
   }
+}
+
+// The reference's prefill entry point takes any I: scalar form for I % 8 != 0.
+__global__ void __launch_bounds__(256)
+    silu_mul_scalar_kernel(const float* gu, int I, long long n, uint16_t* act) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const long long r = idx / I, i = idx % I;
+  act[idx] = static_cast<uint16_t>(f32_to_bf16_bits(swiglu(gu[r * 2 * I + i], gu[r * 2 * I + I + i])));
 }
 
 template <bool F32>
 int launch_swiglu(const char* fn, const SwigluParams& p) {
   cudaStream_t st = current_stream();
   const long long tiles = (p.items + kThreads * kUnroll - 1) / (kThreads * kUnroll);
-  if (tiles > INT_MAX) return fail(fn, "tensor too large");
+  if (tiles > INT_MAX || p.items > 0xffffffffLL) return fail(fn, "tensor too large");
   const unsigned grid = static_cast<unsigned>(tiles);
   if (p.act_fp8 == nullptr) {
     swiglu_kernel<F32, kPlain, false><<<grid, kThreads, 0, st>>>(p);
@@ -186,7 +202,7 @@ int granite4_kernel_swiglu_fp8(const void* d_gate, const void* d_up, int in_is_f
     return g4::fail(fn, "I must be a multiple of 8 and rows 16-byte aligned");
   g4::SwigluParams p{};
   p.gate = d_gate, p.up = d_up, p.act_bf16 = d_act_bf16, p.act_fp8 = d_act_fp8;
-  p.scale_amax = d_scale_amax, p.ld = ld, p.ipr = I / 8;
+  p.scale_amax = d_scale_amax, p.ld = ld, p.ipr = static_cast<unsigned>(I / 8);
   p.items = static_cast<long long>(rows) * p.ipr, p.contiguous = (ld == I);
   return in_is_f32 ? g4::launch_swiglu<true>(fn, p) : g4::launch_swiglu<false>(fn, p);
 }
@@ -195,6 +211,13 @@ int granite4_prefill_silu_mul(const float* gu, int I, int rows, uint16_t* act) {
   const char* fn = "prefill_silu_mul";
   if (rows <= 0 || I <= 0) return -1;  // engine/src/prefill_gemm.cu:1469
   if (gu == nullptr || act == nullptr) return g4::fail(fn, "invalid arguments");
+  if (I % 8 != 0 || !g4::aligned16(gu) || !g4::aligned16(act)) {
+    const long long n = static_cast<long long>(rows) * I;
+    g4::silu_mul_scalar_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0,
+                                 g4::current_stream()>>>(gu, I, n, act);
+    G4_LAUNCH_CHECK(fn);
+    return 0;
+  }
   return granite4_kernel_swiglu_fp8(gu, gu + I, 1, 2LL * I, rows, I, act, nullptr, nullptr);
 }
 

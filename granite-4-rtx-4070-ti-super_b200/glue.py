@@ -78,7 +78,7 @@ class GlueSequence:
 
     def __init__(self, rows: int, shapes: GraniteShapes = GraniteShapes(), device="cuda",
                  seed: int = 0, sets: int = 2, layers: int | None = None, pool_rows: int | None = None,
-                 max_pos: int | None = None):
+                 max_pos: int | None = None, workspace: bool = True):
         s = self.shapes = shapes
         self.rows, self.device = rows, torch.device(device)
         self.layers = s.layers if layers is None else layers
@@ -107,6 +107,12 @@ class GlueSequence:
         self.act_fp8 = torch.empty(rows, s.intermediate, dtype=torch.uint8, device=self.device)
         self.out = torch.empty(rows, s.hidden, dtype=bf, device=self.device)
         self.scales = torch.zeros(self.layers, 3, 2, dtype=torch.float32, device=self.device)
+        # scratch the FP8 ops may use between their two sweeps: 1/rms per row, and the bf16
+        # activation of SwiGLU (so the exponential is evaluated once). workspace=False runs the
+        # same ops without any scratch (the second sweep then recomputes).
+        self.workspace = workspace
+        self.rstd = torch.empty(rows, dtype=torch.float32, device=self.device) if workspace else None
+        self.act_ws = torch.empty(rows, s.intermediate, dtype=bf, device=self.device) if workspace else None
         # int8 paged pool per layer: codes [L][Hk][pool_rows][d], scales [L][Hk][pool_rows]
         self.cache_k = torch.zeros(self.layers, s.kv_heads, self.pool_rows, s.head_dim, dtype=torch.int8,
                                    device=self.device)
@@ -131,27 +137,40 @@ class GlueSequence:
         if rc != 0:
             raise RuntimeError(f"{what} returned {rc}")
 
-    def run_layer(self, layer: int):
+    def layer_ops(self, layer: int):
+        """The four launcher calls of one layer as (name, thunk) pairs, in order."""
         s, k = self.shapes, kernels
         buf = self.sets[layer % len(self.sets)]
-        self._check(k.add_rmsnorm_fp8(buf["y_attn"], self.h, self.w[layer, 0], s.eps, s.residual_multiplier,
-                                      h_out=self.h, n_fp8=self.n_fp8, scale_amax=self.scales[layer, 0]),
-                    "add_rmsnorm_fp8")
-        self._check(k.rope_kv_int8_paged(buf["qkv"], self.tables.cos, self.tables.sin, self.pos_rows,
-                                         self.kv_rows, s.q_heads, s.kv_heads, s.head_dim, self.pool_rows,
-                                         self.max_pos, 0, self.q_rot, self.cache_k[layer], self.cache_v[layer],
-                                         self.k_scale[layer], self.v_scale[layer]), "rope_kv_int8_paged")
-        self._check(k.add_rmsnorm_fp8(buf["y_mlp"], self.h, self.w[layer, 1], s.eps, s.residual_multiplier,
-                                      h_out=self.h, n_fp8=self.n_fp8, scale_amax=self.scales[layer, 1]),
-                    "add_rmsnorm_fp8")
-        self._check(k.swiglu_fp8(buf["gate"], buf["up"], act_fp8=self.act_fp8,
-                                 scale_amax=self.scales[layer, 2]), "swiglu_fp8")
-        self.launches += KERNELS_PER_LAYER
+        ws = self.workspace
+        return [
+            ("add_rmsnorm_fp8", lambda: k.add_rmsnorm_fp8(
+                buf["y_attn"], self.h, self.w[layer, 0], s.eps, s.residual_multiplier, h_out=self.h,
+                n_fp8=self.n_fp8, scale_amax=self.scales[layer, 0], rstd=self.rstd if ws else None)),
+            ("rope_kv_int8", lambda: k.rope_kv_int8_paged(
+                buf["qkv"], self.tables.cos, self.tables.sin, self.pos_rows, self.kv_rows, s.q_heads,
+                s.kv_heads, s.head_dim, self.pool_rows, self.max_pos, 0, self.q_rot, self.cache_k[layer],
+                self.cache_v[layer], self.k_scale[layer], self.v_scale[layer])),
+            ("add_rmsnorm_fp8", lambda: k.add_rmsnorm_fp8(
+                buf["y_mlp"], self.h, self.w[layer, 1], s.eps, s.residual_multiplier, h_out=self.h,
+                n_fp8=self.n_fp8, scale_amax=self.scales[layer, 1], rstd=self.rstd if ws else None)),
+            ("swiglu_fp8", lambda: k.swiglu_fp8(
+                buf["gate"], buf["up"], act_bf16=self.act_ws if ws else None, act_fp8=self.act_fp8,
+                scale_amax=self.scales[layer, 2])),
+        ]
 
-    def run(self):
-        """One step: all layers, then the final norm. Enqueues only; does not synchronise."""
+    def final_op(self):
+        s = self.shapes
+        return ("final_norm", lambda: kernels.rmsnorm(self.h, self.w_final, s.eps, self.rows, s.hidden,
+                                                      self.out))
+
+    def run(self, wrap=None):
+        """One step: all layers, then the final norm. Enqueues only; does not synchronise.
+        `wrap(name, thunk)` may run the thunk itself (e.g. between two events) and must return
+        its status code."""
         for layer in range(self.layers):
-            self.run_layer(layer)
-        self._check(kernels.rmsnorm(self.h, self.w_final, self.shapes.eps, self.rows, self.shapes.hidden,
-                                    self.out), "rmsnorm")
+            for name, thunk in self.layer_ops(layer):
+                self._check(wrap(name, thunk) if wrap else thunk(), name)
+            self.launches += KERNELS_PER_LAYER
+        name, thunk = self.final_op()
+        self._check(wrap(name, thunk) if wrap else thunk(), name)
         self.launches += KERNELS_FINAL

@@ -65,15 +65,16 @@ def rmsnorm(d_x, d_w, eps, rows, cols, d_out, batched=False):
 
 
 def add_rmsnorm_fp8(y, res, w, eps, resid_mult, h_out=None, n_bf16=None, n_fp8=None,
-                    scale_amax=None):
+                    scale_amax=None, rstd=None):
     """granite4_kernel_add_rmsnorm_fp8. y / res: bf16 or float32 [rows][cols]; res may be None.
-    scale_amax: float32[2] receiving {scale, amax} when n_fp8 is given."""
+    scale_amax: float32[2] receiving {scale, amax} when n_fp8 is given. rstd: optional
+    float32[rows], receives 1/rms of every row and lets the FP8 sweep skip the reduction."""
     lib = _enter(y)
     rows, cols = y.shape
     return lib.granite4_kernel_add_rmsnorm_fp8(
         _p(y), int(y.dtype == torch.float32), _p(res), int(res is not None and res.dtype == torch.float32),
         _p(w, *_BF16_OK), eps, resid_mult, rows, cols, _p(h_out, *_BF16_OK), _p(n_bf16, *_BF16_OK),
-        _p(n_fp8, torch.uint8), _p(scale_amax, torch.float32))
+        _p(n_fp8, torch.uint8), _p(scale_amax, torch.float32), _p(rstd, torch.float32))
 
 
 def fp8_quant(x, codes, scale_amax):

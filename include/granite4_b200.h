@@ -118,13 +118,17 @@ int granite4_kernel_rmsnorm_batched(const uint16_t* d_x, const uint16_t* d_w, fl
  * d_y is bf16 (y_is_f32 == 0) or f32; d_res likewise. Outputs, each optional:
  * d_h_out [rows][cols] bf16 (may alias d_res), d_n_bf16, d_n_fp8.
  * d_scale_amax: float[2] = {scale, amax}, required when d_n_fp8 is given.
+ * d_rstd: optional float[rows]; receives r of every row. It is also scratch:
+ * with it (and d_h_out) the second sweep that writes the codes is a plain
+ * streaming pass over h instead of a second reduction per row.
  * cols must be a multiple of 8, at most 32768, and every row 16-byte aligned.
  * With d_n_fp8 this enqueues a 8-byte memset and two kernels (the scale depends
  * on every row, so the codes are written by a second sweep). */
 int granite4_kernel_add_rmsnorm_fp8(const void* d_y, int y_is_f32, const void* d_res,
                                     int res_is_f32, const uint16_t* d_w, float eps,
                                     float resid_mult, int rows, int cols, uint16_t* d_h_out,
-                                    uint16_t* d_n_bf16, uint8_t* d_n_fp8, float* d_scale_amax);
+                                    uint16_t* d_n_bf16, uint8_t* d_n_fp8, float* d_scale_amax,
+                                    float* d_rstd);
 /* Added: per-tensor FP8 quantisation of a bf16 tensor of n elements (n % 8 ==
  * 0) with the same rule; d_scale_amax as above. */
 int granite4_kernel_fp8_quant(const uint16_t* d_x, long long n, uint8_t* d_codes,

@@ -111,11 +111,11 @@ def test_invalid_arguments_are_refused_before_any_launch(g4, capfd):
     assert lib.granite4_gpu_multi_rope_append(16, 16, 16, 16, 16, 16, 1, 32, 8, 128, 4, 16, 16, 16, 16,
                                               64, 16) == -1                  # only int8 is built
     assert lib.granite4_kernel_add_rmsnorm_fp8(16, 0, 16, 0, 16, 1e-5, 0.22, 4, 4097, 16, None, None,
-                                               None) == -1                   # cols % 8
+                                               None, None) == -1             # cols % 8
     assert lib.granite4_kernel_add_rmsnorm_fp8(16, 0, 16, 0, 16, 1e-5, 0.22, 4, 4096, None, None, 16,
-                                               None) == -1                   # fp8 needs scale buffer
+                                               None, None) == -1             # fp8 needs scale buffer
     assert lib.granite4_kernel_add_rmsnorm_fp8(24, 0, 16, 0, 16, 1e-5, 0.22, 4, 4096, 16, None, None,
-                                               None) == -1                   # misaligned
+                                               None, None) == -1             # misaligned
     assert lib.granite4_kernel_swiglu_fp8(16, 16, 0, 100, 4, 12800, 16, None, None) == -1  # ld < I
     assert lib.granite4_kernel_swiglu_fp8(16, 16, 0, 12800, 4, 12800, None, None, None) == -1
     assert lib.granite4_kernel_rope_kv_int8_paged(16, 16, 16, None, 16, 4, 32, 8, 128, 64, 64, 0, 16, 16,
