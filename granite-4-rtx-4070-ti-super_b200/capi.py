@@ -47,7 +47,34 @@ SIGNATURES = {
     "granite4_prefill_silu_mul": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "granite4_kernel_swiglu_fp8": (C.c_int, [_vp, _vp, C.c_int, C.c_longlong, C.c_int, C.c_int,
                                              _vp, _vp, _vp]),
+    "granite4_glue_layer": (C.c_int, [_vp]),
+    "granite4_host_glue_create": (_vp, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                        C.c_int, C.c_int, C.c_double]),
+    "granite4_host_glue_destroy": (None, [_vp]),
+    "granite4_host_glue_layer": (C.c_int, [_vp, C.c_int, _vp]),
+    "granite4_host_glue_final_norm": (C.c_int, [_vp, _vp, C.c_float, C.c_int, _vp]),
+    "granite4_host_glue_sync": (C.c_int, [_vp]),
+    "granite4_host_glue_h2d_bytes": (C.c_longlong, [_vp, C.c_int]),
+    "granite4_host_glue_d2h_bytes": (C.c_longlong, [_vp, C.c_int]),
 }
+
+
+class GlueLayerArgs(C.Structure):
+    """granite4_glue_layer_args: device pointers of one layer's glue."""
+    _fields_ = [(n, _vp) for n in (
+        "y_attn", "y_mlp", "qkv", "gate", "up", "w_attn_norm", "w_mlp_norm", "cos_tbl", "sin_tbl",
+        "pos_rows", "kv_rows", "hidden", "n_attn_fp8", "n_mlp_fp8", "q_rot", "cache_k", "cache_v",
+        "k_scale", "v_scale", "act_fp8", "scales", "rstd", "act_ws")] + [(n, C.c_int) for n in (
+            "rows", "hidden_size", "intermediate", "q_heads", "kv_heads", "head_dim", "pool_rows",
+            "max_pos")] + [("eps", C.c_float), ("resid_mult", C.c_float)]
+
+
+class HostLayerIO(C.Structure):
+    """granite4_host_layer_io: HOST pointers of one layer call."""
+    _fields_ = [(n, _vp) for n in (
+        "y_attn", "y_mlp", "qkv", "gate", "up", "w_attn_norm", "w_mlp_norm", "pos_rows", "kv_rows",
+        "hidden_in", "hidden_out", "n_attn_fp8", "n_mlp_fp8", "q_rot", "act_fp8", "scales")] + [
+            ("rows", C.c_int), ("eps", C.c_float), ("resid_mult", C.c_float)]
 
 MAX_VERIFY_ROWS = 16
 MAX_TREE_DEPTH = 8

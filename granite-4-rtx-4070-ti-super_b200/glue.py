@@ -16,11 +16,12 @@ GPUs each run this on their own rows with nothing exchanged.
 """
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 
 import torch
 
-from . import kernels
+from . import capi, kernels
 
 
 @dataclass(frozen=True)
@@ -125,10 +126,12 @@ class GlueSequence:
         self.pos_rows = torch.arange(rows, dtype=torch.int32, device=self.device) % self.max_pos
         self.kv_rows = torch.arange(rows, dtype=torch.int32, device=self.device) % self.pool_rows
         self.launches = 0
+        self._args = None
 
     def set_rows(self, pos_rows, kv_rows):
         self.pos_rows = torch.as_tensor(pos_rows, dtype=torch.int32).to(self.device)
         self.kv_rows = torch.as_tensor(kv_rows, dtype=torch.int32).to(self.device)
+        self._args = None
 
     def reset(self):
         self.h.copy_(self.h0)
@@ -163,6 +166,43 @@ class GlueSequence:
         return ("final_norm", lambda: kernels.rmsnorm(self.h, self.w_final, s.eps, self.rows, s.hidden,
                                                       self.out))
 
+    def _layer_args(self, layer: int) -> capi.GlueLayerArgs:
+        s = self.shapes
+        buf = self.sets[layer % len(self.sets)]
+        a = capi.GlueLayerArgs()
+        a.y_attn, a.y_mlp, a.qkv = buf["y_attn"].data_ptr(), buf["y_mlp"].data_ptr(), buf["qkv"].data_ptr()
+        a.gate, a.up = buf["gate"].data_ptr(), buf["up"].data_ptr()
+        a.w_attn_norm, a.w_mlp_norm = self.w[layer, 0].data_ptr(), self.w[layer, 1].data_ptr()
+        a.cos_tbl, a.sin_tbl = self.tables.cos_ptr, self.tables.sin_ptr
+        a.pos_rows, a.kv_rows = self.pos_rows.data_ptr(), self.kv_rows.data_ptr()
+        a.hidden, a.n_attn_fp8, a.n_mlp_fp8 = self.h.data_ptr(), self.n_fp8.data_ptr(), self.n_fp8.data_ptr()
+        a.q_rot, a.act_fp8 = self.q_rot.data_ptr(), self.act_fp8.data_ptr()
+        a.cache_k, a.cache_v = self.cache_k[layer].data_ptr(), self.cache_v[layer].data_ptr()
+        a.k_scale, a.v_scale = self.k_scale[layer].data_ptr(), self.v_scale[layer].data_ptr()
+        a.scales = self.scales[layer].data_ptr()
+        a.rstd = self.rstd.data_ptr() if self.workspace else None
+        a.act_ws = self.act_ws.data_ptr() if self.workspace else None
+        a.rows, a.hidden_size, a.intermediate = self.rows, s.hidden, s.intermediate
+        a.q_heads, a.kv_heads, a.head_dim = s.q_heads, s.kv_heads, s.head_dim
+        a.pool_rows, a.max_pos, a.eps, a.resid_mult = self.pool_rows, self.max_pos, s.eps, s.residual_multiplier
+        return a
+
+    def run_fast(self):
+        """The same step with one library call per layer (granite4_glue_layer): identical
+        launches, a fraction of the host time. Argument blocks are built once and reused."""
+        lib = capi.lib()
+        if self._args is None:
+            self._args = [self._layer_args(layer) for layer in range(self.layers)]
+            self._arg_refs = [C.byref(a) for a in self._args]
+        torch.cuda.set_device(self.device)
+        lib.granite4_b200_set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+        for ref in self._arg_refs:
+            self._check(lib.granite4_glue_layer(ref), "granite4_glue_layer")
+        self.launches += self.layers * KERNELS_PER_LAYER
+        name, thunk = self.final_op()
+        self._check(thunk(), name)
+        self.launches += KERNELS_FINAL
+
     def run(self, wrap=None):
         """One step: all layers, then the final norm. Enqueues only; does not synchronise.
         `wrap(name, thunk)` may run the thunk itself (e.g. between two events) and must return
@@ -174,3 +214,73 @@ class GlueSequence:
         name, thunk = self.final_op()
         self._check(wrap(name, thunk) if wrap else thunk(), name)
         self.launches += KERNELS_FINAL
+
+
+class HostGlue:
+    """The layer glue over HOST buffers (granite4_host_glue_*): the library stages pinned host
+    tensors through device memory it owns, overlapping the copies of one layer call with the
+    kernels and the read-back of the previous one. The residual stream and the int8 KV pool
+    stay on the device between calls."""
+
+    def __init__(self, max_rows: int, shapes: GraniteShapes = GraniteShapes(), device="cuda",
+                 layers: int | None = None, pool_rows: int | None = None, max_pos: int | None = None):
+        self.shapes, self.max_rows = shapes, max_rows
+        self.device = torch.device(device)
+        self.layers = shapes.layers if layers is None else layers
+        self.pool_rows = max_rows if pool_rows is None else pool_rows
+        self.max_pos = max_rows if max_pos is None else max_pos
+        torch.cuda.set_device(self.device)
+        self._lib = capi.lib()
+        self._ctx = self._lib.granite4_host_glue_create(
+            max_rows, shapes.hidden, shapes.intermediate, shapes.q_heads, shapes.kv_heads, shapes.head_dim,
+            self.layers, self.pool_rows, self.max_pos, shapes.rope_theta)
+        if not self._ctx:
+            raise RuntimeError("granite4_host_glue_create failed")
+
+    def h2d_bytes(self, rows):
+        return self._lib.granite4_host_glue_h2d_bytes(self._ctx, rows)
+
+    def d2h_bytes(self, rows):
+        return self._lib.granite4_host_glue_d2h_bytes(self._ctx, rows)
+
+    def layer(self, layer: int, io: "capi.HostLayerIO"):
+        rc = self._lib.granite4_host_glue_layer(self._ctx, layer, C.byref(io))
+        if rc != 0:
+            raise RuntimeError(f"granite4_host_glue_layer returned {rc}")
+
+    def final_norm(self, w_host, eps, rows, out_host):
+        rc = self._lib.granite4_host_glue_final_norm(self._ctx, w_host.data_ptr(), eps, rows,
+                                                     out_host.data_ptr())
+        if rc != 0:
+            raise RuntimeError(f"granite4_host_glue_final_norm returned {rc}")
+
+    def sync(self):
+        if self._lib.granite4_host_glue_sync(self._ctx) != 0:
+            raise RuntimeError("granite4_host_glue_sync failed")
+
+    def close(self):
+        if getattr(self, "_ctx", None):
+            self._lib.granite4_host_glue_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def host_layer_io(tensors: dict, rows: int, eps: float, resid_mult: float) -> "capi.HostLayerIO":
+    """Fill a HostLayerIO from CPU tensors (pinned for asynchronous copies). Keys are the struct's
+    pointer fields; hidden_in / hidden_out may be absent."""
+    io = capi.HostLayerIO()
+    for name, _ in capi.HostLayerIO._fields_:
+        if name in ("rows", "eps", "resid_mult"):
+            continue
+        t = tensors.get(name)
+        if t is not None:
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError(f"{name}: expected a contiguous CPU tensor")
+            setattr(io, name, t.data_ptr())
+    io.rows, io.eps, io.resid_mult = rows, eps, resid_mult
+    return io

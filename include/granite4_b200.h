@@ -225,6 +225,106 @@ int granite4_kernel_swiglu_fp8(const void* d_gate, const void* d_up, int in_is_f
                                int rows, int I, uint16_t* d_act_bf16, uint8_t* d_act_fp8,
                                float* d_scale_amax);
 
+/* ------------------------------------------------------------------------ */
+/* One layer's glue in one call (added)                                      */
+/* ------------------------------------------------------------------------ */
+/* The four glue launches of one transformer layer, in the order the
+ * reference's prefill path issues them between its GEMMs
+ * (engine/src/forward_gpu.cu:2786-2845): residual add + norm -> FP8 on the
+ * attention output, RoPE + int8 paged KV write on the QKV output, residual add
+ * + norm -> FP8 on the MLP output, SwiGLU -> FP8 on the gate/up output. It only
+ * saves host launch overhead: results are those of the four entry points above.
+ * Every pointer is device memory. */
+typedef struct granite4_glue_layer_args {
+  /* stand-ins for GEMM / attention outputs, bf16 */
+  const uint16_t* y_attn; /* [rows][hidden]  O-projection output   */
+  const uint16_t* y_mlp;  /* [rows][hidden]  down-projection output */
+  const uint16_t* qkv;    /* [rows][(q_heads + 2 kv_heads) head_dim] */
+  const uint16_t* gate;   /* [rows][intermediate] */
+  const uint16_t* up;     /* [rows][intermediate] */
+  /* weights and tables */
+  const uint16_t* w_attn_norm; /* [hidden] bf16, norm after the attention block */
+  const uint16_t* w_mlp_norm;  /* [hidden] bf16, norm after the MLP block */
+  const float* cos_tbl;        /* [max_pos][head_dim / 2] */
+  const float* sin_tbl;
+  const int* pos_rows; /* [rows] RoPE position of each row */
+  const int* kv_rows;  /* [rows] pool row of each row */
+  /* residual stream, updated in place twice */
+  uint16_t* hidden; /* [rows][hidden] bf16 */
+  /* outputs */
+  uint8_t* n_attn_fp8; /* [rows][hidden] e4m3: norm after the attention block (input of the MLP GEMMs) */
+  uint8_t* n_mlp_fp8;  /* [rows][hidden] e4m3: norm after the MLP block (input of the next QKV GEMM) */
+  uint16_t* q_rot;     /* [rows][q_heads head_dim] bf16 */
+  int8_t* cache_k;     /* [kv_heads][pool_rows][head_dim] */
+  int8_t* cache_v;
+  float* k_scale; /* [kv_heads][pool_rows] */
+  float* v_scale;
+  uint8_t* act_fp8; /* [rows][intermediate] e4m3 */
+  float* scales;    /* [3][2]: {scale, amax} of n_attn, n_mlp, act */
+  /* optional scratch between the two sweeps of the FP8 ops (may be NULL) */
+  float* rstd;      /* [rows] */
+  uint16_t* act_ws; /* [rows][intermediate] bf16 */
+  int rows, hidden_size, intermediate, q_heads, kv_heads, head_dim, pool_rows, max_pos;
+  float eps, resid_mult;
+} granite4_glue_layer_args;
+int granite4_glue_layer(const granite4_glue_layer_args* a);
+
+/* ------------------------------------------------------------------------ */
+/* The same layer through HOST buffers (added)                               */
+/* ------------------------------------------------------------------------ */
+/* For callers whose activations live in host memory: a context owns device
+ * staging for max_rows rows (two sets, so the copies of one call overlap the
+ * kernels and the read-back of the previous one), the int8 KV pool of every
+ * layer, the RoPE tables, three streams and their events.
+ * granite4_host_glue_create ALLOCATES (cudaMalloc, streams, events);
+ * granite4_host_glue_destroy frees. */
+typedef struct granite4_host_glue granite4_host_glue;
+granite4_host_glue* granite4_host_glue_create(int max_rows, int hidden_size, int intermediate,
+                                              int q_heads, int kv_heads, int head_dim, int layers,
+                                              int pool_rows, int max_pos, double rope_theta);
+void granite4_host_glue_destroy(granite4_host_glue* ctx);
+/* Host-side arguments of one layer call; every pointer is HOST memory (pinned
+ * memory makes the copies asynchronous; pageable memory works but serialises). */
+typedef struct granite4_host_layer_io {
+  const uint16_t* y_attn;
+  const uint16_t* y_mlp;
+  const uint16_t* qkv;
+  const uint16_t* gate;
+  const uint16_t* up;
+  const uint16_t* w_attn_norm;
+  const uint16_t* w_mlp_norm;
+  const int* pos_rows;
+  const int* kv_rows;
+  /* The residual stream is context state that stays on the device from one layer call to
+   * the next. hidden_in (optional): upload it before this layer (the first layer's input);
+   * hidden_out (optional): read it back after this layer (the last layer's output). */
+  const uint16_t* hidden_in; /* [rows][hidden] or NULL */
+  uint16_t* hidden_out;      /* [rows][hidden] or NULL */
+  uint8_t* n_attn_fp8;
+  uint8_t* n_mlp_fp8;
+  uint16_t* q_rot;
+  uint8_t* act_fp8;
+  float* scales; /* [3][2] */
+  int rows;
+  float eps, resid_mult;
+} granite4_host_layer_io;
+/* Enqueues: host -> device copies of the inputs, the layer's kernels, device ->
+ * host copies of the outputs (the KV pool stays on the device; it is the
+ * context's state, as in the reference). Returns as soon as everything is
+ * enqueued; the outputs are valid after granite4_host_glue_sync. At most two
+ * calls are in flight: a third call first waits for the oldest one. */
+int granite4_host_glue_layer(granite4_host_glue* ctx, int layer, const granite4_host_layer_io* io);
+/* The final norm (a5) of the resident residual stream with the HOST weights h_w
+ * [hidden]; the normed rows are copied to the HOST buffer h_out [rows][hidden].
+ * Asynchronous like granite4_host_glue_layer. */
+int granite4_host_glue_final_norm(granite4_host_glue* ctx, const uint16_t* h_w, float eps, int rows,
+                                  uint16_t* h_out);
+int granite4_host_glue_sync(granite4_host_glue* ctx);
+/* Bytes one call copies host -> device and device -> host for `rows` rows, not
+ * counting the optional transfers of the residual stream. */
+long long granite4_host_glue_h2d_bytes(const granite4_host_glue* ctx, int rows);
+long long granite4_host_glue_d2h_bytes(const granite4_host_glue* ctx, int rows);
+
 #ifdef __cplusplus
 }
 #endif

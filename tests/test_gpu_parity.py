@@ -635,3 +635,79 @@ def test_row_sharding_changes_nothing_but_the_fp8_scale(K):
             b = c[sl].view(torch.float8_e4m3fn).float() * sa[0]
             # two different e4m3 grids, each within half a step (1/16 relative) of the value
             assert ((a - b).abs() <= 0.126 * torch.maximum(a.abs(), b.abs()) + 2.0 ** -8 * sa[0]).all()
+
+
+def test_one_call_per_layer_equals_the_separate_launches(K):
+    from granite4_b200 import glue
+    rows, layers = 40, 2
+    a = glue.GlueSequence(rows, device=DEV, seed=5, layers=layers, pool_rows=64, max_pos=128)
+    b = glue.GlueSequence(rows, device=DEV, seed=5, layers=layers, pool_rows=64, max_pos=128)
+    for s in (a, b):
+        s.set_rows(np.arange(rows) + 9, np.random.default_rng(1).permutation(64)[:rows])
+        s.reset()
+    a.run()
+    b.run_fast()
+    torch.cuda.synchronize()
+    for x, y in ((a.h, b.h), (a.out, b.out), (a.n_fp8, b.n_fp8), (a.act_fp8, b.act_fp8), (a.q_rot, b.q_rot),
+                 (a.cache_k, b.cache_k), (a.cache_v, b.cache_v), (a.k_scale, b.k_scale), (a.scales, b.scales)):
+        assert torch.equal(x, y)
+    assert a.launches == b.launches
+
+
+def test_host_buffer_path_equals_the_device_path(K):
+    """granite4_host_glue_*: the same layers with every activation staged from / to pinned host
+    memory, the residual stream and the KV pool resident in the context."""
+    from granite4_b200 import glue
+    rows, layers = 48, 3
+    seq = glue.GlueSequence(rows, device=DEV, seed=7, layers=layers, pool_rows=64, max_pos=128, sets=1)
+    pos, kvr = np.arange(rows) + 3, np.random.default_rng(2).permutation(64)[:rows]
+    seq.set_rows(pos, kvr)
+    seq.reset()
+    s = seq.shapes
+    hg = glue.HostGlue(rows + 5, s, device=DEV, layers=layers, pool_rows=64, max_pos=128)
+    src = seq.sets[0]
+    host = {k: src[k].cpu().pin_memory() for k in ("y_attn", "y_mlp", "qkv", "gate", "up")}
+    host["pos_rows"] = seq.pos_rows.cpu().pin_memory()
+    host["kv_rows"] = seq.kv_rows.cpu().pin_memory()
+    outs = []
+    for layer in range(layers):
+        t = dict(host)
+        t["w_attn_norm"] = seq.w[layer, 0].cpu().pin_memory()
+        t["w_mlp_norm"] = seq.w[layer, 1].cpu().pin_memory()
+        t["n_attn_fp8"] = torch.empty(rows, s.hidden, dtype=torch.uint8).pin_memory()
+        t["n_mlp_fp8"] = torch.empty(rows, s.hidden, dtype=torch.uint8).pin_memory()
+        t["q_rot"] = torch.empty(rows, s.q_heads * s.head_dim, dtype=torch.bfloat16).pin_memory()
+        t["act_fp8"] = torch.empty(rows, s.intermediate, dtype=torch.uint8).pin_memory()
+        t["scales"] = torch.zeros(6, dtype=torch.float32).pin_memory()
+        if layer == 0:
+            t["hidden_in"] = seq.h0.cpu().pin_memory()
+        if layer == layers - 1:
+            t["hidden_out"] = torch.empty(rows, s.hidden, dtype=torch.bfloat16).pin_memory()
+        outs.append(t)
+        hg.layer(layer, glue.host_layer_io(t, rows, s.eps, s.residual_multiplier))
+    final = torch.empty(rows, s.hidden, dtype=torch.bfloat16).pin_memory()
+    w_final = seq.w_final.cpu().pin_memory()
+    hg.final_norm(w_final, s.eps, rows, final)
+    hg.sync()
+    # device path, layer by layer, keeping each layer's outputs
+    want = []
+    for layer in range(layers):
+        for name, thunk in seq.layer_ops(layer):
+            assert thunk() == 0
+            if name == "add_rmsnorm_fp8":
+                want.append(seq.n_fp8.cpu().clone())
+        want.append(seq.q_rot.cpu().clone())
+        want.append(seq.act_fp8.cpu().clone())
+        want.append(seq.scales[layer].cpu().clone().reshape(-1))
+    assert seq.final_op()[1]() == 0
+    torch.cuda.synchronize()
+    for layer in range(layers):
+        n1, n2, q, act, sc = want[5 * layer: 5 * layer + 5]
+        t = outs[layer]
+        assert torch.equal(t["n_attn_fp8"], n1) and torch.equal(t["n_mlp_fp8"], n2)
+        assert torch.equal(t["q_rot"], q) and torch.equal(t["act_fp8"], act) and torch.equal(t["scales"], sc)
+    assert torch.equal(outs[-1]["hidden_out"], seq.h.cpu())
+    assert torch.equal(final, seq.out.cpu())
+    assert hg.h2d_bytes(rows) == rows * (2 * (2 * 4096 + 6144 + 2 * 12800) + 8) + 4 * 4096
+    assert hg.d2h_bytes(rows) == rows * (2 * 4096 + 2 * 4096 + 12800) + 24
+    hg.close()
