@@ -38,6 +38,25 @@ WORKLOAD = ("box-scale sweep: 65536 tokens row-sharded, 40-layer glue sequence "
             "Granite 8B shapes H4096/I12800/32q/8kv/d128")
 
 
+def shard_bounds(total: int, world: int, rank: int):
+    """Contiguous row range of `rank`: GPU g of N takes rows [g * total / N, (g + 1) * total / N)."""
+    if total % world:
+        raise SystemExit(f"the GPU count must divide {total}")
+    per = total // world
+    return rank * per, (rank + 1) * per
+
+
+def max_over_ranks(value: float, device):
+    """Max of a per-rank duration over the process group (the only collective in the bench; it
+    carries a timing, never data of the path). device None: CPU tensor (gloo)."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device=device if device is not None else "cpu")
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(path):
@@ -211,9 +230,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     shapes = glue.GraniteShapes()
-    if TOTAL_TOKENS % world:
-        raise SystemExit("the GPU count must divide 65536")
-    rows = int(os.environ.get("G4_BENCH_ROWS", TOTAL_TOKENS // world))  # override only for profiling
+    lo, hi = shard_bounds(TOTAL_TOKENS, world, rank)
+    rows = int(os.environ.get("G4_BENCH_ROWS", hi - lo))  # override only for profiling
     total_tokens = rows * world
     prof_layers = os.environ.get("G4_BENCH_LAYERS")  # fewer layers: only for short profiler captures
     workspace = os.environ.get("G4_BENCH_WORKSPACE", "1") != "0"  # 0: the scratch-free second sweeps
@@ -270,20 +288,15 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     clocks = sampler.stop(wall0, wall2) if rank == 0 else None
     ms_ops = evo0.elapsed_time(evo1)
 
-    t = torch.tensor([ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = t.item()
+    ms_max = max_over_ranks(ms, device)
     status = capi.lib().device_status()
 
     # ---- end to end through the host-buffer entry points ------------------------------------
     e2e = None
     if not args.no_e2e:
         e2e_ms, h2d, d2h, e2e_steps = run_e2e(seq, rows, device, min(args.steps, 2))
-        te = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e = {"value": total_tokens * e2e_steps / (te.item() * 1e-3), "unit": UNIT,
+        e2e_ms = max_over_ranks(e2e_ms, device)
+        e2e = {"value": total_tokens * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                "timing": "host clock around enqueue + granite4_host_glue_sync, max over ranks",
                "api": "granite4_host_glue_layer x layers + granite4_host_glue_final_norm, pinned "
