@@ -29,6 +29,8 @@ SIGNATURES = {
     "granite4_kernel_add_rmsnorm_fp8": (C.c_int, [_vp, C.c_int, _vp, C.c_int, _vp, C.c_float,
                                                   C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
                                                   _vp]),
+    "granite4_kernel_add_rmsnorm_fp8_noalloc": (C.c_int, [_vp, C.c_int, _vp, C.c_int, _vp, C.c_float,
+                                                          C.c_float, C.c_int, C.c_int, _vp, _vp, _vp]),
     "granite4_kernel_fp8_quant": (C.c_int, [_vp, C.c_longlong, _vp, _vp]),
     "granite4_rope_tables_build": (C.c_int, [C.c_double, C.c_int, C.c_int, C.POINTER(_vp),
                                              C.POINTER(_vp)]),

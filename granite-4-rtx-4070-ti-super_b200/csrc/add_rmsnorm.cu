@@ -474,3 +474,81 @@ int granite4_kernel_fp8_quant(const uint16_t* d_x, long long n, uint8_t* d_codes
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// The fused add + norm + FP8 op for callers that cannot hand over scratch memory.
+//
+// Some hosts of this library have no way to allocate device memory when the call is made: a
+// serving engine that carved up the whole card at start-up (the reference engine sizes its KV
+// arena to what is left of the 16 GB and its launchers allocate nothing by convention), or a
+// thin binding from another language (ctypes, cgo) that loads this library but not the CUDA
+// runtime, so it has no cudaMalloc of its own to call. granite4_kernel_add_rmsnorm_fp8 asks such
+// a caller for the per-row 1/rms buffer if it wants the cheap second sweep; this variant keeps
+// that buffer inside the library instead, in a fixed array that every GPU loading the library
+// holds until the process exits.
+constexpr int kNoAllocMaxRows = 65536;  // 256 KB of scratch per device
+static __device__ __align__(256) float g_noalloc_rstd[kNoAllocMaxRows];
+
+namespace g4 {
+namespace {
+// Device address of g_noalloc_rstd on each device. In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use; the address is looked up once per
+// device, with that device current, and cached.
+float* g_noalloc_rstd_ptr[64];
+
+float* noalloc_rstd_ptr(const char* fn) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    fail(fn, "cannot identify the current device");
+    return nullptr;
+  }
+  if (g_noalloc_rstd_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_rstd);
+    if (e != cudaSuccess || p == nullptr) {
+      std::fprintf(stderr, "granite4: %s: cudaGetSymbolAddress failed: %s\n", fn,
+                   cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_noalloc_rstd_ptr[dev] = static_cast<float*>(p);
+  }
+  return g_noalloc_rstd_ptr[dev];
+}
+}  // namespace
+}  // namespace g4
+
+extern "C" {
+
+// The first call on a device looks up the scratch array's device address (one
+// cudaGetSymbolAddress); make that first call before starting any stream capture. Calls share
+// the one array per device: two calls whose kernels can overlap on the GPU (different streams,
+// no dependency between them) race on it. Nothing is allocated or freed, here or by anything
+// this calls.
+int granite4_kernel_add_rmsnorm_fp8_noalloc(const void* d_y, int y_is_f32, const void* d_res,
+                                            int res_is_f32, const uint16_t* d_w, float eps,
+                                            float resid_mult, int rows, int cols,
+                                            uint16_t* d_h_out, uint8_t* d_n_fp8,
+                                            float* d_scale_amax) {
+  const char* fn = "granite4_kernel_add_rmsnorm_fp8_noalloc";
+  if (d_y == nullptr || d_w == nullptr || d_h_out == nullptr || d_n_fp8 == nullptr ||
+      d_scale_amax == nullptr || !std::isfinite(eps) || eps <= 0.0f || !std::isfinite(resid_mult) ||
+      rows <= 0 || cols <= 0 || static_cast<long long>(rows) * cols > INT_MAX)
+    return g4::fail(fn, "invalid arguments");
+  if (rows > kNoAllocMaxRows)
+    return g4::fail(fn, "more than 65536 rows: the built-in scratch holds one float per row for at "
+                        "most 65536 rows; split the batch or use granite4_kernel_add_rmsnorm_fp8 with "
+                        "your own d_rstd");
+  if (cols % 8 != 0 || cols > g4::max_vector_cols())
+    return g4::fail(fn, "cols must be a multiple of 8 and at most 32768");
+  if (!g4::aligned16(d_y) || !g4::aligned16(d_res) || !g4::aligned16(d_w) ||
+      !g4::aligned16(d_h_out) || !g4::aligned16(d_n_fp8))
+    return g4::fail(fn, "pointers must be 16-byte aligned");
+  float* rstd = g4::noalloc_rstd_ptr(fn);
+  if (rstd == nullptr) return -1;
+  // The first sweep writes rstd[0 .. rows) in full before the second sweep reads it, so nothing
+  // in the shared array has to be cleared between calls.
+  return g4::add_rmsnorm_launch(fn, d_y, y_is_f32, d_res, res_is_f32, d_w, eps, resid_mult, rows,
+                                cols, d_h_out, nullptr, d_n_fp8, d_scale_amax, rstd);
+}
+
+}  // extern "C"

@@ -77,6 +77,17 @@ def add_rmsnorm_fp8(y, res, w, eps, resid_mult, h_out=None, n_bf16=None, n_fp8=N
         _p(n_fp8, torch.uint8), _p(scale_amax, torch.float32), _p(rstd, torch.float32))
 
 
+def add_rmsnorm_fp8_noalloc(y, res, w, eps, resid_mult, h_out, n_fp8, scale_amax):
+    """granite4_kernel_add_rmsnorm_fp8_noalloc: the op for callers that cannot allocate device
+    memory; its per-row scratch is a fixed array inside the library (at most 65536 rows)."""
+    lib = _enter(y)
+    rows, cols = y.shape
+    return lib.granite4_kernel_add_rmsnorm_fp8_noalloc(
+        _p(y), int(y.dtype == torch.float32), _p(res), int(res is not None and res.dtype == torch.float32),
+        _p(w, *_BF16_OK), eps, resid_mult, rows, cols, _p(h_out, *_BF16_OK), _p(n_fp8, torch.uint8),
+        _p(scale_amax, torch.float32))
+
+
 def fp8_quant(x, codes, scale_amax):
     """granite4_kernel_fp8_quant: per-tensor e4m3 of a bf16 tensor."""
     lib = _enter(x)

@@ -129,6 +129,22 @@ int granite4_kernel_add_rmsnorm_fp8(const void* d_y, int y_is_f32, const void* d
                                     float resid_mult, int rows, int cols, uint16_t* d_h_out,
                                     uint16_t* d_n_bf16, uint8_t* d_n_fp8, float* d_scale_amax,
                                     float* d_rstd);
+/* Added; no counterpart in the reference. The same op (h and FP8 codes out) for
+ * callers that cannot allocate device memory at call time and so have no
+ * d_rstd buffer to offer: an engine that gave the whole card to its arenas at
+ * start-up, or a foreign-language binding that loads this library without the
+ * CUDA runtime and has no cudaMalloc to call. The per-row scratch lives in a
+ * 256 KB array inside the library instead (held by every GPU that loads it,
+ * until the process exits), which limits rows to 65536; more rows are refused
+ * with -1 and a message. The first call on a device resolves the array's
+ * device address; make it before any stream capture. All calls on a device
+ * share the array, so calls whose kernels may overlap on the GPU race on it;
+ * nothing in it needs clearing between calls. Calls no allocator. */
+int granite4_kernel_add_rmsnorm_fp8_noalloc(const void* d_y, int y_is_f32, const void* d_res,
+                                            int res_is_f32, const uint16_t* d_w, float eps,
+                                            float resid_mult, int rows, int cols,
+                                            uint16_t* d_h_out, uint8_t* d_n_fp8,
+                                            float* d_scale_amax);
 /* Added: per-tensor FP8 quantisation of a bf16 tensor of n elements (n % 8 ==
  * 0) with the same rule; d_scale_amax as above. */
 int granite4_kernel_fp8_quant(const uint16_t* d_x, long long n, uint8_t* d_codes,
