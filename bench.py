@@ -291,6 +291,9 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     ms_max = max_over_ranks(ms, device)
     status = capi.lib().device_status()
 
+    # ---- the embedding gather (a1; not part of the sweep) and the small, latency-bound shapes ----
+    extras = small_shapes_and_embed(seq, rows, device, stream) if rank == 0 else None
+
     # ---- end to end through the host-buffer entry points ------------------------------------
     e2e = None
     if not args.no_e2e:
@@ -339,6 +342,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                          "timing": f"event pair around each op, {op_steps} steps after the main region"},
             "sequence_roofline": {"achieved": seq_gbs, "unit": "GB/s per GPU", "frac": seq_gbs / peak},
             "ops": ops,
+            "embed": extras["embed"],
+            "small_shapes": extras["small"],
             "clocks": clocks,
             "gpu_launches": launches,
             "device_status": status,
@@ -360,8 +365,85 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
 
 # DRAM bytes per token row each op really moves (both sweeps of the FP8 ops), from the ncu
 # captures summarised under profiles/: the second sweep re-reads the bf16 intermediate.
-TRAFFIC_PER_ROW = {"add_rmsnorm_fp8": 36864, "rope_kv_int8": 23108, "swiglu_fp8": 115200,
-                   "final_norm": 16384}
+TRAFFIC_PER_ROW = {"add_rmsnorm_fp8": 26542, "rope_kv_int8": 17358, "swiglu_fp8": 104285,
+                   "final_norm": 10475}
+
+
+def small_shapes_and_embed(seq, rows, device, stream):
+    """(1) The embedding gather at the shard's row count on a Granite-size table (100352 x 4096,
+    ids uniform, multiplier 12). (2) BASELINE configs 1-3: one decode row, the decode chain at 1
+    and 8 rows replayed from a CUDA graph, one 500-row prefill layer - latency-bound shapes,
+    reported in microseconds, not against the bandwidth roofline."""
+    import torch
+    from granite4_b200 import glue, kernels as k
+    s = seq.shapes
+    peak, _ = load_peaks()
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(device)
+        a.record(stream)
+        for _ in range(iters):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize(device)
+        return a.elapsed_time(b) / iters * 1e3
+
+    g = torch.Generator(device=device).manual_seed(1234)
+    table = (0.02 * torch.randn(s.vocab, s.hidden, generator=g, device=device)).to(torch.bfloat16)
+    ids = torch.randint(0, s.vocab, (rows,), generator=g, device=device, dtype=torch.int32)
+    out = torch.empty(rows, s.hidden, dtype=torch.bfloat16, device=device)
+    us = timed(lambda: k.embed_gather(ids, table, s.embedding_multiplier, out), 10)
+    bpr = glue.bytes_per_row(s)["embed"]
+    embed = {"rows": rows, "mean_us": us, "achieved_gbs": bpr * rows / (us * 1e-6) / 1e9,
+             "frac": bpr * rows / (us * 1e-6) / 1e9 / peak, "bytes_per_row": bpr}
+
+    small = {}
+    for n in (1, 8, 500):
+        sq = glue.GlueSequence(n, s, device=device, seed=7, sets=1, layers=1, pool_rows=8192, max_pos=8192)
+        pos = torch.randint(0, 8192, (n,), generator=g, device=device, dtype=torch.int32)
+        sq.set_rows(pos, torch.randperm(8192, generator=g, device=device)[:n].to(torch.int32))
+        sq.reset()
+        tok = ids[:n].contiguous()
+        f32y = torch.randn(n, s.hidden, generator=g, device=device)
+        f32r = torch.randn(n, s.hidden, generator=g, device=device)
+        hb, nb = torch.empty_like(sq.h), torch.empty_like(sq.h)
+
+        def chain():
+            k.embed_gather(tok, table, s.embedding_multiplier, sq.h)
+            for _, thunk in sq.layer_ops(0):
+                thunk()
+        entry = {"chain_eager_us": timed(chain, 50)}
+        # the same chain replayed from a CUDA graph (every launcher is capturable: no allocation,
+        # no synchronisation, positions read from device memory)
+        side = torch.cuda.Stream(device)
+        with torch.cuda.stream(side):
+            chain()
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                chain()
+            for _ in range(3):
+                graph.replay()
+            side.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side)
+            for _ in range(100):
+                graph.replay()
+            b.record(side)
+            side.synchronize()
+            entry["chain_graph_us"] = a.elapsed_time(b) / 100 * 1e3
+        if n == 1:  # config 1: f32 x and residual, bf16 + FP8 out
+            entry["add_rmsnorm_f32_fp8_us"] = timed(
+                lambda: k.add_rmsnorm_fp8(f32y, f32r, sq.w[0, 0], s.eps, s.residual_multiplier, hb, nb,
+                                          sq.n_fp8, sq.scales[0, 0]), 50)
+        small[f"rows_{n}"] = entry
+        del sq
+    del table
+    torch.cuda.empty_cache()
+    return {"embed": embed, "small": small}
 
 
 def run_e2e(seq, rows, device, steps):

@@ -191,6 +191,88 @@ __global__ void __launch_bounds__(max_threads_for(V))
   if (PHASE == kEncode && blockIdx.x == 0 && t == 0) p.scale_amax[0] = fs.scale;
 }
 
+// The stats sweep for the shape every launch of the Granite sequence has: bf16 y (and res),
+// cols8 == 4 * blockDim.x (a 4096-wide row on 128 threads). Same arithmetic in the same order as
+// add_rmsnorm_kernel<false, false, 4, kStats> - the results are bit-identical - with the bounds
+// tests, the input-type switches and the unused outputs compiled away.
+template <bool HAS_RES, bool WANT_AMAX>
+__global__ void __launch_bounds__(256) add_rmsnorm_fast_kernel(const NormParams p) {
+  constexpr int V = 4;
+  const int T = blockDim.x;
+  const int t = threadIdx.x;
+  const int row = blockIdx.x;
+  const size_t row_chunk0 = static_cast<size_t>(row) * p.cols8;
+  const uint4* yp = reinterpret_cast<const uint4*>(p.y) + row_chunk0 + t;
+  const uint4* rp = reinterpret_cast<const uint4*>(p.res) + row_chunk0 + t;
+  uint4 yraw[V], rraw[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) yraw[j] = ld_stream(yp + j * T);
+  if (HAS_RES) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) rraw[j] = ld_stream(rp + j * T);
+  }
+  float h[V][8];
+  double acc = 0.0;
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    unpack8(yraw[j], h[j]);
+    if (HAS_RES) {
+      float rv[8];
+      unpack8(rraw[j], rv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) h[j][e] = __fadd_rn(rv[e], __fmul_rn(p.rm, h[j][e]));
+    }
+    const uint4 hb = pack8(h[j]);
+    unpack8(hb, h[j]);
+    if (p.h_out != nullptr) reinterpret_cast<uint4*>(p.h_out)[row_chunk0 + t + j * T] = hb;
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const double d = static_cast<double>(h[j][e]);
+      acc = fma(d, d, acc);
+    }
+  acc = warp_sum(acc);
+  __shared__ double s_part[8];
+  __shared__ uint32_t s_amax[8];
+  const int warp = t >> 5, lane = t & 31, nwarps = T >> 5;
+  if (lane == 0) s_part[warp] = acc;
+  __syncthreads();
+  double total = 0.0;
+  for (int i = 0; i < nwarps; ++i) total += s_part[i];
+  const float ms = static_cast<float>(p.inv_cols != 0.0 ? total * p.inv_cols
+                                                         : total / static_cast<double>(p.cols));
+  const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, p.eps)));
+  if (p.rstd != nullptr && t == 0) p.rstd[row] = r;
+  if (p.n_bf16 == nullptr && !WANT_AMAX) return;  // h (and r) were all that was asked for
+  uint32_t amax = 0u;
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    const int c = t + j * T;
+    float wv[8], n[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(p.w) + c), wv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) n[e] = __fmul_rn(__fmul_rn(h[j][e], r), wv[e]);
+    const uint4 nb = pack8(n);
+    if (p.n_bf16 != nullptr) {
+      uint4* dst = reinterpret_cast<uint4*>(p.n_bf16) + row_chunk0 + c;
+      if (WANT_AMAX) *dst = nb; else st_stream(dst, nb);
+    }
+    if (WANT_AMAX) amax = amax_acc(amax, nb);
+  }
+  if (WANT_AMAX) {
+    amax = amax_warp(amax);
+    if (lane == 0) s_amax[warp] = amax;
+    __syncthreads();
+    if (t == 0) {
+      uint32_t m = 0u;
+      for (int i = 0; i < nwarps; ++i) m = max_u16x2(m, s_amax[i]);
+      atomic_amax(p.scale_amax + 1, amax_value(m));
+    }
+  }
+}
+
 // Second sweep with r known per row: a plain streaming pass. A CTA takes kRowsPerCta
 // consecutive rows; a thread takes the chunks t, t + T, ... of each, so every
 // thread has kRowsPerCta * ceil(cols8 / T) independent 128-bit loads to issue
@@ -199,6 +281,10 @@ constexpr int kRowsPerCta = 4;
 constexpr int kEncodeThreads = 256;
 constexpr int kEncodeMaxIter = 2;  // cols8 <= 512 per pass of the unrolled body
 
+// FULL: cols8 == kEncodeThreads * kEncodeMaxIter (a 4096-wide row) and rows a multiple of
+// kRowsPerCta - the shape of every launch of the Granite sequence - so that no bounds test is
+// left in the loop bodies.
+template <bool FULL>
 __global__ void __launch_bounds__(kEncodeThreads) norm_encode_kernel(const NormParams p) {
   const int t = threadIdx.x;
   const int tiles = (p.rows + kRowsPerCta - 1) / kRowsPerCta;
@@ -208,32 +294,37 @@ __global__ void __launch_bounds__(kEncodeThreads) norm_encode_kernel(const NormP
   if (blockIdx.x == 0 && t == 0) p.scale_amax[0] = fs.scale;
   const uint4* h = reinterpret_cast<const uint4*>(p.h_out);
   uint2* out = reinterpret_cast<uint2*>(p.n_fp8);
-  for (int c0 = 0; c0 < p.cols8; c0 += kEncodeThreads * kEncodeMaxIter) {
+  const int pass_cols = kEncodeThreads * kEncodeMaxIter;
+  for (int c0 = 0; c0 < (FULL ? pass_cols : p.cols8); c0 += pass_cols) {
     uint4 hv[kRowsPerCta][kEncodeMaxIter];
     uint4 wv[kEncodeMaxIter];
+    float rr[kRowsPerCta];
 #pragma unroll
     for (int k = 0; k < kEncodeMaxIter; ++k) {
       const int c = c0 + k * kEncodeThreads + t;
-      if (c < p.cols8) {
+      if (FULL || c < p.cols8) {
         wv[k] = __ldg(reinterpret_cast<const uint4*>(p.w) + c);
 #pragma unroll
         for (int j = 0; j < kRowsPerCta; ++j)
-          if (row0 + j < p.rows) hv[j][k] = ld_stream(h + static_cast<size_t>(row0 + j) * p.cols8 + c);
+          if (FULL || row0 + j < p.rows)
+            hv[j][k] = ld_stream(h + static_cast<size_t>(row0 + j) * p.cols8 + c);
       }
     }
 #pragma unroll
-    for (int j = 0; j < kRowsPerCta; ++j) {
-      if (row0 + j >= p.rows) continue;
-      const float r = __ldg(p.rstd + row0 + j);
+    for (int j = 0; j < kRowsPerCta; ++j) rr[j] = (FULL || row0 + j < p.rows) ? __ldg(p.rstd + row0 + j) : 0.0f;
 #pragma unroll
-      for (int k = 0; k < kEncodeMaxIter; ++k) {
-        const int c = c0 + k * kEncodeThreads + t;
-        if (c >= p.cols8) continue;
-        float hf[8], wf[8], n[8];
+    for (int k = 0; k < kEncodeMaxIter; ++k) {
+      const int c = c0 + k * kEncodeThreads + t;
+      if (!FULL && c >= p.cols8) continue;
+      float wf[8];
+      unpack8(wv[k], wf);  // once per column chunk, shared by the rows
+#pragma unroll
+      for (int j = 0; j < kRowsPerCta; ++j) {
+        if (!FULL && row0 + j >= p.rows) continue;
+        float hf[8], n[8];
         unpack8(hv[j][k], hf);
-        unpack8(wv[k], wf);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) n[e] = __fmul_rn(__fmul_rn(hf[e], r), wf[e]);
+        for (int e = 0; e < 8; ++e) n[e] = __fmul_rn(__fmul_rn(hf[e], rr[j]), wf[e]);
         st_stream(out + static_cast<size_t>(row0 + j) * p.cols8 + c, fp8x8_quant(pack8(n), fs));
       }
     }
@@ -369,7 +460,21 @@ int add_rmsnorm_launch(const char* fn, const void* d_y, int y_is_f32, const void
   p.inv_cols = (cols & (cols - 1)) == 0 ? 1.0 / static_cast<double>(cols) : 0.0;
   if (d_n_fp8 != nullptr)
     G4_CUDA_TRY(fn, cudaMemsetAsync(d_scale_amax, 0, 2 * sizeof(float), st));
-  launch_phase<kStats>(p, y_is_f32 != 0, res_is_f32 != 0, st);
+  const int fast_threads = p.cols8 / 4;
+  const bool fast = !y_is_f32 && (d_res == nullptr || !res_is_f32) && p.cols8 % 4 == 0 &&
+                    fast_threads % 32 == 0 && fast_threads <= 256 && pick_v(p.cols8) == 4;
+  if (fast) {
+    const bool amax = p.scale_amax != nullptr;
+    if (d_res != nullptr) {
+      if (amax) add_rmsnorm_fast_kernel<true, true><<<rows, fast_threads, 0, st>>>(p);
+      else add_rmsnorm_fast_kernel<true, false><<<rows, fast_threads, 0, st>>>(p);
+    } else {
+      if (amax) add_rmsnorm_fast_kernel<false, true><<<rows, fast_threads, 0, st>>>(p);
+      else add_rmsnorm_fast_kernel<false, false><<<rows, fast_threads, 0, st>>>(p);
+    }
+  } else {
+    launch_phase<kStats>(p, y_is_f32 != 0, res_is_f32 != 0, st);
+  }
   G4_LAUNCH_CHECK(fn);
   if (d_n_fp8 != nullptr) {
     if (d_n_bf16 != nullptr) {
@@ -381,7 +486,11 @@ int add_rmsnorm_launch(const char* fn, const void* d_y, int y_is_f32, const void
     } else if (d_h_out != nullptr && d_rstd != nullptr) {
       NormParams q = p;
       q.reverse = 1;
-      norm_encode_kernel<<<(rows + kRowsPerCta - 1) / kRowsPerCta, kEncodeThreads, 0, st>>>(q);
+      const unsigned grid = static_cast<unsigned>((rows + kRowsPerCta - 1) / kRowsPerCta);
+      if (q.cols8 == kEncodeThreads * kEncodeMaxIter && rows % kRowsPerCta == 0)
+        norm_encode_kernel<true><<<grid, kEncodeThreads, 0, st>>>(q);
+      else
+        norm_encode_kernel<false><<<grid, kEncodeThreads, 0, st>>>(q);
     } else {
       NormParams q = p;
       q.reverse = 1;

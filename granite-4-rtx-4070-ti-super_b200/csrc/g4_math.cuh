@@ -167,12 +167,14 @@ __device__ __forceinline__ uint2 fp8x8_quant(uint4 p, const Fp8Scale s) {
 // s == 0 -> 0.
 struct Kv8Scale {
   float s;
-  float inv;  // 1 / s, or 0 when s == 0 (every code is then 0)
+  float inv;  // ~1 / s (SFU reciprocal; only the short path uses it), or 0 when s == 0
 };
 __device__ __forceinline__ Kv8Scale kv8_scale(float amax) {
   Kv8Scale k;
   k.s = __fdiv_rn(amax, 127.0f);
-  k.inv = k.s != 0.0f ? __fdiv_rn(1.0f, k.s) : 0.0f;
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(k.s));
+  k.inv = k.s != 0.0f ? r : 0.0f;
   return k;
 }
 static __device__ __noinline__ int kv8_quant_exact(float x, float s) {
@@ -184,19 +186,45 @@ static __device__ __noinline__ int kv8_quant_exact(float x, float s) {
   t = fminf(fmaxf(t, -127.0f), 127.0f);
   return static_cast<int>(t);
 }
-// Short path: x * inv is within 2e-5 of the true quotient (|q| <= 127), so its
+// Short path: x * inv is within 4e-5 of the true quotient (|q| <= 127), so its
 // nearest integer is the right code unless the fraction is that close to one
-// half; those elements take the exact path. |x| <= amax keeps |q| <= 127 + 2e-5,
-// which rounds into range without a clamp. The magic constant 1.5 * 2^23 makes
-// the f32 add itself round to the nearest integer and leaves it in the low bits.
-__device__ __forceinline__ int kv8_quant(float x, const Kv8Scale k) {
-  const float q = __fmul_rn(x, k.inv);
-  const float t = __fadd_rn(q, 12582912.0f);
-  const float d = __fsub_rn(q, __fsub_rn(t, 12582912.0f));
-  int code = static_cast<int>(__float_as_uint(t)) - 0x4b400000;
-  // written so that a NaN (an overflowed 1 / s for a subnormal s) also goes the exact way
-  if (!(fabsf(d) <= 0.4999f)) code = kv8_quant_exact(x, k.s);
-  return code;
+// half; such a group of eight takes the exact path. |x| <= amax keeps
+// |q| <= 127 + 1e-4, which rounds into range without a clamp. Adding the magic
+// constant 1.5 * 2^23 makes the f32 add itself round to the nearest integer and
+// leaves it, as a two's complement byte, in the low 8 bits of the sum.
+// Eight values -> eight codes in two words; one branch for the whole group.
+__device__ __forceinline__ uint2 kv8_quant8(const float (&x)[8], const Kv8Scale k) {
+  float t[8];
+  bool doubt = false;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float q = __fmul_rn(x[e], k.inv);
+    t[e] = __fadd_rn(q, 12582912.0f);
+    const float d = __fsub_rn(q, __fsub_rn(t[e], 12582912.0f));
+    // written so that a NaN (an overflowed reciprocal of a subnormal s) also raises the doubt
+    doubt = doubt || !(fabsf(d) <= 0.4999f);
+  }
+  uint2 out;
+  if (!doubt) {
+    const uint32_t b0 = __float_as_uint(t[0]), b1 = __float_as_uint(t[1]), b2 = __float_as_uint(t[2]),
+                   b3 = __float_as_uint(t[3]), b4 = __float_as_uint(t[4]), b5 = __float_as_uint(t[5]),
+                   b6 = __float_as_uint(t[6]), b7 = __float_as_uint(t[7]);
+    out.x = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+    out.y = __byte_perm(__byte_perm(b4, b5, 0x0040), __byte_perm(b6, b7, 0x0040), 0x5410);
+  } else {
+    // rare (one group in several hundred): redo the test per element, exact path where it fails
+    uint32_t c[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float q = __fmul_rn(x[e], k.inv);
+      const float d = __fsub_rn(q, __fsub_rn(t[e], 12582912.0f));
+      c[e] = __float_as_uint(t[e]) & 0xffu;
+      if (!(fabsf(d) <= 0.4999f)) c[e] = static_cast<uint32_t>(kv8_quant_exact(x[e], k.s)) & 0xffu;
+    }
+    out.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+    out.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+  }
+  return out;
 }
 __device__ __forceinline__ uint32_t pack_i8x4(int a, int b, int c, int d) {
   return (static_cast<uint32_t>(a) & 0xffu) | ((static_cast<uint32_t>(b) & 0xffu) << 8) |

@@ -17,11 +17,12 @@
 // Kernel layout (d = 128): eight lanes own one head. Lane j holds columns
 // [8j, 8j+8) and [64+8j, 64+8j+8), i.e. both halves of its eight rotation
 // pairs, so the rotation needs no exchange and the row amax is three xor
-// shuffles. A 128-thread CTA covers 16 heads of one token row; loads are 128-bit
-// (a warp reads four whole heads = 1 KB), q_rot stores are 128-bit, code stores
-// are two 8-byte pieces per lane that together fill the head's 128-byte cache
-// row. The cos/sin row of the token (512 B) is read through the read-only path
-// by every head group and stays in L1.
+// shuffles. A 128-thread CTA covers one token row: thread (g, j) owns lane j of
+// the heads g, g + 16, g + 32 (all 48 heads of a Granite row), so the cos / sin
+// values of lane j are loaded once per row and reused for every head. Loads are
+// 128-bit (a warp reads four whole heads = 1 KB) and all issued before the first
+// is used, q_rot stores are 128-bit, code stores are two 8-byte pieces per lane
+// that together fill the head's 128-byte cache row.
 //
 // Algorithmic bytes per token row (Hq 32, Hk 8): q 8192 + k 2048 + v 2048 +
 // cos/sin 512 + ids 8 read; q_rot 8192 + codes 2048 + scales 64 written =
@@ -62,7 +63,6 @@ struct RopeKvParams {
   int max_pos;  // bound for pos_rows (kPerRowArrays)
   int rows, Hq, Hk;
   long long stride;
-  int groups;       // 16-head groups per row
   int rotate_k;     // 0: K rows are appended as they are (plain append)
   int k_from_bf16;  // quantise the bf16-rounded rotated K
 };
@@ -70,112 +70,103 @@ struct RopeKvParams {
 constexpr int kD = 128;
 constexpr int kHeadsPerCta = 16;
 
-// Rows one CTA walks through. All the loads of the kRows rows (activations,
-// then table rows) are issued before the first is used, which is what hides the
-// memory latency here: the per-row work is too short for occupancy alone to do it.
-constexpr int kRows = 2;
+// One 128-thread CTA handles kRows token rows, all heads: thread (g, j) = (tid / 8, tid % 8) owns
+// lane j of the heads g, g + 16, g + 32, ... of each row. The cos / sin values of lane j depend
+// only on the row, so they are loaded once per row and reused for every head of the thread.
+// All the activation loads of a row are issued before the first is used.
+constexpr int kMaxHeadsPerThread = 4;  // (Hq + 2 Hk) <= 64 heads per row in this kernel
 
+template <int kRows>
 __global__ void __launch_bounds__(kHeadsPerCta * 8) rope_kv_int8_kernel(const RopeKvParams p) {
-  const int r0 = (blockIdx.x / p.groups) * kRows;
-  const int head = (blockIdx.x % p.groups) * kHeadsPerCta + (threadIdx.x >> 3);
+  const int g = threadIdx.x >> 3;
   const int j = threadIdx.x & 7;
   const int heads_total = p.Hq + 2 * p.Hk;
-  // Whole 8-lane groups leave together, so the shuffles below stay converged
-  // within the groups that remain (the mask names only their own lanes).
-  if (head >= heads_total) return;
-  const bool is_q = head < p.Hq;
-  const bool is_k = !is_q && head < p.Hq + p.Hk;
-  const bool rotate = is_q || (is_k && p.rotate_k);
-
-  int pos[kRows], kv_row[kRows];
-  bool ok[kRows];
-  uint4 xlo[kRows], xhi[kRows];
+  const unsigned gmask = 0xffu << (threadIdx.x & 24);  // the 8 lanes that share this thread's heads
 #pragma unroll
   for (int i = 0; i < kRows; ++i) {
-    const int r = r0 + i;
-    ok[i] = r < p.rows;
-    pos[i] = kv_row[i] = 0;
-    if (!ok[i]) continue;
+    const int r = blockIdx.x * kRows + i;
+    if (r >= p.rows) return;  // uniform over the CTA
+    int pos, kv_row;
     if (p.mode == kRunOfPositions) {
-      pos[i] = p.base_pos + r;
-      kv_row[i] = p.d_pt != nullptr ? __ldg(p.d_pt + pos[i]) : pos[i];
+      pos = p.base_pos + r;
+      kv_row = p.d_pt != nullptr ? __ldg(p.d_pt + pos) : pos;
     } else if (p.mode == kPerRowArrays) {
-      pos[i] = __ldg(p.pos_rows + r);
-      kv_row[i] = __ldg(p.kv_rows + r);
+      pos = __ldg(p.pos_rows + r);
+      kv_row = __ldg(p.kv_rows + r);
+      // a bad index skips the row instead of touching memory outside the tables or the pool
+      if (pos < 0 || pos >= p.max_pos || kv_row < 0 || kv_row >= p.stride) continue;
     } else {
-      pos[i] = p.mr->pos[r];
-      const int slot = p.mr->tree ? p.mr->slot[r] : pos[i];
-      kv_row[i] = p.mr->pt[r][slot];
+      pos = p.mr->pos[r];
+      const int slot = p.mr->tree ? p.mr->slot[r] : pos;
+      kv_row = p.mr->pt[r][slot];
     }
-    const uint16_t* src;
-    if (is_q) src = p.q + static_cast<size_t>(r) * p.pitch_q + static_cast<size_t>(head) * kD;
-    else if (is_k) src = p.k + static_cast<size_t>(r) * p.pitch_k + static_cast<size_t>(head - p.Hq) * kD;
-    else src = p.v + static_cast<size_t>(r) * p.pitch_v + static_cast<size_t>(head - p.Hq - p.Hk) * kD;
-    xlo[i] = ld_stream(reinterpret_cast<const uint4*>(src) + j);
-    xhi[i] = ld_stream(reinterpret_cast<const uint4*>(src) + 8 + j);
-  }
-  if (p.mode == kPerRowArrays) {
-    // a bad index skips the row instead of touching memory outside the tables or the pool
+    // activations of every head this thread owns in this row
+    uint4 xlo[kMaxHeadsPerThread], xhi[kMaxHeadsPerThread];
 #pragma unroll
-    for (int i = 0; i < kRows; ++i)
-      if (pos[i] < 0 || pos[i] >= p.max_pos || kv_row[i] < 0 || kv_row[i] >= p.stride) ok[i] = false;
-  }
-  float4 c0[kRows], c1[kRows], s0[kRows], s1[kRows];
-  if (rotate) {
-#pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-      if (!ok[i]) continue;
-      const float4* cp = reinterpret_cast<const float4*>(p.cos_tbl + static_cast<size_t>(pos[i]) * (kD / 2)) + 2 * j;
-      const float4* sp = reinterpret_cast<const float4*>(p.sin_tbl + static_cast<size_t>(pos[i]) * (kD / 2)) + 2 * j;
-      c0[i] = __ldg(cp), c1[i] = __ldg(cp + 1), s0[i] = __ldg(sp), s1[i] = __ldg(sp + 1);
+    for (int k = 0; k < kMaxHeadsPerThread; ++k) {
+      const int head = g + k * kHeadsPerCta;
+      if (head >= heads_total) break;
+      const uint16_t* src;
+      if (head < p.Hq) src = p.q + static_cast<size_t>(r) * p.pitch_q + static_cast<size_t>(head) * kD;
+      else if (head < p.Hq + p.Hk) src = p.k + static_cast<size_t>(r) * p.pitch_k + static_cast<size_t>(head - p.Hq) * kD;
+      else src = p.v + static_cast<size_t>(r) * p.pitch_v + static_cast<size_t>(head - p.Hq - p.Hk) * kD;
+      xlo[k] = ld_stream(reinterpret_cast<const uint4*>(src) + j);
+      xhi[k] = ld_stream(reinterpret_cast<const uint4*>(src) + 8 + j);
     }
-  }
-  const unsigned gmask = 0xffu << (threadIdx.x & 24);  // the 8 lanes of this head
+    float c[8], s[8];
+    if (p.cos_tbl != nullptr) {
+      const float4* cp = reinterpret_cast<const float4*>(p.cos_tbl + static_cast<size_t>(pos) * (kD / 2)) + 2 * j;
+      const float4* sp = reinterpret_cast<const float4*>(p.sin_tbl + static_cast<size_t>(pos) * (kD / 2)) + 2 * j;
+      const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+      c[0] = c0.x, c[1] = c0.y, c[2] = c0.z, c[3] = c0.w, c[4] = c1.x, c[5] = c1.y, c[6] = c1.z, c[7] = c1.w;
+      s[0] = s0.x, s[1] = s0.y, s[2] = s0.z, s[3] = s0.w, s[4] = s1.x, s[5] = s1.y, s[6] = s1.z, s[7] = s1.w;
+    } else {
 #pragma unroll
-  for (int i = 0; i < kRows; ++i) {
-    if (!ok[i]) continue;  // uniform over the CTA: every thread works on the same rows
-    const int r = r0 + i;
-    float lo[8], hi[8];
-    unpack8(xlo[i], lo);
-    unpack8(xhi[i], hi);
-    if (rotate) {
-      const float c[8] = {c0[i].x, c0[i].y, c0[i].z, c0[i].w, c1[i].x, c1[i].y, c1[i].z, c1[i].w};
-      const float s[8] = {s0[i].x, s0[i].y, s0[i].z, s0[i].w, s1[i].x, s1[i].y, s1[i].z, s1[i].w};
+      for (int e = 0; e < 8; ++e) c[e] = 1.0f, s[e] = 0.0f;
+    }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        float a, b;
-        rope_pair(lo[e], hi[e], c[e], s[e], a, b);
-        lo[e] = a, hi[e] = b;
+    for (int k = 0; k < kMaxHeadsPerThread; ++k) {
+      const int head = g + k * kHeadsPerCta;
+      if (head >= heads_total) break;
+      const bool is_q = head < p.Hq;
+      const bool is_k = !is_q && head < p.Hq + p.Hk;
+      float lo[8], hi[8];
+      unpack8(xlo[k], lo);
+      unpack8(xhi[k], hi);
+      if (is_q || (is_k && p.rotate_k)) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float a, b;
+          rope_pair(lo[e], hi[e], c[e], s[e], a, b);
+          lo[e] = a, hi[e] = b;
+        }
       }
-    }
-    if (is_q) {
-      uint4* dst = reinterpret_cast<uint4*>(p.q_rot + (static_cast<size_t>(r) * p.Hq + head) * kD);
-      st_stream(dst + j, pack8(lo));
-      st_stream(dst + 8 + j, pack8(hi));
-      continue;
-    }
-    if (is_k && p.rotate_k && p.k_from_bf16) {
+      if (is_q) {
+        uint4* dst = reinterpret_cast<uint4*>(p.q_rot + (static_cast<size_t>(r) * p.Hq + head) * kD);
+        st_stream(dst + j, pack8(lo));
+        st_stream(dst + 8 + j, pack8(hi));
+        continue;
+      }
+      if (is_k && p.rotate_k && p.k_from_bf16) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) lo[e] = round_bf16(lo[e]), hi[e] = round_bf16(hi[e]);
-    }
-    float amax = 0.0f;
+        for (int e = 0; e < 8; ++e) lo[e] = round_bf16(lo[e]), hi[e] = round_bf16(hi[e]);
+      }
+      float amax = 0.0f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fmaxf(fabsf(lo[e]), fabsf(hi[e])));
-    amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
-    amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 4));
-    const Kv8Scale sc = kv8_scale(amax);
-    const int hkv = is_k ? head - p.Hq : head - p.Hq - p.Hk;
-    const size_t srow = static_cast<size_t>(hkv) * p.stride + kv_row[i];
-    int8_t* cache = (is_k ? p.cache_k : p.cache_v) + srow * kD;
-    if (j == 0) (is_k ? p.k_scale : p.v_scale)[srow] = sc.s;
-    uint2 cl, ch;
-    cl.x = pack_i8x4(kv8_quant(lo[0], sc), kv8_quant(lo[1], sc), kv8_quant(lo[2], sc), kv8_quant(lo[3], sc));
-    cl.y = pack_i8x4(kv8_quant(lo[4], sc), kv8_quant(lo[5], sc), kv8_quant(lo[6], sc), kv8_quant(lo[7], sc));
-    ch.x = pack_i8x4(kv8_quant(hi[0], sc), kv8_quant(hi[1], sc), kv8_quant(hi[2], sc), kv8_quant(hi[3], sc));
-    ch.y = pack_i8x4(kv8_quant(hi[4], sc), kv8_quant(hi[5], sc), kv8_quant(hi[6], sc), kv8_quant(hi[7], sc));
-    st_stream(reinterpret_cast<uint2*>(cache) + j, cl);
-    st_stream(reinterpret_cast<uint2*>(cache) + 8 + j, ch);
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fmaxf(fabsf(lo[e]), fabsf(hi[e])));
+      // is_q / is_k depend on g only, so the 8 lanes of a head take the same path here
+      amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 4));
+      const Kv8Scale sc = kv8_scale(amax);
+      const int hkv = is_k ? head - p.Hq : head - p.Hq - p.Hk;
+      const size_t srow = static_cast<size_t>(hkv) * p.stride + kv_row;
+      int8_t* cache = (is_k ? p.cache_k : p.cache_v) + srow * kD;
+      if (j == 0) (is_k ? p.k_scale : p.v_scale)[srow] = sc.s;
+      const uint2 cl = kv8_quant8(lo, sc), ch = kv8_quant8(hi, sc);
+      st_stream(reinterpret_cast<uint2*>(cache) + j, cl);
+      st_stream(reinterpret_cast<uint2*>(cache) + 8 + j, ch);
+    }
   }
 }
 
@@ -224,10 +215,8 @@ __global__ void __launch_bounds__(1024)
 
 int launch_rope_kv(const char* fn, RopeKvParams& p) {
   const int heads_total = p.Hq + 2 * p.Hk;
-  p.groups = (heads_total + kHeadsPerCta - 1) / kHeadsPerCta;
-  const long long ctas = static_cast<long long>((p.rows + kRows - 1) / kRows) * p.groups;
-  if (ctas > INT_MAX) return fail(fn, "too many rows");
-  rope_kv_int8_kernel<<<static_cast<unsigned>(ctas), kHeadsPerCta * 8, 0, current_stream()>>>(p);
+  if (heads_total > kMaxHeadsPerThread * kHeadsPerCta) return fail(fn, "more than 64 heads per row");
+  rope_kv_int8_kernel<1><<<static_cast<unsigned>(p.rows), kHeadsPerCta * 8, 0, current_stream()>>>(p);
   G4_LAUNCH_CHECK(fn);
   return 0;
 }
