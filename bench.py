@@ -365,7 +365,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
 
 # DRAM bytes per token row each op really moves (both sweeps of the FP8 ops), from the ncu
 # captures summarised under profiles/: the second sweep re-reads the bf16 intermediate.
-TRAFFIC_PER_ROW = {"add_rmsnorm_fp8": 26542, "rope_kv_int8": 17358, "swiglu_fp8": 104285,
+TRAFFIC_PER_ROW = {"add_rmsnorm_fp8": 26542, "rope_kv_int8": 16597, "swiglu_fp8": 104285,
                    "final_norm": 10475}
 
 

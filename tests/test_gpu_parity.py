@@ -57,6 +57,13 @@ def bf16_ulp_distance(a, b):
     return np.abs(key(a) - key(b))
 
 
+def rand_bf16(seed, shape, sigma=1.0):
+    """Seeded N(0, sigma) values rounded to bf16 (round to nearest even), as bit patterns."""
+    x = (sigma * np.random.default_rng(seed).standard_normal(shape, dtype=np.float32)).astype(np.float32)
+    u = x.view(np.uint32)
+    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
 def assert_scale(got, want):
     assert abs(float(got) - float(want)) <= 1e-6 * abs(float(want)), (got, want)
 
@@ -711,3 +718,115 @@ def test_host_buffer_path_equals_the_device_path(K):
     assert hg.h2d_bytes(rows) == rows * (2 * (2 * 4096 + 6144 + 2 * 12800) + 8) + 4 * 4096
     assert hg.d2h_bytes(rows) == rows * (2 * 4096 + 2 * 4096 + 12800) + 24
     hg.close()
+
+
+# =========================================================================== BASELINE configs at full size
+def test_config3_prefill_500_tokens_full_chain(K, port):
+    """BASELINE config 3: one 500-token prompt, positions 0..499, the whole op chain over
+    [500 x 4096] hidden and [500 x 12800] MLP activations, K/V into an int8 pool of 16-token
+    pages through the kept prefill entry points."""
+    from granite4_b200 import paging
+    rows, H, I, vocab, stride = 500, 4096, 12800, 3000, 512
+    rng = np.random.default_rng(33)
+    emb = port.fill_bf16(301, 0.08, vocab * H).reshape(vocab, H)
+    ids = rng.integers(0, vocab, rows).astype(np.int32)
+    y = port.fill_bf16(302, 3.0, rows * H).reshape(rows, H)
+    w = port.fill_bf16(303, 1.2, H)
+    qkv = port.fill_bf16(304, 4.0, rows * 48 * 128).reshape(rows, -1)
+    gu = port.fill_bf16(305, 5.0, rows * 2 * I).reshape(rows, 2 * I)
+    bt = rng.permutation(stride // 16)[: (rows + 15) // 16]
+    d_pt = np.zeros(stride, np.int32)
+    d_pt[:rows] = paging.row_table(bt, rows)
+    # oracle
+    h0 = port.embed_rows(ids, 0, rows, emb, 12.0)
+    h1, n1 = port.add_rmsnorm(y, h0, w, 1e-5, 0.22)
+    c1, s1, _ = port.quant_fp8(n1)
+    cos, sin = port.rope_tables(1e7, 128, stride)
+    rk = port.rope_kv_int8(qkv, cos, sin, np.arange(rows, dtype=np.int32), d_pt[:rows], Hq, Hk, D, stride, 0)
+    act = port.swiglu(gu[:, :I], gu[:, I:])
+    # device
+    h = empty_bf16(rows, H)
+    assert K.prefill_embed_rows(dev(ids), 0, rows, dev(emb), 12.0, h) == 0
+    assert (host(h) == h0).all()
+    c = torch.empty(rows, H, dtype=torch.uint8, device=DEV)
+    sa = torch.zeros(2, dtype=torch.float32, device=DEV)
+    assert K.add_rmsnorm_fp8(dev(y), h, dev(w), 1e-5, 0.22, h_out=h, n_fp8=c, scale_amax=sa) == 0
+    assert (host(h) == h1).all() and (host(c) == c1).all()
+    assert_scale(sa[0].item(), s1)
+    t = K.RopeTables(1e7, D, stride, DEV)
+    ck, cv, ks, vs = _pool(stride)
+    q_rot = empty_bf16(rows, Hq * D)
+    assert K.prefill_rope_split_append_int8(dev(qkv), t.cos, t.sin, 0, rows, Hq, Hk, D, stride, q_rot, ck, cv,
+                                            ks, vs, dev(d_pt)) == 0
+    for got, want in zip((q_rot, ck, cv, ks, vs), rk):
+        assert (host(got) == want).all()
+    gud = dev(gu)
+    a = empty_bf16(rows, I)
+    c2 = torch.empty(rows, I, dtype=torch.uint8, device=DEV)
+    assert K.swiglu_fp8(gud[:, :I], gud[:, I:], a, c2, sa, ld=2 * I) == 0
+    got = host(a)
+    assert bf16_ulp_distance(got, act).max() <= 1
+    assert (host(c2) == port.quant_fp8_with_scale(got, port.fp8_scale_from_amax(port.amax_bf16(got)))).all()
+    t.close()
+
+
+def test_config4_long_context_full_size(K, port):
+    """BASELINE config 4 at full size: 4 sequences x 8192 tokens, RoPE positions offset up to
+    131071, K/V into a 122880-row int8 pool with randomly permuted 16-token pages; bf16 N(0,1)-like
+    activations, norm weights around 1. RoPE + KV and add + norm + FP8 are compared with the oracle
+    over all 32768 rows."""
+    from granite4_b200 import paging
+    n_seq, per_seq, pool_pages, max_pos = 4, 8192, 7680, 131072
+    rows, stride = n_seq * per_seq, pool_pages * 16
+    tables = paging.permuted_block_tables(n_seq, per_seq // 16, pool_pages, seed=44)
+    first = [0, 40000, 90001, max_pos - per_seq]
+    pos, kvr = paging.batch_rows(tables, first, per_seq)
+    paging.validate_rows(kvr, stride)
+    qkv = rand_bf16(401, (rows, 48 * 128))
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+    ck, cv, ks, vs = _pool(stride)
+    q_rot = empty_bf16(rows, Hq * D)
+    assert K.rope_kv_int8_paged(dev(qkv), t.cos, t.sin, dev(pos), dev(kvr), Hq, Hk, D, stride, max_pos, 0,
+                                q_rot, ck, cv, ks, vs) == 0
+    cos, sin = port.rope_tables(1e7, D, max_pos)
+    want = port.rope_kv_int8(qkv, cos, sin, pos, kvr, Hq, Hk, D, stride, 0)
+    for got, w_ in zip((q_rot, ck, cv, ks, vs), want):
+        assert (host(got) == w_).all()
+    t.close()
+    del qkv, want
+    y, res = rand_bf16(402, (rows, 4096)), rand_bf16(403, (rows, 4096))
+    w = np.array([port.f32_to_bf16(v) for v in 1 + 0.02 * np.random.default_rng(5).standard_normal(4096)],
+                 np.uint16)
+    hw, nw = port.add_rmsnorm(y, res, w, 1e-5, 0.22)
+    cw, sw, aw = port.quant_fp8(nw)
+    h = empty_bf16(rows, 4096)
+    c = torch.empty(rows, 4096, dtype=torch.uint8, device=DEV)
+    sa = torch.zeros(2, dtype=torch.float32, device=DEV)
+    rstd = torch.empty(rows, dtype=torch.float32, device=DEV)
+    assert K.add_rmsnorm_fp8(dev(y), dev(res), dev(w), 1e-5, 0.22, h_out=h, n_fp8=c, scale_amax=sa,
+                             rstd=rstd) == 0
+    assert (host(h) == hw).all() and sa[1].item() == aw and sa[0].item() == sw
+    assert (host(c) == cw).all()
+
+
+def test_rope_kv_plain_and_bulk_kernels_agree(K, port, monkeypatch):
+    """The persistent bulk-copy kernel (default) and the one-CTA-per-row kernel (G4_ROPE_BULK=0)
+    share their arithmetic; 1000 rows with scattered positions, both K rounding modes."""
+    rows, stride, max_pos = 1000, 1024, 4096
+    qkv = rand_bf16(501, (rows, 48 * 128), 2.0)
+    rng = np.random.default_rng(6)
+    pos = rng.integers(0, max_pos, rows).astype(np.int32)
+    kvr = rng.permutation(stride)[:rows].astype(np.int32)
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+    cos, sin = port.rope_tables(1e7, D, max_pos)
+    for mode in (0, 1):
+        want = port.rope_kv_int8(qkv, cos, sin, pos, kvr, Hq, Hk, D, stride, mode)
+        for bulk in ("1", "0"):
+            monkeypatch.setenv("G4_ROPE_BULK", bulk)
+            ck, cv, ks, vs = _pool(stride)
+            q_rot = empty_bf16(rows, Hq * D)
+            assert K.rope_kv_int8_paged(dev(qkv), t.cos, t.sin, dev(pos), dev(kvr), Hq, Hk, D, stride,
+                                        max_pos, mode, q_rot, ck, cv, ks, vs) == 0
+            for got, w_ in zip((q_rot, ck, cv, ks, vs), want):
+                assert (host(got) == w_).all(), (mode, bulk)
+    t.close()
