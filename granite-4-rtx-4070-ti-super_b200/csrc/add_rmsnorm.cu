@@ -31,6 +31,7 @@
 // Algorithmic bytes per row at cols = 4096, bf16 y and res, h + FP8 out:
 // 8192 + 8192 read, 8192 + 4096 written = 28 672; the second sweep adds another
 // 8192-byte read of h.
+#include "g4_cluster.cuh"
 #include "g4_host.h"
 #include "g4_math.cuh"
 
@@ -60,7 +61,9 @@ struct NormParams {
   double inv_cols;  // 1 / cols when cols is a power of two (the scaling is then exact), else 0
 };
 
-enum { kStats = 0, kEncode = 1 };
+// kCluster: the whole grid is one cluster of at most 16 CTAs with one row each; stats and encode in
+// one launch (g4_cluster.cuh).
+enum { kStats = 0, kEncode = 1, kCluster = 2 };
 
 // Load one 8-element chunk as floats.
 template <bool F32>
@@ -83,7 +86,11 @@ __global__ void __launch_bounds__(max_threads_for(V))
     add_rmsnorm_kernel(const NormParams p) {
   const int T = blockDim.x;
   const int t = threadIdx.x;
-  const int row = p.reverse ? p.rows - 1 - static_cast<int>(blockIdx.x) : blockIdx.x;
+  // A cluster is a power of two wide: its spare CTAs redo the last row without storing anything,
+  // so that they reach the cluster barrier with a harmless contribution.
+  const bool live = PHASE != kCluster || static_cast<int>(blockIdx.x) < p.rows;
+  const int row = PHASE == kCluster ? (live ? static_cast<int>(blockIdx.x) : p.rows - 1)
+                                    : (p.reverse ? p.rows - 1 - static_cast<int>(blockIdx.x) : blockIdx.x);
   const size_t row_chunk0 = static_cast<size_t>(row) * p.cols8;
 
   float h[V][8];
@@ -121,7 +128,7 @@ __global__ void __launch_bounds__(max_threads_for(V))
   for (int j = 0; j < V; ++j) {
     const uint4 hb = pack8(h[j]);
     unpack8(hb, h[j]);
-    if (PHASE == kStats && p.h_out != nullptr) {
+    if (PHASE != kEncode && live && p.h_out != nullptr) {
       const int c = t + j * T;
       // default cache policy: the second sweep re-reads it
       if (c < p.cols8) reinterpret_cast<uint4*>(p.h_out)[row_chunk0 + c] = hb;
@@ -152,12 +159,13 @@ __global__ void __launch_bounds__(max_threads_for(V))
   const float ms = static_cast<float>(p.inv_cols != 0.0 ? total * p.inv_cols
                                                          : total / static_cast<double>(p.cols));
   const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, p.eps)));
-  if (PHASE == kStats && p.rstd != nullptr && t == 0) p.rstd[row] = r;
+  if (PHASE != kEncode && live && p.rstd != nullptr && t == 0) p.rstd[row] = r;
 
   // ---- normalise -----------------------------------------------------------------
   Fp8Scale fs{};
   if (PHASE == kEncode) fs = fp8_scale_from_amax(__ldcg(p.scale_amax + 1));
   uint32_t amax = 0u;
+  uint4 kept[PHASE == kCluster ? V : 1];  // kCluster: n stays in registers across the barrier
 #pragma unroll
   for (int j = 0; j < V; ++j) {
     const int c = t + j * T;
@@ -167,7 +175,12 @@ __global__ void __launch_bounds__(max_threads_for(V))
 #pragma unroll
       for (int e = 0; e < 8; ++e) n[e] = __fmul_rn(__fmul_rn(h[j][e], r), wv[e]);
       const uint4 nb = pack8(n);
-      if (PHASE == kStats) {
+      if (PHASE == kCluster) {
+        if (live && p.n_bf16 != nullptr)
+          st_stream(reinterpret_cast<uint4*>(p.n_bf16) + row_chunk0 + c, nb);
+        kept[PHASE == kCluster ? j : 0] = nb;
+        amax = amax_acc(amax, nb);
+      } else if (PHASE == kStats) {
         if (p.n_bf16 != nullptr) {
           uint4* dst = reinterpret_cast<uint4*>(p.n_bf16) + row_chunk0 + c;
           if (p.n_fp8 != nullptr) *dst = nb; else st_stream(dst, nb);
@@ -189,6 +202,20 @@ __global__ void __launch_bounds__(max_threads_for(V))
     }
   }
   if (PHASE == kEncode && blockIdx.x == 0 && t == 0) p.scale_amax[0] = fs.scale;
+  if (PHASE == kCluster) {
+    __shared__ uint32_t s_slots[kMaxClusterCtas];
+    const float tensor_amax = __uint_as_float(cluster_amax_bits(amax, s_amax, s_slots));
+    fs = fp8_scale_from_amax(tensor_amax);
+    if (live) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const int c = t + j * T;
+        if (c < p.cols8)
+          st_stream(reinterpret_cast<uint2*>(p.n_fp8) + row_chunk0 + c, fp8x8_quant(kept[PHASE == kCluster ? j : 0], fs));
+      }
+    }
+    if (blockIdx.x == 0 && t == 0) p.scale_amax[0] = fs.scale, p.scale_amax[1] = tensor_amax;
+  }
 }
 
 // The stats sweep for the shape every launch of the Granite sequence has: bf16 y (and res),
@@ -458,6 +485,24 @@ int add_rmsnorm_launch(const char* fn, const void* d_y, int y_is_f32, const void
   p.rstd = d_rstd;
   p.eps = eps, p.rm = rm, p.rows = rows, p.cols = cols, p.cols8 = cols / 8, p.reverse = 0;
   p.inv_cols = (cols & (cols - 1)) == 0 ? 1.0 / static_cast<double>(cols) : 0.0;
+  if (d_n_fp8 != nullptr && rows <= kMaxClusterCtas && p.cols8 <= max_threads_for(1) && cluster_enabled()) {
+    const int ctas = cluster_ctas_for(rows);
+    const int threads = (p.cols8 + 31) / 32 * 32;
+    cudaError_t e;
+    if (y_is_f32) {
+      e = res_is_f32 ? cluster_launch(add_rmsnorm_kernel<true, true, 1, kCluster>, ctas, threads, p, st)
+                     : cluster_launch(add_rmsnorm_kernel<true, false, 1, kCluster>, ctas, threads, p, st);
+    } else {
+      e = res_is_f32 ? cluster_launch(add_rmsnorm_kernel<false, true, 1, kCluster>, ctas, threads, p, st)
+                     : cluster_launch(add_rmsnorm_kernel<false, false, 1, kCluster>, ctas, threads, p, st);
+    }
+    if (e == cudaSuccess) return 0;
+    if (e != cudaErrorInvalidConfiguration) {
+      std::fprintf(stderr, "granite4: %s: cluster launch failed: %s\n", fn, cudaGetErrorString(e));
+      return -1;
+    }
+    // the device cannot place such a cluster: the multi-launch form below takes over
+  }
   if (d_n_fp8 != nullptr)
     G4_CUDA_TRY(fn, cudaMemsetAsync(d_scale_amax, 0, 2 * sizeof(float), st));
   const int fast_threads = p.cols8 / 4;

@@ -3,7 +3,8 @@
 //
 // Rules these helpers rely on: both addresses of a bulk copy are 16-byte
 // aligned and the size is a multiple of 16 bytes; a CTA only ever copies into
-// its own shared memory (no cluster launch, no cross-CTA delivery of any kind);
+// its own shared memory (the destination is named in the CTA's own window, so
+// no copy is ever delivered to another CTA);
 // every wait is bounded - a wait that runs out reports failure to the caller,
 // which records it in the library's device status word and winds the CTA down
 // instead of spinning.
@@ -60,7 +61,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes,
                                           uint64_t* bar) {
   asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+      "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
           "r"(smem_u32(smem_dst)),
       "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");

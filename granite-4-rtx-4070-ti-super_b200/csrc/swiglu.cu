@@ -26,6 +26,7 @@
 //
 // Algorithmic bytes per row at I = 12800, bf16 in, FP8 out: 2 * 25 600 read +
 // 12 800 written = 64 000.
+#include "g4_cluster.cuh"
 #include "g4_host.h"
 #include "g4_math.cuh"
 
@@ -151,6 +152,40 @@ __global__ void __launch_bounds__(kThreads) swiglu_kernel(const SwigluParams p) 
   }
 }
 
+// Small tensors (a decode or verify step: up to 16 rows of 12800): the whole grid is one cluster,
+// the activations stay in registers between the amax exchange and the encode step, so one launch
+// replaces the memset and the two sweeps (g4_cluster.cuh). A CTA owns kClusterThreads * kUnroll
+// consecutive items.
+constexpr int kClusterThreads = 512;
+constexpr long long kClusterItemsPerCta = static_cast<long long>(kClusterThreads) * kUnroll;
+
+template <bool F32>
+__global__ void __launch_bounds__(kClusterThreads) swiglu_cluster_kernel(const SwigluParams p) {
+  const long long tile0 = static_cast<long long>(blockIdx.x) * kClusterItemsPerCta + threadIdx.x;
+  uint4 a[kUnroll];
+  uint32_t amax = 0u;
+#pragma unroll
+  for (int k = 0; k < kUnroll; ++k) {
+    const long long it = tile0 + k * kClusterThreads;
+    a[k] = make_uint4(0, 0, 0, 0);
+    if (it < p.items) {
+      a[k] = swiglu8<F32>(p.gate, p.up, item_offset(p, it));
+      if (p.act_bf16 != nullptr) st_stream(reinterpret_cast<uint4*>(p.act_bf16) + it, a[k]);
+    }
+    amax = amax_acc(amax, a[k]);
+  }
+  __shared__ uint32_t s_warp[kClusterThreads / 32];
+  __shared__ uint32_t s_slots[kMaxClusterCtas];
+  const float tensor_amax = __uint_as_float(cluster_amax_bits(amax, s_warp, s_slots));
+  const Fp8Scale fs = fp8_scale_from_amax(tensor_amax);
+#pragma unroll
+  for (int k = 0; k < kUnroll; ++k) {
+    const long long it = tile0 + k * kClusterThreads;
+    if (it < p.items) st_stream(reinterpret_cast<uint2*>(p.act_fp8) + it, fp8x8_quant(a[k], fs));
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) p.scale_amax[0] = fs.scale, p.scale_amax[1] = tensor_amax;
+}
+
 // The reference's prefill entry point takes any I: scalar form for I % 8 != 0.
 __global__ void __launch_bounds__(256)
     silu_mul_scalar_kernel(const float* gu, int I, long long n, uint16_t* act) {
@@ -170,6 +205,16 @@ int launch_swiglu(const char* fn, const SwigluParams& p) {
     swiglu_kernel<F32, kPlain, false><<<grid, kThreads, 0, st>>>(p);
     G4_LAUNCH_CHECK(fn);
     return 0;
+  }
+  if (p.items <= kMaxClusterCtas * kClusterItemsPerCta && cluster_enabled()) {
+    const int ctas = cluster_ctas_for((p.items + kClusterItemsPerCta - 1) / kClusterItemsPerCta);
+    const cudaError_t e = cluster_launch(swiglu_cluster_kernel<F32>, ctas, kClusterThreads, p, st);
+    if (e == cudaSuccess) return 0;
+    if (e != cudaErrorInvalidConfiguration) {
+      std::fprintf(stderr, "granite4: %s: cluster launch failed: %s\n", fn, cudaGetErrorString(e));
+      return -1;
+    }
+    // the device cannot place such a cluster: the multi-launch form below takes over
   }
   G4_CUDA_TRY(fn, cudaMemsetAsync(p.scale_amax, 0, 2 * sizeof(float), st));
   swiglu_kernel<F32, kAmax, false><<<grid, kThreads, 0, st>>>(p);
