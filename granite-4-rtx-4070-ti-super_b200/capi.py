@@ -43,6 +43,18 @@ SIGNATURES = {
     "granite4_gpu_multi_rope_append": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int,
                                                  C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
                                                  C.c_int, _vp]),
+    "granite4_gpu_multi_rope": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
+    "granite4_gpu_multi_kv_append": (C.c_int, [_vp, _vp, C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_int,
+                                               C.c_int, C.c_int, C.c_int]),
+    "granite4_kernel_rope_at_pos": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, _vp]),
+    "granite4_kernel_rope_at_pos_batched": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
+    "granite4_kernel_kv_append_batched": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int,
+                                                    C.c_int, C.c_int, _vp]),
+    "granite4_kernel_verify_qkv_stage": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int,
+                                                   C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
+                                                   _vp]),
+    "granite4_prefill_rope_split_append": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int,
+                                                     C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
     "granite4_kernel_rope_kv_int8_paged": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int,
                                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                                      _vp, _vp, _vp, _vp, _vp]),

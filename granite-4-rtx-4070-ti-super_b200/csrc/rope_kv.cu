@@ -361,10 +361,16 @@ __global__ void __launch_bounds__(256)
 __global__ void __launch_bounds__(1024)
     kv_append_int8_generic_kernel(const uint16_t* src_k, const uint16_t* src_v, int8_t* cache_k,
                                   int8_t* cache_v, float* k_scale, float* v_scale, int base_pos,
-                                  int stride, int Hk, int d, const int* d_pt) {
+                                  int stride, int Hk, int d, const int* d_pt,
+                                  const granite4_multi_rows* mr) {
   const int hkv = blockIdx.x, r = blockIdx.y, i = threadIdx.x;
-  const int pos = base_pos + r;
-  const int row = d_pt != nullptr ? d_pt[pos] : pos;
+  int row;
+  if (mr != nullptr) {
+    row = mr->pt[r][mr->tree ? mr->slot[r] : mr->pos[r]];
+  } else {
+    const int pos = base_pos + r;
+    row = d_pt != nullptr ? d_pt[pos] : pos;
+  }
   const bool act = i < d;  // the CTA is d rounded up to whole warps
   const size_t src = (static_cast<size_t>(r) * Hk + hkv) * d + i;
   const float x = act ? bf16_to_f32(src_k[src]) : 0.0f, y = act ? bf16_to_f32(src_v[src]) : 0.0f;
@@ -415,6 +421,35 @@ int launch_rope_kv(const char* fn, RopeKvParams& p) {
 }
 
 }  // namespace
+
+// bf16-cache form (rope_bf16.cu).
+int multi_rope_append_bf16(const char* fn, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                           const float* cos_tbl, const float* sin_tbl,
+                           const granite4_multi_rows* d_rows, int rows, int Hq, int Hk, int d,
+                           uint16_t* cache_k, uint16_t* cache_v, int stride, uint16_t* q_rot);
+
+// The int8 append of the multi-row helpers: K and V rows as they are, row r into the pool row its
+// descriptor names (engine/src/forward_gpu.cu:3919-3923, kv_append_int8_multi_kernel :427-452).
+int multi_kv_append_int8(const char* fn, const uint16_t* k, const uint16_t* v, int8_t* cache_k,
+                         int8_t* cache_v, float* k_scale, float* v_scale,
+                         const granite4_multi_rows* d_rows, int rows, int stride, int Hk, int d) {
+  if (k_scale == nullptr || v_scale == nullptr || d > 1024) return fail(fn, "invalid arguments");
+  const bool fast = d == kD && aligned16(k) && aligned16(v) && aligned16(cache_k) && aligned16(cache_v);
+  if (!fast) {
+    kv_append_int8_generic_kernel<<<dim3(Hk, rows), (d + 31) / 32 * 32, 0, current_stream()>>>(
+        k, v, cache_k, cache_v, k_scale, v_scale, 0, stride, Hk, d, nullptr, d_rows);
+    G4_LAUNCH_CHECK(fn);
+    return 0;
+  }
+  RopeKvParams p{};
+  p.q = nullptr, p.k = k, p.v = v;
+  p.pitch_k = p.pitch_v = static_cast<long long>(Hk) * d;
+  p.cache_k = cache_k, p.cache_v = cache_v, p.k_scale = k_scale, p.v_scale = v_scale;
+  p.mode = kDescriptor, p.mr = d_rows;
+  p.rows = rows, p.Hq = 0, p.Hk = Hk, p.stride = stride, p.rotate_k = 0, p.k_from_bf16 = 0;
+  return launch_rope_kv(fn, p);
+}
+
 }  // namespace g4
 
 extern "C" {
@@ -488,7 +523,7 @@ int granite4_kernel_kv_append_int8_batched(const uint16_t* d_src_k, const uint16
     g4::kv_append_int8_generic_kernel<<<dim3(Hk, rows), (d + 31) / 32 * 32, 0,
                                         g4::current_stream()>>>(
         d_src_k, d_src_v, d_cache_k, d_cache_v, d_cache_k_scale, d_cache_v_scale, base_pos, stride,
-        Hk, d, d_pt);
+        Hk, d, d_pt, nullptr);
     G4_LAUNCH_CHECK(fn);
     return 0;
   }
@@ -537,7 +572,11 @@ int granite4_gpu_multi_rope_append(const uint16_t* q, const uint16_t* k, const u
   const char* fn = "gpu_multi_rope_append";
   // engine/src/forward_gpu.cu:3911 (-1 also tells the caller to take its unfused path)
   if (d_rows == nullptr || rows < 1 || rows > GRANITE4_MAX_VERIFY_ROWS) return -1;
-  if (bits != 8 || d != g4::kD) return -1;  // other cache formats are not built here
+  if (bits == 16)
+    return g4::multi_rope_append_bf16(fn, q, k, v, cos_tbl, sin_tbl, d_rows, rows, Hq, Hk, d,
+                                      static_cast<uint16_t*>(cache_k), static_cast<uint16_t*>(cache_v),
+                                      stride, q_rot);
+  if (bits != 8 || d != g4::kD) return -1;  // the 4- and 5-bit cache formats are not built here
   if (q == nullptr || k == nullptr || v == nullptr || cos_tbl == nullptr || sin_tbl == nullptr ||
       cache_k == nullptr || cache_v == nullptr || k_scale == nullptr || v_scale == nullptr ||
       q_rot == nullptr || Hq <= 0 || Hk <= 0 || stride <= 0)

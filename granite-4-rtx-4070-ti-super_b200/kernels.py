@@ -178,6 +178,66 @@ def gpu_multi_rope_append(q, k, v, cos_tbl, sin_tbl, d_rows, rows, Hq, Hk, d, bi
         _p(v_scale, torch.float32), stride, _p(q_rot, *_BF16_OK))
 
 
+def gpu_multi_rope(x, cos_tbl, sin_tbl, d_rows, rows, heads, d, out):
+    """engine/src/forward_gpu_api.h:219-220: row r rotated at position d_rows.pos[r]."""
+    lib = _enter(x)
+    return lib.granite4_gpu_multi_rope(_p(x, *_BF16_OK), _tbl(cos_tbl), _tbl(sin_tbl), _p(d_rows), rows,
+                                       heads, d, _p(out, *_BF16_OK))
+
+
+def gpu_multi_kv_append(k, v, bits, cache_k, cache_v, k_scale, v_scale, d_rows, rows, stride, Hk, d):
+    """engine/src/forward_gpu_api.h:227-229: bits 8 (int8 + scales) or 16 (bf16 copy)."""
+    lib = _enter(k)
+    return lib.granite4_gpu_multi_kv_append(
+        _p(k, *_BF16_OK), _p(v, *_BF16_OK), bits, _p(cache_k), _p(cache_v),
+        _p(k_scale, torch.float32), _p(v_scale, torch.float32), _p(d_rows), rows, stride, Hk, d)
+
+
+def rope_at_pos(d_x, d_cos_row, d_sin_row, heads, d, d_out):
+    """engine/src/forward_gpu.cu:3814-3826: one position; the table pointers are that position's
+    row (pass e.g. ``tables.cos[pos]`` of a float32 tensor, or an integer device address)."""
+    lib = _enter(d_x)
+    return lib.granite4_kernel_rope_at_pos(_p(d_x, *_BF16_OK), _tbl(d_cos_row), _tbl(d_sin_row), heads,
+                                           d, _p(d_out, *_BF16_OK))
+
+
+def rope_at_pos_batched(d_x, d_cos_rows, d_sin_rows, rows, heads, d, d_out):
+    """engine/src/forward_gpu.cu:3828-3842: row r uses row r of the table pointers."""
+    lib = _enter(d_x)
+    return lib.granite4_kernel_rope_at_pos_batched(_p(d_x, *_BF16_OK), _tbl(d_cos_rows),
+                                                   _tbl(d_sin_rows), rows, heads, d,
+                                                   _p(d_out, *_BF16_OK))
+
+
+def kv_append_batched(d_src_k, d_src_v, d_cache_k, d_cache_v, base_pos, rows, stride, Hk, d,
+                      d_pt=None):
+    """engine/src/kernels_phase2.cu:1087-1105: bf16 cache append of rows <= 16."""
+    lib = _enter(d_src_k)
+    return lib.granite4_kernel_kv_append_batched(
+        _p(d_src_k, *_BF16_OK), _p(d_src_v, *_BF16_OK), _p(d_cache_k, *_BF16_OK),
+        _p(d_cache_v, *_BF16_OK), base_pos, rows, stride, Hk, d, _p(d_pt, torch.int32))
+
+
+def verify_qkv_stage(d_q, d_k, d_v, d_cos_rows, d_sin_rows, base_pos, rows, Hq, Hk, d, cache_stride,
+                     d_q_rot, d_k_rot, d_cache_k, d_cache_v, d_pt=None):
+    """engine/src/forward_gpu.cu:3847-3874: RoPE q and k, append rotated k and raw v (bf16)."""
+    lib = _enter(d_q)
+    return lib.granite4_kernel_verify_qkv_stage(
+        _p(d_q, *_BF16_OK), _p(d_k, *_BF16_OK), _p(d_v, *_BF16_OK), _tbl(d_cos_rows),
+        _tbl(d_sin_rows), base_pos, rows, Hq, Hk, d, cache_stride, _p(d_q_rot, *_BF16_OK),
+        _p(d_k_rot, *_BF16_OK), _p(d_cache_k, *_BF16_OK), _p(d_cache_v, *_BF16_OK),
+        _p(d_pt, torch.int32))
+
+
+def prefill_rope_split_append(qkv, cos_tbl, sin_tbl, base_pos, rows, Hq, Hk, d, stride, q_rot,
+                              cache_k, cache_v, d_pt=None):
+    """engine/src/prefill_gemm.h:48-52: the prefill step for a bf16 cache."""
+    lib = _enter(qkv)
+    return lib.granite4_prefill_rope_split_append(
+        _p(qkv, *_BF16_OK), _tbl(cos_tbl), _tbl(sin_tbl), base_pos, rows, Hq, Hk, d, stride,
+        _p(q_rot, *_BF16_OK), _p(cache_k, *_BF16_OK), _p(cache_v, *_BF16_OK), _p(d_pt, torch.int32))
+
+
 def multi_rows_to_device(desc: capi.MultiRows, device):
     """Upload a MultiRows descriptor; returns a uint8 CUDA tensor to pass as d_rows."""
     raw = bytes(desc)

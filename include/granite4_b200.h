@@ -201,14 +201,68 @@ typedef struct granite4_multi_rows {
  * engine/src/forward_gpu.cu:598-665, :3907-3914. Decode / verify form: separate
  * q [rows][Hq d], k, v [rows][Hk d]; row r's RoPE position is d_rows->pos[r] and
  * its pool row d_rows->pt[r][slot] (slot = pos, or d_rows->slot[r] for tree
- * rows). K is rounded to bf16 after the rotation and then quantised. Only
- * bits == 8 and d == 128 are built here; anything else returns -1, which the
- * reference's callers treat as "use the unfused path". rows <= 16. */
+ * rows). K is rounded to bf16 after the rotation and then quantised (bits == 8,
+ * d == 128) or stored as bf16 (bits == 16, any even d <= 256; the scale
+ * pointers are not used). The reference's 4- and 5-bit cache formats are not
+ * built here: they return -1, which the reference's callers treat as "use the
+ * unfused path". rows <= 16. */
 int granite4_gpu_multi_rope_append(const uint16_t* q, const uint16_t* k, const uint16_t* v,
                                    const float* cos_tbl, const float* sin_tbl,
                                    const granite4_multi_rows* d_rows, int rows, int Hq, int Hk,
                                    int d, int bits, void* cache_k, void* cache_v, float* k_scale,
                                    float* v_scale, int stride, uint16_t* q_rot);
+/* Kept: granite4::gpu_multi_rope, engine/src/forward_gpu_api.h:219-220,
+ * engine/src/forward_gpu.cu:380-407, :3898-3906. x [rows][heads d]; row r is
+ * rotated with table row d_rows->pos[r]. The descriptor's page tables are not
+ * read. rows <= 16, d even. */
+int granite4_gpu_multi_rope(const uint16_t* x, const float* cos_tbl, const float* sin_tbl,
+                            const granite4_multi_rows* d_rows, int rows, int heads, int d,
+                            uint16_t* out);
+/* Kept: granite4::gpu_multi_kv_append, engine/src/forward_gpu_api.h:227-229,
+ * engine/src/forward_gpu.cu:3915-3936. Appends K / V rows [rows][Hk d] as they
+ * are at pool row d_rows->pt[r][slot]: bits == 8 quantises to int8 + f32 scales,
+ * bits == 16 copies bf16 (scale pointers unused). Other formats return -1. */
+int granite4_gpu_multi_kv_append(const uint16_t* k, const uint16_t* v, int bits, void* cache_k,
+                                 void* cache_v, float* k_scale, float* v_scale,
+                                 const granite4_multi_rows* d_rows, int rows, int stride, int Hk,
+                                 int d);
+/* Kept: engine/src/forward_gpu.cu:796-821, :3814-3826. One position: every head
+ * of x [heads][d] is rotated with d_cos / d_sin, which point at that position's
+ * own [d/2] table row. d even, <= 256. */
+#define GRANITE4_MAX_HEAD_DIM 256
+int granite4_kernel_rope_at_pos(const uint16_t* d_x, const float* d_cos, const float* d_sin,
+                                int heads, int d, uint16_t* d_out);
+/* Kept: engine/src/forward_gpu.cu:824-854, :3828-3842. Row r of x [rows][heads d]
+ * is rotated with row r of the table pointers passed (the caller offsets them
+ * to the first position). rows <= 16. */
+int granite4_kernel_rope_at_pos_batched(const uint16_t* d_x, const float* d_cos,
+                                        const float* d_sin, int rows, int heads, int d,
+                                        uint16_t* d_out);
+/* Kept: engine/src/kernels_phase2.cu:381-400, :1087-1105. bf16 cache form of the
+ * batched append: K / V rows [rows][Hk d] copied to [Hk][stride][d] at pool row
+ * d_pt[base_pos + r] (NULL: base_pos + r). rows <= 16; d must be even here (the
+ * reference also takes odd d, which no RoPE model has). */
+int granite4_kernel_kv_append_batched(const uint16_t* d_src_k, const uint16_t* d_src_v,
+                                      uint16_t* d_cache_k, uint16_t* d_cache_v, int base_pos,
+                                      int rows, int stride, int Hk, int d, const int* d_pt);
+/* Kept: engine/src/forward_gpu.cu:3844-3874. Verify staging for a bf16 cache:
+ * RoPE(q) -> d_q_rot, RoPE(k) -> d_k_rot, then d_k_rot and raw v appended at pool
+ * rows d_pt[base_pos + r]. Row r uses row r of the table pointers passed. The
+ * reference issues three launches; this is one. rows <= 16. */
+int granite4_kernel_verify_qkv_stage(const uint16_t* d_q, const uint16_t* d_k, const uint16_t* d_v,
+                                     const float* d_cos, const float* d_sin, int base_pos, int rows,
+                                     int Hq, int Hk, int d, int cache_stride, uint16_t* d_q_rot,
+                                     uint16_t* d_k_rot, uint16_t* d_cache_k, uint16_t* d_cache_v,
+                                     const int* d_pt);
+/* Kept: granite4::prefill_rope_split_append, engine/src/prefill_gemm.h:48-52,
+ * engine/src/prefill_gemm.cu:306-347, :1310-1324. bf16 cache form of the prefill
+ * step: token-major qkv at positions base_pos + r; RoPE(q) -> q_rot, RoPE(k) and
+ * raw v into the [Hk][stride][d] bf16 caches at pool row d_pt[pos] (NULL: pos).
+ * Any even d; rows <= 65535. */
+int granite4_prefill_rope_split_append(const uint16_t* qkv, const float* cos_tbl,
+                                       const float* sin_tbl, int base_pos, int rows, int Hq, int Hk,
+                                       int d, int stride, uint16_t* q_rot, uint16_t* cache_k,
+                                       uint16_t* cache_v, const int* d_pt);
 /* Added: the prefill form with per-row positions and pool rows, for batches
  * whose rows are not one consecutive run of positions (several sequences,
  * offsets, permuted page tables). d_pos_rows[r] in [0, max_pos) indexes the

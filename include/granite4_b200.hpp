@@ -47,6 +47,18 @@ int gpu_multi_rope_append(const std::uint16_t* q, const std::uint16_t* k, const 
                           const float* cos_tbl, const float* sin_tbl, const GpuMultiRows* d_rows,
                           int rows, int Hq, int Hk, int d, int bits, void* cache_k, void* cache_v,
                           float* k_scale, float* v_scale, int stride, std::uint16_t* q_rot);
+// engine/src/forward_gpu_api.h:219-220
+int gpu_multi_rope(const std::uint16_t* x, const float* cos_tbl, const float* sin_tbl,
+                   const GpuMultiRows* d_rows, int rows, int heads, int d, std::uint16_t* out);
+// engine/src/forward_gpu_api.h:227-229
+int gpu_multi_kv_append(const std::uint16_t* k, const std::uint16_t* v, int bits, void* cache_k,
+                        void* cache_v, float* k_scale, float* v_scale, const GpuMultiRows* d_rows,
+                        int rows, int stride, int Hk, int d);
+// engine/src/prefill_gemm.h:48-52
+int prefill_rope_split_append(const std::uint16_t* qkv, const float* cos_tbl, const float* sin_tbl,
+                              int base_pos, int rows, int Hq, int Hk, int d, int stride,
+                              std::uint16_t* q_rot, std::uint16_t* cache_k, std::uint16_t* cache_v,
+                              const int* d_pt = nullptr);
 
 }  // namespace granite4
 

@@ -830,3 +830,226 @@ def test_rope_kv_plain_and_bulk_kernels_agree(K, port, monkeypatch):
             for got, w_ in zip((q_rot, ck, cv, ks, vs), want):
                 assert (host(got) == w_).all(), (mode, bulk)
     t.close()
+
+
+# =========================================================================== one-cluster forms
+@pytest.mark.parametrize("rows", [1, 2, 3, 8, 9, 16, 17])
+@pytest.mark.parametrize("f32", [False, True])
+def test_add_rmsnorm_cluster_and_two_sweep_forms_agree(K, port, rows, f32, monkeypatch):
+    """Up to 16 rows the op is one launch of one thread-block cluster (amax exchanged through
+    distributed shared memory); G4_CLUSTER=0 forces the memset + two-sweep form. Same bits either
+    way, and both equal the oracle. 17 rows is past the cluster limit and takes the two sweeps in
+    both settings."""
+    cols = 4096
+    yb = rand_bf16(700 + rows, (rows, cols), 2.0)
+    rb = rand_bf16(800 + rows, (rows, cols), 3.0)
+    w = rand_bf16(900, (cols,), 1.0)
+    if f32:
+        y = (yb.astype(np.uint32) << np.uint32(16)).view(np.float32) * np.float32(1.37)
+        res = (rb.astype(np.uint32) << np.uint32(16)).view(np.float32) * np.float32(0.91)
+    else:
+        y, res = yb, rb
+    hw, nw = port.add_rmsnorm(y, res, w, 1e-5, 0.22)
+    cw, sw, aw = port.quant_fp8(nw)
+    outs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("G4_CLUSTER", mode)
+        h, n = empty_bf16(rows, cols), empty_bf16(rows, cols)
+        c = torch.empty(rows, cols, dtype=torch.uint8, device=DEV)
+        sa = torch.full((2,), -1.0, dtype=torch.float32, device=DEV)
+        rstd = torch.zeros(rows, dtype=torch.float32, device=DEV)
+        assert K.add_rmsnorm_fp8(dev(y), dev(res), dev(w), 1e-5, 0.22, h, n, c, sa, rstd) == 0
+        assert (host(h) == hw).all() and (host(n) == nw).all() and (host(c) == cw).all(), mode
+        assert sa[1].item() == aw and sa[0].item() == sw
+        # FP8 codes alone (nothing else written)
+        c2 = torch.empty_like(c)
+        sa2 = torch.full((2,), -1.0, dtype=torch.float32, device=DEV)
+        assert K.add_rmsnorm_fp8(dev(y), dev(res), dev(w), 1e-5, 0.22, None, None, c2, sa2) == 0
+        assert torch.equal(c2, c) and torch.equal(sa2, sa)
+        outs[mode] = (h, n, c, sa, rstd)
+    for a, b in zip(outs["1"], outs["0"]):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("rows", [1, 2, 5, 16, 17])
+@pytest.mark.parametrize("layout", ["bf16", "bf16_fused", "f32_fused"])
+def test_swiglu_cluster_and_two_sweep_forms_agree(K, port, rows, layout, monkeypatch):
+    I = 12800
+    gub = rand_bf16(1000 + rows, (rows, 2 * I), 3.0)
+    if layout == "f32_fused":
+        gu = (gub.astype(np.uint32) << np.uint32(16)).view(np.float32) * np.float32(1.11)
+    else:
+        gu = gub
+    gud = dev(gu)
+    if layout == "bf16":
+        g, u, ld = gud[:, :I].contiguous(), gud[:, I:].contiguous(), None
+    else:
+        g, u, ld = gud[:, :I], gud[:, I:], 2 * I
+    outs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("G4_CLUSTER", mode)
+        act = empty_bf16(rows, I)
+        c = torch.empty(rows, I, dtype=torch.uint8, device=DEV)
+        sa = torch.full((2,), -1.0, dtype=torch.float32, device=DEV)
+        kw = {} if ld is None else {"ld": ld}
+        assert K.swiglu_fp8(g, u, act, c, sa, **kw) == 0
+        c2 = torch.empty_like(c)
+        sa2 = torch.full((2,), -1.0, dtype=torch.float32, device=DEV)
+        assert K.swiglu_fp8(g, u, None, c2, sa2, **kw) == 0
+        assert torch.equal(c2, c) and torch.equal(sa2, sa)
+        outs[mode] = (act, c, sa)
+    for a, b in zip(outs["1"], outs["0"]):
+        assert torch.equal(a, b)
+    got = host(outs["1"][0])
+    want = port.swiglu(gu[:, :I], gu[:, I:])
+    assert bf16_ulp_distance(got, want).max() <= 1
+    amax = port.amax_bf16(got)
+    assert outs["1"][2][1].item() == amax
+    assert (host(outs["1"][1]) == port.quant_fp8_with_scale(got, port.fp8_scale_from_amax(amax))).all()
+
+
+# =========================================================================== bf16-cache forms
+def _rope_heads(port, x, cos_rows, sin_rows, heads, d):
+    """Oracle RoPE of x [rows][heads * d] with one table row per token row."""
+    rows = x.shape[0]
+    c = np.ascontiguousarray(np.repeat(cos_rows, heads, axis=0))
+    s = np.ascontiguousarray(np.repeat(sin_rows, heads, axis=0))
+    return port.rope_rows(np.ascontiguousarray(x.reshape(rows * heads, d)), c, s).reshape(rows, heads * d)
+
+
+def _scatter_rows(src, kv_rows, Hk, d, stride):
+    """[rows][Hk * d] -> [Hk][stride][d] at the given pool rows (zeros elsewhere)."""
+    out = np.zeros((Hk, stride, d), np.uint16)
+    out[:, kv_rows, :] = src.reshape(-1, Hk, d).transpose(1, 0, 2)
+    return out
+
+
+@pytest.mark.parametrize("d", [128, 64, 6])
+def test_rope_at_pos_single_and_batched(K, port, d):
+    """granite4_kernel_rope_at_pos / _batched: the caller offsets the table pointers to the
+    position; d = 6 takes the element-wise kernel, the others the 128-bit one."""
+    heads, rows, max_pos, base = 5, 7, 512, 300
+    cos, sin = port.rope_tables(1e7, d, max_pos)
+    t = K.RopeTables(1e7, d, max_pos, DEV)
+    x = rand_bf16(1200 + d, (rows, heads * d), 2.0)
+    out = empty_bf16(rows, heads * d)
+    assert K.rope_at_pos_batched(dev(x), t.cos[base:], t.sin[base:], rows, heads, d, out) == 0
+    want = _rope_heads(port, x, cos[base:base + rows], sin[base:base + rows], heads, d)
+    assert (host(out) == want).all()
+    one = empty_bf16(1, heads * d)
+    assert K.rope_at_pos(dev(x[3:4]), t.cos[base + 3], t.sin[base + 3], heads, d, one) == 0
+    assert (host(one)[0] == want[3]).all()
+    assert K.rope_at_pos_batched(dev(x), t.cos, t.sin, 17, heads, d, out) == -1  # rows > 16
+    assert K.rope_at_pos(dev(x), t.cos, t.sin, heads, 7, one) == -1              # odd d
+    t.close()
+
+
+def test_kv_append_batched_bf16_and_verify_qkv_stage(K, port):
+    rows, stride, base, max_pos = 9, 64, 21, 128
+    cos, sin = port.rope_tables(1e7, D, max_pos)
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+    q = rand_bf16(1301, (rows, Hq * D), 2.0)
+    k = rand_bf16(1302, (rows, Hk * D), 2.0)
+    v = rand_bf16(1303, (rows, Hk * D), 2.0)
+    pt = np.random.default_rng(13).permutation(stride).astype(np.int32)
+    kv_rows = pt[base:base + rows]
+    # plain bf16 append, with and without a page table
+    for table, where in ((dev(pt), kv_rows), (None, np.arange(base, base + rows))):
+        ck, cv = torch.zeros(Hk, stride, D, dtype=torch.int16, device=DEV), torch.zeros(Hk, stride, D, dtype=torch.int16, device=DEV)
+        assert K.kv_append_batched(dev(k), dev(v), ck, cv, base, rows, stride, Hk, D, table) == 0
+        assert (host(ck) == _scatter_rows(k, where, Hk, D, stride)).all()
+        assert (host(cv) == _scatter_rows(v, where, Hk, D, stride)).all()
+    # verify staging: RoPE q, RoPE k (kept as k_rot too), append rotated k + raw v
+    q_rot, k_rot = empty_bf16(rows, Hq * D), empty_bf16(rows, Hk * D)
+    ck, cv = torch.zeros(Hk, stride, D, dtype=torch.int16, device=DEV), torch.zeros(Hk, stride, D, dtype=torch.int16, device=DEV)
+    assert K.verify_qkv_stage(dev(q), dev(k), dev(v), t.cos[base:], t.sin[base:], base, rows, Hq, Hk, D,
+                              stride, q_rot, k_rot, ck, cv, dev(pt)) == 0
+    want_q = _rope_heads(port, q, cos[base:base + rows], sin[base:base + rows], Hq, D)
+    want_k = _rope_heads(port, k, cos[base:base + rows], sin[base:base + rows], Hk, D)
+    assert (host(q_rot) == want_q).all() and (host(k_rot) == want_k).all()
+    assert (host(ck) == _scatter_rows(want_k, kv_rows, Hk, D, stride)).all()
+    assert (host(cv) == _scatter_rows(v, kv_rows, Hk, D, stride)).all()
+    # the reference's argument checks: stride must cover the last position, Hq a multiple of Hk
+    assert K.verify_qkv_stage(dev(q), dev(k), dev(v), t.cos, t.sin, base, rows, Hq, Hk, D, base + rows - 1,
+                              q_rot, k_rot, ck, cv, None) == -1
+    assert K.verify_qkv_stage(dev(q), dev(k), dev(v), t.cos, t.sin, base, rows, 31, Hk, D, stride,
+                              q_rot, k_rot, ck, cv, None) == -1
+    t.close()
+
+
+@pytest.mark.parametrize("d,hq,hk", [(128, 32, 8), (72, 4, 2)])
+def test_prefill_rope_split_append_bf16_cache(K, port, d, hq, hk):
+    rows, base, stride, max_pos = 300, 17, 512, 400
+    cos, sin = port.rope_tables(1e7, d, max_pos)
+    t = K.RopeTables(1e7, d, max_pos, DEV)
+    qkv = rand_bf16(1400 + d, (rows, (hq + 2 * hk) * d), 2.0)
+    pt = np.random.default_rng(14).permutation(stride).astype(np.int32)
+    q_rot = empty_bf16(rows, hq * d)
+    ck, cv = torch.zeros(hk, stride, d, dtype=torch.int16, device=DEV), torch.zeros(hk, stride, d, dtype=torch.int16, device=DEV)
+    assert K.prefill_rope_split_append(dev(qkv), t.cos, t.sin, base, rows, hq, hk, d, stride, q_rot, ck,
+                                       cv, dev(pt)) == 0
+    c, s = cos[base:base + rows], sin[base:base + rows]
+    want_q = _rope_heads(port, np.ascontiguousarray(qkv[:, :hq * d]), c, s, hq, d)
+    want_k = _rope_heads(port, np.ascontiguousarray(qkv[:, hq * d:(hq + hk) * d]), c, s, hk, d)
+    kv_rows = pt[base:base + rows]
+    assert (host(q_rot) == want_q).all()
+    assert (host(ck) == _scatter_rows(want_k, kv_rows, hk, d, stride)).all()
+    assert (host(cv) == _scatter_rows(np.ascontiguousarray(qkv[:, (hq + hk) * d:]), kv_rows, hk, d, stride)).all()
+    assert K.prefill_rope_split_append(dev(qkv), t.cos, t.sin, base, rows, hq, hk, d, base + rows - 1, q_rot,
+                                       ck, cv, None) == -1
+    t.close()
+
+
+@pytest.mark.parametrize("d", [128, 64])
+def test_gpu_multi_rope_and_kv_append_descriptor_forms(K, port, d):
+    """gpu_multi_rope, gpu_multi_kv_append (int8 and bf16) and the bf16 form of
+    gpu_multi_rope_append over one device row descriptor with tree slots."""
+    from granite4_b200 import capi
+    rows, stride, max_pos, hq, hk = 6, 80, 1024, 8, 2
+    cos, sin = port.rope_tables(1e7, d, max_pos)
+    t = K.RopeTables(1e7, d, max_pos, DEV)
+    q = rand_bf16(1501, (rows, hq * d), 2.0)
+    k = rand_bf16(1502, (rows, hk * d), 2.0)
+    v = rand_bf16(1503, (rows, hk * d), 2.0)
+    pos = np.array([5, 1000, 33, 0, 512, 77], np.int32)
+    table = np.random.default_rng(15).permutation(stride).astype(np.int32)
+    d_table = dev(np.ascontiguousarray(table[np.arange(max_pos) % stride]))
+    desc = capi.MultiRows()
+    desc.n, desc.tree = rows, 1
+    for r in range(rows):
+        desc.pos[r] = int(pos[r])
+        desc.slot[r] = 10 + r
+        desc.pt[r] = d_table.data_ptr()
+    kv_rows = table[(10 + np.arange(rows)) % stride]
+    d_rows = K.multi_rows_to_device(desc, DEV)
+    # RoPE only: positions from the descriptor; page tables untouched
+    out = empty_bf16(rows, hq * d)
+    assert K.gpu_multi_rope(dev(q), t.cos, t.sin, d_rows, rows, hq, d, out) == 0
+    want_q = _rope_heads(port, q, cos[pos], sin[pos], hq, d)
+    assert (host(out) == want_q).all()
+    # int8 append of K / V as they are
+    ck = torch.zeros(hk, stride, d, dtype=torch.int8, device=DEV)
+    cv = torch.zeros_like(ck)
+    ks = torch.zeros(hk, stride, dtype=torch.float32, device=DEV)
+    vs = torch.zeros_like(ks)
+    assert K.gpu_multi_kv_append(dev(k), dev(v), 8, ck, cv, ks, vs, d_rows, rows, stride, hk, d) == 0
+    want = port.kv_append_int8(k, v, kv_rows, hk, d, stride)
+    for got, w_ in zip((ck, cv, ks, vs), want):
+        assert (host(got) == w_).all()
+    # bf16 append
+    bk = torch.zeros(hk, stride, d, dtype=torch.int16, device=DEV)
+    bv = torch.zeros_like(bk)
+    assert K.gpu_multi_kv_append(dev(k), dev(v), 16, bk, bv, None, None, d_rows, rows, stride, hk, d) == 0
+    assert (host(bk) == _scatter_rows(k, kv_rows, hk, d, stride)).all()
+    assert (host(bv) == _scatter_rows(v, kv_rows, hk, d, stride)).all()
+    assert K.gpu_multi_kv_append(dev(k), dev(v), 4, bk, bv, None, None, d_rows, rows, stride, hk, d) == -1
+    # fused RoPE + bf16 append
+    bk2, bv2 = torch.zeros_like(bk), torch.zeros_like(bk)
+    q_rot = empty_bf16(rows, hq * d)
+    assert K.gpu_multi_rope_append(dev(q), dev(k), dev(v), t.cos, t.sin, d_rows, rows, hq, hk, d, 16, bk2,
+                                   bv2, None, None, stride, q_rot) == 0
+    want_k = _rope_heads(port, k, cos[pos], sin[pos], hk, d)
+    assert (host(q_rot) == want_q).all()
+    assert (host(bk2) == _scatter_rows(want_k, kv_rows, hk, d, stride)).all()
+    assert torch.equal(bv2, bv)
+    t.close()
