@@ -228,6 +228,9 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL's own log lines (its version banner among them) go to stdout unless told otherwise;
+        # stdout is reserved for the one JSON line.
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
     shapes = glue.GraniteShapes()
     lo, hi = shard_bounds(TOTAL_TOKENS, world, rank)
@@ -317,6 +320,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                          "share": sum(dur) / (ms_ops if ms_ops > 0 else 1.0),
                          "achieved_gbs": per_row * rows / (mean_ms * 1e-3) / 1e9,
                          "frac": per_row * rows / (mean_ms * 1e-3) / 1e9 / peak,
+                         "frac_of_nominal_8000": per_row * rows / (mean_ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
                          "bytes_per_row": per_row}
         dominant = max(ops, key=lambda k: ops[k]["share"])
         tokens_per_s = total_tokens * args.steps / (ms_max * 1e-3)
@@ -344,6 +348,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "ops": ops,
             "embed": extras["embed"],
             "small_shapes": extras["small"],
+            "argmax": extras["argmax"],
             "clocks": clocks,
             "gpu_launches": launches,
             "device_status": status,
@@ -362,6 +367,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         dist.barrier()
         dist.destroy_process_group()
 
+
+NOMINAL_HBM_GBS = 8000.0  # the data-sheet figure the reference's target is stated against
 
 # DRAM bytes per token row each op really moves (both sweeps of the FP8 ops), from the ncu
 # captures summarised under profiles/: the second sweep re-reads the bf16 intermediate.
@@ -398,10 +405,32 @@ def small_shapes_and_embed(seq, rows, device, stream):
     us = timed(lambda: k.embed_gather(ids, table, s.embedding_multiplier, out), 10)
     bpr = glue.bytes_per_row(s)["embed"]
     embed = {"rows": rows, "mean_us": us, "achieved_gbs": bpr * rows / (us * 1e-6) / 1e9,
-             "frac": bpr * rows / (us * 1e-6) / 1e9 / peak, "bytes_per_row": bpr}
+             "frac": bpr * rows / (us * 1e-6) / 1e9 / peak,
+             "frac_of_nominal_8000": bpr * rows / (us * 1e-6) / 1e9 / NOMINAL_HBM_GBS, "bytes_per_row": bpr}
+
+    def graph_replay_us(fn, iters=100):
+        """fn captured once into a CUDA graph on a side stream, then replayed (every launcher is
+        capturable: no allocation, no synchronisation, positions read from device memory)."""
+        side = torch.cuda.Stream(device)
+        with torch.cuda.stream(side):
+            fn()
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+            for _ in range(3):
+                graph.replay()
+            side.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side)
+            for _ in range(iters):
+                graph.replay()
+            b.record(side)
+            side.synchronize()
+            return a.elapsed_time(b) / iters * 1e3
 
     small = {}
-    for n in (1, 8, 500):
+    for n in (1, 2, 4, 8, 500):
         sq = glue.GlueSequence(n, s, device=device, seed=7, sets=1, layers=1, pool_rows=8192, max_pos=8192)
         pos = torch.randint(0, 8192, (n,), generator=g, device=device, dtype=torch.int32)
         sq.set_rows(pos, torch.randperm(8192, generator=g, device=device)[:n].to(torch.int32))
@@ -416,34 +445,32 @@ def small_shapes_and_embed(seq, rows, device, stream):
             for _, thunk in sq.layer_ops(0):
                 thunk()
         entry = {"chain_eager_us": timed(chain, 50)}
-        # the same chain replayed from a CUDA graph (every launcher is capturable: no allocation,
-        # no synchronisation, positions read from device memory)
-        side = torch.cuda.Stream(device)
-        with torch.cuda.stream(side):
-            chain()
-            side.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                chain()
-            for _ in range(3):
-                graph.replay()
-            side.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(side)
-            for _ in range(100):
-                graph.replay()
-            b.record(side)
-            side.synchronize()
-            entry["chain_graph_us"] = a.elapsed_time(b) / 100 * 1e3
+        entry["chain_graph_us"] = graph_replay_us(chain)
         if n == 1:  # config 1: f32 x and residual, bf16 + FP8 out
-            entry["add_rmsnorm_f32_fp8_us"] = timed(
-                lambda: k.add_rmsnorm_fp8(f32y, f32r, sq.w[0, 0], s.eps, s.residual_multiplier, hb, nb,
-                                          sq.n_fp8, sq.scales[0, 0]), 50)
+            def c1():
+                k.add_rmsnorm_fp8(f32y, f32r, sq.w[0, 0], s.eps, s.residual_multiplier, hb, nb, sq.n_fp8,
+                                  sq.scales[0, 0])
+            entry["add_rmsnorm_f32_fp8_us"] = timed(c1, 50)
+            entry["add_rmsnorm_f32_fp8_graph_us"] = graph_replay_us(c1)
         small[f"rows_{n}"] = entry
         del sq
     del table
     torch.cuda.empty_cache()
-    return {"embed": embed, "small": small}
+
+    # Greedy pick over the logits (the decode step's last glue op; 2 V bytes read per row): a
+    # prefill-size batch against the bandwidth roofline, decode sizes as latencies.
+    a_rows = min(rows, 8192)
+    logits = torch.randn(a_rows, s.vocab, generator=g, device=device).to(torch.bfloat16)
+    picked = torch.empty(a_rows, dtype=torch.int32, device=device)
+    us = timed(lambda: k.argmax_rows(logits, picked), 10)
+    a_bytes = (2 * s.vocab + 4) * a_rows
+    argmax = {"rows": a_rows, "mean_us": us, "achieved_gbs": a_bytes / (us * 1e-6) / 1e9,
+              "frac": a_bytes / (us * 1e-6) / 1e9 / peak, "bytes_per_row": 2 * s.vocab + 4}
+    for n in (1, 8):
+        argmax[f"rows_{n}_graph_us"] = graph_replay_us(lambda: k.argmax_rows(logits[:n], picked[:n]))
+    del logits
+    torch.cuda.empty_cache()
+    return {"embed": embed, "small": small, "argmax": argmax}
 
 
 def run_e2e(seq, rows, device, steps):

@@ -255,6 +255,31 @@ def rope_kv_int8_paged(qkv, cos_tbl, sin_tbl, pos_rows, kv_rows, Hq, Hk, d, stri
         _p(k_scale, torch.float32), _p(v_scale, torch.float32))
 
 
+# ---- decode-step glue -----------------------------------------------------------------------
+def argmax_rows(logits, out, d_pos=None, vocab_map=None):
+    """granite4_kernel_argmax_rows: first index of each row's maximum of bf16 logits [rows][V]."""
+    lib = _enter(logits)
+    rows, V = logits.shape
+    return lib.granite4_kernel_argmax_rows(_p(logits, *_BF16_OK), rows, V, _p(out, torch.int32),
+                                           _p(d_pos, torch.int32), _p(vocab_map, torch.int32))
+
+
+def multi_scatter_advance(d_rows, ids):
+    """granite4_kernel_multi_scatter_advance: d_rows is the uint8 tensor holding a MultiRows."""
+    lib = _enter(ids)
+    return lib.granite4_kernel_multi_scatter_advance(_p(d_rows), _p(ids, torch.int32))
+
+
+def kv_move(src_rows, dst_rows, bits, cache_k, cache_v, k_scale, v_scale, layers, Hk, stride, d):
+    """granite4_kernel_kv_move: src_rows / dst_rows are host sequences of physical pool rows."""
+    lib = _enter(cache_k)
+    n = len(src_rows)
+    arr = C.c_int * max(n, 1)
+    return lib.granite4_kernel_kv_move(arr(*src_rows), arr(*dst_rows), n, bits, _p(cache_k), _p(cache_v),
+                                       _p(k_scale, torch.float32), _p(v_scale, torch.float32), layers,
+                                       Hk, stride, d)
+
+
 # ---- a4 -----------------------------------------------------------------------------------
 def prefill_silu_mul(gu, I, rows, act):
     """engine/src/prefill_gemm.h:105: gu float32 [rows][2 I] -> act bf16 [rows][I]."""

@@ -278,6 +278,32 @@ int granite4_kernel_rope_kv_int8_paged(const uint16_t* d_qkv, const float* d_cos
                                        float* d_k_scale, float* d_v_scale);
 
 /* ------------------------------------------------------------------------ */
+/* Decode-step glue around the path: greedy pick, token chaining, KV moves   */
+/* ------------------------------------------------------------------------ */
+/* Added (the reference keeps these kernels private to its forward pass:
+ * argmax_rows_kernel engine/src/forward_gpu.cu:280-333, argmax_map_kernel
+ * engine/src/eagle_gpu.cu:155-178). d_out[r] = first index of the maximum of
+ * bf16 logits row r ([rows][V]); NaN never wins, a row with nothing above -inf
+ * gives 0. d_vocab_map (optional): the id written is d_vocab_map[index]. d_pos
+ * (optional, rows must be 1): the id goes to d_out[*d_pos + 1] and *d_pos is
+ * advanced, which chains captured decode steps on the device. */
+int granite4_kernel_argmax_rows(const uint16_t* d_logits, int rows, int V, int32_t* d_out,
+                                int* d_pos, const int32_t* d_vocab_map);
+/* Added (multi_scatter_advance_kernel, engine/src/forward_gpu.cu:758-764): for
+ * r < d_rows->n: d_rows->tok[r][pos[r] + 1] = d_ids[r]; pos[r] += 1. */
+int granite4_kernel_multi_scatter_advance(granite4_multi_rows* d_rows, const int32_t* d_ids);
+/* Added (kv_move_kernel / gpu_ctx_kv_move, engine/src/forward_gpu.cu:3473-3536):
+ * copy KV rows src_rows[i] -> dst_rows[i], i in order, in every layer and kv
+ * head of a [layers][Hk][stride][d] pool (int8 codes + [layers][Hk][stride]
+ * scales for bits == 8, bf16 for bits == 16). src_rows / dst_rows are HOST
+ * arrays of n <= 8 physical pool rows (the caller maps logical positions
+ * through its row table, as gpu_ctx_kv_move does). A later move must not read a
+ * row an earlier one overwrites (-1). One launch for all layers. */
+int granite4_kernel_kv_move(const int* src_rows, const int* dst_rows, int n, int bits,
+                            void* d_cache_k, void* d_cache_v, float* d_k_scale, float* d_v_scale,
+                            int layers, int Hk, int stride, int d);
+
+/* ------------------------------------------------------------------------ */
 /* a4. SwiGLU, bf16 and FP8 outputs                                          */
 /* ------------------------------------------------------------------------ */
 /* Kept: granite4::prefill_silu_mul, engine/src/prefill_gemm.h:105,

@@ -294,3 +294,19 @@ void g4o_swiglu(const void* gate, const void* up, int in_is_f32, long ld, long r
       act[(size_t)r * I + i] = g4o_f32_to_bf16(sg * u);
     }
 }
+
+void g4o_argmax_rows(const uint16_t* logits, long rows, int V, int32_t* out) {
+  for (long r = 0; r < rows; ++r) {
+    const uint16_t* p = logits + (size_t)r * V;
+    int best = 0;
+    float bv = g4o_bf16_to_f32(p[0]);
+    for (int i = 1; i < V; ++i) {
+      const float v = g4o_bf16_to_f32(p[i]);
+      if (v > bv) {
+        bv = v;
+        best = i;
+      }
+    }
+    out[r] = best;
+  }
+}

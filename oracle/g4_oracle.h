@@ -109,6 +109,12 @@ void g4o_kv_append_int8(const uint16_t* src_k, const uint16_t* src_v, const int3
 void g4o_swiglu(const void* gate, const void* up, int in_is_f32, long ld, long rows, int I,
                 uint16_t* act);
 
+/* Greedy pick: out[r] = first index of the maximum of bf16 logits row r
+ * (engine/src/kernel_math.h:592-601 sample_greedy_f32: strict > keeps the first
+ * maximum). Rows without NaN only: the host rule starts from element 0 whatever
+ * it is, the device kernel (engine/src/forward_gpu.cu:284-333) skips NaN. */
+void g4o_argmax_rows(const uint16_t* logits, long rows, int V, int32_t* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -67,6 +67,7 @@ class Oracle:
         f("kv_append_int8", None, [_P, _P, _P, C.c_long, C.c_int, C.c_int, C.c_long, _P, _P, _P,
                                    _P])
         f("swiglu", None, [_P, _P, C.c_int, C.c_long, C.c_long, C.c_int, _P])
+        f("argmax_rows", None, [_P, C.c_long, C.c_int, _P])
 
     def _fn(self, name, res, args):
         fn = getattr(self._lib, self._p + name)
@@ -192,6 +193,13 @@ class Oracle:
         self._c_swiglu(C.c_void_p(gate.ctypes.data), C.c_void_p(up.ctypes.data),
                        int(gate.dtype == np.float32), ld, rows, I, _ptr(act))
         return act
+
+    def argmax_rows(self, logits):
+        """bf16 logits [rows][V] (no NaN) -> int32 [rows], first index of each row's maximum."""
+        rows, V = logits.shape
+        out = np.empty(rows, np.int32)
+        self._c_argmax_rows(_ptr(np.ascontiguousarray(logits)), rows, V, _ptr(out))
+        return out
 
     # ---- the whole per-layer glue sequence over a slice of rows, for timing ---------
     def layer_glue(self, y_attn, y_mlp, res, w1, w2, qkv, gate, up, cos_tbl, sin_tbl, pos_rows,

@@ -190,4 +190,12 @@ void g4ref_swiglu(const void* gate, const void* up, int in_is_f32, long ld, long
     }
 }
 
+void g4ref_argmax_rows(const std::uint16_t* logits, long rows, int V, std::int32_t* out) {
+  std::vector<float> f(V);
+  for (long r = 0; r < rows; ++r) {
+    for (int i = 0; i < V; ++i) f[i] = bf16_to_f32_host(logits[static_cast<std::size_t>(r) * V + i]);
+    out[r] = sample_greedy_f32(f.data(), V);
+  }
+}
+
 }  // extern "C"

@@ -1053,3 +1053,102 @@ def test_gpu_multi_rope_and_kv_append_descriptor_forms(K, port, d):
     assert (host(bk2) == _scatter_rows(want_k, kv_rows, hk, d, stride)).all()
     assert torch.equal(bv2, bv)
     t.close()
+
+
+# =========================================================================== decode-step glue
+@pytest.mark.parametrize("rows,V", [(1, 100352), (5, 100352), (16, 100352), (40, 100352), (3, 1000),
+                                    (4, 4099), (2, 8192)])
+@pytest.mark.parametrize("cluster", ["1", "0"])
+def test_argmax_rows_matches_oracle(K, port, rows, V, cluster, monkeypatch):
+    """Greedy pick, bit-exact index: up to 16 rows of a wide vocabulary run as one cluster per row
+    (several SMs read one row), otherwise one CTA per row; V = 4099 takes the element-wise kernel.
+    Every row holds its maximum at least twice, so the first-index rule is exercised."""
+    monkeypatch.setenv("G4_CLUSTER", cluster)
+    rng = np.random.default_rng(rows * 7 + V)
+    logits = rand_bf16(1600 + rows + V, (rows, V), 3.0)
+    for r in range(rows):
+        a, b = sorted(rng.choice(V, 2, replace=False).tolist())
+        logits[r, a] = logits[r, b] = port.f32_to_bf16(40.0 + r)
+    out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    assert K.argmax_rows(dev(logits), out) == 0
+    want = port.argmax_rows(logits)
+    assert (out.cpu().numpy() == want).all()
+
+
+def test_argmax_special_values_map_and_chaining(K, port):
+    V = 100352
+    ninf, nan, pz, nz = 0xFF80, 0x7FC0, 0x0000, 0x8000
+    logits = np.full((4, V), ninf, np.uint16)
+    logits[0, 5] = nan                      # nothing above -inf: 0 (NaN never wins)
+    logits[1, 70000] = nz
+    logits[1, 90000] = pz                   # -0 == +0: the first of them
+    logits[2, 99999] = port.f32_to_bf16(-3.0)
+    logits[2, 100351] = port.f32_to_bf16(-3.0)
+    logits[3, :] = nan
+    logits[3, 12345] = port.f32_to_bf16(-1e30)
+    out = torch.full((4,), -1, dtype=torch.int32, device=DEV)
+    assert K.argmax_rows(dev(logits), out) == 0
+    assert out.cpu().tolist() == [0, 70000, 99999, 12345]
+    # vocabulary map (the draft head's reduced vocabulary)
+    vmap = torch.arange(V, dtype=torch.int32, device=DEV) * 2 + 1
+    assert K.argmax_rows(dev(logits), out, vocab_map=vmap) == 0
+    assert out.cpu().tolist() == [1, 140001, 199999, 24691]
+    # device-side chaining: the id lands at tokens[pos + 1] and pos advances
+    tokens = torch.zeros(16, dtype=torch.int32, device=DEV)
+    d_pos = torch.tensor([3], dtype=torch.int32, device=DEV)
+    row = dev(logits[2:3])
+    assert K.argmax_rows(row, tokens, d_pos=d_pos) == 0
+    assert K.argmax_rows(row, tokens, d_pos=d_pos) == 0
+    assert d_pos.item() == 5 and tokens.cpu().tolist()[3:7] == [0, 99999, 99999, 0]
+    assert K.argmax_rows(dev(logits), out, d_pos=d_pos) == -1  # chaining is a one-row form
+
+
+def test_multi_scatter_advance(K):
+    from granite4_b200 import capi
+    n = 5
+    bufs = [torch.zeros(32, dtype=torch.int32, device=DEV) for _ in range(n)]
+    desc = capi.MultiRows()
+    desc.n = n
+    for r in range(n):
+        desc.pos[r] = 3 * r
+        desc.tok[r] = bufs[r].data_ptr()
+    d_rows = K.multi_rows_to_device(desc, DEV)
+    ids = torch.arange(100, 100 + n, dtype=torch.int32, device=DEV)
+    assert K.multi_scatter_advance(d_rows, ids) == 0
+    assert K.multi_scatter_advance(d_rows, ids + 10) == 0
+    back = capi.MultiRows.from_buffer_copy(bytes(d_rows.cpu().numpy().tobytes()))
+    for r in range(n):
+        assert back.pos[r] == 3 * r + 2
+        got = bufs[r].cpu().tolist()
+        assert got[3 * r + 1] == 100 + r and got[3 * r + 2] == 110 + r and sum(got) == 210 + 2 * r
+
+
+@pytest.mark.parametrize("bits", [8, 16])
+def test_kv_move_all_layers_in_order(K, bits):
+    """Accepted-path moves: rows src[i] -> dst[i] in order, in every layer and kv head, codes and
+    scales together (engine/src/forward_gpu.cu:3473-3536)."""
+    layers, hk, stride, d = 3, 8, 64, 128
+    g = torch.Generator(device=DEV).manual_seed(bits)
+    if bits == 8:
+        ck = torch.randint(-127, 128, (layers, hk, stride, d), generator=g, device=DEV, dtype=torch.int8)
+        cv = torch.randint(-127, 128, (layers, hk, stride, d), generator=g, device=DEV, dtype=torch.int8)
+        ks = torch.rand(layers, hk, stride, generator=g, device=DEV)
+        vs = torch.rand(layers, hk, stride, generator=g, device=DEV)
+    else:
+        ck = torch.randint(-30000, 30000, (layers, hk, stride, d), generator=g, device=DEV, dtype=torch.int16)
+        cv = torch.randint(-30000, 30000, (layers, hk, stride, d), generator=g, device=DEV, dtype=torch.int16)
+        ks = vs = None
+    src, dst = [20, 23, 27, 40], [17, 18, 19, 20]   # the last move overwrites a row an earlier one read
+    want = [t.clone() if t is not None else None for t in (ck, cv, ks, vs)]
+    for s_, d_ in zip(src, dst):
+        for t in want:
+            if t is not None:
+                t[:, :, d_] = t[:, :, s_]
+    assert K.kv_move(src, dst, bits, ck, cv, ks, vs, layers, hk, stride, d) == 0
+    for got, w_ in zip((ck, cv, ks, vs), want):
+        if got is not None:
+            assert torch.equal(got, w_)
+    assert K.kv_move([], [], bits, ck, cv, ks, vs, layers, hk, stride, d) == 0          # nothing to do
+    assert K.kv_move([5, 9], [9, 3], bits, ck, cv, ks, vs, layers, hk, stride, d) == -1  # reads an overwritten row
+    assert K.kv_move([64], [3], bits, ck, cv, ks, vs, layers, hk, stride, d) == -1       # outside the pool
+    assert K.kv_move(list(range(9)), list(range(9)), bits, ck, cv, ks, vs, layers, hk, stride, d) == -1

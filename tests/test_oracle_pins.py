@@ -278,3 +278,19 @@ def test_port_matches_reference_fp8_doubles(port, ref):
     v = rng.standard_normal(40000) * np.exp2(rng.integers(-14, 10, 40000))
     for x in v:
         assert port.fp8_encode(x) == ref.fp8_encode(x)
+
+
+def test_greedy_pick_known_answers_and_reference(port, ref):
+    # engine/tests/test_kernel_math.cc:683-688 (values rounded to bf16 keep their order)
+    def bits(vals):
+        return np.array([[port.f32_to_bf16(v) for v in vals]], np.uint16)
+    assert port.argmax_rows(bits([0.1, 0.6, 0.2, 0.1]))[0] == 1
+    assert port.argmax_rows(bits([0.5, 0.5]))[0] == 0          # tie -> smallest id
+    assert port.argmax_rows(bits([-0.0, 0.0, -1.0]))[0] == 0   # +0 is not above -0
+    rng = np.random.default_rng(77)
+    logits = (rng.standard_normal((64, 1000)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    logits[:, 500:] = logits[:, :500]  # every maximum appears twice: the first must win
+    got = port.argmax_rows(logits)
+    assert (got < 500).all()
+    if ref is not None:
+        assert (got == ref.argmax_rows(logits)).all()
