@@ -123,7 +123,9 @@ int granite4_kernel_rmsnorm_batched(const uint16_t* d_x, const uint16_t* d_w, fl
  * streaming pass over h instead of a second reduction per row.
  * cols must be a multiple of 8, at most 32768, and every row 16-byte aligned.
  * With d_n_fp8 this enqueues a 8-byte memset and two kernels (the scale depends
- * on every row, so the codes are written by a second sweep). */
+ * on every row, so the codes are written by a second sweep); with at most 16
+ * rows and cols <= 8192 it is a single launch of one thread-block cluster that
+ * keeps the rows in registers (same bits). */
 int granite4_kernel_add_rmsnorm_fp8(const void* d_y, int y_is_f32, const void* d_res,
                                     int res_is_f32, const uint16_t* d_w, float eps,
                                     float resid_mult, int rows, int cols, uint16_t* d_h_out,

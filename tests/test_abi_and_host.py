@@ -55,11 +55,14 @@ def test_cpp_entry_points_keep_the_reference_mangled_names(g4):
     for sym in ("_ZN8granite418prefill_embed_rowsEPKiiiPKtfPti",
                 "_ZN8granite430prefill_rope_split_append_int8EPKtPKfS3_iiiiiiPtPaS5_PfS6_PKi",
                 "_ZN8granite416prefill_silu_mulEPKfiiPt",
-                "_ZN8granite421gpu_multi_rope_appendEPKtS1_S1_PKfS3_PKNS_12GpuMultiRowsEiiiiiPvS7_PfS8_iPt"):
+                "_ZN8granite421gpu_multi_rope_appendEPKtS1_S1_PKfS3_PKNS_12GpuMultiRowsEiiiiiPvS7_PfS8_iPt",
+                "_ZN8granite414gpu_multi_ropeEPKtPKfS3_PKNS_12GpuMultiRowsEiiiPt",
+                "_ZN8granite419gpu_multi_kv_appendEPKtS1_iPvS2_PfS3_PKNS_12GpuMultiRowsEiiii",
+                "_ZN8granite425prefill_rope_split_appendEPKtPKfS3_iiiiiiPtS4_S4_PKi"):
         assert sym in out
     hpp = open(HEADER_CPP).read()
     for fn in ("prefill_embed_rows", "prefill_rope_split_append_int8", "prefill_silu_mul",
-               "gpu_multi_rope_append"):
+               "gpu_multi_rope_append", "gpu_multi_rope(", "gpu_multi_kv_append", "prefill_rope_split_append("):
         assert fn in hpp
 
 
