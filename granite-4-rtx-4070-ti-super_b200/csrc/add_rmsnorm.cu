@@ -84,6 +84,7 @@ constexpr int max_threads_for(int V) { return V == 1 ? 1024 : (V == 4 ? 256 : 51
 template <bool Y_F32, bool RES_F32, int V, int PHASE>
 __global__ void __launch_bounds__(max_threads_for(V))
     add_rmsnorm_kernel(const NormParams p) {
+  pdl_begin();
   const int T = blockDim.x;
   const int t = threadIdx.x;
   // A cluster is a power of two wide: its spare CTAs redo the last row without storing anything,
@@ -224,6 +225,7 @@ __global__ void __launch_bounds__(max_threads_for(V))
 // tests, the input-type switches and the unused outputs compiled away.
 template <bool HAS_RES, bool WANT_AMAX>
 __global__ void __launch_bounds__(256) add_rmsnorm_fast_kernel(const NormParams p) {
+  pdl_begin();
   constexpr int V = 4;
   const int T = blockDim.x;
   const int t = threadIdx.x;
@@ -313,6 +315,7 @@ constexpr int kEncodeMaxIter = 2;  // cols8 <= 512 per pass of the unrolled body
 // left in the loop bodies.
 template <bool FULL>
 __global__ void __launch_bounds__(kEncodeThreads) norm_encode_kernel(const NormParams p) {
+  pdl_begin();
   const int t = threadIdx.x;
   const int tiles = (p.rows + kRowsPerCta - 1) / kRowsPerCta;
   const int tile = p.reverse ? tiles - 1 - static_cast<int>(blockIdx.x) : blockIdx.x;
@@ -387,6 +390,7 @@ __global__ void __launch_bounds__(256)
 // Elementwise per-tensor FP8 of a bf16 tensor: amax sweep, then encode sweep.
 constexpr int kQuantUnroll = 4;
 __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* x, long long n8, float* scale_amax) {
+  pdl_begin();
   uint32_t amax = 0u;
   const long long base = static_cast<long long>(blockIdx.x) * (256 * kQuantUnroll) + threadIdx.x;
   uint4 v[kQuantUnroll];
@@ -410,6 +414,7 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* x, long lon
 
 __global__ void __launch_bounds__(256)
     encode_bf16_kernel(const uint4* x, long long n8, uint2* codes, float* scale_amax) {
+  pdl_begin();
   const Fp8Scale fs = fp8_scale_from_amax(__ldcg(scale_amax + 1));
   if (blockIdx.x == 0 && threadIdx.x == 0) scale_amax[0] = fs.scale;
   // last element first: the tail of the tensor is what the amax sweep left in L2
@@ -447,26 +452,26 @@ int pick_v(int cols8) {
 constexpr int kMaxVectorCols = 8 * 8 * max_threads_for(8);  // 32768
 
 template <bool Y_F32, bool RES_F32, int PHASE>
-void launch_v(const NormParams& p, int V, int threads, cudaStream_t st) {
+cudaError_t launch_v(const NormParams& p, int V, int threads, cudaStream_t st) {
+  const dim3 grid(static_cast<unsigned>(p.rows)), block(static_cast<unsigned>(threads));
   switch (V) {
-    case 1: add_rmsnorm_kernel<Y_F32, RES_F32, 1, PHASE><<<p.rows, threads, 0, st>>>(p); break;
-    case 2: add_rmsnorm_kernel<Y_F32, RES_F32, 2, PHASE><<<p.rows, threads, 0, st>>>(p); break;
-    case 4: add_rmsnorm_kernel<Y_F32, RES_F32, 4, PHASE><<<p.rows, threads, 0, st>>>(p); break;
-    default: add_rmsnorm_kernel<Y_F32, RES_F32, 8, PHASE><<<p.rows, threads, 0, st>>>(p); break;
+    case 1: return launch_pdl(add_rmsnorm_kernel<Y_F32, RES_F32, 1, PHASE>, grid, block, 0, st, p);
+    case 2: return launch_pdl(add_rmsnorm_kernel<Y_F32, RES_F32, 2, PHASE>, grid, block, 0, st, p);
+    case 4: return launch_pdl(add_rmsnorm_kernel<Y_F32, RES_F32, 4, PHASE>, grid, block, 0, st, p);
+    default: return launch_pdl(add_rmsnorm_kernel<Y_F32, RES_F32, 8, PHASE>, grid, block, 0, st, p);
   }
 }
 
 template <int PHASE>
-void launch_phase(const NormParams& p, bool y_f32, bool res_f32, cudaStream_t st) {
+cudaError_t launch_phase(const NormParams& p, bool y_f32, bool res_f32, cudaStream_t st) {
   const int V = pick_v(p.cols8);
   const int threads = ((p.cols8 + V - 1) / V + 31) / 32 * 32;
   if (y_f32) {
-    if (res_f32) launch_v<true, true, PHASE>(p, V, threads, st);
-    else launch_v<true, false, PHASE>(p, V, threads, st);
-  } else {
-    if (res_f32) launch_v<false, true, PHASE>(p, V, threads, st);
-    else launch_v<false, false, PHASE>(p, V, threads, st);
+    if (res_f32) return launch_v<true, true, PHASE>(p, V, threads, st);
+    return launch_v<true, false, PHASE>(p, V, threads, st);
   }
+  if (res_f32) return launch_v<false, true, PHASE>(p, V, threads, st);
+  return launch_v<false, false, PHASE>(p, V, threads, st);
 }
 
 long long quant_grid(long long n8) { return (n8 + 256 * kQuantUnroll - 1) / (256 * kQuantUnroll); }
@@ -503,50 +508,49 @@ int add_rmsnorm_launch(const char* fn, const void* d_y, int y_is_f32, const void
     }
     // the device cannot place such a cluster: the multi-launch form below takes over
   }
-  if (d_n_fp8 != nullptr)
+  if (d_n_fp8 != nullptr && !amax_prezeroed())
     G4_CUDA_TRY(fn, cudaMemsetAsync(d_scale_amax, 0, 2 * sizeof(float), st));
   const int fast_threads = p.cols8 / 4;
   const bool fast = !y_is_f32 && (d_res == nullptr || !res_is_f32) && p.cols8 % 4 == 0 &&
                     fast_threads % 32 == 0 && fast_threads <= 256 && pick_v(p.cols8) == 4;
   if (fast) {
     const bool amax = p.scale_amax != nullptr;
+    const dim3 grid(static_cast<unsigned>(rows)), block(static_cast<unsigned>(fast_threads));
     if (d_res != nullptr) {
-      if (amax) add_rmsnorm_fast_kernel<true, true><<<rows, fast_threads, 0, st>>>(p);
-      else add_rmsnorm_fast_kernel<true, false><<<rows, fast_threads, 0, st>>>(p);
+      if (amax) G4_LAUNCH_PDL(fn, add_rmsnorm_fast_kernel<true, true>, grid, block, 0, st, p);
+      else G4_LAUNCH_PDL(fn, add_rmsnorm_fast_kernel<true, false>, grid, block, 0, st, p);
     } else {
-      if (amax) add_rmsnorm_fast_kernel<false, true><<<rows, fast_threads, 0, st>>>(p);
-      else add_rmsnorm_fast_kernel<false, false><<<rows, fast_threads, 0, st>>>(p);
+      if (amax) G4_LAUNCH_PDL(fn, add_rmsnorm_fast_kernel<false, true>, grid, block, 0, st, p);
+      else G4_LAUNCH_PDL(fn, add_rmsnorm_fast_kernel<false, false>, grid, block, 0, st, p);
     }
   } else {
-    launch_phase<kStats>(p, y_is_f32 != 0, res_is_f32 != 0, st);
+    G4_CUDA_TRY(fn, launch_phase<kStats>(p, y_is_f32 != 0, res_is_f32 != 0, st));
   }
-  G4_LAUNCH_CHECK(fn);
   if (d_n_fp8 != nullptr) {
     if (d_n_bf16 != nullptr) {
       // n already sits in memory as bf16: encode it elementwise.
       const long long n8 = static_cast<long long>(rows) * (cols / 8);
-      encode_bf16_kernel<<<static_cast<unsigned>(quant_grid(n8)), 256, 0, st>>>(
-          reinterpret_cast<const uint4*>(d_n_bf16), n8, reinterpret_cast<uint2*>(d_n_fp8),
-          d_scale_amax);
+      G4_LAUNCH_PDL(fn, encode_bf16_kernel, dim3(static_cast<unsigned>(quant_grid(n8))), dim3(256), 0, st,
+                    reinterpret_cast<const uint4*>(d_n_bf16), n8, reinterpret_cast<uint2*>(d_n_fp8),
+                    d_scale_amax);
     } else if (d_h_out != nullptr && d_rstd != nullptr) {
       NormParams q = p;
       q.reverse = 1;
       const unsigned grid = static_cast<unsigned>((rows + kRowsPerCta - 1) / kRowsPerCta);
       if (q.cols8 == kEncodeThreads * kEncodeMaxIter && rows % kRowsPerCta == 0)
-        norm_encode_kernel<true><<<grid, kEncodeThreads, 0, st>>>(q);
+        G4_LAUNCH_PDL(fn, norm_encode_kernel<true>, dim3(grid), dim3(kEncodeThreads), 0, st, q);
       else
-        norm_encode_kernel<false><<<grid, kEncodeThreads, 0, st>>>(q);
+        G4_LAUNCH_PDL(fn, norm_encode_kernel<false>, dim3(grid), dim3(kEncodeThreads), 0, st, q);
     } else {
       NormParams q = p;
       q.reverse = 1;
       if (d_h_out != nullptr) {  // re-read the bf16 hidden state, not y and res
         q.y = d_h_out, q.res = nullptr;
-        launch_phase<kEncode>(q, false, false, st);
+        G4_CUDA_TRY(fn, launch_phase<kEncode>(q, false, false, st));
       } else {
-        launch_phase<kEncode>(q, y_is_f32 != 0, res_is_f32 != 0, st);
+        G4_CUDA_TRY(fn, launch_phase<kEncode>(q, y_is_f32 != 0, res_is_f32 != 0, st));
       }
     }
-    G4_LAUNCH_CHECK(fn);
   }
   return 0;
 }
@@ -618,12 +622,10 @@ int granite4_kernel_fp8_quant(const uint16_t* d_x, long long n, uint8_t* d_codes
   const long long grid = g4::quant_grid(n8);
   if (grid > INT_MAX) return g4::fail(fn, "tensor too large");
   G4_CUDA_TRY(fn, cudaMemsetAsync(d_scale_amax, 0, 2 * sizeof(float), st));
-  g4::amax_bf16_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(
-      reinterpret_cast<const uint4*>(d_x), n8, d_scale_amax);
-  G4_LAUNCH_CHECK(fn);
-  g4::encode_bf16_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(
-      reinterpret_cast<const uint4*>(d_x), n8, reinterpret_cast<uint2*>(d_codes), d_scale_amax);
-  G4_LAUNCH_CHECK(fn);
+  G4_LAUNCH_PDL(fn, g4::amax_bf16_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, st,
+                reinterpret_cast<const uint4*>(d_x), n8, d_scale_amax);
+  G4_LAUNCH_PDL(fn, g4::encode_bf16_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, st,
+                reinterpret_cast<const uint4*>(d_x), n8, reinterpret_cast<uint2*>(d_codes), d_scale_amax);
   return 0;
 }
 

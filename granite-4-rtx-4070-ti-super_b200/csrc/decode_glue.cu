@@ -56,6 +56,7 @@ __device__ __forceinline__ float pair_max(uint32_t m) {
 // ctas_per_row CTAs, one cluster per row.
 template <bool VEC, bool CLUSTER>
 __global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const ArgmaxParams p) {
+  pdl_begin();
   const int T = blockDim.x, t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = T >> 5;
   const int C = CLUSTER ? p.ctas_per_row : 1;
   const int row = CLUSTER ? static_cast<int>(blockIdx.x) / C : blockIdx.x;
@@ -216,23 +217,26 @@ int granite4_kernel_argmax_rows(const uint16_t* d_logits, int rows, int V, int32
     cfg.gridDim = dim3(static_cast<unsigned>(rows * p.ctas_per_row));
     cfg.blockDim = dim3(512);
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = static_cast<unsigned>(p.ctas_per_row);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     void (*kernel)(g4::ArgmaxParams) = g4::argmax_rows_kernel<true, true>;
     if (g4::cluster_fits(reinterpret_cast<const void*>(kernel), cfg, p.ctas_per_row, 512)) {
+      cfg.numAttrs = g4::pdl_enabled() ? 2 : 1;
       G4_CUDA_TRY(fn, cudaLaunchKernelEx(&cfg, kernel, p));
       return 0;
     }
     p.ctas_per_row = 1;
   }
-  if (vec) g4::argmax_rows_kernel<true, false><<<static_cast<unsigned>(rows), g4::kArgmaxThreads, 0, st>>>(p);
-  else g4::argmax_rows_kernel<false, false><<<static_cast<unsigned>(rows), g4::kArgmaxThreads, 0, st>>>(p);
-  G4_LAUNCH_CHECK(fn);
+  const dim3 grid(static_cast<unsigned>(rows)), block(g4::kArgmaxThreads);
+  if (vec) G4_LAUNCH_PDL(fn, g4::argmax_rows_kernel<true, false>, grid, block, 0, st, p);
+  else G4_LAUNCH_PDL(fn, g4::argmax_rows_kernel<false, false>, grid, block, 0, st, p);
   return 0;
 }
 

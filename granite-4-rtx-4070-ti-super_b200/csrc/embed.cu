@@ -45,6 +45,7 @@ __device__ __forceinline__ uint4 scale8(uint4 v, float mult) {
 __global__ void __launch_bounds__(256)
     embed_vec_kernel(const int32_t* tokens, long long start, long long rows, const uint4* emb,
                      int vocab, float mult, uint4* out, int H8) {
+  pdl_begin();
   const int lane = threadIdx.x & 31;
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -76,6 +77,7 @@ constexpr int kBulkThreads = 128;
 __global__ void __launch_bounds__(kBulkThreads)
     embed_bulk_kernel(const int32_t* tokens, long long start, long long rows, const uint16_t* emb,
                       int vocab, float mult, uint16_t* out, int H, unsigned int* status) {
+  pdl_begin();
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t row_bytes = static_cast<uint32_t>(H) * 2u;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(kStages) * row_bytes);
@@ -174,15 +176,14 @@ int embed_launch(const char* fn, const int32_t* d_tokens, long long start, long 
     }
     const long long per_sm = std::max<long long>(1, std::min<long long>(8, (200 * 1024) / smem));
     const unsigned grid = static_cast<unsigned>(std::min<long long>(rows, sm_count() * per_sm));
-    embed_bulk_kernel<<<grid, kBulkThreads, smem, st>>>(d_tokens, start, rows, emb, vocab, mult, out,
-                                                       H, status);
+    G4_LAUNCH_PDL(fn, embed_bulk_kernel, dim3(grid), dim3(kBulkThreads), smem, st, d_tokens, start, rows, emb,
+                  vocab, mult, out, H, status);
   } else {
     const long long warps = rows;
     const unsigned grid =
         static_cast<unsigned>(std::min<long long>((warps + 7) / 8, sm_count() * 8LL));
-    embed_vec_kernel<<<grid, 256, 0, st>>>(d_tokens, start, rows,
-                                           reinterpret_cast<const uint4*>(emb), vocab, mult,
-                                           reinterpret_cast<uint4*>(out), H / 8);
+    G4_LAUNCH_PDL(fn, embed_vec_kernel, dim3(grid), dim3(256), 0, st, d_tokens, start, rows,
+                  reinterpret_cast<const uint4*>(emb), vocab, mult, reinterpret_cast<uint4*>(out), H / 8);
   }
   G4_LAUNCH_CHECK(fn);
   return 0;

@@ -96,15 +96,19 @@ cudaError_t cluster_launch(void (*kernel)(Params), int ctas, int threads, const 
   cfg.blockDim = dim3(static_cast<unsigned>(threads));
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(ctas);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // the kernels launched through here all start with pdl_begin() (g4_math.cuh)
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (!cluster_fits(reinterpret_cast<const void*>(kernel), cfg, ctas, threads))
     return cudaErrorInvalidConfiguration;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 

@@ -57,4 +57,45 @@ inline int fail(const char* fn, const char* why) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// granite4_glue_layer clears the {scale, amax} slots of all three FP8 ops of a layer with one
+// memset and sets this (per thread) while it calls the launchers, which then skip their own.
+bool amax_prezeroed();
+void set_amax_prezeroed(bool on);
+
+// Programmatic dependent launch: a kernel launched through launch_pdl may be staged on the GPU
+// while the kernel before it on the stream is still draining; it must (and every kernel launched
+// this way does, as its first statements, in every CTA) execute pdl_begin() from g4_math.cuh,
+// which holds it until the preceding kernel has completed and its writes are visible. What is
+// saved is the launch latency and the ramp of each kernel boundary, which is all a decode-size
+// or small-shard launch consists of. G4_PDL=0 in the environment launches everything fully
+// serialised (read per call).
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1u : 0u;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define G4_LAUNCH_PDL(fn, ...)                                                      \
+  do {                                                                             \
+    cudaError_t e_ = g4::launch_pdl(__VA_ARGS__);                                  \
+    if (e_ != cudaSuccess) {                                                       \
+      (void)cudaGetLastError();                                                    \
+      std::fprintf(stderr, "granite4: %s: CUDA error at %s:%d: %s\n", fn, __FILE__, \
+                   __LINE__, cudaGetErrorString(e_));                              \
+      return -1;                                                                   \
+    }                                                                              \
+  } while (0)
+
 }  // namespace g4

@@ -283,4 +283,20 @@ __device__ __forceinline__ void atomic_amax(float* slot, float v) {
   atomicMax(reinterpret_cast<unsigned int*>(slot), __float_as_uint(v));
 }
 
+// First statements of every kernel that is launched with programmatic stream serialisation
+// (g4_host.h launch_pdl), executed by every thread of every CTA before anything else - above all
+// before any early return, or a CTA that left without waiting would let the grid count as
+// complete, and its successor start, while the predecessor still runs.
+// griddepcontrol.wait blocks until the previous kernel has completed and its writes are visible;
+// it is a no-op in a kernel launched without the attribute. Only a decode-size grid (a few CTAs)
+// also signals launch_dependents early, so that the next small kernel is already resident when
+// this one ends; a large grid leaves the signal to its CTAs' exits. Measured on B200: with an
+// early signal in every kernel, the staged CTAs of the next kernel (thousands of them behind a
+// persistent kernel, which has all its CTAs resident from the start) sat on the SMs waiting and
+// cost the running kernel 12 % of the whole step.
+__device__ __forceinline__ void pdl_begin() {
+  if (gridDim.x * gridDim.y <= 64u) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 }  // namespace g4

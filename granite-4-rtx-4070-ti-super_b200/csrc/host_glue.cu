@@ -22,6 +22,14 @@ extern "C" int granite4_glue_layer(const granite4_glue_layer_args* a) {
   if (a == nullptr) return g4::fail(fn, "invalid arguments");
   float* sc = a->scales;
   if (sc == nullptr) return g4::fail(fn, "scales buffer missing");
+  // One memset clears the {scale, amax} slots of all three FP8 ops, so that the seven kernels of
+  // the layer follow one another on the stream with no other operation between them (each is
+  // staged while its predecessor drains, g4_host.h launch_pdl).
+  G4_CUDA_TRY(fn, cudaMemsetAsync(sc, 0, 6 * sizeof(float), g4::current_stream()));
+  struct Prezeroed {
+    Prezeroed() { g4::set_amax_prezeroed(true); }
+    ~Prezeroed() { g4::set_amax_prezeroed(false); }
+  } prezeroed;
   if (granite4_kernel_add_rmsnorm_fp8(a->y_attn, 0, a->hidden, 0, a->w_attn_norm, a->eps, a->resid_mult,
                                       a->rows, a->hidden_size, a->hidden, nullptr, a->n_attn_fp8, sc,
                                       a->rstd) != 0)

@@ -80,6 +80,7 @@ constexpr int kMaxHeadsPerThread = 4;  // (Hq + 2 Hk) <= 64 heads per row in thi
 
 template <int kRows>
 __global__ void __launch_bounds__(kHeadsPerCta * 8) rope_kv_int8_kernel(const RopeKvParams p) {
+  pdl_begin();
   const int g = threadIdx.x >> 3;
   const int j = threadIdx.x & 7;
   const int heads_total = p.Hq + 2 * p.Hk;
@@ -195,6 +196,7 @@ struct RowMeta {
 
 __global__ void __launch_bounds__(kBulkThreads) rope_kv_bulk_kernel(const RopeKvParams p,
                                                                     unsigned int* status) {
+  pdl_begin();
   extern __shared__ __align__(128) unsigned char smem[];
   const int heads_total = p.Hq + 2 * p.Hk;
   const uint32_t act_bytes = static_cast<uint32_t>(heads_total) * kD * 2u;
@@ -412,11 +414,11 @@ int launch_rope_kv(const char* fn, RopeKvParams& p) {
     }
     const int per_sm = static_cast<int>(std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / smem)));
     const unsigned grid = static_cast<unsigned>(std::min<long long>(p.rows, static_cast<long long>(sm_count()) * per_sm));
-    rope_kv_bulk_kernel<<<grid, kBulkThreads, smem, st>>>(p, status);
+    G4_LAUNCH_PDL(fn, rope_kv_bulk_kernel, dim3(grid), dim3(kBulkThreads), smem, st, p, status);
   } else {
-    rope_kv_int8_kernel<1><<<static_cast<unsigned>(p.rows), kHeadsPerCta * 8, 0, st>>>(p);
+    G4_LAUNCH_PDL(fn, rope_kv_int8_kernel<1>, dim3(static_cast<unsigned>(p.rows)), dim3(kHeadsPerCta * 8), 0,
+                  st, p);
   }
-  G4_LAUNCH_CHECK(fn);
   return 0;
 }
 

@@ -6,6 +6,8 @@
 
 #include "../../include/granite4_b200.h"
 
+#include <cstdlib>
+
 namespace g4 {
 
 namespace {
@@ -31,6 +33,17 @@ unsigned int* device_status_ptr() {
 
 cudaStream_t current_stream() { return t_stream; }
 void set_current_stream(cudaStream_t s) { t_stream = s ? s : cudaStreamPerThread; }
+
+namespace {
+thread_local bool t_amax_prezeroed = false;
+}
+bool amax_prezeroed() { return t_amax_prezeroed; }
+void set_amax_prezeroed(bool on) { t_amax_prezeroed = on; }
+
+bool pdl_enabled() {
+  const char* v = std::getenv("G4_PDL");
+  return !(v != nullptr && v[0] == '0');
+}
 
 int sm_count() {
   int dev = 0;

@@ -84,6 +84,7 @@ __device__ __forceinline__ uint4 swiglu8(const void* gate, const void* up, long 
 // kEncode: codes, from the bf16 buffer (FROM_BF16) or recomputed.
 template <bool F32, int MODE, bool FROM_BF16>
 __global__ void __launch_bounds__(kThreads) swiglu_kernel(const SwigluParams p) {
+  pdl_begin();
   const long long tile0 = static_cast<long long>(blockIdx.x) * (kThreads * kUnroll) + threadIdx.x;
   Fp8Scale fs{};
   if (MODE == kEncode) {
@@ -161,6 +162,7 @@ constexpr long long kClusterItemsPerCta = static_cast<long long>(kClusterThreads
 
 template <bool F32>
 __global__ void __launch_bounds__(kClusterThreads) swiglu_cluster_kernel(const SwigluParams p) {
+  pdl_begin();
   const long long tile0 = static_cast<long long>(blockIdx.x) * kClusterItemsPerCta + threadIdx.x;
   uint4 a[kUnroll];
   uint32_t amax = 0u;
@@ -202,8 +204,7 @@ int launch_swiglu(const char* fn, const SwigluParams& p) {
   if (tiles > INT_MAX || p.items > 0xffffffffLL) return fail(fn, "tensor too large");
   const unsigned grid = static_cast<unsigned>(tiles);
   if (p.act_fp8 == nullptr) {
-    swiglu_kernel<F32, kPlain, false><<<grid, kThreads, 0, st>>>(p);
-    G4_LAUNCH_CHECK(fn);
+    G4_LAUNCH_PDL(fn, swiglu_kernel<F32, kPlain, false>, dim3(grid), dim3(kThreads), 0, st, p);
     return 0;
   }
   if (p.items <= kMaxClusterCtas * kClusterItemsPerCta && cluster_enabled()) {
@@ -216,14 +217,12 @@ int launch_swiglu(const char* fn, const SwigluParams& p) {
     }
     // the device cannot place such a cluster: the multi-launch form below takes over
   }
-  G4_CUDA_TRY(fn, cudaMemsetAsync(p.scale_amax, 0, 2 * sizeof(float), st));
-  swiglu_kernel<F32, kAmax, false><<<grid, kThreads, 0, st>>>(p);
-  G4_LAUNCH_CHECK(fn);
+  if (!amax_prezeroed()) G4_CUDA_TRY(fn, cudaMemsetAsync(p.scale_amax, 0, 2 * sizeof(float), st));
+  G4_LAUNCH_PDL(fn, swiglu_kernel<F32, kAmax, false>, dim3(grid), dim3(kThreads), 0, st, p);
   if (p.act_bf16 != nullptr)
-    swiglu_kernel<F32, kEncode, true><<<grid, kThreads, 0, st>>>(p);
+    G4_LAUNCH_PDL(fn, swiglu_kernel<F32, kEncode, true>, dim3(grid), dim3(kThreads), 0, st, p);
   else
-    swiglu_kernel<F32, kEncode, false><<<grid, kThreads, 0, st>>>(p);
-  G4_LAUNCH_CHECK(fn);
+    G4_LAUNCH_PDL(fn, swiglu_kernel<F32, kEncode, false>, dim3(grid), dim3(kThreads), 0, st, p);
   return 0;
 }
 
