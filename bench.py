@@ -349,6 +349,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "embed": extras["embed"],
             "small_shapes": extras["small"],
             "argmax": extras["argmax"],
+            "attention_decode": extras["attention"],
             "clocks": clocks,
             "gpu_launches": launches,
             "device_status": status,
@@ -470,7 +471,38 @@ def small_shapes_and_embed(seq, rows, device, stream):
         argmax[f"rows_{n}_graph_us"] = graph_replay_us(lambda: k.argmax_rows(logits[:n], picked[:n]))
     del logits
     torch.cuda.empty_cache()
-    return {"embed": embed, "small": small, "argmax": argmax}
+
+    # Decode attention over the int8 paged pool (the reader of the KV write): 264 B per cache
+    # position and kv head. One layer's pool of 131072 rows (270 MB, larger than L2), 16-token pages
+    # in permuted order; a single sequence at full context, eight sequences of 32768, and a
+    # four-row verify step.
+    stride, page = 131072, 16
+    ck = torch.randint(-127, 128, (s.kv_heads, stride, s.head_dim), generator=g, device=device, dtype=torch.int8)
+    cv = torch.randint(-127, 128, (s.kv_heads, stride, s.head_dim), generator=g, device=device, dtype=torch.int8)
+    ksc = torch.rand(s.kv_heads, stride, generator=g, device=device) * 0.02 + 0.005
+    vsc = torch.rand(s.kv_heads, stride, generator=g, device=device) * 0.02 + 0.005
+    pages = torch.randperm(stride // page, generator=g, device=device)
+    table = (pages.repeat_interleave(page) * page + torch.arange(stride, device=device) % page).to(torch.int32)
+    attention = {}
+    for name, n, group, ctx in (("1_row_ctx_131072", 1, 1, 131072), ("8_rows_ctx_32768", 8, 1, 32768),
+                                ("verify_4_rows_ctx_32768", 4, 4, 32768)):
+        qa = torch.randn(n, s.q_heads * s.head_dim, generator=g, device=device).to(torch.bfloat16)
+        pos = torch.full((n,), ctx - 1, dtype=torch.int32, device=device)
+        if group > 1:
+            pos = pos - torch.arange(n - 1, -1, -1, device=device, dtype=torch.int32)
+        oa = torch.empty_like(qa)
+        need = k.attn_decode_scratch_bytes(n, group, s.kv_heads, ctx)
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
+        us = timed(lambda: k.attn_decode_int8_paged(qa, ck, cv, ksc, vsc, pos, s.q_heads, s.kv_heads, s.head_dim,
+                                                    stride, ctx, 1.0 / 128, oa, rows_per_group=group, pt=table,
+                                                    scratch=scratch), 20)
+        groups = (n + group - 1) // group
+        nbytes = groups * s.kv_heads * ctx * (2 * s.head_dim + 8)
+        attention[name] = {"mean_us": us, "achieved_gbs": nbytes / (us * 1e-6) / 1e9,
+                           "frac": nbytes / (us * 1e-6) / 1e9 / peak, "bytes": nbytes}
+    del ck, cv, ksc, vsc, table
+    torch.cuda.empty_cache()
+    return {"embed": embed, "small": small, "argmax": argmax, "attention": attention}
 
 
 def run_e2e(seq, rows, device, steps):

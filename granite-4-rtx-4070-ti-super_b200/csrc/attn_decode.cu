@@ -1,0 +1,541 @@
+// Decode / verify attention over the int8 paged KV pool: the reader of what the
+// RoPE + KV-write kernel stores.
+//
+// Formulation (reference: contract engine/src/attention_gpu.h:15-68, kernel
+// engine/src/attention_split.cu; host golden form engine/src/kernel_math.h:265-331):
+//   row r of q [rows][Hq d] sits at position pos[r] of its sequence and attends
+//   to cache positions 0..pos[r]; cache position t lives in pool row pt[t];
+//   k_t = code_k[hkv][pt[t]][:] * k_scale[hkv][pt[t]],  v_t likewise;
+//   logits = scale * q . k_t,  p = softmax(logits),  out = sum_t p_t v_t
+//   with q head h reading kv head h / 4 (Hq == 4 Hk, d == 128 only, as the
+//   reference's split kernel).
+// The reference dequantises every cache row to bf16 and rounds logits and
+// probabilities to bf16 between its steps; its device tests accept 0.03 absolute
+// against that form (engine/tests/test_kernels.cu:2055, :2282). Here the codes stay
+// integers: they convert exactly to fp16, the row scale multiplies the logit
+// (K) and the probability (V) instead of 128 elements, and nothing is rounded
+// below fp16 / f32 on the way - inside the same tolerance, and closer to the
+// exact result.
+//
+// This op is memory-bound: per cache position and kv head it reads 2 x 128 code
+// bytes + 2 scales (264 B) for 1024 multiply-adds, more than the f32 pipes
+// deliver at HBM speed, so the two contractions run on the tensor cores
+// (mma.sync m16n8k16, fp16 in, f32 accumulate; the 16 rows of the tile are the 4
+// q heads of the kv head x up to 4 query rows of one sequence).
+//
+// Decomposition: grid (split, kv head, row group). A CTA has 4 warps and owns a
+// contiguous range of cache positions; each warp works alone on tiles of 16
+// positions (gathers the 16 K and V code rows through the page table, converts
+// them into its own shared-memory tile, S = Q K^T, online softmax, O += P V) with
+// its own running (max, sum, O), so the main loop has no CTA barrier. The warps'
+// states are merged in shared memory at the end, the splits' states by a second
+// small kernel (flash-decoding).
+//
+// Algorithmic bytes per (row group, kv head): (pos + 1) * 264.
+#include "g4_host.h"
+#include "g4_math.cuh"
+
+#include "../../include/granite4_b200.h"
+
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+namespace g4 {
+namespace {
+
+constexpr int kAD = 128;       // head dim
+constexpr int kTile = 16;      // cache positions per warp tile
+constexpr int kWarps = 4;
+constexpr int kGqa = 4;        // q heads per kv head
+constexpr int kGroupRows = 4;  // query rows per CTA (4 x 4 = the 16 rows of the mma tile)
+constexpr int kSplitAlign = kTile * kWarps;
+constexpr int kCtasPerSm = 3;  // register and shared-memory budget of the main kernel
+
+// Shared memory of one warp. Raw code rows arrive by 16-byte asynchronous copies (cp.async),
+// kStages tiles deep, so the bytes in flight occupy no registers. K rows are padded to 144 bytes:
+// the 32-bit fragment loads of the 32 lanes (8 positions x 4 k-groups) then hit 32 different
+// banks. V needs its tile transposed for the second contraction, which ldmatrix.trans does on
+// 16-bit elements, so the V codes are converted into an fp16 tile first (rows padded to 272 bytes).
+constexpr int kStages = 3;
+constexpr int kKPitch = kAD + 16;            // bytes per raw K row
+constexpr int kRawK = kTile * kKPitch;       // 2304
+constexpr int kRawV = kTile * kAD;           // 2048
+constexpr int kVPitch = kAD + 8;             // halves per fp16 V row
+constexpr int kVTile = kTile * kVPitch * 2;  // 4352 bytes
+constexpr int kWarpSmem = kStages * (kRawK + kRawV) + kVTile;  // 17408
+constexpr size_t kAttnSmemBytes = static_cast<size_t>(kWarps) * kWarpSmem;
+static_assert(kWarpSmem >= (16 * kAD + 32) * 4, "a warp parks its final state in its own block");
+
+struct AttnParams {
+  const uint16_t* q;
+  const int8_t* ck;
+  const int8_t* cv;
+  const float* ks;
+  const float* vs;
+  const int* row_pos;
+  const int* const* row_pt;  // per-row tables, or NULL
+  const int* pt;             // one table for every row, or NULL (identity)
+  float* part_o;             // [groups][Hk][splits][16][128]
+  float* part_ml;            // [groups][Hk][splits][16][2]
+  uint16_t* out;
+  int rows, group_rows, Hq, Hk;
+  long long stride;
+  int splits, split_len, max_len;
+  float scale_log2;  // scale * log2(e)
+};
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// Four int8 codes (one 32-bit word) -> four fp16 values, exactly: bias each byte to unsigned,
+// drop it into the mantissa of 1024.0 (0x6400) and subtract 1152.
+__device__ __forceinline__ void codes4_to_half(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  w ^= 0x80808080u;
+  const uint32_t a = __byte_perm(w, 0x64646464u, 0x4140);
+  const uint32_t b = __byte_perm(w, 0x64646464u, 0x4342);
+  const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
+  const __half2 x = __hsub2(*reinterpret_cast<const __half2*>(&a), bias);
+  const __half2 y = __hsub2(*reinterpret_cast<const __half2*>(&b), bias);
+  lo = *reinterpret_cast<const uint32_t*>(&x);
+  hi = *reinterpret_cast<const uint32_t*>(&y);
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool real) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  const int src_bytes = real ? 16 : 0;  // 0: nothing is read, the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(const AttnParams p) {
+  pdl_begin();
+  extern __shared__ __align__(128) unsigned char s_dyn[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int split = blockIdx.x, hkv = blockIdx.y, grp = blockIdx.z;
+  const int r0 = grp * p.group_rows;
+  const int nrows = min(p.group_rows, p.rows - r0);
+  unsigned char* wsm = s_dyn + static_cast<size_t>(warp) * kWarpSmem;
+  unsigned char* raw_k = wsm;                    // [kStages][16][144]
+  unsigned char* raw_v = wsm + kStages * kRawK;  // [kStages][16][128]
+  __half(*vtile)[kVPitch] = reinterpret_cast<__half(*)[kVPitch]>(wsm + kStages * (kRawK + kRawV));
+
+  // positions of the group's rows; the mma rows g and g + 8 belong to query rows g / 4 and 2 + g / 4
+  int pos_lo = -1, pos_hi = -1, pos_max = -1;
+  for (int j = 0; j < nrows; ++j) {
+    int pj = __ldg(p.row_pos + r0 + j);
+    pj = pj < 0 ? -1 : min(pj, p.max_len - 1);
+    pos_max = max(pos_max, pj);
+    if (j == (g >> 2)) pos_lo = pj;
+    if (j == 2 + (g >> 2)) pos_hi = pj;
+  }
+  const int* pt = p.row_pt != nullptr ? p.row_pt[r0] : p.pt;
+  const int t_begin = split * p.split_len;
+  const int t_end = min(t_begin + p.split_len, pos_max + 1);
+
+  // ---- Q fragments: 16 rows (query row j = m / 4, head hl = m % 4) x 128 dims, as fp16 scaled by
+  // a power of two so that the largest magnitude sits near 2^10. Within each 16-wide k-step the
+  // contraction index is permuted: lane group t takes dims 4 t .. 4 t + 3 (first operand register
+  // 4 t, 4 t + 1, second 4 t + 2, 4 t + 3) instead of 2 t, 2 t + 1 and 2 t + 8, 2 t + 9. A dot product
+  // does not care about the order, and the matching K operand is then four consecutive code
+  // bytes: one 32-bit shared-memory load per mma.
+  uint32_t qa[8][4];
+  float logit_scale;
+  {
+    float qf[8][8];  // per k-step: row g dims 4t, 4t+1 | row g+8 same | row g dims 4t+2, 4t+3 | row g+8 same
+    float qmax = 0.0f;
+#pragma unroll
+    for (int half_rows = 0; half_rows < 2; ++half_rows) {
+      const int m = g + 8 * half_rows;
+      const int j = m >> 2, hl = m & 3;
+      const bool live = j < nrows;
+      const uint16_t* qrow = p.q + (static_cast<size_t>(r0 + (live ? j : 0)) * p.Hq + hkv * kGqa + hl) * kAD;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint2 w = live ? __ldg(reinterpret_cast<const uint2*>(qrow + kk * 16 + 4 * t)) : make_uint2(0u, 0u);
+        const float d0 = bf16_to_f32(w.x & 0xffffu), d1 = bf16_to_f32(w.x >> 16);
+        const float d2 = bf16_to_f32(w.y & 0xffffu), d3 = bf16_to_f32(w.y >> 16);
+        qf[kk][half_rows * 2 + 0] = d0, qf[kk][half_rows * 2 + 1] = d1;
+        qf[kk][4 + half_rows * 2 + 0] = d2, qf[kk][4 + half_rows * 2 + 1] = d3;
+        qmax = fmaxf(qmax, fmaxf(fmaxf(fabsf(d0), fabsf(d1)), fmaxf(fabsf(d2), fabsf(d3))));
+      }
+    }
+    qmax = warp_max(qmax);
+    int qexp = 0;
+    if (qmax > 0.0f && qmax < INFINITY)
+      qexp = min(max(((__float_as_int(qmax) >> 23) & 0xff) - 127 - 10, -100), 100);
+    const float qdown = __int_as_float((127 - qexp) << 23);  // 2^-qexp
+    logit_scale = p.scale_log2 * __int_as_float((127 + qexp) << 23);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      // operand registers: (row g, k lo), (row g + 8, k lo), (row g, k hi), (row g + 8, k hi)
+      qa[kk][0] = pack_half2(qf[kk][0] * qdown, qf[kk][1] * qdown);
+      qa[kk][1] = pack_half2(qf[kk][2] * qdown, qf[kk][3] * qdown);
+      qa[kk][2] = pack_half2(qf[kk][4] * qdown, qf[kk][5] * qdown);
+      qa[kk][3] = pack_half2(qf[kk][6] * qdown, qf[kk][7] * qdown);
+    }
+  }
+
+  float o[16][4];
+#pragma unroll
+  for (int nd = 0; nd < 16; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  const size_t head_row0 = static_cast<size_t>(hkv) * p.stride;
+
+  // ---- gather. Lane l (and l + 16) looks up the pool row of tile position l and fetches that
+  // position's two scales. The code rows are copied four rows per instruction: in copy i lane l
+  // moves 16-byte piece l % 8 of row 4 i + l / 8, so one instruction covers four whole 128-byte
+  // rows (every 32-byte sector requested once). While tile i is computed, the raw codes of tiles
+  // i + 1 and i + 2 are in flight into this warp's stages and the table entries of tile i + 3 are
+  // being looked up, so neither of the two dependent global latencies (table -> row address ->
+  // codes) is exposed.
+  const int n_load = lane >> 1, h_load = lane & 1;  // this lane's part of the V conversion
+  constexpr int kStep = kTile * kWarps;
+  auto table_row = [&](int tile0) -> int {
+    const int tpos = tile0 + (lane & 15);
+    if (tpos >= t_end) return 0;
+    const int prow = pt != nullptr ? __ldg(pt + tpos) : tpos;
+    return min(max(prow, 0), static_cast<int>(p.stride) - 1);
+  };
+  auto gather = [&](int stage, int tile0, int prow, float& sk, float& sv) {
+    const int piece = (lane & 7) * 16;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int n = 4 * i + (lane >> 3);
+      const int pr = __shfl_sync(0xffffffffu, prow, n);
+      const bool have = tile0 + n < t_end;
+      const size_t off = (head_row0 + pr) * kAD + piece;
+      cp_async16(raw_k + stage * kRawK + n * kKPitch + piece, p.ck + off, have);
+      cp_async16(raw_v + stage * kRawV + n * kAD + piece, p.cv + off, have);
+    }
+    cp_async_commit();
+    const bool mine = tile0 + (lane & 15) < t_end;
+    sk = mine ? __ldg(p.ks + head_row0 + prow) : 0.0f;
+    sv = mine ? __ldg(p.vs + head_row0 + prow) : 0.0f;
+  };
+  const int t_first = t_begin + warp * kTile;
+  float sk_q[kStages], sv_q[kStages];  // scales of the tiles in flight, oldest first (lane n: position n)
+  {
+    const int pr0 = table_row(t_first), pr1 = table_row(t_first + kStep);
+    gather(0, t_first, pr0, sk_q[0], sv_q[0]);
+    gather(1, t_first + kStep, pr1, sk_q[1], sv_q[1]);
+  }
+  int prow_next = table_row(t_first + 2 * kStep);
+  int stage = 0;
+
+  for (int t0 = t_first; t0 < t_end; t0 += kStep) {
+    cp_async_wait<1>();  // all but the newest group have landed: tile i is in shared memory
+    __syncwarp();        // ... for every lane, and every lane is done with tile i - 1
+    // tile i + 2 goes into the stage tile i - 1 was read out of
+    gather((stage + 2) % kStages, t0 + 2 * kStep, prow_next, sk_q[2], sv_q[2]);
+    prow_next = table_row(t0 + 3 * kStep);
+
+    // ---- V: this lane's 64 codes -> fp16 tile (for the transposing fragment loads further down)
+    {
+      const unsigned char* src = raw_v + stage * kRawV + n_load * kAD + h_load * 64;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + i * 16);
+        uint32_t h[8];
+        codes4_to_half(raw.x, h[0], h[1]);
+        codes4_to_half(raw.y, h[2], h[3]);
+        codes4_to_half(raw.z, h[4], h[5]);
+        codes4_to_half(raw.w, h[6], h[7]);
+        uint4* dst = reinterpret_cast<uint4*>(&vtile[n_load][h_load * 64 + i * 16]);
+        dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+        dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+      }
+    }
+    const float sk_cur = sk_q[0], sv_cur = sv_q[0];
+    sk_q[0] = sk_q[1], sv_q[0] = sv_q[1];
+    sk_q[1] = sk_q[2], sv_q[1] = sv_q[2];
+
+    // ---- S = Q K^T over the tile: two 8-position column blocks, K operands straight from the
+    // raw codes (two accumulators per block halve the dependent mma chain)
+    float s[2][4];
+    const unsigned char* kstage = raw_k + stage * kRawK;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      float sa[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      const unsigned char* krow = kstage + (nt * 8 + g) * kKPitch + 4 * t;
+#pragma unroll
+      for (int kk = 0; kk < 8; kk += 2) {
+        uint32_t b0, b1, c0, c1;
+        codes4_to_half(*reinterpret_cast<const uint32_t*>(krow + kk * 16), b0, b1);
+        codes4_to_half(*reinterpret_cast<const uint32_t*>(krow + kk * 16 + 16), c0, c1);
+        mma_f16(sa, qa[kk], b0, b1);
+        mma_f16(sb, qa[kk + 1], c0, c1);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[nt][i] = sa[i] + sb[i];
+    }
+    stage = (stage + 1) % kStages;
+
+    // ---- scale, mask, online softmax; thread holds columns n = nt * 8 + 2 t + {0, 1} of rows g, g + 8
+    float pr[2][4];
+    float tile_max[2] = {-INFINITY, -INFINITY};
+    float svn[2][2];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int n = nt * 8 + 2 * t + e;
+        const float skn = __shfl_sync(0xffffffffu, sk_cur, n);
+        svn[nt][e] = __shfl_sync(0xffffffffu, sv_cur, n);
+        const int tp = t0 + n;
+        const float f = skn * logit_scale;
+        const float a = (tp <= pos_lo && tp < t_end) ? s[nt][e] * f : -INFINITY;
+        const float b = (tp <= pos_hi && tp < t_end) ? s[nt][2 + e] * f : -INFINITY;
+        s[nt][e] = a, s[nt][2 + e] = b;
+        tile_max[0] = fmaxf(tile_max[0], a);
+        tile_max[1] = fmaxf(tile_max[1], b);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      float mx = tile_max[hr];
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[hr], mx);
+      corr[hr] = (m_new == -INFINITY) ? 1.0f : exp2f(m_run[hr] - m_new);  // exp2f(-inf) = 0
+      const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+      float sum = 0.0f;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float pv = exp2f(s[nt][2 * hr + e] - base);  // masked: exp2f(-inf) = 0
+          pr[nt][2 * hr + e] = pv;
+          sum += pv;
+        }
+      l_run[hr] = l_run[hr] * corr[hr] + sum;  // this thread's columns only; quads are summed at the end
+      m_run[hr] = m_new;
+    }
+    // the running maximum settles after a few tiles; most tiles need no rescaling at all
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+      for (int nd = 0; nd < 16; ++nd) {
+        o[nd][0] *= corr[0], o[nd][1] *= corr[0];
+        o[nd][2] *= corr[1], o[nd][3] *= corr[1];
+      }
+    }
+    // ---- O += (P diag(v_scale)) V: P's accumulator layout is the A-operand layout ------------------
+    uint32_t pa[4];
+    pa[0] = pack_half2(pr[0][0] * svn[0][0], pr[0][1] * svn[0][1]);
+    pa[1] = pack_half2(pr[0][2] * svn[0][0], pr[0][3] * svn[0][1]);
+    pa[2] = pack_half2(pr[1][0] * svn[1][0], pr[1][1] * svn[1][1]);
+    pa[3] = pack_half2(pr[1][2] * svn[1][0], pr[1][3] * svn[1][1]);
+    __syncwarp();  // every lane's part of the fp16 V tile is written
+#pragma unroll
+    for (int nd = 0; nd < 16; nd += 2) {
+      // matrices: (pos 0-7, dims nd*8..), (pos 8-15, same dims), (pos 0-7, dims (nd+1)*8..), (pos 8-15, ..)
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, &vtile[lane & 15][(nd + (lane >> 4)) * 8]);
+      mma_f16(o[nd], pa, b[0], b[1]);
+      mma_f16(o[nd + 1], pa, b[2], b[3]);
+    }
+  }
+
+  cp_async_wait<0>();  // nothing of this thread's may still be landing when the memory is reused
+  // ---- merge the four warps' states (each warp parks its state at the start of its own block) ----
+#pragma unroll
+  for (int hr = 0; hr < 2; ++hr) {
+    l_run[hr] += __shfl_xor_sync(0xffffffffu, l_run[hr], 1);
+    l_run[hr] += __shfl_xor_sync(0xffffffffu, l_run[hr], 2);
+  }
+  __syncwarp();
+  float* wo = reinterpret_cast<float*>(wsm);  // [16][128] floats
+  float* wml = wo + 16 * kAD;                 // [16][2]
+#pragma unroll
+  for (int nd = 0; nd < 16; ++nd) {
+    *reinterpret_cast<float2*>(wo + g * kAD + nd * 8 + 2 * t) = make_float2(o[nd][0], o[nd][1]);
+    *reinterpret_cast<float2*>(wo + (g + 8) * kAD + nd * 8 + 2 * t) = make_float2(o[nd][2], o[nd][3]);
+  }
+  if (t == 0) {
+    wml[g * 2] = m_run[0], wml[g * 2 + 1] = l_run[0];
+    wml[(g + 8) * 2] = m_run[1], wml[(g + 8) * 2 + 1] = l_run[1];
+  }
+  __syncthreads();
+  const size_t part = (static_cast<size_t>(grp) * p.Hk + hkv) * p.splits + split;
+  for (int m = 0; m < 16; ++m) {
+    const int j = m >> 2, hl = m & 3;
+    if (j >= nrows) break;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w)
+      mm = fmaxf(mm, reinterpret_cast<const float*>(s_dyn + static_cast<size_t>(w) * kWarpSmem)[16 * kAD + m * 2]);
+    float l = 0.0f, acc = 0.0f;
+    const int dim = threadIdx.x;  // 128 threads = 128 dims
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float* base = reinterpret_cast<const float*>(s_dyn + static_cast<size_t>(w) * kWarpSmem);
+      const float mw = base[16 * kAD + m * 2];
+      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - mm);
+      l += f * base[16 * kAD + m * 2 + 1];
+      acc += f * base[m * kAD + dim];
+    }
+    if (p.splits == 1) {
+      const float v = l > 0.0f ? acc / l : 0.0f;
+      p.out[(static_cast<size_t>(r0 + j) * p.Hq + hkv * kGqa + hl) * kAD + dim] =
+          static_cast<uint16_t>(f32_to_bf16_bits(v));
+    } else {
+      p.part_o[(part * 16 + m) * kAD + dim] = acc;
+      if (dim == 0) p.part_ml[(part * 16 + m) * 2] = mm, p.part_ml[(part * 16 + m) * 2 + 1] = l;
+    }
+  }
+}
+
+// Merge of the splits: one CTA per (kv head, row group, tile row), thread = dim. The splits'
+// weights exp2(m_s - M) are computed once into shared memory, then every thread sums its dim.
+constexpr int kMaxSplits = 512;
+__global__ void __launch_bounds__(kAD) attn_combine_kernel(const AttnParams p) {
+  pdl_begin();
+  const int hkv = blockIdx.x, grp = blockIdx.y, m = blockIdx.z, dim = threadIdx.x;
+  const int r0 = grp * p.group_rows;
+  const int nrows = min(p.group_rows, p.rows - r0);
+  if (m >= 4 * nrows) return;
+  const int j = m >> 2, hl = m & 3;
+  const size_t part0 = (static_cast<size_t>(grp) * p.Hk + hkv) * p.splits;
+  __shared__ float s_w[kMaxSplits];
+  __shared__ float s_red[2][kAD / 32];
+  float mm = -INFINITY;
+  for (int s = dim; s < p.splits; s += kAD) mm = fmaxf(mm, __ldcg(p.part_ml + ((part0 + s) * 16 + m) * 2));
+  mm = warp_max(mm);
+  if ((dim & 31) == 0) s_red[0][dim >> 5] = mm;
+  __syncthreads();
+  mm = fmaxf(fmaxf(s_red[0][0], s_red[0][1]), fmaxf(s_red[0][2], s_red[0][3]));
+  float l = 0.0f;
+  for (int s = dim; s < p.splits; s += kAD) {
+    const float ms = __ldcg(p.part_ml + ((part0 + s) * 16 + m) * 2);
+    const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - mm);
+    s_w[s] = f;
+    l += f * __ldcg(p.part_ml + ((part0 + s) * 16 + m) * 2 + 1);
+  }
+  l = warp_sum(l);
+  if ((dim & 31) == 0) s_red[1][dim >> 5] = l;
+  __syncthreads();
+  l = (s_red[1][0] + s_red[1][1]) + (s_red[1][2] + s_red[1][3]);
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  const float* po = p.part_o + (part0 * 16 + m) * kAD + dim;
+  const size_t split_pitch = static_cast<size_t>(16) * kAD;
+  int s = 0;
+  for (; s + 4 <= p.splits; s += 4) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] += s_w[s + u] * __ldcg(po + (s + u) * split_pitch);
+  }
+  for (; s < p.splits; ++s) acc[0] += s_w[s] * __ldcg(po + s * split_pitch);
+  const float total = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+  const float v = l > 0.0f ? total / l : 0.0f;
+  p.out[(static_cast<size_t>(r0 + j) * p.Hq + hkv * kGqa + hl) * kAD + dim] =
+      static_cast<uint16_t>(f32_to_bf16_bits(v));
+}
+
+struct SplitPlan {
+  int groups, splits, split_len;
+};
+
+SplitPlan plan_splits(int rows, int group_rows, int Hk, int max_len) {
+  SplitPlan s{};
+  s.groups = (rows + group_rows - 1) / group_rows;
+  const int tiles = (max_len + kSplitAlign - 1) / kSplitAlign;  // units of 64 positions
+  // aim at one resident wave over the whole launch, at least 64 positions per split
+  const long long ctas_wanted = static_cast<long long>(kCtasPerSm) * sm_count();
+  // rounded down: the launch is then at most one resident wave (a second, nearly empty wave would
+  // double the time)
+  long long splits = ctas_wanted / (static_cast<long long>(s.groups) * Hk);
+  splits = std::max<long long>(1, std::min<long long>(std::min<long long>(splits, tiles), kMaxSplits));
+  const int tiles_per_split = static_cast<int>((tiles + splits - 1) / splits);
+  s.split_len = tiles_per_split * kSplitAlign;
+  s.splits = (tiles + tiles_per_split - 1) / tiles_per_split;
+  return s;
+}
+
+}  // namespace
+}  // namespace g4
+
+extern "C" {
+
+long long granite4_attn_decode_scratch_bytes(int rows, int rows_per_group, int Hk, int max_len) {
+  if (rows <= 0 || rows_per_group <= 0 || rows_per_group > g4::kGroupRows || Hk <= 0 || max_len <= 0)
+    return -1;
+  const g4::SplitPlan s = g4::plan_splits(rows, rows_per_group, Hk, max_len);
+  return static_cast<long long>(s.groups) * Hk * s.splits * 16 * (g4::kAD + 2) * static_cast<long long>(sizeof(float));
+}
+
+int granite4_kernel_attn_decode_int8_paged(const uint16_t* d_q, const int8_t* d_cache_k,
+                                           const int8_t* d_cache_v, const float* d_k_scale,
+                                           const float* d_v_scale, const int* d_row_pos,
+                                           const int* const* d_row_pt, const int* d_pt, int rows,
+                                           int rows_per_group, int Hq, int Hk, int d, int stride,
+                                           int max_len, float scale, void* d_scratch,
+                                           long long scratch_bytes, uint16_t* d_out) {
+  const char* fn = "granite4_kernel_attn_decode_int8_paged";
+  if (d_q == nullptr || d_cache_k == nullptr || d_cache_v == nullptr || d_k_scale == nullptr ||
+      d_v_scale == nullptr || d_row_pos == nullptr || d_out == nullptr || rows <= 0 ||
+      rows_per_group <= 0 || rows_per_group > g4::kGroupRows || stride <= 0 || max_len <= 0 ||
+      max_len > stride || !std::isfinite(scale))
+    return g4::fail(fn, "invalid arguments");
+  if (d != g4::kAD || Hk <= 0 || Hq != g4::kGqa * Hk) return -1;  // engine/src/attention_gpu.h:18-19
+  if (!g4::aligned16(d_cache_k) || !g4::aligned16(d_cache_v) || !g4::aligned16(d_q))
+    return g4::fail(fn, "q and the caches must be 16-byte aligned");
+  const g4::SplitPlan s = g4::plan_splits(rows, rows_per_group, Hk, max_len);
+  if (s.groups > 65535) return g4::fail(fn, "too many row groups");
+  g4::AttnParams p{};
+  p.q = d_q, p.ck = d_cache_k, p.cv = d_cache_v, p.ks = d_k_scale, p.vs = d_v_scale;
+  p.row_pos = d_row_pos, p.row_pt = d_row_pt, p.pt = d_pt, p.out = d_out;
+  p.rows = rows, p.group_rows = rows_per_group, p.Hq = Hq, p.Hk = Hk, p.stride = stride;
+  p.splits = s.splits, p.split_len = s.split_len, p.max_len = max_len;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  if (s.splits > 1) {
+    const long long need = granite4_attn_decode_scratch_bytes(rows, rows_per_group, Hk, max_len);
+    if (d_scratch == nullptr || scratch_bytes < need || !g4::aligned16(d_scratch))
+      return g4::fail(fn, "scratch missing or smaller than granite4_attn_decode_scratch_bytes()");
+    p.part_o = static_cast<float*>(d_scratch);
+    p.part_ml = p.part_o + static_cast<size_t>(s.groups) * Hk * s.splits * 16 * g4::kAD;
+  }
+  cudaStream_t st = g4::current_stream();
+  {
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(g4::attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(g4::kAttnSmemBytes)));
+      attr_set[dev] = true;
+    }
+  }
+  G4_LAUNCH_PDL(fn, g4::attn_decode_kernel,
+                dim3(static_cast<unsigned>(s.splits), static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups)),
+                dim3(g4::kWarps * 32), g4::kAttnSmemBytes, st, p);
+  if (s.splits > 1)
+    G4_LAUNCH_PDL(fn, g4::attn_combine_kernel,
+                  dim3(static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups), 4u * rows_per_group),
+                  dim3(g4::kAD), 0, st, p);
+  return 0;
+}
+
+}  // extern "C"

@@ -280,6 +280,27 @@ def kv_move(src_rows, dst_rows, bits, cache_k, cache_v, k_scale, v_scale, layers
                                        Hk, stride, d)
 
 
+def attn_decode_scratch_bytes(rows, rows_per_group, Hk, max_len):
+    return capi.lib().granite4_attn_decode_scratch_bytes(rows, rows_per_group, Hk, max_len)
+
+
+def attn_decode_int8_paged(q, cache_k, cache_v, k_scale, v_scale, row_pos, Hq, Hk, d, stride, max_len,
+                           scale, out, rows_per_group=1, row_pt=None, pt=None, scratch=None):
+    """granite4_kernel_attn_decode_int8_paged. row_pt: int64 CUDA tensor of per-row table addresses
+    (``table.data_ptr()`` values), pt: one int32 table for every row; scratch: uint8 CUDA tensor of
+    at least attn_decode_scratch_bytes(...) bytes (allocated here when not given)."""
+    lib = _enter(q)
+    rows = q.shape[0]
+    need = lib.granite4_attn_decode_scratch_bytes(rows, rows_per_group, Hk, max_len)
+    if scratch is None and need > 0:
+        scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+    return lib.granite4_kernel_attn_decode_int8_paged(
+        _p(q, *_BF16_OK), _p(cache_k, torch.int8), _p(cache_v, torch.int8), _p(k_scale, torch.float32),
+        _p(v_scale, torch.float32), _p(row_pos, torch.int32), _p(row_pt, torch.int64),
+        _p(pt, torch.int32), rows, rows_per_group, Hq, Hk, d, stride, max_len, scale,
+        _p(scratch, torch.uint8), 0 if scratch is None else scratch.numel(), _p(out, *_BF16_OK))
+
+
 # ---- a4 -----------------------------------------------------------------------------------
 def prefill_silu_mul(gu, I, rows, act):
     """engine/src/prefill_gemm.h:105: gu float32 [rows][2 I] -> act bf16 [rows][I]."""

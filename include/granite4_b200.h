@@ -306,6 +306,35 @@ int granite4_kernel_kv_move(const int* src_rows, const int* dst_rows, int n, int
                             int layers, int Hk, int stride, int d);
 
 /* ------------------------------------------------------------------------ */
+/* Decode / verify attention over the int8 paged pool                        */
+/* ------------------------------------------------------------------------ */
+/* Added; the int8 multi-sequence mode of granite4::attn_split
+ * (engine/src/attention_gpu.h:15-68) as a C entry point. Row r of d_q
+ * [rows][Hq 128] (bf16, already rotated) is at position d_row_pos[r] of its
+ * sequence and attends to cache positions 0..d_row_pos[r]; position t of that
+ * sequence lives in pool row table[t], where table is d_row_pt[r] when
+ * d_row_pt is given (a device array of per-row device tables), else d_pt for
+ * every row, else the identity. rows_per_group (1..4) consecutive rows belong
+ * to ONE sequence (a verify step's rows; they share the first row's table) and
+ * read each cache tile once; use 1 for independent decode rows. The pool is
+ * what granite4_kernel_rope_kv_int8_paged writes: codes [Hk][stride][128] int8,
+ * scales [Hk][stride] f32. logits = scale * q . k. d_out [rows][Hq 128] bf16.
+ * max_len bounds every position + 1 (it sizes the split of the cache range and
+ * the scratch): d_scratch must hold granite4_attn_decode_scratch_bytes(...)
+ * bytes, 16-byte aligned (may be NULL when that returns a plan of one split,
+ * i.e. for short contexts with many rows). Only d == 128 and Hq == 4 Hk are
+ * built; anything else returns -1 like the reference's kernel. A row with a
+ * negative position gets zeros. */
+long long granite4_attn_decode_scratch_bytes(int rows, int rows_per_group, int Hk, int max_len);
+int granite4_kernel_attn_decode_int8_paged(const uint16_t* d_q, const int8_t* d_cache_k,
+                                           const int8_t* d_cache_v, const float* d_k_scale,
+                                           const float* d_v_scale, const int* d_row_pos,
+                                           const int* const* d_row_pt, const int* d_pt, int rows,
+                                           int rows_per_group, int Hq, int Hk, int d, int stride,
+                                           int max_len, float scale, void* d_scratch,
+                                           long long scratch_bytes, uint16_t* d_out);
+
+/* ------------------------------------------------------------------------ */
 /* a4. SwiGLU, bf16 and FP8 outputs                                          */
 /* ------------------------------------------------------------------------ */
 /* Kept: granite4::prefill_silu_mul, engine/src/prefill_gemm.h:105,

@@ -310,3 +310,59 @@ void g4o_argmax_rows(const uint16_t* logits, long rows, int V, int32_t* out) {
     out[r] = best;
   }
 }
+
+/* ------------------------------------------------------------------------ */
+/* Decode attention over the int8 pool (checker for the "next" row f1)        */
+/* ------------------------------------------------------------------------ */
+/* The reference's golden pipeline, engine/src/kernel_math.h:265-331, on cache rows
+ * dequantised the way its kernels do (engine/src/attention_split.cu:229-234:
+ * bf16(code * scale)): logits rounded to bf16, softmax with the maximum
+ * subtracted and the sum in double (:226-233), probabilities rounded to bf16,
+ * value accumulation in float, output rounded to bf16. */
+void g4o_attn_decode_int8(const uint16_t* q, const int8_t* ck, const int8_t* cv, const float* ks,
+                          const float* vs, const int32_t* row_pos, const int32_t* const* row_pt,
+                          long rows, int Hq, int Hk, int d, long stride, float scale,
+                          uint16_t* out) {
+  const int gh = Hq / Hk;
+  for (long r = 0; r < rows; ++r) {
+    const int len = row_pos[r] + 1;
+    const int32_t* pt = row_pt != NULL ? row_pt[r] : NULL;
+    for (int hq = 0; hq < Hq; ++hq) {
+      uint16_t* o = out + ((size_t)r * Hq + hq) * d;
+      if (len <= 0) {
+        memset(o, 0, (size_t)d * sizeof(uint16_t));
+        continue;
+      }
+      const int hkv = hq / gh;
+      const uint16_t* qh = q + ((size_t)r * Hq + hq) * d;
+      float* logit = (float*)malloc((size_t)len * sizeof(float));
+      float* prob = (float*)malloc((size_t)len * sizeof(float));
+      float m = -INFINITY;
+      for (int t = 0; t < len; ++t) {
+        const size_t row = (size_t)hkv * stride + (pt != NULL ? pt[t] : t);
+        float acc = 0.0f;
+        for (int i = 0; i < d; ++i) {
+          const float k = g4o_bf16_to_f32(g4o_f32_to_bf16(g4o_kv8_dequant(ck[row * d + i], ks[row])));
+          acc += k * g4o_bf16_to_f32(qh[i]);
+        }
+        logit[t] = g4o_bf16_to_f32(g4o_f32_to_bf16(scale * acc));
+        if (logit[t] > m) m = logit[t];
+      }
+      double sum = 0.0;
+      for (int t = 0; t < len; ++t) sum += exp((double)(logit[t] - m));
+      for (int t = 0; t < len; ++t)
+        prob[t] = g4o_bf16_to_f32(g4o_f32_to_bf16((float)(exp((double)(logit[t] - m)) / sum)));
+      for (int i = 0; i < d; ++i) {
+        float acc = 0.0f;
+        for (int t = 0; t < len; ++t) {
+          const size_t row = (size_t)hkv * stride + (pt != NULL ? pt[t] : t);
+          const float v = g4o_bf16_to_f32(g4o_f32_to_bf16(g4o_kv8_dequant(cv[row * d + i], vs[row])));
+          acc += prob[t] * v;
+        }
+        o[i] = g4o_f32_to_bf16(acc);
+      }
+      free(logit);
+      free(prob);
+    }
+  }
+}

@@ -115,6 +115,15 @@ void g4o_swiglu(const void* gate, const void* up, int in_is_f32, long ld, long r
  * it is, the device kernel (engine/src/forward_gpu.cu:284-333) skips NaN. */
 void g4o_argmax_rows(const uint16_t* logits, long rows, int V, int32_t* out);
 
+/* Decode attention over the int8 pool, one independent sequence per query row:
+ * row r attends to cache positions 0..row_pos[r], position t in pool row
+ * row_pt[r][t] (row_pt == NULL: t). The reference's golden pipeline
+ * (engine/src/kernel_math.h:265-331) over rows dequantised to bf16. */
+void g4o_attn_decode_int8(const uint16_t* q, const int8_t* ck, const int8_t* cv, const float* ks,
+                          const float* vs, const int32_t* row_pos, const int32_t* const* row_pt,
+                          long rows, int Hq, int Hk, int d, long stride, float scale,
+                          uint16_t* out);
+
 #ifdef __cplusplus
 }
 #endif

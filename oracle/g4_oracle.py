@@ -68,6 +68,8 @@ class Oracle:
                                    _P])
         f("swiglu", None, [_P, _P, C.c_int, C.c_long, C.c_long, C.c_int, _P])
         f("argmax_rows", None, [_P, C.c_long, C.c_int, _P])
+        f("attn_decode_int8", None, [_P, _P, _P, _P, _P, _P, _P, C.c_long, C.c_int, C.c_int, C.c_int,
+                                     C.c_long, C.c_float, _P])
 
     def _fn(self, name, res, args):
         fn = getattr(self._lib, self._p + name)
@@ -199,6 +201,23 @@ class Oracle:
         rows, V = logits.shape
         out = np.empty(rows, np.int32)
         self._c_argmax_rows(_ptr(np.ascontiguousarray(logits)), rows, V, _ptr(out))
+        return out
+
+    def attn_decode_int8(self, q, ck, cv, ks, vs, row_pos, row_tables, Hq, Hk, d, scale):
+        """q [rows][Hq d] bf16 bits; pool codes [Hk][stride][d] int8 + scales [Hk][stride];
+        row_tables: None (identity) or a list of int32 arrays, one position -> pool row table
+        per query row. Returns out [rows][Hq d] bf16 bits (golden bf16 pipeline)."""
+        rows = q.shape[0]
+        stride = ck.shape[1]
+        out = np.empty((rows, Hq * d), np.uint16)
+        pos = np.ascontiguousarray(row_pos, np.int32)
+        if row_tables is None:
+            tables = None
+        else:
+            keep = [np.ascontiguousarray(t, np.int32) for t in row_tables]
+            tables = (C.c_void_p * rows)(*[t.ctypes.data for t in keep])
+        self._c_attn_decode_int8(_ptr(q), _ptr(ck), _ptr(cv), _ptr(ks), _ptr(vs), _ptr(pos), tables,
+                                 rows, Hq, Hk, d, stride, scale, _ptr(out))
         return out
 
     # ---- the whole per-layer glue sequence over a slice of rows, for timing ---------

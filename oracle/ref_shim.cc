@@ -190,6 +190,38 @@ void g4ref_swiglu(const void* gate, const void* up, int in_is_f32, long ld, long
     }
 }
 
+// The reference's golden attention (gqa_attention_bf16, kernel_math.h:312-331) on the cache rows
+// of each query row's sequence, gathered through its table and dequantised to bf16 as the
+// reference's attention kernels do (attention_split.cu:229-234).
+void g4ref_attn_decode_int8(const std::uint16_t* q, const std::int8_t* ck, const std::int8_t* cv,
+                            const float* ks, const float* vs, const std::int32_t* row_pos,
+                            const std::int32_t* const* row_pt, long rows, int Hq, int Hk, int d,
+                            long stride, float scale, std::uint16_t* out) {
+  for (long r = 0; r < rows; ++r) {
+    const int len = row_pos[r] + 1;
+    std::uint16_t* o = out + static_cast<std::size_t>(r) * Hq * d;
+    if (len <= 0) {
+      std::memset(o, 0, static_cast<std::size_t>(Hq) * d * sizeof(std::uint16_t));
+      continue;
+    }
+    std::vector<std::uint16_t> k(static_cast<std::size_t>(Hk) * len * d), v(k.size());
+    for (int h = 0; h < Hk; ++h)
+      for (int t = 0; t < len; ++t) {
+        const std::size_t row = static_cast<std::size_t>(h) * stride + (row_pt != nullptr ? row_pt[r][t] : t);
+        for (int i = 0; i < d; ++i) {
+          k[(static_cast<std::size_t>(h) * len + t) * d + i] =
+              f32_to_bf16_host(kv8_dequant_host(ck[row * d + i], ks[row]));
+          v[(static_cast<std::size_t>(h) * len + t) * d + i] =
+              f32_to_bf16_host(kv8_dequant_host(cv[row * d + i], vs[row]));
+        }
+      }
+    std::vector<std::uint16_t> res;
+    gqa_attention_bf16(q + static_cast<std::size_t>(r) * Hq * d, k.data(), v.data(), scale, Hq, Hk, d, len,
+                       &res);
+    std::memcpy(o, res.data(), res.size() * sizeof(std::uint16_t));
+  }
+}
+
 void g4ref_argmax_rows(const std::uint16_t* logits, long rows, int V, std::int32_t* out) {
   std::vector<float> f(V);
   for (long r = 0; r < rows; ++r) {

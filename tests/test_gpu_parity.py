@@ -1152,3 +1152,148 @@ def test_kv_move_all_layers_in_order(K, bits):
     assert K.kv_move([5, 9], [9, 3], bits, ck, cv, ks, vs, layers, hk, stride, d) == -1  # reads an overwritten row
     assert K.kv_move([64], [3], bits, ck, cv, ks, vs, layers, hk, stride, d) == -1       # outside the pool
     assert K.kv_move(list(range(9)), list(range(9)), bits, ck, cv, ks, vs, layers, hk, stride, d) == -1
+
+
+# =========================================================================== decode attention
+ATT_TOL = 0.03  # absolute; the reference's own bar for its split attention (engine/tests/test_kernels.cu:2055)
+
+
+def _bf16_to_f32_np(bits):
+    return (bits.astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def _attn_f64(q, ck, cv, ks, vs, pos, tables, scale):
+    """Unrounded float64 evaluation (no bf16 steps), [rows][Hq][d]."""
+    rows = q.shape[0]
+    qf = _bf16_to_f32_np(q).astype(np.float64).reshape(rows, Hq, D)
+    out = np.zeros((rows, Hq, D))
+    for r in range(rows):
+        if pos[r] < 0:
+            continue
+        sel = np.arange(pos[r] + 1) if tables is None else tables[r][:pos[r] + 1]
+        for h in range(Hq):
+            k = ck[h // 4, sel].astype(np.float64) * ks[h // 4, sel, None]
+            v = cv[h // 4, sel].astype(np.float64) * vs[h // 4, sel, None]
+            lg = scale * (k @ qf[r, h])
+            p = np.exp(lg - lg.max())
+            out[r, h] = (p / p.sum()) @ v
+    return out
+
+
+def _att_pool(seed, stride):
+    rng = np.random.default_rng(seed)
+    ck = rng.integers(-127, 128, (Hk, stride, D), dtype=np.int8)
+    cv = rng.integers(-127, 128, (Hk, stride, D), dtype=np.int8)
+    ks = (rng.random((Hk, stride), dtype=np.float32) * 0.02 + 0.005).astype(np.float32)
+    vs = (rng.random((Hk, stride), dtype=np.float32) * 0.02 + 0.005).astype(np.float32)
+    return ck, cv, ks, vs
+
+
+def test_attention_independent_decode_rows_per_row_tables(K, port):
+    """Seven sequences in one step, each row with its own position and page table; the cache range
+    is split over many CTAs (flash-decoding) and merged by the second kernel."""
+    stride = max_len = 4096
+    ck, cv, ks, vs = _att_pool(31, stride)
+    pos = np.array([0, 15, 16, 63, 64, 1000, 4095], np.int32)
+    rows = len(pos)
+    q = rand_bf16(1700, (rows, Hq * D), 2.0)
+    rng = np.random.default_rng(32)
+    tables = [rng.permutation(stride).astype(np.int32) for _ in range(rows)]
+    d_tables = [dev(t) for t in tables]
+    row_pt = torch.tensor([t.data_ptr() for t in d_tables], dtype=torch.int64, device=DEV)
+    out = empty_bf16(rows, Hq * D)
+    scale = 1.0 / 128
+    assert K.attn_decode_scratch_bytes(rows, 1, Hk, max_len) > 0
+    assert K.attn_decode_int8_paged(dev(q), dev(ck), dev(cv), dev(ks), dev(vs), dev(pos), Hq, Hk, D, stride,
+                                    max_len, scale, out, rows_per_group=1, row_pt=row_pt) == 0
+    got = _bf16_to_f32_np(host(out)).reshape(rows, Hq, D)
+    want = _bf16_to_f32_np(port.attn_decode_int8(q, ck, cv, ks, vs, pos, tables, Hq, Hk, D, scale))
+    exact = _attn_f64(q, ck, cv, ks, vs, pos, tables, scale)
+    err_oracle = np.abs(got - want.reshape(rows, Hq, D)).max()
+    err_exact = np.abs(got - exact).max()
+    print(f"attention: max |gpu - golden bf16 pipeline| {err_oracle:.4f}, max |gpu - float64| {err_exact:.5f}")
+    assert err_oracle < ATT_TOL
+    assert err_exact < 0.01  # the kernel rounds less than the golden pipeline does
+
+
+def test_attention_verify_group_shares_one_sequence(K, port):
+    """Four consecutive rows of one sequence (a verify step) in one CTA tile: each row sees its own
+    causal prefix; one shared table; 6 rows with groups of 4 leave a ragged last group."""
+    stride, max_len, base = 2048, 1500, 1200
+    ck, cv, ks, vs = _att_pool(41, stride)
+    rows = 6
+    pos = np.array([base, base + 1, base + 2, base + 3, 77, 78], np.int32)
+    q = rand_bf16(1800, (rows, Hq * D), 2.0)
+    table = np.random.default_rng(42).permutation(stride).astype(np.int32)
+    out = empty_bf16(rows, Hq * D)
+    # rows 0-3 and rows 4-5 are two sequences that happen to share a table here
+    for scale, check_golden in ((1.0 / 128, True), (0.0883, False)):
+        # 1/128 is Granite's attention multiplier (engine/src/kernel_math.h:13). With 1/sqrt(128) the
+        # softmax is peaked and the golden pipeline's own bf16 rounding of the logits moves its
+        # result by more than the 0.03 bar, so there the unrounded evaluation is the only judge.
+        assert K.attn_decode_int8_paged(dev(q), dev(ck), dev(cv), dev(ks), dev(vs), dev(pos), Hq, Hk, D,
+                                        stride, max_len, scale, out, rows_per_group=4, pt=dev(table)) == 0
+        got = _bf16_to_f32_np(host(out)).reshape(rows, Hq, D)
+        assert np.abs(got - _attn_f64(q, ck, cv, ks, vs, pos, [table] * rows, scale)).max() < 0.01
+        if check_golden:
+            want = _bf16_to_f32_np(port.attn_decode_int8(q, ck, cv, ks, vs, pos, [table] * rows, Hq, Hk, D, scale))
+            assert np.abs(got - want.reshape(rows, Hq, D)).max() < ATT_TOL
+
+
+def test_attention_short_context_single_split_and_edge_rows(K, port):
+    """Contexts of at most 64 positions run as one split (no scratch, no merge kernel); identity
+    table; a negative position gives zeros."""
+    stride = max_len = 64
+    ck, cv, ks, vs = _att_pool(51, stride)
+    pos = np.array([0, 1, 7, 8, 15, 16, 17, 31, 32, 33, 47, 48, 62, 63, -1, 5], np.int32)
+    rows = len(pos)
+    q = rand_bf16(1900, (rows, Hq * D), 2.0)
+    out = torch.full((rows, Hq * D), 0x7FC0, dtype=torch.int16, device=DEV)
+    scale = 1.0 / 128
+    assert K.attn_decode_int8_paged(dev(q), dev(ck), dev(cv), dev(ks), dev(vs), dev(pos), Hq, Hk, D, stride,
+                                    max_len, scale, out, rows_per_group=1) == 0
+    got = _bf16_to_f32_np(host(out)).reshape(rows, Hq, D)
+    want = _bf16_to_f32_np(port.attn_decode_int8(q, ck, cv, ks, vs, pos, None, Hq, Hk, D, scale))
+    assert np.abs(got - want.reshape(rows, Hq, D)).max() < ATT_TOL
+    assert (host(out)[14] == 0).all()
+    # one position: the output is that position's dequantised V row
+    v0 = cv[:, 0].astype(np.float32) * vs[:, 0, None]
+    assert np.abs(got[0].reshape(Hk, 4, D) - v0[:, None, :]).max() < 0.02
+    # shapes the kernel does not build are refused like the reference's (-1)
+    assert K.attn_decode_int8_paged(dev(q), dev(ck), dev(cv), dev(ks), dev(vs), dev(pos), 16, Hk, D, stride,
+                                    max_len, scale, out) == -1
+    assert K.attn_decode_int8_paged(dev(q), dev(ck), dev(cv), dev(ks), dev(vs), dev(pos), Hq, Hk, 64, stride,
+                                    max_len, scale, out) == -1
+
+
+def test_attention_reads_what_the_rope_kv_kernel_wrote(K, port):
+    """The layout end to end on the device: a 300-token prefill chunk is rotated and quantised into
+    a paged pool by granite4_kernel_rope_kv_int8_paged, then one decode row attends over it. The
+    expected value is computed from the rotated K / raw V before quantisation, so the bound is the
+    int8 quantisation error, not a rounding of the kernel."""
+    n, stride, max_pos = 300, 512, 512
+    qkv = rand_bf16(2000, (n, 48 * D), 1.0)
+    table = np.random.default_rng(61).permutation(stride).astype(np.int32)
+    pos = np.arange(n, dtype=np.int32)
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+    ck, cv, ks, vs = _pool(stride)
+    q_rot = empty_bf16(n, Hq * D)
+    assert K.rope_kv_int8_paged(dev(qkv), t.cos, t.sin, dev(pos), dev(table[:n].copy()), Hq, Hk, D, stride,
+                                max_pos, 0, q_rot, ck, cv, ks, vs) == 0
+    # the last token's rotated q attends over all 300 positions
+    out = empty_bf16(1, Hq * D)
+    scale = 1.0 / 128
+    assert K.attn_decode_int8_paged(q_rot[n - 1:n].contiguous(), ck, cv, ks, vs, dev(np.array([n - 1], np.int32)),
+                                    Hq, Hk, D, stride, max_pos, scale, out, pt=dev(table)) == 0
+    got = _bf16_to_f32_np(host(out)).reshape(Hq, D)
+    cos, sin = port.rope_tables(1e7, D, max_pos)
+    krot = _bf16_to_f32_np(_rope_heads(port, np.ascontiguousarray(qkv[:, Hq * D:(Hq + Hk) * D]), cos[:n], sin[:n],
+                                      Hk, D)).astype(np.float64).reshape(n, Hk, D)
+    v = _bf16_to_f32_np(np.ascontiguousarray(qkv[:, (Hq + Hk) * D:])).astype(np.float64).reshape(n, Hk, D)
+    qf = _bf16_to_f32_np(host(q_rot)[n - 1]).astype(np.float64).reshape(Hq, D)
+    for h in range(Hq):
+        lg = scale * (krot[:, h // 4] @ qf[h])
+        p = np.exp(lg - lg.max())
+        want = (p / p.sum()) @ v[:, h // 4]
+        assert np.abs(got[h] - want).max() < 0.03
+    t.close()

@@ -294,3 +294,42 @@ def test_greedy_pick_known_answers_and_reference(port, ref):
     assert (got < 500).all()
     if ref is not None:
         assert (got == ref.argmax_rows(logits)).all()
+
+
+def _random_pool(seed, Hk, stride, d):
+    rng = np.random.default_rng(seed)
+    ck = rng.integers(-127, 128, (Hk, stride, d), dtype=np.int8)
+    cv = rng.integers(-127, 128, (Hk, stride, d), dtype=np.int8)
+    ks = (rng.random((Hk, stride), dtype=np.float32) * 0.02 + 0.005).astype(np.float32)
+    vs = (rng.random((Hk, stride), dtype=np.float32) * 0.02 + 0.005).astype(np.float32)
+    return ck, cv, ks, vs
+
+
+def test_attention_oracle_matches_reference_golden_pipeline(port, ref):
+    """Decode attention over an int8 pool: the port restates gqa_attention_bf16
+    (engine/src/kernel_math.h:265-331) over rows dequantised to bf16; bit for bit against the
+    reference's own function, and close to an unrounded float64 evaluation."""
+    Hq, Hk, d, stride = 8, 2, 128, 96
+    ck, cv, ks, vs = _random_pool(21, Hk, stride, d)
+    rng = np.random.default_rng(22)
+    q = (rng.standard_normal((3, Hq * d)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    pos = np.array([0, 40, 95], np.int32)
+    tables = [rng.permutation(stride).astype(np.int32) for _ in range(3)]
+    scale = 1.0 / 128
+    got = port.attn_decode_int8(q, ck, cv, ks, vs, pos, tables, Hq, Hk, d, scale)
+    if ref is not None:
+        assert (got == ref.attn_decode_int8(q, ck, cv, ks, vs, pos, tables, Hq, Hk, d, scale)).all()
+    qf = (q.astype(np.uint32) << 16).view(np.float32).astype(np.float64).reshape(3, Hq, d)
+    gotf = (got.astype(np.uint32) << 16).view(np.float32).reshape(3, Hq, d)
+    for r in range(3):
+        rows_ = tables[r][:pos[r] + 1]
+        for h in range(Hq):
+            k = ck[h // 4, rows_].astype(np.float64) * ks[h // 4, rows_, None]
+            v = cv[h // 4, rows_].astype(np.float64) * vs[h // 4, rows_, None]
+            lg = scale * (k @ qf[r, h])
+            p = np.exp(lg - lg.max())
+            want = (p / p.sum()) @ v
+            assert np.abs(gotf[r, h] - want).max() < 0.03  # the reference's own device tolerance
+    # no cache positions (negative position): zeros
+    z = port.attn_decode_int8(q[:1], ck, cv, ks, vs, np.array([-1], np.int32), None, Hq, Hk, d, scale)
+    assert (z == 0).all()
