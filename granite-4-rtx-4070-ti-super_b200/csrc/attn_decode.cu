@@ -52,18 +52,15 @@ constexpr int kGroupRows = 4;  // query rows per CTA (4 x 4 = the 16 rows of the
 constexpr int kSplitAlign = kTile * kWarps;
 constexpr int kCtasPerSm = 3;  // register and shared-memory budget of the main kernel
 
-// Shared memory of one warp. Raw code rows arrive by 16-byte asynchronous copies (cp.async),
-// kStages tiles deep, so the bytes in flight occupy no registers. K rows are padded to 144 bytes:
-// the 32-bit fragment loads of the 32 lanes (8 positions x 4 k-groups) then hit 32 different
-// banks. V needs its tile transposed for the second contraction, which ldmatrix.trans does on
-// 16-bit elements, so the V codes are converted into an fp16 tile first (rows padded to 272 bytes).
-constexpr int kStages = 3;
-constexpr int kKPitch = kAD + 16;            // bytes per raw K row
-constexpr int kRawK = kTile * kKPitch;       // 2304
-constexpr int kRawV = kTile * kAD;           // 2048
-constexpr int kVPitch = kAD + 8;             // halves per fp16 V row
-constexpr int kVTile = kTile * kVPitch * 2;  // 4352 bytes
-constexpr int kWarpSmem = kStages * (kRawK + kRawV) + kVTile;  // 17408
+// Shared memory of one warp: kStages tiles of raw K and V code rows, filled by 16-byte asynchronous
+// copies (cp.async), so the bytes in flight occupy no registers. Rows are padded to 144 bytes: the
+// 32-bit K fragment loads of the 32 lanes (8 positions x 4 k-groups) and the eight 16-byte row
+// pieces of an ldmatrix then hit different banks. Both mma operands are built from the raw bytes
+// in registers; no converted copy of a tile is ever written back to shared memory.
+constexpr int kStages = 4;
+constexpr int kPitch = kAD + 16;          // bytes per raw code row
+constexpr int kRawTile = kTile * kPitch;  // 2304
+constexpr int kWarpSmem = kStages * 2 * kRawTile;  // 18432
 constexpr size_t kAttnSmemBytes = static_cast<size_t>(kWarps) * kWarpSmem;
 static_assert(kWarpSmem >= (16 * kAD + 32) * 4, "a warp parks its final state in its own block");
 
@@ -100,17 +97,24 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "r"(addr));
 }
 
-// Four int8 codes (one 32-bit word) -> four fp16 values, exactly: bias each byte to unsigned,
-// drop it into the mantissa of 1024.0 (0x6400) and subtract 1152.
+// Four int8 codes (one 32-bit word) -> four fp16 values code + 1152, exactly: bias each byte to
+// unsigned (code + 128) and drop it into the mantissa of 1024.0 (0x6400). The constant 1152 is not
+// subtracted per element (that would cost as much again): a contraction sum_k a_k (c_k + 1152)
+// equals sum_k a_k c_k + 1152 sum_k a_k, and sum_k a_k is one number per tile row (the sum of
+// the q row, computed once; the sum of the probabilities, which one extra mma against a column
+// of ones accumulates). Products of two fp16 values are exact in the f32 accumulator and the
+// offset term is ~30 times the signal, so the f32 sum loses under 1e-5 relative to it.
+constexpr float kCodeBias = 1152.0f;
 __device__ __forceinline__ void codes4_to_half(uint32_t w, uint32_t& lo, uint32_t& hi) {
   w ^= 0x80808080u;
-  const uint32_t a = __byte_perm(w, 0x64646464u, 0x4140);
-  const uint32_t b = __byte_perm(w, 0x64646464u, 0x4342);
-  const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
-  const __half2 x = __hsub2(*reinterpret_cast<const __half2*>(&a), bias);
-  const __half2 y = __hsub2(*reinterpret_cast<const __half2*>(&b), bias);
-  lo = *reinterpret_cast<const uint32_t*>(&x);
-  hi = *reinterpret_cast<const uint32_t*>(&y);
+  lo = __byte_perm(w, 0x64646464u, 0x4140);
+  hi = __byte_perm(w, 0x64646464u, 0x4342);
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
@@ -139,9 +143,8 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
   const int r0 = grp * p.group_rows;
   const int nrows = min(p.group_rows, p.rows - r0);
   unsigned char* wsm = s_dyn + static_cast<size_t>(warp) * kWarpSmem;
-  unsigned char* raw_k = wsm;                    // [kStages][16][144]
-  unsigned char* raw_v = wsm + kStages * kRawK;  // [kStages][16][128]
-  __half(*vtile)[kVPitch] = reinterpret_cast<__half(*)[kVPitch]>(wsm + kStages * (kRawK + kRawV));
+  unsigned char* raw_k = wsm;                       // [kStages][16][144]
+  unsigned char* raw_v = wsm + kStages * kRawTile;  // [kStages][16][144]
 
   // positions of the group's rows; the mma rows g and g + 8 belong to query rows g / 4 and 2 + g / 4
   int pos_lo = -1, pos_hi = -1, pos_max = -1;
@@ -164,6 +167,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
   // bytes: one 32-bit shared-memory load per mma.
   uint32_t qa[8][4];
   float logit_scale;
+  float q_off[2];  // rows g and g + 8
   {
     float qf[8][8];  // per k-step: row g dims 4t, 4t+1 | row g+8 same | row g dims 4t+2, 4t+3 | row g+8 same
     float qmax = 0.0f;
@@ -197,12 +201,36 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
       qa[kk][2] = pack_half2(qf[kk][4] * qdown, qf[kk][5] * qdown);
       qa[kk][3] = pack_half2(qf[kk][6] * qdown, qf[kk][7] * qdown);
     }
+    // 1152 x the sum of each q row as the mma sees it (the fp16 values), for the code offset
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qa[kk][hr]));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qa[kk][2 + hr]));
+        sum += (a.x + a.y) + (b.x + b.y);
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      q_off[hr] = kCodeBias * sum;
+    }
   }
 
+  // O accumulators: o[2 b + par] is the n-tile of 16-dim block b whose column c stands for dim
+  // 16 b + 2 c + par (see the V operand below); a thread's four values of a block (par 0 / 1,
+  // columns 2 t / 2 t + 1) are therefore the four consecutive dims 16 b + 4 t .. + 3.
   float o[16][4];
 #pragma unroll
   for (int nd = 0; nd < 16; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.0f;
+  float osum[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // P against a column of ones: sum of the fp16 probabilities
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  // the lowest position among the group's rows: tiles entirely below it need no causal mask
+  int pos_min = pos_max;
+  for (int j = 0; j < nrows; ++j) {
+    const int pj = __ldg(p.row_pos + r0 + j);
+    pos_min = min(pos_min, pj < 0 ? -1 : min(pj, p.max_len - 1));
+  }
   const size_t head_row0 = static_cast<size_t>(hkv) * p.stride;
 
   // ---- gather. Lane l (and l + 16) looks up the pool row of tile position l and fetches that
@@ -212,7 +240,6 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
   // i + 1 and i + 2 are in flight into this warp's stages and the table entries of tile i + 3 are
   // being looked up, so neither of the two dependent global latencies (table -> row address ->
   // codes) is exposed.
-  const int n_load = lane >> 1, h_load = lane & 1;  // this lane's part of the V conversion
   constexpr int kStep = kTile * kWarps;
   auto table_row = [&](int tile0) -> int {
     const int tpos = tile0 + (lane & 15);
@@ -228,8 +255,8 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
       const int pr = __shfl_sync(0xffffffffu, prow, n);
       const bool have = tile0 + n < t_end;
       const size_t off = (head_row0 + pr) * kAD + piece;
-      cp_async16(raw_k + stage * kRawK + n * kKPitch + piece, p.ck + off, have);
-      cp_async16(raw_v + stage * kRawV + n * kAD + piece, p.cv + off, have);
+      cp_async16(raw_k + stage * kRawTile + n * kPitch + piece, p.ck + off, have);
+      cp_async16(raw_v + stage * kRawTile + n * kPitch + piece, p.cv + off, have);
     }
     cp_async_commit();
     const bool mine = tile0 + (lane & 15) < t_end;
@@ -239,48 +266,34 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
   const int t_first = t_begin + warp * kTile;
   float sk_q[kStages], sv_q[kStages];  // scales of the tiles in flight, oldest first (lane n: position n)
   {
-    const int pr0 = table_row(t_first), pr1 = table_row(t_first + kStep);
+    const int pr0 = table_row(t_first), pr1 = table_row(t_first + kStep), pr2 = table_row(t_first + 2 * kStep);
     gather(0, t_first, pr0, sk_q[0], sv_q[0]);
     gather(1, t_first + kStep, pr1, sk_q[1], sv_q[1]);
+    gather(2, t_first + 2 * kStep, pr2, sk_q[2], sv_q[2]);
   }
-  int prow_next = table_row(t_first + 2 * kStep);
+  int prow_next = table_row(t_first + 3 * kStep);
   int stage = 0;
 
   for (int t0 = t_first; t0 < t_end; t0 += kStep) {
-    cp_async_wait<1>();  // all but the newest group have landed: tile i is in shared memory
-    __syncwarp();        // ... for every lane, and every lane is done with tile i - 1
-    // tile i + 2 goes into the stage tile i - 1 was read out of
-    gather((stage + 2) % kStages, t0 + 2 * kStep, prow_next, sk_q[2], sv_q[2]);
-    prow_next = table_row(t0 + 3 * kStep);
-
-    // ---- V: this lane's 64 codes -> fp16 tile (for the transposing fragment loads further down)
-    {
-      const unsigned char* src = raw_v + stage * kRawV + n_load * kAD + h_load * 64;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(src + i * 16);
-        uint32_t h[8];
-        codes4_to_half(raw.x, h[0], h[1]);
-        codes4_to_half(raw.y, h[2], h[3]);
-        codes4_to_half(raw.z, h[4], h[5]);
-        codes4_to_half(raw.w, h[6], h[7]);
-        uint4* dst = reinterpret_cast<uint4*>(&vtile[n_load][h_load * 64 + i * 16]);
-        dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
-        dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
-      }
-    }
+    cp_async_wait<kStages - 2>();  // all but the newest two groups have landed: tile i is in shared memory
+    __syncwarp();                  // ... for every lane, and every lane is done with tile i - 1
+    // tile i + 3 goes into the stage tile i - 1 was read out of
+    gather((stage + kStages - 1) % kStages, t0 + (kStages - 1) * kStep, prow_next, sk_q[kStages - 1],
+           sv_q[kStages - 1]);
+    prow_next = table_row(t0 + kStages * kStep);
     const float sk_cur = sk_q[0], sv_cur = sv_q[0];
-    sk_q[0] = sk_q[1], sv_q[0] = sv_q[1];
-    sk_q[1] = sk_q[2], sv_q[1] = sv_q[2];
+#pragma unroll
+    for (int i = 0; i + 1 < kStages; ++i) sk_q[i] = sk_q[i + 1], sv_q[i] = sv_q[i + 1];
 
     // ---- S = Q K^T over the tile: two 8-position column blocks, K operands straight from the
     // raw codes (two accumulators per block halve the dependent mma chain)
     float s[2][4];
-    const unsigned char* kstage = raw_k + stage * kRawK;
+    const unsigned char* kstage = raw_k + stage * kRawTile;
+    const unsigned char* vstage = raw_v + stage * kRawTile;
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       float sa[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      const unsigned char* krow = kstage + (nt * 8 + g) * kKPitch + 4 * t;
+      const unsigned char* krow = kstage + (nt * 8 + g) * kPitch + 4 * t;
 #pragma unroll
       for (int kk = 0; kk < 8; kk += 2) {
         uint32_t b0, b1, c0, c1;
@@ -298,17 +311,21 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
     float pr[2][4];
     float tile_max[2] = {-INFINITY, -INFINITY};
     float svn[2][2];
+    const bool unmasked = t0 + kTile <= t_end && t0 + kTile - 1 <= pos_min;  // warp-uniform
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int n = nt * 8 + 2 * t + e;
-        const float skn = __shfl_sync(0xffffffffu, sk_cur, n);
+        const float f = __shfl_sync(0xffffffffu, sk_cur, n) * logit_scale;
         svn[nt][e] = __shfl_sync(0xffffffffu, sv_cur, n);
-        const int tp = t0 + n;
-        const float f = skn * logit_scale;
-        const float a = (tp <= pos_lo && tp < t_end) ? s[nt][e] * f : -INFINITY;
-        const float b = (tp <= pos_hi && tp < t_end) ? s[nt][2 + e] * f : -INFINITY;
+        float a = (s[nt][e] - q_off[0]) * f;
+        float b = (s[nt][2 + e] - q_off[1]) * f;
+        if (!unmasked) {
+          const int tp = t0 + n;
+          if (tp > pos_lo || tp >= t_end) a = -INFINITY;
+          if (tp > pos_hi || tp >= t_end) b = -INFINITY;
+        }
         s[nt][e] = a, s[nt][2 + e] = b;
         tile_max[0] = fmaxf(tile_max[0], a);
         tile_max[1] = fmaxf(tile_max[1], b);
@@ -321,14 +338,14 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_new = fmaxf(m_run[hr], mx);
-      corr[hr] = (m_new == -INFINITY) ? 1.0f : exp2f(m_run[hr] - m_new);  // exp2f(-inf) = 0
+      corr[hr] = (m_new == -INFINITY) ? 1.0f : ex2_approx(m_run[hr] - m_new);  // 2^-inf = 0
       const float base = (m_new == -INFINITY) ? 0.0f : m_new;
       float sum = 0.0f;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const float pv = exp2f(s[nt][2 * hr + e] - base);  // masked: exp2f(-inf) = 0
+          const float pv = ex2_approx(s[nt][2 * hr + e] - base);  // masked: 2^-inf = 0
           pr[nt][2 * hr + e] = pv;
           sum += pv;
         }
@@ -342,6 +359,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
         o[nd][0] *= corr[0], o[nd][1] *= corr[0];
         o[nd][2] *= corr[1], o[nd][3] *= corr[1];
       }
+      osum[0] *= corr[0], osum[1] *= corr[0], osum[2] *= corr[1], osum[3] *= corr[1];
     }
     // ---- O += (P diag(v_scale)) V: P's accumulator layout is the A-operand layout ------------------
     uint32_t pa[4];
@@ -349,15 +367,31 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
     pa[1] = pack_half2(pr[0][2] * svn[0][0], pr[0][3] * svn[0][1]);
     pa[2] = pack_half2(pr[1][0] * svn[1][0], pr[1][1] * svn[1][1]);
     pa[3] = pack_half2(pr[1][2] * svn[1][0], pr[1][3] * svn[1][1]);
-    __syncwarp();  // every lane's part of the fp16 V tile is written
+    // V operand straight from the raw bytes: the tile is read as 16-bit elements (two adjacent
+    // dims of one position), transposed by ldmatrix; a register then holds positions 2 t, 2 t + 1 for
+    // dims 2 g and 2 g + 1 of a 16-dim block, and one byte permute each picks the (position pair,
+    // dim) halves of the even-dim and of the odd-dim n-tile, already in fp16 form (code + 1152).
 #pragma unroll
-    for (int nd = 0; nd < 16; nd += 2) {
-      // matrices: (pos 0-7, dims nd*8..), (pos 8-15, same dims), (pos 0-7, dims (nd+1)*8..), (pos 8-15, ..)
-      uint32_t b[4];
-      ldmatrix_x4_trans(b, &vtile[lane & 15][(nd + (lane >> 4)) * 8]);
-      mma_f16(o[nd], pa, b[0], b[1]);
-      mma_f16(o[nd + 1], pa, b[2], b[3]);
+    for (int blk = 0; blk < 8; blk += 2) {
+      // matrices: (pos 0-7, block blk), (pos 8-15, block blk), (pos 0-7, block blk + 1), (pos 8-15, ..)
+      uint32_t r[4];
+      ldmatrix_x4_trans(r, vstage + (lane & 15) * kPitch + (blk + (lane >> 4)) * 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) r[i] ^= 0x80808080u;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t lo = r[2 * u], hi = r[2 * u + 1];  // positions 0-7 / 8-15 of block blk + u
+        mma_f16(o[2 * (blk + u)], pa, __byte_perm(lo, 0x64646464u, 0x4240), __byte_perm(hi, 0x64646464u, 0x4240));
+        mma_f16(o[2 * (blk + u) + 1], pa, __byte_perm(lo, 0x64646464u, 0x4341), __byte_perm(hi, 0x64646464u, 0x4341));
+      }
     }
+    mma_f16(osum, pa, 0x3c003c00u, 0x3c003c00u);  // the column of ones
+  }
+  // take the code offset out of the accumulators: O = O_mma - 1152 * sum(p)
+#pragma unroll
+  for (int nd = 0; nd < 16; ++nd) {
+    o[nd][0] -= kCodeBias * osum[0], o[nd][1] -= kCodeBias * osum[0];
+    o[nd][2] -= kCodeBias * osum[2], o[nd][3] -= kCodeBias * osum[2];
   }
 
   cp_async_wait<0>();  // nothing of this thread's may still be landing when the memory is reused
@@ -371,9 +405,12 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
   float* wo = reinterpret_cast<float*>(wsm);  // [16][128] floats
   float* wml = wo + 16 * kAD;                 // [16][2]
 #pragma unroll
-  for (int nd = 0; nd < 16; ++nd) {
-    *reinterpret_cast<float2*>(wo + g * kAD + nd * 8 + 2 * t) = make_float2(o[nd][0], o[nd][1]);
-    *reinterpret_cast<float2*>(wo + (g + 8) * kAD + nd * 8 + 2 * t) = make_float2(o[nd][2], o[nd][3]);
+  for (int blk = 0; blk < 8; ++blk) {
+    // dims 16 blk + 4 t + {0, 1, 2, 3} = (even tile col 2t, odd tile col 2t, even col 2t+1, odd col 2t+1)
+    *reinterpret_cast<float4*>(wo + g * kAD + blk * 16 + 4 * t) =
+        make_float4(o[2 * blk][0], o[2 * blk + 1][0], o[2 * blk][1], o[2 * blk + 1][1]);
+    *reinterpret_cast<float4*>(wo + (g + 8) * kAD + blk * 16 + 4 * t) =
+        make_float4(o[2 * blk][2], o[2 * blk + 1][2], o[2 * blk][3], o[2 * blk + 1][3]);
   }
   if (t == 0) {
     wml[g * 2] = m_run[0], wml[g * 2 + 1] = l_run[0];
