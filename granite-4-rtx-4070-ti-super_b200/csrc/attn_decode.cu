@@ -312,6 +312,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
     float tile_max[2] = {-INFINITY, -INFINITY};
     float svn[2][2];
     const bool unmasked = t0 + kTile <= t_end && t0 + kTile - 1 <= pos_min;  // warp-uniform
+    const bool upper = nrows > 2;  // tile rows 8..15 carry query rows 2 and 3; a decode row leaves them empty
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
@@ -320,7 +321,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
         const float f = __shfl_sync(0xffffffffu, sk_cur, n) * logit_scale;
         svn[nt][e] = __shfl_sync(0xffffffffu, sv_cur, n);
         float a = (s[nt][e] - q_off[0]) * f;
-        float b = (s[nt][2 + e] - q_off[1]) * f;
+        float b = upper ? (s[nt][2 + e] - q_off[1]) * f : -INFINITY;
         if (!unmasked) {
           const int tp = t0 + n;
           if (tp > pos_lo || tp >= t_end) a = -INFINITY;
@@ -334,6 +335,11 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
     float corr[2];
 #pragma unroll
     for (int hr = 0; hr < 2; ++hr) {
+      if (hr == 1 && !upper) {
+        corr[1] = 1.0f;
+        pr[0][2] = pr[0][3] = pr[1][2] = pr[1][3] = 0.0f;
+        continue;
+      }
       float mx = tile_max[hr];
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -476,19 +482,44 @@ __global__ void __launch_bounds__(kAD) attn_combine_kernel(const AttnParams p) {
   if ((dim & 31) == 0) s_red[1][dim >> 5] = l;
   __syncthreads();
   l = (s_red[1][0] + s_red[1][1]) + (s_red[1][2] + s_red[1][3]);
-  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  const float* po = p.part_o + (part0 * 16 + m) * kAD + dim;
-  const size_t split_pitch = static_cast<size_t>(16) * kAD;
-  int s = 0;
-  for (; s + 4 <= p.splits; s += 4) {
+  // each warp sums a quarter of the splits for all 128 dims (lane = four dims), eight loads in
+  // flight per lane; the four partial sums meet in shared memory
+  __shared__ float4 s_acc[kAD / 32][32];
+  const int warp = dim >> 5, lane = dim & 31;
+  const float4* po = reinterpret_cast<const float4*>(p.part_o + (part0 * 16 + m) * kAD) + lane;
+  const size_t split_pitch4 = static_cast<size_t>(16) * kAD / 4;
+  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  int s = warp;
+  for (; s + 7 * (kAD / 32) < p.splits; s += 8 * (kAD / 32)) {
+    float4 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u] += s_w[s + u] * __ldcg(po + (s + u) * split_pitch);
+    for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + (s + u * (kAD / 32)) * split_pitch4);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const float w = s_w[s + u * (kAD / 32)];
+      acc.x += w * v[u].x, acc.y += w * v[u].y, acc.z += w * v[u].z, acc.w += w * v[u].w;
+    }
   }
-  for (; s < p.splits; ++s) acc[0] += s_w[s] * __ldcg(po + s * split_pitch);
-  const float total = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-  const float v = l > 0.0f ? total / l : 0.0f;
-  p.out[(static_cast<size_t>(r0 + j) * p.Hq + hkv * kGqa + hl) * kAD + dim] =
-      static_cast<uint16_t>(f32_to_bf16_bits(v));
+  for (; s < p.splits; s += kAD / 32) {
+    const float4 v = __ldcg(po + s * split_pitch4);
+    const float w = s_w[s];
+    acc.x += w * v.x, acc.y += w * v.y, acc.z += w * v.z, acc.w += w * v.w;
+  }
+  s_acc[warp][lane] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    float4 t = s_acc[0][lane];
+#pragma unroll
+    for (int w = 1; w < kAD / 32; ++w) {
+      const float4 o = s_acc[w][lane];
+      t.x += o.x, t.y += o.y, t.z += o.z, t.w += o.w;
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    uint16_t* dst = p.out + (static_cast<size_t>(r0 + j) * p.Hq + hkv * kGqa + hl) * kAD + lane * 4;
+    const uint32_t lo = f32_to_bf16_bits(t.x * inv) | (f32_to_bf16_bits(t.y * inv) << 16);
+    const uint32_t hi = f32_to_bf16_bits(t.z * inv) | (f32_to_bf16_bits(t.w * inv) << 16);
+    *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+  }
 }
 
 struct SplitPlan {
