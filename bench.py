@@ -228,10 +228,21 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        # NCCL's own log lines (its version banner among them) go to stdout unless told otherwise;
-        # stdout is reserved for the one JSON line.
+        # NCCL writes its version banner (and anything NCCL_DEBUG asks for) to stdout when the
+        # communicator is created, i.e. at the first collective; stdout is reserved for the one JSON
+        # line, so file descriptor 1 points at stderr until that has happened.
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=device)
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=device)
+            dist.barrier()
+            torch.cuda.synchronize(device)
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
     shapes = glue.GraniteShapes()
     lo, hi = shard_bounds(TOTAL_TOKENS, world, rank)
     rows = int(os.environ.get("G4_BENCH_ROWS", hi - lo))  # override only for profiling
