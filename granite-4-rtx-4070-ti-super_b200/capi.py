@@ -62,6 +62,23 @@ SIGNATURES = {
     "granite4_kernel_multi_scatter_advance": (C.c_int, [_vp, _vp]),
     "granite4_kernel_kv_move": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.c_int, _vp,
                                           _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "granite4_kv_pool_create": (_vp, [C.c_int, C.c_int]),
+    "granite4_kv_pool_destroy": (None, [_vp]),
+    "granite4_kv_pool_create_sequence": (C.c_int, [_vp]),
+    "granite4_kv_pool_match_prefix": (C.c_longlong, [_vp, C.c_int, _vp, C.c_longlong]),
+    "granite4_kv_pool_reserve": (C.c_int, [_vp, C.c_int, C.c_longlong, _vp, C.c_longlong]),
+    "granite4_kv_pool_mark_written": (C.c_int, [_vp, C.c_int, C.c_longlong]),
+    "granite4_kv_pool_row_table": (C.c_int, [_vp, C.c_int, C.c_longlong, _vp]),
+    "granite4_kv_pool_reset_sequence": (None, [_vp, C.c_int]),
+    "granite4_kv_pool_truncate_sequence": (None, [_vp, C.c_int, C.c_longlong]),
+    "granite4_kv_pool_release": (None, [_vp, C.c_int]),
+    "granite4_kv_pool_clear": (None, [_vp]),
+    "granite4_kv_pool_count": (C.c_longlong, [_vp, C.c_int]),
+    "granite4_kv_pool_sequence_tokens": (C.c_longlong, [_vp, C.c_int]),
+    "granite4_kv_pool_block_table": (C.c_longlong, [_vp, C.c_int, _vp, C.c_longlong]),
+    "granite4_kv_pool_ref_count": (C.c_int, [_vp, C.c_int]),
+    "granite4_kv_pool_page_in_cache": (C.c_int, [_vp, C.c_int]),
+    "granite4_kv_pool_move_rows": (C.c_int, [_vp, C.c_int, _vp, _vp, C.c_int, _vp, _vp]),
     "granite4_attn_decode_scratch_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "granite4_kernel_attn_decode_int8_paged": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int,
                                                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

@@ -56,3 +56,97 @@ def batch_rows(block_tables, first_positions, tokens_per_sequence: int,
         pos.append(np.arange(p0, p0 + tokens_per_sequence, dtype=np.int32))
         rows.append(row_table(bt, tokens_per_sequence, tokens_per_page))
     return np.concatenate(pos), np.concatenate(rows)
+
+
+class KvPool:
+    """The library's host-side paged KV pool (``granite4_kv_pool_*``): the reference's
+    ``PagedKV`` (``engine/src/kv_pool.h:102-199``) behind the C ABI. Method names and meanings
+    are the reference's; token id lists are sequences of non-negative ints."""
+
+    COUNTS = {"free_pages": 0, "used_pages": 1, "shared_pages": 2, "cached_pages": 3,
+              "evicted_pages": 4, "retained_pages": 5, "live_sequences": 6}
+
+    def __init__(self, num_pages: int, tokens_per_page: int = TOKENS_PER_PAGE):
+        from . import capi
+        self._lib = capi.lib()
+        self._p = self._lib.granite4_kv_pool_create(num_pages, tokens_per_page)
+        if not self._p:
+            raise ValueError("granite4_kv_pool_create failed")
+        self.num_pages, self.tokens_per_page = num_pages, tokens_per_page
+
+    def close(self):
+        if getattr(self, "_p", None):
+            self._lib.granite4_kv_pool_destroy(self._p)
+            self._p = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _tok(tokens):
+        a = np.ascontiguousarray(tokens, dtype=np.uint32)
+        return a, a.ctypes.data, a.size
+
+    def create_sequence(self) -> int:
+        return self._lib.granite4_kv_pool_create_sequence(self._p)
+
+    def match_prefix(self, seq: int, tokens) -> int:
+        a, ptr, n = self._tok(tokens)
+        return self._lib.granite4_kv_pool_match_prefix(self._p, seq, ptr, n)
+
+    def reserve(self, seq: int, token_count: int, tokens) -> bool:
+        a, ptr, n = self._tok(tokens)
+        return bool(self._lib.granite4_kv_pool_reserve(self._p, seq, token_count, ptr, n))
+
+    def mark_written(self, seq: int, page_index: int) -> bool:
+        return bool(self._lib.granite4_kv_pool_mark_written(self._p, seq, page_index))
+
+    def row_table(self, seq: int, n: int):
+        """int32 [n] pool rows of positions [0, n), or None when n exceeds the sequence."""
+        out = np.empty(max(n, 1), np.int32)
+        ok = self._lib.granite4_kv_pool_row_table(self._p, seq, n, out.ctypes.data)
+        return out[:n] if ok else None
+
+    def reset_sequence(self, seq: int):
+        self._lib.granite4_kv_pool_reset_sequence(self._p, seq)
+
+    def truncate_sequence(self, seq: int, n_tokens: int):
+        self._lib.granite4_kv_pool_truncate_sequence(self._p, seq, n_tokens)
+
+    def release(self, seq: int):
+        self._lib.granite4_kv_pool_release(self._p, seq)
+
+    def clear(self):
+        self._lib.granite4_kv_pool_clear(self._p)
+
+    def count(self, name: str) -> int:
+        return self._lib.granite4_kv_pool_count(self._p, self.COUNTS[name])
+
+    def sequence_tokens(self, seq: int) -> int:
+        return self._lib.granite4_kv_pool_sequence_tokens(self._p, seq)
+
+    def block_table(self, seq: int):
+        n = self._lib.granite4_kv_pool_block_table(self._p, seq, None, 0)
+        out = np.empty(max(n, 1), np.int32)
+        self._lib.granite4_kv_pool_block_table(self._p, seq, out.ctypes.data, n)
+        return out[:n]
+
+    def ref_count(self, page: int) -> int:
+        return self._lib.granite4_kv_pool_ref_count(self._p, page)
+
+    def page_in_cache(self, page: int) -> bool:
+        return bool(self._lib.granite4_kv_pool_page_in_cache(self._p, page))
+
+    def move_rows(self, seq: int, src_pos, dst_pos):
+        """Pool rows (src, dst) of logical positions for granite4_kernel_kv_move, or None when
+        the reference's checks refuse the move list."""
+        n = len(src_pos)
+        s = np.ascontiguousarray(src_pos, np.int32)
+        d = np.ascontiguousarray(dst_pos, np.int32)
+        so, do = np.empty(max(n, 1), np.int32), np.empty(max(n, 1), np.int32)
+        rc = self._lib.granite4_kv_pool_move_rows(self._p, seq, s.ctypes.data, d.ctypes.data, n, so.ctypes.data,
+                                                  do.ctypes.data)
+        return (so[:n], do[:n]) if rc == 0 else None

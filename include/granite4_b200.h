@@ -306,6 +306,63 @@ int granite4_kernel_kv_move(const int* src_rows, const int* dst_rows, int n, int
                             int layers, int Hk, int stride, int d);
 
 /* ------------------------------------------------------------------------ */
+/* Host-side paged KV pool (no device work)                                  */
+/* ------------------------------------------------------------------------ */
+/* Added; the reference's granite4::PagedKV (engine/src/kv_pool.h:102-199,
+ * engine/src/kv_pool.cc) behind a C interface: 16-token pages (any page size),
+ * dense per-sequence block tables, a prefix cache over full pages keyed by the
+ * chained FNV-1a hash of the token prefix (verified against the stored token
+ * ids), reference counts, least-recently-used eviction of cached pages nobody
+ * references. Same page ids, row tables and counts as the reference for the same
+ * sequence of calls, with one deliberate difference: truncate_sequence always
+ * shortens the token record of the last kept page to what is left of it (the
+ * reference leaves it long when no page is dropped, after which a further
+ * reserve on that sequence records more than a page's worth of ids for it).
+ * Returns: create_sequence the new id or -1; match_prefix the number of leading
+ * tokens now covered by shared cached pages (a multiple of the page size; only
+ * on a sequence that holds nothing yet); reserve / mark_written / row_table 1 on
+ * success, 0 otherwise. row_table writes out[p] = page * tokens_per_page + p %
+ * tokens_per_page for p < n <= the sequence's token count: the d_pt / kv_rows
+ * table of the KV-write and attention entry points. Not thread-safe. */
+typedef struct granite4_kv_pool granite4_kv_pool;
+enum {
+  GRANITE4_KV_POOL_FREE_PAGES = 0,
+  GRANITE4_KV_POOL_USED_PAGES = 1,
+  GRANITE4_KV_POOL_SHARED_PAGES = 2,   /* reference count > 1 */
+  GRANITE4_KV_POOL_CACHED_PAGES = 3,   /* entries of the prefix cache */
+  GRANITE4_KV_POOL_EVICTED_PAGES = 4,  /* evictions so far */
+  GRANITE4_KV_POOL_RETAINED_PAGES = 5, /* cached, reference count 0 */
+  GRANITE4_KV_POOL_LIVE_SEQUENCES = 6
+};
+granite4_kv_pool* granite4_kv_pool_create(int num_pages, int tokens_per_page);
+void granite4_kv_pool_destroy(granite4_kv_pool* pool);
+int granite4_kv_pool_create_sequence(granite4_kv_pool* pool);
+long long granite4_kv_pool_match_prefix(granite4_kv_pool* pool, int seq, const uint32_t* tokens,
+                                        long long n);
+int granite4_kv_pool_reserve(granite4_kv_pool* pool, int seq, long long token_count,
+                             const uint32_t* tokens, long long n);
+int granite4_kv_pool_mark_written(granite4_kv_pool* pool, int seq, long long page_index);
+int granite4_kv_pool_row_table(const granite4_kv_pool* pool, int seq, long long n, int* out);
+void granite4_kv_pool_reset_sequence(granite4_kv_pool* pool, int seq);
+void granite4_kv_pool_truncate_sequence(granite4_kv_pool* pool, int seq, long long n_tokens);
+void granite4_kv_pool_release(granite4_kv_pool* pool, int seq);
+void granite4_kv_pool_clear(granite4_kv_pool* pool);
+long long granite4_kv_pool_count(const granite4_kv_pool* pool, int which);
+long long granite4_kv_pool_sequence_tokens(const granite4_kv_pool* pool, int seq);
+/* Writes min(capacity, pages) page ids to out (may be NULL); returns the number of pages. */
+long long granite4_kv_pool_block_table(const granite4_kv_pool* pool, int seq, int* out,
+                                       long long capacity);
+int granite4_kv_pool_ref_count(const granite4_kv_pool* pool, int page);
+int granite4_kv_pool_page_in_cache(const granite4_kv_pool* pool, int page);
+/* The host half of gpu_ctx_kv_move (engine/src/forward_gpu.cu:3508-3522): maps n
+ * <= 8 logical (src, dst) positions of a sequence to pool rows for
+ * granite4_kernel_kv_move, with the reference's checks (positions inside the
+ * sequence's pages, dst <= src, no later move reading a row an earlier one
+ * overwrites). 0, or -1 if a check fails. */
+int granite4_kv_pool_move_rows(const granite4_kv_pool* pool, int seq, const int* src_pos,
+                               const int* dst_pos, int n, int* src_rows, int* dst_rows);
+
+/* ------------------------------------------------------------------------ */
 /* Decode / verify attention over the int8 paged pool                        */
 /* ------------------------------------------------------------------------ */
 /* Added; the int8 multi-sequence mode of granite4::attn_split

@@ -1297,3 +1297,58 @@ def test_attention_reads_what_the_rope_kv_kernel_wrote(K, port):
         want = (p / p.sum()) @ v[:, h // 4]
         assert np.abs(got[h] - want).max() < 0.03
     t.close()
+
+
+# =========================================================================== pool controller -> kernels
+def test_pool_tables_drive_kv_write_attention_and_moves(K, port):
+    """The host pool hands out the row tables, the kernels follow them: sequence B adopts the two
+    cached pages of sequence A's prompt, writes only its own tail, and attends over the shared
+    pages through its own table; then an accepted-path move list is mapped to pool rows and
+    applied to the pool."""
+    from granite4_b200 import paging
+    pages, B = 24, 16
+    stride, max_pos = pages * B, 64
+    pool = paging.KvPool(pages, B)
+    prompt = list(range(100, 140))                        # 40 tokens
+    a = pool.create_sequence()
+    assert pool.reserve(a, 40, prompt)
+    rows_a = pool.row_table(a, 40)
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+    ck, cv, ks, vs = _pool(stride)
+    qkv_a = rand_bf16(2500, (40, 48 * D), 1.0)
+    q_rot = empty_bf16(40, Hq * D)
+    assert K.rope_kv_int8_paged(dev(qkv_a), t.cos, t.sin, dev(np.arange(40, dtype=np.int32)), dev(rows_a), Hq, Hk,
+                                D, stride, max_pos, 0, q_rot, ck, cv, ks, vs) == 0
+    assert pool.mark_written(a, 0) and pool.mark_written(a, 1)
+    # B: same first 32 tokens, then its own
+    b = pool.create_sequence()
+    prompt_b = prompt[:32] + list(range(900, 916))
+    assert pool.match_prefix(b, prompt_b) == 32
+    assert pool.reserve(b, 48, prompt_b)
+    rows_b = pool.row_table(b, 48)
+    assert (rows_b[:32] == rows_a[:32]).all() and not set(rows_b[32:]) & set(rows_a)
+    qkv_b = rand_bf16(2501, (16, 48 * D), 1.0)
+    q_rot_b = empty_bf16(16, Hq * D)
+    assert K.rope_kv_int8_paged(dev(qkv_b), t.cos, t.sin, dev(np.arange(32, 48, dtype=np.int32)),
+                                dev(np.ascontiguousarray(rows_b[32:])), Hq, Hk, D, stride, max_pos, 0, q_rot_b,
+                                ck, cv, ks, vs) == 0
+    # B's last token attends over positions 0..47 through B's table
+    out = empty_bf16(1, Hq * D)
+    scale = 1.0 / 128
+    assert K.attn_decode_int8_paged(q_rot_b[15:16].contiguous(), ck, cv, ks, vs, dev(np.array([47], np.int32)),
+                                    Hq, Hk, D, stride, max_pos, scale, out, pt=dev(np.ascontiguousarray(
+                                        np.concatenate([rows_b, np.zeros(max_pos - 48, np.int32)])))) == 0
+    want = port.attn_decode_int8(host(q_rot_b)[15:16], host(ck), host(cv), host(ks), host(vs),
+                                 np.array([47], np.int32), [rows_b], Hq, Hk, D, scale)
+    assert np.abs(_bf16_to_f32_np(host(out)) - _bf16_to_f32_np(want)).max() < ATT_TOL
+    # accepted draft path: positions 45 and 47 become 44 and 45
+    src, dst = pool.move_rows(b, [45, 47], [44, 45])
+    before = [x.clone() for x in (ck, cv, ks, vs)]
+    assert K.kv_move(src.tolist(), dst.tolist(), 8, ck, cv, ks, vs, 1, Hk, stride, D) == 0
+    for x in before:
+        for s_, d_ in zip(src.tolist(), dst.tolist()):
+            x[:, d_] = x[:, s_]
+    for got, w_ in zip((ck, cv, ks, vs), before):
+        assert torch.equal(got, w_)
+    pool.close()
+    t.close()
