@@ -40,6 +40,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace g4 {
 namespace {
@@ -132,6 +133,40 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Merge of the four warps' parked states ([16][128] O, then [16][2] (max, sum), at the start of each
+// warp's shared-memory block) into the CTA's result: written out directly when there is one split,
+// else as this split's partial state. Called by all 128 threads after a __syncthreads().
+__device__ __forceinline__ void merge_warps(const AttnParams& p, const unsigned char* s_dyn, int warp_bytes,
+                                            int grp, int hkv, int split, int r0, int nrows) {
+  const size_t part = (static_cast<size_t>(grp) * p.Hk + hkv) * p.splits + split;
+  for (int m = 0; m < 16; ++m) {
+    const int j = m >> 2, hl = m & 3;
+    if (j >= nrows) break;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w)
+      mm = fmaxf(mm, reinterpret_cast<const float*>(s_dyn + static_cast<size_t>(w) * warp_bytes)[16 * kAD + m * 2]);
+    float l = 0.0f, acc = 0.0f;
+    const int dim = threadIdx.x;  // 128 threads = 128 dims
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float* base = reinterpret_cast<const float*>(s_dyn + static_cast<size_t>(w) * warp_bytes);
+      const float mw = base[16 * kAD + m * 2];
+      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - mm);
+      l += f * base[16 * kAD + m * 2 + 1];
+      acc += f * base[m * kAD + dim];
+    }
+    if (p.splits == 1) {
+      const float v = l > 0.0f ? acc / l : 0.0f;
+      p.out[(static_cast<size_t>(r0 + j) * p.Hq + hkv * kGqa + hl) * kAD + dim] =
+          static_cast<uint16_t>(f32_to_bf16_bits(v));
+    } else {
+      p.part_o[(part * 16 + m) * kAD + dim] = acc;
+      if (dim == 0) p.part_ml[(part * 16 + m) * 2] = mm, p.part_ml[(part * 16 + m) * 2 + 1] = l;
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(const AttnParams p) {
@@ -423,33 +458,239 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(co
     wml[(g + 8) * 2] = m_run[1], wml[(g + 8) * 2 + 1] = l_run[1];
   }
   __syncthreads();
-  const size_t part = (static_cast<size_t>(grp) * p.Hk + hkv) * p.splits + split;
-  for (int m = 0; m < 16; ++m) {
-    const int j = m >> 2, hl = m & 3;
-    if (j >= nrows) break;
-    float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w)
-      mm = fmaxf(mm, reinterpret_cast<const float*>(s_dyn + static_cast<size_t>(w) * kWarpSmem)[16 * kAD + m * 2]);
-    float l = 0.0f, acc = 0.0f;
-    const int dim = threadIdx.x;  // 128 threads = 128 dims
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-      const float* base = reinterpret_cast<const float*>(s_dyn + static_cast<size_t>(w) * kWarpSmem);
-      const float mw = base[16 * kAD + m * 2];
-      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - mm);
-      l += f * base[16 * kAD + m * 2 + 1];
-      acc += f * base[m * kAD + dim];
-    }
-    if (p.splits == 1) {
-      const float v = l > 0.0f ? acc / l : 0.0f;
-      p.out[(static_cast<size_t>(r0 + j) * p.Hq + hkv * kGqa + hl) * kAD + dim] =
-          static_cast<uint16_t>(f32_to_bf16_bits(v));
-    } else {
-      p.part_o[(part * 16 + m) * kAD + dim] = acc;
-      if (dim == 0) p.part_ml[(part * 16 + m) * 2] = mm, p.part_ml[(part * 16 + m) * 2 + 1] = l;
-    }
+  merge_warps(p, s_dyn, kWarpSmem, grp, hkv, split, r0, nrows);
+}
+
+// ---- groups of one or two query rows (plain decode), transposed ------------------------------------
+// With 4 or 8 live rows the 16-row mma tile of the kernel above is mostly padding. Here the cache
+// positions take the 16-row side instead: S^T = K Q^T (A = 16 positions x dims from the raw K
+// codes, B = the 8 columns (query row, head) of q) and O^T = V^T P^T (A = 16 dims x 16 positions
+// from the raw V codes through ldmatrix.trans, B = P^T, which is the S^T accumulator transposed by
+// movmatrix). Half the mma instructions per tile, half the O accumulators (so four CTAs per SM),
+// and the softmax of a column runs down the lanes (three xor shuffles over g).
+constexpr int kStagesT = 3;
+constexpr int kWarpSmemT = kStagesT * 2 * kRawTile;  // 13824
+constexpr size_t kAttnSmemBytesT = static_cast<size_t>(kWarps) * kWarpSmemT;
+constexpr int kCtasPerSmT = 4;
+static_assert(kWarpSmemT >= (16 * kAD + 32) * 4, "a warp parks its final state in its own block");
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSmT) attn_decode_t_kernel(const AttnParams p) {
+  pdl_begin();
+  extern __shared__ __align__(128) unsigned char s_dyn[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int split = blockIdx.x, hkv = blockIdx.y, grp = blockIdx.z;
+  const int r0 = grp * p.group_rows;
+  const int nrows = min(p.group_rows, p.rows - r0);  // 1 or 2
+  unsigned char* wsm = s_dyn + static_cast<size_t>(warp) * kWarpSmemT;
+  unsigned char* raw_k = wsm;
+  unsigned char* raw_v = wsm + kStagesT * kRawTile;
+
+  // column c = 4 j + hl stands for (query row j, head hl). As accumulator owner a thread has columns
+  // 2 t and 2 t + 1 (both of query row t / 2); as B-operand owner it has column g.
+  int pos_col = -1, pos_max = -1, pos_min = INT_MAX;
+  for (int j = 0; j < nrows; ++j) {
+    int pj = __ldg(p.row_pos + r0 + j);
+    pj = pj < 0 ? -1 : min(pj, p.max_len - 1);
+    pos_max = max(pos_max, pj);
+    pos_min = min(pos_min, pj);
+    if (j == (t >> 1)) pos_col = pj;
   }
+  const int* pt = p.row_pt != nullptr ? p.row_pt[r0] : p.pt;
+  const int t_begin = split * p.split_len;
+  const int t_end = min(t_begin + p.split_len, pos_max + 1);
+
+  // ---- q as the B operand: (dims 16 kk + 4 t .. + 3 of column g), fp16, scaled by a power of two
+  uint32_t qb[8][2];
+  float logit_scale;
+  float q_off[2];  // 1152 x the sum of q over the dims, for the accumulator's columns 2 t, 2 t + 1
+  {
+    const int j = g >> 2, hl = g & 3;
+    const bool live = j < nrows;
+    const uint16_t* qrow = p.q + (static_cast<size_t>(r0 + (live ? j : 0)) * p.Hq + hkv * kGqa + hl) * kAD;
+    float qf[8][4];
+    float qmax = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const uint2 w = live ? __ldg(reinterpret_cast<const uint2*>(qrow + kk * 16 + 4 * t)) : make_uint2(0u, 0u);
+      qf[kk][0] = bf16_to_f32(w.x & 0xffffu), qf[kk][1] = bf16_to_f32(w.x >> 16);
+      qf[kk][2] = bf16_to_f32(w.y & 0xffffu), qf[kk][3] = bf16_to_f32(w.y >> 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qmax = fmaxf(qmax, fabsf(qf[kk][i]));
+    }
+    qmax = warp_max(qmax);
+    int qexp = 0;
+    if (qmax > 0.0f && qmax < INFINITY)
+      qexp = min(max(((__float_as_int(qmax) >> 23) & 0xff) - 127 - 10, -100), 100);
+    const float qdown = __int_as_float((127 - qexp) << 23);
+    logit_scale = p.scale_log2 * __int_as_float((127 + qexp) << 23);
+    float sum = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      qb[kk][0] = pack_half2(qf[kk][0] * qdown, qf[kk][1] * qdown);
+      qb[kk][1] = pack_half2(qf[kk][2] * qdown, qf[kk][3] * qdown);
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qb[kk][0]));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qb[kk][1]));
+      sum += (a.x + a.y) + (b.x + b.y);
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);  // the whole row of column g, in all four lanes of quad g
+    q_off[0] = kCodeBias * __shfl_sync(0xffffffffu, sum, (2 * t) * 4);
+    q_off[1] = kCodeBias * __shfl_sync(0xffffffffu, sum, (2 * t + 1) * 4);
+  }
+
+  // O^T accumulators: block b, rows g / g + 8 = dims 16 b + 2 g / 16 b + 2 g + 1, columns 2 t, 2 t + 1
+  float o[8][4];
+#pragma unroll
+  for (int b = 0; b < 8; ++b) o[b][0] = o[b][1] = o[b][2] = o[b][3] = 0.0f;
+  float osum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  const size_t head_row0 = static_cast<size_t>(hkv) * p.stride;
+
+  constexpr int kStep = kTile * kWarps;
+  auto table_row = [&](int tile0) -> int {
+    const int tpos = tile0 + (lane & 15);
+    if (tpos >= t_end) return 0;
+    const int prow = pt != nullptr ? __ldg(pt + tpos) : tpos;
+    return min(max(prow, 0), static_cast<int>(p.stride) - 1);
+  };
+  auto gather = [&](int stage, int tile0, int prow, float& sk, float& sv) {
+    const int piece = (lane & 7) * 16;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int n = 4 * i + (lane >> 3);
+      const int pr = __shfl_sync(0xffffffffu, prow, n);
+      const bool have = tile0 + n < t_end;
+      const size_t off = (head_row0 + pr) * kAD + piece;
+      cp_async16(raw_k + stage * kRawTile + n * kPitch + piece, p.ck + off, have);
+      cp_async16(raw_v + stage * kRawTile + n * kPitch + piece, p.cv + off, have);
+    }
+    cp_async_commit();
+    const bool mine = tile0 + (lane & 15) < t_end;
+    sk = mine ? __ldg(p.ks + head_row0 + prow) : 0.0f;
+    sv = mine ? __ldg(p.vs + head_row0 + prow) : 0.0f;
+  };
+  const int t_first = t_begin + warp * kTile;
+  float sk_q[kStagesT], sv_q[kStagesT];
+  {
+    const int pr0 = table_row(t_first), pr1 = table_row(t_first + kStep);
+    gather(0, t_first, pr0, sk_q[0], sv_q[0]);
+    gather(1, t_first + kStep, pr1, sk_q[1], sv_q[1]);
+  }
+  int prow_next = table_row(t_first + 2 * kStep);
+  int stage = 0;
+
+  for (int t0 = t_first; t0 < t_end; t0 += kStep) {
+    cp_async_wait<kStagesT - 2>();
+    __syncwarp();
+    gather((stage + kStagesT - 1) % kStagesT, t0 + (kStagesT - 1) * kStep, prow_next, sk_q[kStagesT - 1],
+           sv_q[kStagesT - 1]);
+    prow_next = table_row(t0 + kStagesT * kStep);
+    const float sk_cur = sk_q[0], sv_cur = sv_q[0];
+#pragma unroll
+    for (int i = 0; i + 1 < kStagesT; ++i) sk_q[i] = sk_q[i + 1], sv_q[i] = sv_q[i + 1];
+    const unsigned char* kstage = raw_k + stage * kRawTile;
+    const unsigned char* vstage = raw_v + stage * kRawTile;
+    stage = (stage + 1) % kStagesT;
+
+    // ---- S^T = K Q^T: rows = positions g and g + 8, columns 2 t, 2 t + 1
+    float sa[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const unsigned char* k_lo = kstage + g * kPitch + 4 * t;
+    const unsigned char* k_hi = k_lo + 8 * kPitch;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      uint32_t a[4];
+      codes4_to_half(*reinterpret_cast<const uint32_t*>(k_lo + kk * 16), a[0], a[2]);
+      codes4_to_half(*reinterpret_cast<const uint32_t*>(k_hi + kk * 16), a[1], a[3]);
+      mma_f16((kk & 1) ? sb : sa, a, qb[kk][0], qb[kk][1]);
+    }
+    // ---- scale, mask, online softmax down the lanes
+    const float f_lo = __shfl_sync(0xffffffffu, sk_cur, g) * logit_scale;
+    const float f_hi = __shfl_sync(0xffffffffu, sk_cur, g + 8) * logit_scale;
+    const float sv_lo = __shfl_sync(0xffffffffu, sv_cur, g), sv_hi = __shfl_sync(0xffffffffu, sv_cur, g + 8);
+    const bool unmasked = t0 + kTile <= t_end && t0 + kTile - 1 <= pos_min;  // warp-uniform
+    const bool ok_lo = unmasked || (t0 + g <= pos_col && t0 + g < t_end);
+    const bool ok_hi = unmasked || (t0 + g + 8 <= pos_col && t0 + g + 8 < t_end);
+    float pr[4], corr[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float x_lo = ok_lo ? (sa[e] + sb[e] - q_off[e]) * f_lo : -INFINITY;
+      const float x_hi = ok_hi ? (sa[2 + e] + sb[2 + e] - q_off[e]) * f_hi : -INFINITY;
+      float mx = fmaxf(x_lo, x_hi);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m_run[e], mx);
+      corr[e] = (m_new == -INFINITY) ? 1.0f : ex2_approx(m_run[e] - m_new);
+      const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+      pr[e] = ex2_approx(x_lo - base);      // position g
+      pr[2 + e] = ex2_approx(x_hi - base);  // position g + 8
+      l_run[e] = l_run[e] * corr[e] + pr[e] + pr[2 + e];  // this lane's two positions; lanes are summed at the end
+      m_run[e] = m_new;
+    }
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        o[b][0] *= corr[0], o[b][1] *= corr[1];
+        o[b][2] *= corr[0], o[b][3] *= corr[1];
+      }
+      osum[0] *= corr[0], osum[1] *= corr[1], osum[2] *= corr[0], osum[3] *= corr[1];
+    }
+    // ---- P^T as the B operand: the accumulator fragments (position g: columns 2 t, 2 t + 1) transposed
+    const uint32_t b0 = movmatrix_trans(pack_half2(pr[0] * sv_lo, pr[1] * sv_lo));  // positions 0-7
+    const uint32_t b1 = movmatrix_trans(pack_half2(pr[2] * sv_hi, pr[3] * sv_hi));  // positions 8-15
+    // ---- O^T += V^T P^T, V operand from the raw bytes (see the kernel above)
+#pragma unroll
+    for (int blk = 0; blk < 8; blk += 2) {
+      uint32_t r[4];
+      ldmatrix_x4_trans(r, vstage + (lane & 15) * kPitch + (blk + (lane >> 4)) * 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) r[i] ^= 0x80808080u;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t lo = r[2 * u], hi = r[2 * u + 1];
+        // rows g / g + 8 = dims 2 g / 2 g + 1 of the block; k = positions 2 t, 2 t + 1 | 2 t + 8, 2 t + 9
+        const uint32_t a[4] = {__byte_perm(lo, 0x64646464u, 0x4240), __byte_perm(lo, 0x64646464u, 0x4341),
+                               __byte_perm(hi, 0x64646464u, 0x4240), __byte_perm(hi, 0x64646464u, 0x4341)};
+        mma_f16(o[blk + u], a, b0, b1);
+      }
+    }
+    const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
+    mma_f16(osum, ones, b0, b1);  // every row: the sum over the positions of P^T's columns
+  }
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    o[b][0] -= kCodeBias * osum[0], o[b][1] -= kCodeBias * osum[1];
+    o[b][2] -= kCodeBias * osum[0], o[b][3] -= kCodeBias * osum[1];
+  }
+
+  cp_async_wait<0>();
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 4);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 8);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 16);
+  }
+  __syncwarp();
+  float* wo = reinterpret_cast<float*>(wsm);  // [16][128]; only the rows of live columns are read
+  float* wml = wo + 16 * kAD;
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    *reinterpret_cast<float2*>(wo + (2 * t) * kAD + b * 16 + 2 * g) = make_float2(o[b][0], o[b][2]);
+    *reinterpret_cast<float2*>(wo + (2 * t + 1) * kAD + b * 16 + 2 * g) = make_float2(o[b][1], o[b][3]);
+  }
+  if (g == 0) {
+    wml[(2 * t) * 2] = m_run[0], wml[(2 * t) * 2 + 1] = l_run[0];
+    wml[(2 * t + 1) * 2] = m_run[1], wml[(2 * t + 1) * 2 + 1] = l_run[1];
+  }
+  __syncthreads();
+  merge_warps(p, s_dyn, kWarpSmemT, grp, hkv, split, r0, nrows);
 }
 
 // Merge of the splits: one CTA per (kv head, row group, tile row), thread = dim. The splits'
@@ -527,11 +768,12 @@ struct SplitPlan {
 };
 
 SplitPlan plan_splits(int rows, int group_rows, int Hk, int max_len) {
+  const int ctas_per_sm = group_rows <= 2 ? kCtasPerSmT : kCtasPerSm;
   SplitPlan s{};
   s.groups = (rows + group_rows - 1) / group_rows;
   const int tiles = (max_len + kSplitAlign - 1) / kSplitAlign;  // units of 64 positions
   // aim at one resident wave over the whole launch, at least 64 positions per split
-  const long long ctas_wanted = static_cast<long long>(kCtasPerSm) * sm_count();
+  const long long ctas_wanted = static_cast<long long>(ctas_per_sm) * sm_count();
   // rounded down: the launch is then at most one resident wave (a second, nearly empty wave would
   // double the time)
   long long splits = ctas_wanted / (static_cast<long long>(s.groups) * Hk);
@@ -593,12 +835,17 @@ int granite4_kernel_attn_decode_int8_paged(const uint16_t* d_q, const int8_t* d_
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
       G4_CUDA_TRY(fn, cudaFuncSetAttribute(g4::attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(g4::kAttnSmemBytes)));
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(g4::attn_decode_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(g4::kAttnSmemBytesT)));
       attr_set[dev] = true;
     }
   }
-  G4_LAUNCH_PDL(fn, g4::attn_decode_kernel,
-                dim3(static_cast<unsigned>(s.splits), static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups)),
-                dim3(g4::kWarps * 32), g4::kAttnSmemBytes, st, p);
+  const dim3 grid(static_cast<unsigned>(s.splits), static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups));
+  const char* force = std::getenv("G4_ATTN_TRANSPOSED");  // 0: the 16-row kernel for every group size (A/B runs)
+  if (rows_per_group <= 2 && !(force != nullptr && force[0] == '0'))
+    G4_LAUNCH_PDL(fn, g4::attn_decode_t_kernel, grid, dim3(g4::kWarps * 32), g4::kAttnSmemBytesT, st, p);
+  else
+    G4_LAUNCH_PDL(fn, g4::attn_decode_kernel, grid, dim3(g4::kWarps * 32), g4::kAttnSmemBytes, st, p);
   if (s.splits > 1)
     G4_LAUNCH_PDL(fn, g4::attn_combine_kernel,
                   dim3(static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups), 4u * rows_per_group),

@@ -226,10 +226,6 @@ __device__ __forceinline__ uint2 kv8_quant8(const float (&x)[8], const Kv8Scale 
   }
   return out;
 }
-__device__ __forceinline__ uint32_t pack_i8x4(int a, int b, int c, int d) {
-  return (static_cast<uint32_t>(a) & 0xffu) | ((static_cast<uint32_t>(b) & 0xffu) << 8) |
-         ((static_cast<uint32_t>(c) & 0xffu) << 16) | (static_cast<uint32_t>(d) << 24);
-}
 
 // ---- RoPE, Llama half split -------------------------------------------------
 // Reference: engine/src/kernel_math.h:208-219. (a, b) = (x[i], x[i + d/2]):

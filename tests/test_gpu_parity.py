@@ -1352,3 +1352,25 @@ def test_pool_tables_drive_kv_write_attention_and_moves(K, port):
         assert torch.equal(got, w_)
     pool.close()
     t.close()
+
+
+@pytest.mark.parametrize("transposed", ["1", "0"])
+def test_attention_pairs_of_rows_both_kernels(K, port, transposed, monkeypatch):
+    """Groups of two rows (and a ragged last group of one) run on the transposed kernel (cache
+    positions on the 16-row side of the mma); G4_ATTN_TRANSPOSED=0 forces the 16-row kernel. Both
+    against the golden pipeline and the unrounded evaluation."""
+    monkeypatch.setenv("G4_ATTN_TRANSPOSED", transposed)
+    stride, max_len = 1024, 900
+    ck, cv, ks, vs = _att_pool(71, stride)
+    pos = np.array([500, 501, 17, 18, 899], np.int32)
+    rows = len(pos)
+    q = rand_bf16(2600, (rows, Hq * D), 2.0)
+    table = np.random.default_rng(72).permutation(stride).astype(np.int32)
+    out = empty_bf16(rows, Hq * D)
+    scale = 1.0 / 128
+    assert K.attn_decode_int8_paged(dev(q), dev(ck), dev(cv), dev(ks), dev(vs), dev(pos), Hq, Hk, D, stride,
+                                    max_len, scale, out, rows_per_group=2, pt=dev(table)) == 0
+    got = _bf16_to_f32_np(host(out)).reshape(rows, Hq, D)
+    want = _bf16_to_f32_np(port.attn_decode_int8(q, ck, cv, ks, vs, pos, [table] * rows, Hq, Hk, D, scale))
+    assert np.abs(got - want.reshape(rows, Hq, D)).max() < ATT_TOL
+    assert np.abs(got - _attn_f64(q, ck, cv, ks, vs, pos, [table] * rows, scale)).max() < 0.01
