@@ -1374,3 +1374,75 @@ def test_attention_pairs_of_rows_both_kernels(K, port, transposed, monkeypatch):
     want = _bf16_to_f32_np(port.attn_decode_int8(q, ck, cv, ks, vs, pos, [table] * rows, Hq, Hk, D, scale))
     assert np.abs(got - want.reshape(rows, Hq, D)).max() < ATT_TOL
     assert np.abs(got - _attn_f64(q, ck, cv, ks, vs, pos, [table] * rows, scale)).max() < 0.01
+
+
+# =========================================================================== random shapes
+@pytest.mark.parametrize("seed", range(12))
+def test_random_shapes_against_the_oracle(K, port, seed):
+    """Shapes nobody tuned for: random row counts (through the one-cluster, two-sweep and generic
+    paths), widths that are multiples of 8 but of nothing else, f32 / bf16 inputs, with and without
+    the optional outputs. add+norm+FP8 and per-tensor FP8 bit-exact, SwiGLU within 1 bf16 ulp with
+    an exact quantiser, RoPE + int8 KV bit-exact, greedy pick exact."""
+    rng = np.random.default_rng(1000 + seed)
+    # ---- add + RMSNorm + FP8
+    rows = int(rng.choice([1, 2, 7, 16, 17, 33, 150, 1025]))
+    cols = int(rng.choice([8, 24, 136, 1000, 4096, 5120, 8200]))
+    f32 = bool(rng.integers(0, 2))
+    yb, rb = rand_bf16(seed * 10 + 1, (rows, cols), 2.0), rand_bf16(seed * 10 + 2, (rows, cols), 3.0)
+    w = rand_bf16(seed * 10 + 3, (cols,), 1.0)
+    y = _bf16_to_f32_np(yb) * np.float32(1.3) if f32 else yb
+    res = _bf16_to_f32_np(rb) * np.float32(0.7) if f32 else rb
+    rm = float(rng.choice([1.0, 0.22, -0.5]))
+    hw, nw = port.add_rmsnorm(y, res, w, 1e-5, rm)
+    cw, sw, aw = port.quant_fp8(nw)
+    want_n, want_r = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+    h = empty_bf16(rows, cols)
+    n = empty_bf16(rows, cols) if want_n else None
+    c = torch.empty(rows, cols, dtype=torch.uint8, device=DEV)
+    sa = torch.full((2,), -1.0, dtype=torch.float32, device=DEV)
+    rstd = torch.zeros(rows, dtype=torch.float32, device=DEV) if want_r else None
+    assert K.add_rmsnorm_fp8(dev(y), dev(res), dev(w), 1e-5, rm, h, n, c, sa, rstd) == 0
+    assert (host(h) == hw).all() and (host(c) == cw).all(), (rows, cols, f32, want_n, want_r)
+    assert sa[0].item() == sw and sa[1].item() == aw
+    if want_n:
+        assert (host(n) == nw).all()
+    # ---- SwiGLU + FP8
+    rows2 = int(rng.choice([1, 3, 16, 17, 40, 300]))
+    I = int(rng.choice([8, 264, 1000, 12800, 13000]))
+    gu = rand_bf16(seed * 10 + 4, (rows2, 2 * I), 3.0)
+    gud = dev(gu)
+    act = empty_bf16(rows2, I) if rng.integers(0, 2) else None
+    c2 = torch.empty(rows2, I, dtype=torch.uint8, device=DEV)
+    sa2 = torch.full((2,), -1.0, dtype=torch.float32, device=DEV)
+    assert K.swiglu_fp8(gud[:, :I], gud[:, I:], act, c2, sa2, ld=2 * I) == 0
+    ref_act = port.swiglu(gu[:, :I], gu[:, I:])
+    if act is not None:
+        got = host(act)
+        assert bf16_ulp_distance(got, ref_act).max() <= 1
+        assert sa2[1].item() == port.amax_bf16(got)
+        assert (host(c2) == port.quant_fp8_with_scale(got, sa2[0].item())).all()
+    else:
+        # without the bf16 copy: the scale must be that of activations within 1 ulp of the host's
+        assert abs(sa2[0].item() - port.fp8_scale_from_amax(port.amax_bf16(ref_act))) <= 2 ** -7 * sa2[0].item()
+    # ---- RoPE + int8 paged KV with scattered positions
+    rows3 = int(rng.choice([1, 5, 64, 333]))
+    stride, max_pos = 512, 2048
+    qkv = rand_bf16(seed * 10 + 5, (rows3, 48 * D), 2.0)
+    pos = rng.integers(0, max_pos, rows3).astype(np.int32)
+    kvr = rng.permutation(stride)[:rows3].astype(np.int32)
+    mode = int(rng.integers(0, 2))
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+    cos, sin = port.rope_tables(1e7, D, max_pos)
+    ck, cv, ks, vs = _pool(stride)
+    q_rot = empty_bf16(rows3, Hq * D)
+    assert K.rope_kv_int8_paged(dev(qkv), t.cos, t.sin, dev(pos), dev(kvr), Hq, Hk, D, stride, max_pos, mode,
+                                q_rot, ck, cv, ks, vs) == 0
+    for got, w_ in zip((q_rot, ck, cv, ks, vs), port.rope_kv_int8(qkv, cos, sin, pos, kvr, Hq, Hk, D, stride, mode)):
+        assert (host(got) == w_).all()
+    t.close()
+    # ---- greedy pick
+    rows4, V = int(rng.choice([1, 9, 16, 17, 70])), int(rng.choice([8, 1000, 4104, 100352]))
+    logits = rand_bf16(seed * 10 + 6, (rows4, V), 3.0)
+    out = torch.full((rows4,), -1, dtype=torch.int32, device=DEV)
+    assert K.argmax_rows(dev(logits), out) == 0
+    assert (out.cpu().numpy() == port.argmax_rows(logits)).all()
