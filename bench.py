@@ -361,6 +361,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "small_shapes": extras["small"],
             "argmax": extras["argmax"],
             "attention_decode": extras["attention"],
+            "decode_step": extras["decode_step"],
             "clocks": clocks,
             "gpu_launches": launches,
             "device_status": status,
@@ -511,9 +512,58 @@ def small_shapes_and_embed(seq, rows, device, stream):
         nbytes = groups * s.kv_heads * ctx * (2 * s.head_dim + 8)
         attention[name] = {"mean_us": us, "achieved_gbs": nbytes / (us * 1e-6) / 1e9,
                            "frac": nbytes / (us * 1e-6) / 1e9 / peak, "bytes": nbytes}
+    # A whole decode step (one layer's glue + attention at ~4096 positions + final norm + greedy
+    # pick + token scatter) of n sessions, captured into a CUDA graph and replayed: everything that
+    # changes between steps is read from the device descriptor, so the replays chain by themselves.
+    from granite4_b200 import capi
+    decode_step = {}
+    emb_small = (0.02 * torch.randn(4096, s.hidden, generator=g, device=device)).to(torch.bfloat16)
+    logits_small = torch.randn(16, 4096, generator=g, device=device).to(torch.bfloat16)
+    w3 = (1.0 + 0.02 * torch.randn(3, s.hidden, generator=g, device=device)).to(torch.bfloat16)
+    for n in (1, 8):
+        sess_tables = [table[r * 8192:(r + 1) * 8192].contiguous() for r in range(n)]
+        toks = [torch.zeros(8192, dtype=torch.int32, device=device) for _ in range(n)]
+        desc = capi.MultiRows()
+        desc.n = n
+        for r in range(n):
+            desc.pos[r] = 4000 + 3 * r
+            desc.pt[r] = sess_tables[r].data_ptr()
+            desc.tok[r] = toks[r].data_ptr()
+        d_rows = k.multi_rows_to_device(desc, device)
+        row_pos = d_rows[capi.MultiRows.pos.offset:capi.MultiRows.pos.offset + 4 * n].view(torch.int32)
+        row_pt = d_rows[capi.MultiRows.pt.offset:capi.MultiRows.pt.offset + 8 * n].view(torch.int64)
+        b = {name: torch.randn(n, c, generator=g, device=device).to(torch.bfloat16)
+             for name, c in (("y_attn", s.hidden), ("y_mlp", s.hidden), ("q", s.q_heads * s.head_dim),
+                             ("k", s.kv_heads * s.head_dim), ("v", s.kv_heads * s.head_dim),
+                             ("gate", s.intermediate), ("up", s.intermediate))}
+        hid = torch.empty(n, s.hidden, dtype=torch.bfloat16, device=device)
+        fin = torch.empty_like(hid)
+        nf8 = torch.empty(n, s.hidden, dtype=torch.uint8, device=device)
+        af8 = torch.empty(n, s.intermediate, dtype=torch.uint8, device=device)
+        sc = torch.zeros(3, 2, dtype=torch.float32, device=device)
+        qr, ao = torch.empty_like(b["q"]), torch.empty_like(b["q"])
+        idv = torch.zeros(n, dtype=torch.int32, device=device)
+        scr = torch.empty(max(k.attn_decode_scratch_bytes(n, 1, s.kv_heads, 8192), 16), dtype=torch.uint8,
+                          device=device)
+
+        def step():
+            k.gpu_multi_embed(d_rows, n, emb_small, s.embedding_multiplier, hid)
+            k.add_rmsnorm_fp8(b["y_attn"], hid, w3[0], s.eps, s.residual_multiplier, h_out=hid, n_fp8=nf8,
+                              scale_amax=sc[0])
+            k.gpu_multi_rope_append(b["q"], b["k"], b["v"], seq.tables.cos, seq.tables.sin, d_rows, n, s.q_heads,
+                                    s.kv_heads, s.head_dim, 8, ck, cv, ksc, vsc, stride, qr)
+            k.attn_decode_int8_paged(qr, ck, cv, ksc, vsc, row_pos, s.q_heads, s.kv_heads, s.head_dim, stride,
+                                     8192, 1.0 / 128, ao, rows_per_group=1, row_pt=row_pt, scratch=scr)
+            k.add_rmsnorm_fp8(b["y_mlp"], hid, w3[1], s.eps, s.residual_multiplier, h_out=hid, n_fp8=nf8,
+                              scale_amax=sc[1])
+            k.swiglu_fp8(b["gate"], b["up"], None, af8, sc[2])
+            k.rmsnorm(hid, w3[2], s.eps, n, s.hidden, fin, batched=True)
+            k.argmax_rows(logits_small[:n], idv)
+            k.multi_scatter_advance(d_rows, idv)
+        decode_step[f"sessions_{n}"] = {"kernels": 10, "graph_replay_us": graph_replay_us(step)}
     del ck, cv, ksc, vsc, table
     torch.cuda.empty_cache()
-    return {"embed": embed, "small": small, "argmax": argmax, "attention": attention}
+    return {"embed": embed, "small": small, "argmax": argmax, "attention": attention, "decode_step": decode_step}
 
 
 def run_e2e(seq, rows, device, steps):

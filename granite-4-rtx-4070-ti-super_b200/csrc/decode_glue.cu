@@ -165,6 +165,29 @@ __global__ void multi_scatter_advance_kernel(granite4_multi_rows* mr, const int3
   mr->pos[r] = pos + 1;
 }
 
+// Embedding rows of a multi-session step: row r takes the token its session holds at the row's slot
+// (engine/src/forward_gpu.cu:359-378, embed_multi_v8_kernel): out[r] = bf16(mult * emb[tok[r][slot]]),
+// slot = pos[r], or slot[r] for tree rows. One CTA per row, 128-bit accesses.
+__global__ void __launch_bounds__(256) multi_embed_kernel(const granite4_multi_rows* mr, const uint4* emb,
+                                                         int vocab, float mult, uint4* out, int H8) {
+  pdl_begin();
+  const int r = blockIdx.x;
+  const int slot = mr->tree ? mr->slot[r] : mr->pos[r];
+  const int tok = mr->tok[r][slot];
+  const bool known = tok >= 0 && tok < vocab;  // an id outside the table gives a zero row
+  for (int c = threadIdx.x; c < H8; c += blockDim.x) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (known) {
+      float f[8];
+      unpack8(__ldg(emb + static_cast<size_t>(tok) * H8 + c), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = __fmul_rn(mult, f[e]);
+      v = pack8(f);
+    }
+    out[static_cast<size_t>(r) * H8 + c] = v;
+  }
+}
+
 struct KvMoveParams {
   int n;
   int src[GRANITE4_MAX_TREE_DEPTH], dst[GRANITE4_MAX_TREE_DEPTH];  // physical pool rows
@@ -245,6 +268,17 @@ int granite4_kernel_multi_scatter_advance(granite4_multi_rows* d_rows, const int
   if (d_rows == nullptr || d_ids == nullptr) return g4::fail(fn, "invalid arguments");
   g4::multi_scatter_advance_kernel<<<1, 32, 0, g4::current_stream()>>>(d_rows, d_ids);
   G4_LAUNCH_CHECK(fn);
+  return 0;
+}
+
+int granite4_gpu_multi_embed(const granite4_multi_rows* d_rows, int rows, const uint16_t* d_emb, int vocab,
+                             float mult, uint16_t* d_out, int H) {
+  const char* fn = "granite4_gpu_multi_embed";
+  if (d_rows == nullptr || d_emb == nullptr || d_out == nullptr || rows < 1 || rows > GRANITE4_MAX_VERIFY_ROWS ||
+      vocab <= 0 || H <= 0 || H % 8 != 0 || !std::isfinite(mult) || !g4::aligned16(d_emb) || !g4::aligned16(d_out))
+    return g4::fail(fn, "invalid arguments");
+  G4_LAUNCH_PDL(fn, g4::multi_embed_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, g4::current_stream(),
+                d_rows, reinterpret_cast<const uint4*>(d_emb), vocab, mult, reinterpret_cast<uint4*>(d_out), H / 8);
   return 0;
 }
 

@@ -264,6 +264,13 @@ def argmax_rows(logits, out, d_pos=None, vocab_map=None):
                                            _p(d_pos, torch.int32), _p(vocab_map, torch.int32))
 
 
+def gpu_multi_embed(d_rows, rows, emb, mult, out):
+    """granite4_gpu_multi_embed: out[r] = bf16(mult * emb[token of row r at its slot])."""
+    lib = _enter(emb)
+    return lib.granite4_gpu_multi_embed(_p(d_rows), rows, _p(emb, *_BF16_OK), emb.shape[0], mult,
+                                        _p(out, *_BF16_OK), emb.shape[1])
+
+
 def multi_scatter_advance(d_rows, ids):
     """granite4_kernel_multi_scatter_advance: d_rows is the uint8 tensor holding a MultiRows."""
     lib = _enter(ids)

@@ -291,6 +291,14 @@ int granite4_kernel_rope_kv_int8_paged(const uint16_t* d_qkv, const float* d_cos
  * advanced, which chains captured decode steps on the device. */
 int granite4_kernel_argmax_rows(const uint16_t* d_logits, int rows, int V, int32_t* d_out,
                                 int* d_pos, const int32_t* d_vocab_map);
+/* Added (embed_multi_v8_kernel, engine/src/forward_gpu.cu:359-378, private to the
+ * reference's forward pass): the embedding rows of a multi-session step.
+ * d_out[r] = bf16(mult * d_emb[tok]) with tok = d_rows->tok[r][slot], slot =
+ * d_rows->pos[r] (d_rows->slot[r] for tree rows); an id outside [0, vocab)
+ * gives a zero row. rows <= 16, H a multiple of 8. Reads the token on the
+ * device, so a captured decode step follows the positions as they advance. */
+int granite4_gpu_multi_embed(const granite4_multi_rows* d_rows, int rows, const uint16_t* d_emb,
+                             int vocab, float mult, uint16_t* d_out, int H);
 /* Added (multi_scatter_advance_kernel, engine/src/forward_gpu.cu:758-764): for
  * r < d_rows->n: d_rows->tok[r][pos[r] + 1] = d_ids[r]; pos[r] += 1. */
 int granite4_kernel_multi_scatter_advance(granite4_multi_rows* d_rows, const int32_t* d_ids);

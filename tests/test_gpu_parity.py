@@ -1446,3 +1446,97 @@ def test_random_shapes_against_the_oracle(K, port, seed):
     out = torch.full((rows4,), -1, dtype=torch.int32, device=DEV)
     assert K.argmax_rows(dev(logits), out) == 0
     assert (out.cpu().numpy() == port.argmax_rows(logits)).all()
+
+
+# =========================================================================== a captured decode step
+def test_decode_step_replayed_from_a_cuda_graph_chains_on_the_device(K, port):
+    """One decode step of four sessions as the reference runs it (engine/src/forward_gpu.cu:2934-2964):
+    embedding of each session's newest token -> add + norm -> RoPE + int8 KV append -> attention over
+    the paged pool -> add + norm -> SwiGLU -> final norm -> greedy pick -> token scatter / position
+    advance, captured once into a CUDA graph and replayed three times. Everything that changes
+    between steps (token, position, pool row) is read from the device descriptor, so the replays
+    walk forward by themselves. The GEMMs between the glue ops are stood in for by fixed buffers."""
+    from granite4_b200 import capi
+    n, stride, max_pos, vocab, H, I = 4, 2048, 1024, 1000, 4096, 12800
+    g = torch.Generator(device=DEV).manual_seed(77)
+    emb = (0.02 * torch.randn(vocab, H, generator=g, device=DEV)).to(torch.bfloat16)
+    w = (1.0 + 0.02 * torch.randn(3, H, generator=g, device=DEV)).to(torch.bfloat16)
+    bufs = {k: torch.randn(n, c, generator=g, device=DEV).to(torch.bfloat16)
+            for k, c in (("y_attn", H), ("y_mlp", H), ("q", Hq * D), ("k", Hk * D), ("v", Hk * D), ("gate", I), ("up", I))}
+    logits = torch.randn(n, vocab, generator=g, device=DEV).to(torch.bfloat16)
+    ck = torch.randint(-127, 128, (Hk, stride, D), generator=g, device=DEV, dtype=torch.int8)
+    cv = torch.randint(-127, 128, (Hk, stride, D), generator=g, device=DEV, dtype=torch.int8)
+    ks = torch.rand(Hk, stride, generator=g, device=DEV) * 0.02 + 0.005
+    vs = torch.rand(Hk, stride, generator=g, device=DEV) * 0.02 + 0.005
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+    pos0 = [10, 100, 37, 511]
+    perm = np.random.default_rng(78).permutation(stride).astype(np.int32)
+    tables = [dev(np.ascontiguousarray(np.resize(perm[r * 512:(r + 1) * 512], max_pos))) for r in range(n)]
+    toks = [torch.zeros(max_pos, dtype=torch.int32, device=DEV) for _ in range(n)]
+    desc = capi.MultiRows()
+    desc.n = n
+    for r in range(n):
+        desc.pos[r] = pos0[r]
+        desc.pt[r] = tables[r].data_ptr()
+        desc.tok[r] = toks[r].data_ptr()
+        toks[r][pos0[r]] = 5 + r
+    d_rows = K.multi_rows_to_device(desc, DEV)
+    row_pos = d_rows[capi.MultiRows.pos.offset:capi.MultiRows.pos.offset + 4 * n].view(torch.int32)
+    row_pt = d_rows[capi.MultiRows.pt.offset:capi.MultiRows.pt.offset + 8 * n].view(torch.int64)
+    hidden = torch.empty(n, H, dtype=torch.bfloat16, device=DEV)
+    n_fp8 = torch.empty(n, H, dtype=torch.uint8, device=DEV)
+    act_fp8 = torch.empty(n, I, dtype=torch.uint8, device=DEV)
+    scales = torch.zeros(3, 2, dtype=torch.float32, device=DEV)
+    q_rot, attn_out = torch.empty(n, Hq * D, dtype=torch.bfloat16, device=DEV), torch.empty(n, Hq * D, dtype=torch.bfloat16, device=DEV)
+    final = torch.empty(n, H, dtype=torch.bfloat16, device=DEV)
+    ids = torch.zeros(n, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(max(K.attn_decode_scratch_bytes(n, 1, Hk, max_pos), 16), dtype=torch.uint8, device=DEV)
+    embedded = torch.empty(n, H, dtype=torch.bfloat16, device=DEV)
+
+    def step():
+        rc = K.gpu_multi_embed(d_rows, n, emb, 12.0, hidden)
+        embedded.copy_(hidden)
+        rc |= K.add_rmsnorm_fp8(bufs["y_attn"], hidden, w[0], 1e-5, 0.22, h_out=hidden, n_fp8=n_fp8, scale_amax=scales[0])
+        rc |= K.gpu_multi_rope_append(bufs["q"], bufs["k"], bufs["v"], t.cos, t.sin, d_rows, n, Hq, Hk, D, 8, ck, cv,
+                                      ks, vs, stride, q_rot)
+        rc |= K.attn_decode_int8_paged(q_rot, ck, cv, ks, vs, row_pos, Hq, Hk, D, stride, max_pos, 1.0 / 128,
+                                       attn_out, rows_per_group=1, row_pt=row_pt, scratch=scratch)
+        rc |= K.add_rmsnorm_fp8(bufs["y_mlp"], hidden, w[1], 1e-5, 0.22, h_out=hidden, n_fp8=n_fp8, scale_amax=scales[1])
+        rc |= K.swiglu_fp8(bufs["gate"], bufs["up"], None, act_fp8, scales[2])
+        rc |= K.rmsnorm(hidden, w[2], 1e-5, n, H, final, batched=True)
+        rc |= K.argmax_rows(logits, ids)
+        rc |= K.multi_scatter_advance(d_rows, ids)
+        assert rc == 0
+
+    side = torch.cuda.Stream(DEV)
+    with torch.cuda.stream(side):
+        # warm-up outside capture on a scratch copy of the state, then restore it
+        snap = [x.clone() for x in (d_rows, ck, cv, ks, vs, *toks)]
+        step()
+        side.synchronize()
+        for dst, src in zip((d_rows, ck, cv, ks, vs, *toks), snap):
+            dst.copy_(src)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+        steps = 3
+        for _ in range(steps):
+            graph.replay()
+        side.synchronize()
+    back = capi.MultiRows.from_buffer_copy(bytes(d_rows.cpu().numpy().tobytes()))
+    picked = port.argmax_rows(host(logits.view(torch.int16)))
+    for r in range(n):
+        assert back.pos[r] == pos0[r] + steps                      # positions advanced on the device
+        got = toks[r].cpu().numpy()
+        assert (got[pos0[r] + 1:pos0[r] + 1 + steps] == picked[r]).all()   # the picked id became the next token
+    # the last replay embedded the token the previous replay picked
+    want_emb = port.embed_rows(picked.astype(np.int32), 0, n, host(emb.view(torch.int16)), 12.0)
+    assert (host(embedded.view(torch.int16)) == want_emb).all()
+    # KV rows were appended at the successive positions: the attention of the last replay equals the
+    # oracle's over the pool as it is now, at the positions the last replay ran at
+    last_pos = np.array([p + steps - 1 for p in pos0], np.int32)
+    want = port.attn_decode_int8(host(q_rot.view(torch.int16)), host(ck), host(cv), host(ks), host(vs), last_pos,
+                                 [host(tb) for tb in tables], Hq, Hk, D, 1.0 / 128)
+    assert np.abs(_bf16_to_f32_np(host(attn_out.view(torch.int16))) - _bf16_to_f32_np(want)).max() < ATT_TOL
+    t.close()
