@@ -513,7 +513,7 @@ def small_shapes_and_embed(seq, rows, device, stream):
         attention[name] = {"mean_us": us, "achieved_gbs": nbytes / (us * 1e-6) / 1e9,
                            "frac": nbytes / (us * 1e-6) / 1e9 / peak, "bytes": nbytes}
     # A whole decode step (one layer's glue + attention at ~4096 positions + final norm + greedy
-    # pick + token scatter) of n sessions, captured into a CUDA graph and replayed: everything that
+    # pick with the token scatter folded in) of n sessions, captured into a CUDA graph and replayed: everything that
     # changes between steps is read from the device descriptor, so the replays chain by themselves.
     from granite4_b200 import capi
     decode_step = {}
@@ -558,9 +558,8 @@ def small_shapes_and_embed(seq, rows, device, stream):
                               scale_amax=sc[1])
             k.swiglu_fp8(b["gate"], b["up"], None, af8, sc[2])
             k.rmsnorm(hid, w3[2], s.eps, n, s.hidden, fin, batched=True)
-            k.argmax_rows(logits_small[:n], idv)
-            k.multi_scatter_advance(d_rows, idv)
-        decode_step[f"sessions_{n}"] = {"kernels": 10, "graph_replay_us": graph_replay_us(step)}
+            k.argmax_advance(logits_small[:n], d_rows, idv)
+        decode_step[f"sessions_{n}"] = {"kernels": 9, "graph_replay_us": graph_replay_us(step)}
     del ck, cv, ksc, vsc, table
     torch.cuda.empty_cache()
     return {"embed": embed, "small": small, "argmax": argmax, "attention": attention, "decode_step": decode_step}

@@ -60,6 +60,7 @@ SIGNATURES = {
                                                      _vp, _vp, _vp, _vp, _vp]),
     "granite4_kernel_argmax_rows": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp, _vp]),
     "granite4_kernel_multi_scatter_advance": (C.c_int, [_vp, _vp]),
+    "granite4_kernel_argmax_advance": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp]),
     "granite4_gpu_multi_embed": (C.c_int, [_vp, C.c_int, _vp, C.c_int, C.c_float, _vp, C.c_int]),
     "granite4_kernel_kv_move": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.c_int, _vp,
                                           _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),

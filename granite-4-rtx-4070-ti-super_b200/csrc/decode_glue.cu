@@ -38,6 +38,7 @@ struct ArgmaxParams {
   int32_t* out;
   int* d_pos;
   const int32_t* map;
+  granite4_multi_rows* advance;  // non-NULL: the pick also becomes the row's next token and its position advances
   int V;
   int rows;
   int ctas_per_row;
@@ -145,7 +146,13 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const Argma
       if (s_cmax[c] > bm || (s_cmax[c] == bm && s_cidx[c] < bi)) bm = s_cmax[c], bi = s_cidx[c];
     int best = (bi == INT_MAX || !(bm > -INFINITY)) ? 0 : bi;
     if (p.map != nullptr) best = p.map[best];
-    if (p.d_pos != nullptr) {
+    if (p.advance != nullptr) {
+      // multi_scatter_advance_kernel of the reference (engine/src/forward_gpu.cu:758-764), folded in
+      const int pos = p.advance->pos[row];
+      p.advance->tok[row][pos + 1] = best;
+      p.advance->pos[row] = pos + 1;
+      if (p.out != nullptr) p.out[row] = best;
+    } else if (p.d_pos != nullptr) {
       const int pos = *p.d_pos;
       p.out[pos + 1] = best;
       *p.d_pos = pos + 1;
@@ -222,22 +229,19 @@ __global__ void __launch_bounds__(128) kv_move_kernel(const KvMoveParams p) {
 
 extern "C" {
 
-int granite4_kernel_argmax_rows(const uint16_t* d_logits, int rows, int V, int32_t* d_out,
-                                int* d_pos, const int32_t* d_vocab_map) {
-  const char* fn = "granite4_kernel_argmax_rows";
-  if (d_logits == nullptr || d_out == nullptr || rows <= 0 || V <= 0 ||
-      (d_pos != nullptr && rows != 1))
-    return g4::fail(fn, "invalid arguments");
-  g4::ArgmaxParams p{};
-  p.logits = d_logits, p.out = d_out, p.d_pos = d_pos, p.map = d_vocab_map, p.V = V, p.rows = rows;
+}  // extern "C"
+
+namespace g4 {
+namespace {
+int launch_argmax(const char* fn, ArgmaxParams p) {
   p.ctas_per_row = 1;
-  cudaStream_t st = g4::current_stream();
-  const bool vec = V % 8 == 0 && g4::aligned16(d_logits);
+  cudaStream_t st = current_stream();
+  const bool vec = p.V % 8 == 0 && aligned16(p.logits);
   // A step of at most 16 rows: several CTAs per row, as one cluster per row.
-  if (vec && rows <= GRANITE4_MAX_VERIFY_ROWS && V >= 8 * 1024 && g4::cluster_enabled()) {
+  if (vec && p.rows <= GRANITE4_MAX_VERIFY_ROWS && p.V >= 8 * 1024 && cluster_enabled()) {
     p.ctas_per_row = 8;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(static_cast<unsigned>(rows * p.ctas_per_row));
+    cfg.gridDim = dim3(static_cast<unsigned>(p.rows * p.ctas_per_row));
     cfg.blockDim = dim3(512);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -249,18 +253,43 @@ int granite4_kernel_argmax_rows(const uint16_t* d_logits, int rows, int V, int32
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    void (*kernel)(g4::ArgmaxParams) = g4::argmax_rows_kernel<true, true>;
-    if (g4::cluster_fits(reinterpret_cast<const void*>(kernel), cfg, p.ctas_per_row, 512)) {
-      cfg.numAttrs = g4::pdl_enabled() ? 2 : 1;
+    void (*kernel)(ArgmaxParams) = argmax_rows_kernel<true, true>;
+    if (cluster_fits(reinterpret_cast<const void*>(kernel), cfg, p.ctas_per_row, 512)) {
+      cfg.numAttrs = pdl_enabled() ? 2 : 1;
       G4_CUDA_TRY(fn, cudaLaunchKernelEx(&cfg, kernel, p));
       return 0;
     }
     p.ctas_per_row = 1;
   }
-  const dim3 grid(static_cast<unsigned>(rows)), block(g4::kArgmaxThreads);
-  if (vec) G4_LAUNCH_PDL(fn, g4::argmax_rows_kernel<true, false>, grid, block, 0, st, p);
-  else G4_LAUNCH_PDL(fn, g4::argmax_rows_kernel<false, false>, grid, block, 0, st, p);
+  const dim3 grid(static_cast<unsigned>(p.rows)), block(kArgmaxThreads);
+  if (vec) G4_LAUNCH_PDL(fn, argmax_rows_kernel<true, false>, grid, block, 0, st, p);
+  else G4_LAUNCH_PDL(fn, argmax_rows_kernel<false, false>, grid, block, 0, st, p);
   return 0;
+}
+}  // namespace
+}  // namespace g4
+
+extern "C" {
+
+int granite4_kernel_argmax_rows(const uint16_t* d_logits, int rows, int V, int32_t* d_out,
+                                int* d_pos, const int32_t* d_vocab_map) {
+  const char* fn = "granite4_kernel_argmax_rows";
+  if (d_logits == nullptr || d_out == nullptr || rows <= 0 || V <= 0 ||
+      (d_pos != nullptr && rows != 1))
+    return g4::fail(fn, "invalid arguments");
+  g4::ArgmaxParams p{};
+  p.logits = d_logits, p.out = d_out, p.d_pos = d_pos, p.map = d_vocab_map, p.V = V, p.rows = rows;
+  return g4::launch_argmax(fn, p);
+}
+
+int granite4_kernel_argmax_advance(const uint16_t* d_logits, int rows, int V, granite4_multi_rows* d_rows,
+                                   int32_t* d_ids_out) {
+  const char* fn = "granite4_kernel_argmax_advance";
+  if (d_logits == nullptr || d_rows == nullptr || rows <= 0 || rows > GRANITE4_MAX_VERIFY_ROWS || V <= 0)
+    return g4::fail(fn, "invalid arguments");
+  g4::ArgmaxParams p{};
+  p.logits = d_logits, p.out = d_ids_out, p.advance = d_rows, p.V = V, p.rows = rows;
+  return g4::launch_argmax(fn, p);
 }
 
 int granite4_kernel_multi_scatter_advance(granite4_multi_rows* d_rows, const int32_t* d_ids) {

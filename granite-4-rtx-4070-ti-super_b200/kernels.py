@@ -264,6 +264,13 @@ def argmax_rows(logits, out, d_pos=None, vocab_map=None):
                                            _p(d_pos, torch.int32), _p(vocab_map, torch.int32))
 
 
+def argmax_advance(logits, d_rows, ids_out=None):
+    """granite4_kernel_argmax_advance: greedy pick + token scatter / position advance in one launch."""
+    lib = _enter(logits)
+    rows, V = logits.shape
+    return lib.granite4_kernel_argmax_advance(_p(logits, *_BF16_OK), rows, V, _p(d_rows), _p(ids_out, torch.int32))
+
+
 def gpu_multi_embed(d_rows, rows, emb, mult, out):
     """granite4_gpu_multi_embed: out[r] = bf16(mult * emb[token of row r at its slot])."""
     lib = _enter(emb)

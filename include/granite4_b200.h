@@ -291,6 +291,14 @@ int granite4_kernel_rope_kv_int8_paged(const uint16_t* d_qkv, const float* d_cos
  * advanced, which chains captured decode steps on the device. */
 int granite4_kernel_argmax_rows(const uint16_t* d_logits, int rows, int V, int32_t* d_out,
                                 int* d_pos, const int32_t* d_vocab_map);
+/* Added: the greedy pick of a multi-session step fused with the token scatter
+ * that follows it in the reference's decode graph (argmax_rows_kernel then
+ * multi_scatter_advance_kernel, engine/src/forward_gpu.cu:2617, :758-764): for
+ * r < rows, id = first index of the maximum of logits row r;
+ * d_rows->tok[r][pos[r] + 1] = id; d_rows->pos[r] += 1; d_ids_out[r] = id when
+ * d_ids_out is given. rows <= 16. */
+int granite4_kernel_argmax_advance(const uint16_t* d_logits, int rows, int V,
+                                   granite4_multi_rows* d_rows, int32_t* d_ids_out);
 /* Added (embed_multi_v8_kernel, engine/src/forward_gpu.cu:359-378, private to the
  * reference's forward pass): the embedding rows of a multi-session step.
  * d_out[r] = bf16(mult * d_emb[tok]) with tok = d_rows->tok[r][slot], slot =

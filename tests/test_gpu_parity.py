@@ -1504,8 +1504,7 @@ def test_decode_step_replayed_from_a_cuda_graph_chains_on_the_device(K, port):
         rc |= K.add_rmsnorm_fp8(bufs["y_mlp"], hidden, w[1], 1e-5, 0.22, h_out=hidden, n_fp8=n_fp8, scale_amax=scales[1])
         rc |= K.swiglu_fp8(bufs["gate"], bufs["up"], None, act_fp8, scales[2])
         rc |= K.rmsnorm(hidden, w[2], 1e-5, n, H, final, batched=True)
-        rc |= K.argmax_rows(logits, ids)
-        rc |= K.multi_scatter_advance(d_rows, ids)
+        rc |= K.argmax_advance(logits, d_rows, ids)   # greedy pick + token scatter / position advance
         assert rc == 0
 
     side = torch.cuda.Stream(DEV)
@@ -1540,3 +1539,35 @@ def test_decode_step_replayed_from_a_cuda_graph_chains_on_the_device(K, port):
                                  [host(tb) for tb in tables], Hq, Hk, D, 1.0 / 128)
     assert np.abs(_bf16_to_f32_np(host(attn_out.view(torch.int16))) - _bf16_to_f32_np(want)).max() < ATT_TOL
     t.close()
+
+
+def test_argmax_advance_equals_pick_then_scatter(K, port):
+    """The fused entry point does what granite4_kernel_argmax_rows followed by
+    granite4_kernel_multi_scatter_advance does; wide vocabulary (one cluster per row) and a narrow one."""
+    from granite4_b200 import capi
+    for V in (100352, 1000):
+        n = 6
+        logits = rand_bf16(2700 + V, (n, V), 3.0)
+        picked = port.argmax_rows(logits)
+        states = []
+        for fused in (True, False):
+            bufs = [torch.zeros(64, dtype=torch.int32, device=DEV) for _ in range(n)]
+            desc = capi.MultiRows()
+            desc.n = n
+            for r in range(n):
+                desc.pos[r] = 2 * r + 1
+                desc.tok[r] = bufs[r].data_ptr()
+            d_rows = K.multi_rows_to_device(desc, DEV)
+            ids = torch.full((n,), -1, dtype=torch.int32, device=DEV)
+            if fused:
+                assert K.argmax_advance(dev(logits), d_rows, ids) == 0
+                assert K.argmax_advance(dev(logits), d_rows, None) == 0
+            else:
+                for _ in range(2):
+                    assert K.argmax_rows(dev(logits), ids) == 0
+                    assert K.multi_scatter_advance(d_rows, ids) == 0
+            back = capi.MultiRows.from_buffer_copy(bytes(d_rows.cpu().numpy().tobytes()))
+            states.append(([back.pos[r] for r in range(n)], [b_.cpu().tolist() for b_ in bufs], ids.cpu().tolist()))
+        assert states[0] == states[1]
+        assert states[0][2] == picked.tolist()
+        assert states[0][0] == [2 * r + 3 for r in range(n)]
