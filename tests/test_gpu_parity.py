@@ -1571,3 +1571,28 @@ def test_argmax_advance_equals_pick_then_scatter(K, port):
         assert states[0] == states[1]
         assert states[0][2] == picked.tolist()
         assert states[0][0] == [2 * r + 3 for r in range(n)]
+
+
+def test_attention_over_a_short_prefill_chunk_as_row_groups(K, port):
+    """A prefill chunk can run on the decode kernels as groups of four consecutive rows (each group
+    reads its own causal prefix): BASELINE config 3 shape, 500 tokens at positions 0..499 written by
+    the RoPE + KV kernel, then attended. Efficient only for short chunks (no K/V reuse across
+    groups), but it is the same arithmetic. 120 of the rows are checked against the oracle."""
+    n, stride, max_pos = 500, 512, 512
+    qkv = rand_bf16(2800, (n, 48 * D), 1.0)
+    table = np.random.default_rng(81).permutation(stride).astype(np.int32)
+    pos = np.arange(n, dtype=np.int32)
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+    ck, cv, ks, vs = _pool(stride)
+    q_rot = empty_bf16(n, Hq * D)
+    assert K.rope_kv_int8_paged(dev(qkv), t.cos, t.sin, dev(pos), dev(np.ascontiguousarray(table[:n])), Hq, Hk, D,
+                                stride, max_pos, 0, q_rot, ck, cv, ks, vs) == 0
+    out = empty_bf16(n, Hq * D)
+    scale = 1.0 / 128
+    assert K.attn_decode_int8_paged(q_rot, ck, cv, ks, vs, dev(pos), Hq, Hk, D, stride, max_pos, scale, out,
+                                    rows_per_group=4, pt=dev(table)) == 0
+    sel = np.r_[0:8, 61:69, 250:258, 404:500]
+    want = port.attn_decode_int8(host(q_rot)[sel], host(ck), host(cv), host(ks), host(vs), pos[sel],
+                                 [table] * len(sel), Hq, Hk, D, scale)
+    assert np.abs(_bf16_to_f32_np(host(out)[sel]) - _bf16_to_f32_np(want)).max() < ATT_TOL
+    t.close()
