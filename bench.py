@@ -391,7 +391,7 @@ TRAFFIC_PER_ROW = {"add_rmsnorm_fp8": 26542, "rope_kv_int8": 16597, "swiglu_fp8"
 
 def small_shapes_and_embed(seq, rows, device, stream):
     """(1) The embedding gather at the shard's row count on a Granite-size table (100352 x 4096,
-    ids uniform, multiplier 12). (2) BASELINE configs 1-3: one decode row, the decode chain at 1
+    ids uniform, multiplier 12). (2) benchmark configurations 1-3: one decode row, the decode chain at 1
     and 8 rows replayed from a CUDA graph, one 500-row prefill layer - latency-bound shapes,
     reported in microseconds, not against the bandwidth roofline."""
     import torch

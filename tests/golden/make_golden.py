@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz from the REFERENCE's own host code.
 
-Run where a reference checkout is mounted (default /root/reference):
+Run where a reference checkout is mounted (its root is the REF default of oracle/Makefile):
 
     python tests/golden/make_golden.py
 

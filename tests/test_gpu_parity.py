@@ -169,7 +169,7 @@ def test_rmsnorm_zero_row_and_known_values(K, port):
 
 
 def test_add_rmsnorm_config1_golden(K):
-    """BASELINE config 1: one decode row, f32 x and residual, rm 0.22, bf16 + FP8 outputs."""
+    """benchmark configuration 1: one decode row, f32 x and residual, rm 0.22, bf16 + FP8 outputs."""
     z = golden("c1_add_rmsnorm_f32")
     h, n = empty_bf16(1, 4096), empty_bf16(1, 4096)
     c = torch.empty(1, 4096, dtype=torch.uint8, device=DEV)
@@ -449,7 +449,7 @@ def test_rope_kv_bad_rows_are_skipped(K, port):
 
 
 def test_long_context_positions_and_pool(K, port):
-    """BASELINE config 4 in shape: 4 sequences, positions up to 131071, a 122880-row pool with
+    """benchmark configuration 4 in shape: 4 sequences, positions up to 131071, a 122880-row pool with
     randomly permuted 16-token pages; a 2048-row sample per sequence is compared with the
     oracle, and the full table is checked to write every row exactly once."""
     from granite4_b200 import paging
@@ -720,9 +720,9 @@ def test_host_buffer_path_equals_the_device_path(K):
     hg.close()
 
 
-# =========================================================================== BASELINE configs at full size
+# =========================================================================== benchmark configurations at full size
 def test_config3_prefill_500_tokens_full_chain(K, port):
-    """BASELINE config 3: one 500-token prompt, positions 0..499, the whole op chain over
+    """benchmark configuration 3: one 500-token prompt, positions 0..499, the whole op chain over
     [500 x 4096] hidden and [500 x 12800] MLP activations, K/V into an int8 pool of 16-token
     pages through the kept prefill entry points."""
     from granite4_b200 import paging
@@ -771,7 +771,7 @@ def test_config3_prefill_500_tokens_full_chain(K, port):
 
 
 def test_config4_long_context_full_size(K, port):
-    """BASELINE config 4 at full size: 4 sequences x 8192 tokens, RoPE positions offset up to
+    """benchmark configuration 4 at full size: 4 sequences x 8192 tokens, RoPE positions offset up to
     131071, K/V into a 122880-row int8 pool with randomly permuted 16-token pages; bf16 N(0,1)-like
     activations, norm weights around 1. RoPE + KV and add + norm + FP8 are compared with the oracle
     over all 32768 rows."""
@@ -1230,7 +1230,7 @@ def test_attention_verify_group_shares_one_sequence(K, port):
     for scale, check_golden in ((1.0 / 128, True), (0.0883, False)):
         # 1/128 is Granite's attention multiplier (engine/src/kernel_math.h:13). With 1/sqrt(128) the
         # softmax is peaked and the golden pipeline's own bf16 rounding of the logits moves its
-        # result by more than the 0.03 bar, so there the unrounded evaluation is the only judge.
+        # result by more than the 0.03 bar, so there the unrounded evaluation is the only yardstick.
         assert K.attn_decode_int8_paged(dev(q), dev(ck), dev(cv), dev(ks), dev(vs), dev(pos), Hq, Hk, D,
                                         stride, max_len, scale, out, rows_per_group=4, pt=dev(table)) == 0
         got = _bf16_to_f32_np(host(out)).reshape(rows, Hq, D)
@@ -1575,7 +1575,7 @@ def test_argmax_advance_equals_pick_then_scatter(K, port):
 
 def test_attention_over_a_short_prefill_chunk_as_row_groups(K, port):
     """A prefill chunk can run on the decode kernels as groups of four consecutive rows (each group
-    reads its own causal prefix): BASELINE config 3 shape, 500 tokens at positions 0..499 written by
+    reads its own causal prefix): benchmark configuration 3 shape, 500 tokens at positions 0..499 written by
     the RoPE + KV kernel, then attended. Efficient only for short chunks (no K/V reuse across
     groups), but it is the same arithmetic. 120 of the rows are checked against the oracle."""
     n, stride, max_pos = 500, 512, 512
