@@ -497,7 +497,8 @@ def small_shapes_and_embed(seq, rows, device, stream):
     table = (pages.repeat_interleave(page) * page + torch.arange(stride, device=device) % page).to(torch.int32)
     attention = {}
     for name, n, group, ctx in (("1_row_ctx_131072", 1, 1, 131072), ("8_rows_ctx_32768", 8, 1, 32768),
-                                ("verify_4_rows_ctx_32768", 4, 4, 32768)):
+                                ("verify_4_rows_ctx_32768", 4, 4, 32768),
+                                ("verify_8_groups_of_4_rows_ctx_32768", 32, 4, 32768)):
         qa = torch.randn(n, s.q_heads * s.head_dim, generator=g, device=device).to(torch.bfloat16)
         pos = torch.full((n,), ctx - 1, dtype=torch.int32, device=device)
         if group > 1:

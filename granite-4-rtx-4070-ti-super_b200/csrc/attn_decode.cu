@@ -18,16 +18,15 @@
 // exact result.
 //
 // This op is memory-bound: per cache position and kv head it reads 2 x 128 code
-// bytes + 2 scales (264 B) for 1024 multiply-adds, more than the f32 pipes
-// deliver at HBM speed, so the two contractions run on the tensor cores
-// (mma.sync m16n8k16, fp16 in, f32 accumulate; the 16 rows of the tile are the 4
-// q heads of the kv head x up to 4 query rows of one sequence).
+// bytes + 2 scales (264 B) for 1024 multiply-adds per query row, more than the
+// f32 pipes deliver at HBM speed, so the two contractions run on the tensor
+// cores (mma.sync m16n8k16, fp16 in, f32 accumulate).
 //
 // Decomposition: grid (split, kv head, row group). A CTA has 4 warps and owns a
 // contiguous range of cache positions; each warp works alone on tiles of 16
-// positions (gathers the 16 K and V code rows through the page table, converts
-// them into its own shared-memory tile, S = Q K^T, online softmax, O += P V) with
-// its own running (max, sum, O), so the main loop has no CTA barrier. The warps'
+// positions (gathers the 16 K and V code rows through the page table into its
+// own shared-memory ring, S^T = K Q^T, online softmax, O^T += V^T P^T) with its
+// own running (max, sum, O), so the main loop has no CTA barrier. The warps'
 // states are merged in shared memory at the end, the splits' states by a second
 // small kernel (flash-decoding).
 //
@@ -40,7 +39,6 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
-#include <cstdlib>
 
 namespace g4 {
 namespace {
@@ -49,21 +47,17 @@ constexpr int kAD = 128;       // head dim
 constexpr int kTile = 16;      // cache positions per warp tile
 constexpr int kWarps = 4;
 constexpr int kGqa = 4;        // q heads per kv head
-constexpr int kGroupRows = 4;  // query rows per CTA (4 x 4 = the 16 rows of the mma tile)
+constexpr int kGroupRows = 4;  // query rows of one sequence per CTA (two column tiles of 2 rows x 4 heads)
 constexpr int kSplitAlign = kTile * kWarps;
-constexpr int kCtasPerSm = 3;  // register and shared-memory budget of the main kernel
+constexpr int kCtasPerSm = 3;  // register budget with two column tiles (groups of three or four rows)
 
-// Shared memory of one warp: kStages tiles of raw K and V code rows, filled by 16-byte asynchronous
+// Shared memory of one warp: kStagesT tiles of raw K and V code rows, filled by 16-byte asynchronous
 // copies (cp.async), so the bytes in flight occupy no registers. Rows are padded to 144 bytes: the
 // 32-bit K fragment loads of the 32 lanes (8 positions x 4 k-groups) and the eight 16-byte row
 // pieces of an ldmatrix then hit different banks. Both mma operands are built from the raw bytes
 // in registers; no converted copy of a tile is ever written back to shared memory.
-constexpr int kStages = 4;
 constexpr int kPitch = kAD + 16;          // bytes per raw code row
 constexpr int kRawTile = kTile * kPitch;  // 2304
-constexpr int kWarpSmem = kStages * 2 * kRawTile;  // 18432
-constexpr size_t kAttnSmemBytes = static_cast<size_t>(kWarps) * kWarpSmem;
-static_assert(kWarpSmem >= (16 * kAD + 32) * 4, "a warp parks its final state in its own block");
 
 struct AttnParams {
   const uint16_t* q;
@@ -169,305 +163,14 @@ __device__ __forceinline__ void merge_warps(const AttnParams& p, const unsigned 
   }
 }
 
-__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) attn_decode_kernel(const AttnParams p) {
-  pdl_begin();
-  extern __shared__ __align__(128) unsigned char s_dyn[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const int split = blockIdx.x, hkv = blockIdx.y, grp = blockIdx.z;
-  const int r0 = grp * p.group_rows;
-  const int nrows = min(p.group_rows, p.rows - r0);
-  unsigned char* wsm = s_dyn + static_cast<size_t>(warp) * kWarpSmem;
-  unsigned char* raw_k = wsm;                       // [kStages][16][144]
-  unsigned char* raw_v = wsm + kStages * kRawTile;  // [kStages][16][144]
-
-  // positions of the group's rows; the mma rows g and g + 8 belong to query rows g / 4 and 2 + g / 4
-  int pos_lo = -1, pos_hi = -1, pos_max = -1;
-  for (int j = 0; j < nrows; ++j) {
-    int pj = __ldg(p.row_pos + r0 + j);
-    pj = pj < 0 ? -1 : min(pj, p.max_len - 1);
-    pos_max = max(pos_max, pj);
-    if (j == (g >> 2)) pos_lo = pj;
-    if (j == 2 + (g >> 2)) pos_hi = pj;
-  }
-  const int* pt = p.row_pt != nullptr ? p.row_pt[r0] : p.pt;
-  const int t_begin = split * p.split_len;
-  const int t_end = min(t_begin + p.split_len, pos_max + 1);
-
-  // ---- Q fragments: 16 rows (query row j = m / 4, head hl = m % 4) x 128 dims, as fp16 scaled by
-  // a power of two so that the largest magnitude sits near 2^10. Within each 16-wide k-step the
-  // contraction index is permuted: lane group t takes dims 4 t .. 4 t + 3 (first operand register
-  // 4 t, 4 t + 1, second 4 t + 2, 4 t + 3) instead of 2 t, 2 t + 1 and 2 t + 8, 2 t + 9. A dot product
-  // does not care about the order, and the matching K operand is then four consecutive code
-  // bytes: one 32-bit shared-memory load per mma.
-  uint32_t qa[8][4];
-  float logit_scale;
-  float q_off[2];  // rows g and g + 8
-  {
-    float qf[8][8];  // per k-step: row g dims 4t, 4t+1 | row g+8 same | row g dims 4t+2, 4t+3 | row g+8 same
-    float qmax = 0.0f;
-#pragma unroll
-    for (int half_rows = 0; half_rows < 2; ++half_rows) {
-      const int m = g + 8 * half_rows;
-      const int j = m >> 2, hl = m & 3;
-      const bool live = j < nrows;
-      const uint16_t* qrow = p.q + (static_cast<size_t>(r0 + (live ? j : 0)) * p.Hq + hkv * kGqa + hl) * kAD;
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint2 w = live ? __ldg(reinterpret_cast<const uint2*>(qrow + kk * 16 + 4 * t)) : make_uint2(0u, 0u);
-        const float d0 = bf16_to_f32(w.x & 0xffffu), d1 = bf16_to_f32(w.x >> 16);
-        const float d2 = bf16_to_f32(w.y & 0xffffu), d3 = bf16_to_f32(w.y >> 16);
-        qf[kk][half_rows * 2 + 0] = d0, qf[kk][half_rows * 2 + 1] = d1;
-        qf[kk][4 + half_rows * 2 + 0] = d2, qf[kk][4 + half_rows * 2 + 1] = d3;
-        qmax = fmaxf(qmax, fmaxf(fmaxf(fabsf(d0), fabsf(d1)), fmaxf(fabsf(d2), fabsf(d3))));
-      }
-    }
-    qmax = warp_max(qmax);
-    int qexp = 0;
-    if (qmax > 0.0f && qmax < INFINITY)
-      qexp = min(max(((__float_as_int(qmax) >> 23) & 0xff) - 127 - 10, -100), 100);
-    const float qdown = __int_as_float((127 - qexp) << 23);  // 2^-qexp
-    logit_scale = p.scale_log2 * __int_as_float((127 + qexp) << 23);
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      // operand registers: (row g, k lo), (row g + 8, k lo), (row g, k hi), (row g + 8, k hi)
-      qa[kk][0] = pack_half2(qf[kk][0] * qdown, qf[kk][1] * qdown);
-      qa[kk][1] = pack_half2(qf[kk][2] * qdown, qf[kk][3] * qdown);
-      qa[kk][2] = pack_half2(qf[kk][4] * qdown, qf[kk][5] * qdown);
-      qa[kk][3] = pack_half2(qf[kk][6] * qdown, qf[kk][7] * qdown);
-    }
-    // 1152 x the sum of each q row as the mma sees it (the fp16 values), for the code offset
-#pragma unroll
-    for (int hr = 0; hr < 2; ++hr) {
-      float sum = 0.0f;
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qa[kk][hr]));
-        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qa[kk][2 + hr]));
-        sum += (a.x + a.y) + (b.x + b.y);
-      }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      q_off[hr] = kCodeBias * sum;
-    }
-  }
-
-  // O accumulators: o[2 b + par] is the n-tile of 16-dim block b whose column c stands for dim
-  // 16 b + 2 c + par (see the V operand below); a thread's four values of a block (par 0 / 1,
-  // columns 2 t / 2 t + 1) are therefore the four consecutive dims 16 b + 4 t .. + 3.
-  float o[16][4];
-#pragma unroll
-  for (int nd = 0; nd < 16; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.0f;
-  float osum[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // P against a column of ones: sum of the fp16 probabilities
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-  // the lowest position among the group's rows: tiles entirely below it need no causal mask
-  int pos_min = pos_max;
-  for (int j = 0; j < nrows; ++j) {
-    const int pj = __ldg(p.row_pos + r0 + j);
-    pos_min = min(pos_min, pj < 0 ? -1 : min(pj, p.max_len - 1));
-  }
-  const size_t head_row0 = static_cast<size_t>(hkv) * p.stride;
-
-  // ---- gather. Lane l (and l + 16) looks up the pool row of tile position l and fetches that
-  // position's two scales. The code rows are copied four rows per instruction: in copy i lane l
-  // moves 16-byte piece l % 8 of row 4 i + l / 8, so one instruction covers four whole 128-byte
-  // rows (every 32-byte sector requested once). While tile i is computed, the raw codes of tiles
-  // i + 1 and i + 2 are in flight into this warp's stages and the table entries of tile i + 3 are
-  // being looked up, so neither of the two dependent global latencies (table -> row address ->
-  // codes) is exposed.
-  constexpr int kStep = kTile * kWarps;
-  auto table_row = [&](int tile0) -> int {
-    const int tpos = tile0 + (lane & 15);
-    if (tpos >= t_end) return 0;
-    const int prow = pt != nullptr ? __ldg(pt + tpos) : tpos;
-    return min(max(prow, 0), static_cast<int>(p.stride) - 1);
-  };
-  auto gather = [&](int stage, int tile0, int prow, float& sk, float& sv) {
-    const int piece = (lane & 7) * 16;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int n = 4 * i + (lane >> 3);
-      const int pr = __shfl_sync(0xffffffffu, prow, n);
-      const bool have = tile0 + n < t_end;
-      const size_t off = (head_row0 + pr) * kAD + piece;
-      cp_async16(raw_k + stage * kRawTile + n * kPitch + piece, p.ck + off, have);
-      cp_async16(raw_v + stage * kRawTile + n * kPitch + piece, p.cv + off, have);
-    }
-    cp_async_commit();
-    const bool mine = tile0 + (lane & 15) < t_end;
-    sk = mine ? __ldg(p.ks + head_row0 + prow) : 0.0f;
-    sv = mine ? __ldg(p.vs + head_row0 + prow) : 0.0f;
-  };
-  const int t_first = t_begin + warp * kTile;
-  float sk_q[kStages], sv_q[kStages];  // scales of the tiles in flight, oldest first (lane n: position n)
-  {
-    const int pr0 = table_row(t_first), pr1 = table_row(t_first + kStep), pr2 = table_row(t_first + 2 * kStep);
-    gather(0, t_first, pr0, sk_q[0], sv_q[0]);
-    gather(1, t_first + kStep, pr1, sk_q[1], sv_q[1]);
-    gather(2, t_first + 2 * kStep, pr2, sk_q[2], sv_q[2]);
-  }
-  int prow_next = table_row(t_first + 3 * kStep);
-  int stage = 0;
-
-  for (int t0 = t_first; t0 < t_end; t0 += kStep) {
-    cp_async_wait<kStages - 2>();  // all but the newest two groups have landed: tile i is in shared memory
-    __syncwarp();                  // ... for every lane, and every lane is done with tile i - 1
-    // tile i + 3 goes into the stage tile i - 1 was read out of
-    gather((stage + kStages - 1) % kStages, t0 + (kStages - 1) * kStep, prow_next, sk_q[kStages - 1],
-           sv_q[kStages - 1]);
-    prow_next = table_row(t0 + kStages * kStep);
-    const float sk_cur = sk_q[0], sv_cur = sv_q[0];
-#pragma unroll
-    for (int i = 0; i + 1 < kStages; ++i) sk_q[i] = sk_q[i + 1], sv_q[i] = sv_q[i + 1];
-
-    // ---- S = Q K^T over the tile: two 8-position column blocks, K operands straight from the
-    // raw codes (two accumulators per block halve the dependent mma chain)
-    float s[2][4];
-    const unsigned char* kstage = raw_k + stage * kRawTile;
-    const unsigned char* vstage = raw_v + stage * kRawTile;
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      float sa[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      const unsigned char* krow = kstage + (nt * 8 + g) * kPitch + 4 * t;
-#pragma unroll
-      for (int kk = 0; kk < 8; kk += 2) {
-        uint32_t b0, b1, c0, c1;
-        codes4_to_half(*reinterpret_cast<const uint32_t*>(krow + kk * 16), b0, b1);
-        codes4_to_half(*reinterpret_cast<const uint32_t*>(krow + kk * 16 + 16), c0, c1);
-        mma_f16(sa, qa[kk], b0, b1);
-        mma_f16(sb, qa[kk + 1], c0, c1);
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) s[nt][i] = sa[i] + sb[i];
-    }
-    stage = (stage + 1) % kStages;
-
-    // ---- scale, mask, online softmax; thread holds columns n = nt * 8 + 2 t + {0, 1} of rows g, g + 8
-    float pr[2][4];
-    float tile_max[2] = {-INFINITY, -INFINITY};
-    float svn[2][2];
-    const bool unmasked = t0 + kTile <= t_end && t0 + kTile - 1 <= pos_min;  // warp-uniform
-    const bool upper = nrows > 2;  // tile rows 8..15 carry query rows 2 and 3; a decode row leaves them empty
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int n = nt * 8 + 2 * t + e;
-        const float f = __shfl_sync(0xffffffffu, sk_cur, n) * logit_scale;
-        svn[nt][e] = __shfl_sync(0xffffffffu, sv_cur, n);
-        float a = (s[nt][e] - q_off[0]) * f;
-        float b = upper ? (s[nt][2 + e] - q_off[1]) * f : -INFINITY;
-        if (!unmasked) {
-          const int tp = t0 + n;
-          if (tp > pos_lo || tp >= t_end) a = -INFINITY;
-          if (tp > pos_hi || tp >= t_end) b = -INFINITY;
-        }
-        s[nt][e] = a, s[nt][2 + e] = b;
-        tile_max[0] = fmaxf(tile_max[0], a);
-        tile_max[1] = fmaxf(tile_max[1], b);
-      }
-    }
-    float corr[2];
-#pragma unroll
-    for (int hr = 0; hr < 2; ++hr) {
-      if (hr == 1 && !upper) {
-        corr[1] = 1.0f;
-        pr[0][2] = pr[0][3] = pr[1][2] = pr[1][3] = 0.0f;
-        continue;
-      }
-      float mx = tile_max[hr];
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float m_new = fmaxf(m_run[hr], mx);
-      corr[hr] = (m_new == -INFINITY) ? 1.0f : ex2_approx(m_run[hr] - m_new);  // 2^-inf = 0
-      const float base = (m_new == -INFINITY) ? 0.0f : m_new;
-      float sum = 0.0f;
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float pv = ex2_approx(s[nt][2 * hr + e] - base);  // masked: 2^-inf = 0
-          pr[nt][2 * hr + e] = pv;
-          sum += pv;
-        }
-      l_run[hr] = l_run[hr] * corr[hr] + sum;  // this thread's columns only; quads are summed at the end
-      m_run[hr] = m_new;
-    }
-    // the running maximum settles after a few tiles; most tiles need no rescaling at all
-    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
-#pragma unroll
-      for (int nd = 0; nd < 16; ++nd) {
-        o[nd][0] *= corr[0], o[nd][1] *= corr[0];
-        o[nd][2] *= corr[1], o[nd][3] *= corr[1];
-      }
-      osum[0] *= corr[0], osum[1] *= corr[0], osum[2] *= corr[1], osum[3] *= corr[1];
-    }
-    // ---- O += (P diag(v_scale)) V: P's accumulator layout is the A-operand layout ------------------
-    uint32_t pa[4];
-    pa[0] = pack_half2(pr[0][0] * svn[0][0], pr[0][1] * svn[0][1]);
-    pa[1] = pack_half2(pr[0][2] * svn[0][0], pr[0][3] * svn[0][1]);
-    pa[2] = pack_half2(pr[1][0] * svn[1][0], pr[1][1] * svn[1][1]);
-    pa[3] = pack_half2(pr[1][2] * svn[1][0], pr[1][3] * svn[1][1]);
-    // V operand straight from the raw bytes: the tile is read as 16-bit elements (two adjacent
-    // dims of one position), transposed by ldmatrix; a register then holds positions 2 t, 2 t + 1 for
-    // dims 2 g and 2 g + 1 of a 16-dim block, and one byte permute each picks the (position pair,
-    // dim) halves of the even-dim and of the odd-dim n-tile, already in fp16 form (code + 1152).
-#pragma unroll
-    for (int blk = 0; blk < 8; blk += 2) {
-      // matrices: (pos 0-7, block blk), (pos 8-15, block blk), (pos 0-7, block blk + 1), (pos 8-15, ..)
-      uint32_t r[4];
-      ldmatrix_x4_trans(r, vstage + (lane & 15) * kPitch + (blk + (lane >> 4)) * 16);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) r[i] ^= 0x80808080u;
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const uint32_t lo = r[2 * u], hi = r[2 * u + 1];  // positions 0-7 / 8-15 of block blk + u
-        mma_f16(o[2 * (blk + u)], pa, __byte_perm(lo, 0x64646464u, 0x4240), __byte_perm(hi, 0x64646464u, 0x4240));
-        mma_f16(o[2 * (blk + u) + 1], pa, __byte_perm(lo, 0x64646464u, 0x4341), __byte_perm(hi, 0x64646464u, 0x4341));
-      }
-    }
-    mma_f16(osum, pa, 0x3c003c00u, 0x3c003c00u);  // the column of ones
-  }
-  // take the code offset out of the accumulators: O = O_mma - 1152 * sum(p)
-#pragma unroll
-  for (int nd = 0; nd < 16; ++nd) {
-    o[nd][0] -= kCodeBias * osum[0], o[nd][1] -= kCodeBias * osum[0];
-    o[nd][2] -= kCodeBias * osum[2], o[nd][3] -= kCodeBias * osum[2];
-  }
-
-  cp_async_wait<0>();  // nothing of this thread's may still be landing when the memory is reused
-  // ---- merge the four warps' states (each warp parks its state at the start of its own block) ----
-#pragma unroll
-  for (int hr = 0; hr < 2; ++hr) {
-    l_run[hr] += __shfl_xor_sync(0xffffffffu, l_run[hr], 1);
-    l_run[hr] += __shfl_xor_sync(0xffffffffu, l_run[hr], 2);
-  }
-  __syncwarp();
-  float* wo = reinterpret_cast<float*>(wsm);  // [16][128] floats
-  float* wml = wo + 16 * kAD;                 // [16][2]
-#pragma unroll
-  for (int blk = 0; blk < 8; ++blk) {
-    // dims 16 blk + 4 t + {0, 1, 2, 3} = (even tile col 2t, odd tile col 2t, even col 2t+1, odd col 2t+1)
-    *reinterpret_cast<float4*>(wo + g * kAD + blk * 16 + 4 * t) =
-        make_float4(o[2 * blk][0], o[2 * blk + 1][0], o[2 * blk][1], o[2 * blk + 1][1]);
-    *reinterpret_cast<float4*>(wo + (g + 8) * kAD + blk * 16 + 4 * t) =
-        make_float4(o[2 * blk][2], o[2 * blk + 1][2], o[2 * blk][3], o[2 * blk + 1][3]);
-  }
-  if (t == 0) {
-    wml[g * 2] = m_run[0], wml[g * 2 + 1] = l_run[0];
-    wml[(g + 8) * 2] = m_run[1], wml[(g + 8) * 2 + 1] = l_run[1];
-  }
-  __syncthreads();
-  merge_warps(p, s_dyn, kWarpSmem, grp, hkv, split, r0, nrows);
-}
-
-// ---- groups of one or two query rows (plain decode), transposed ------------------------------------
-// With 4 or 8 live rows the 16-row mma tile of the kernel above is mostly padding. Here the cache
-// positions take the 16-row side instead: S^T = K Q^T (A = 16 positions x dims from the raw K
-// codes, B = the 8 columns (query row, head) of q) and O^T = V^T P^T (A = 16 dims x 16 positions
-// from the raw V codes through ldmatrix.trans, B = P^T, which is the S^T accumulator transposed by
-// movmatrix). Half the mma instructions per tile, half the O accumulators (so four CTAs per SM),
-// and the softmax of a column runs down the lanes (three xor shuffles over g).
+// ---- the main kernel -----------------------------------------------------------------------------
+// A decode step has few query rows per sequence (1 for plain decode, up to 4 for a verify group),
+// so the cache positions take the 16-row side of the mma and the (query row, head) pairs the
+// 8-column side: S^T = K Q^T (A = 16 positions x dims from the raw K codes, B = the columns of q) and
+// O^T = V^T P^T (A = 16 dims x 16 positions from the raw V codes through ldmatrix.trans, B = P^T,
+// which is the S^T accumulator transposed by movmatrix). The softmax of a column runs down the
+// lanes (three xor shuffles over g). One column tile serves one or two query rows, two tiles
+// three or four; the K and V operands are converted once and feed every tile.
 constexpr int kStagesT = 3;
 constexpr int kWarpSmemT = kStagesT * 2 * kRawTile;  // 13824
 constexpr size_t kAttnSmemBytesT = static_cast<size_t>(kWarps) * kWarpSmemT;
@@ -480,49 +183,60 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   return d;
 }
 
-__global__ void __launch_bounds__(kWarps * 32, kCtasPerSmT) attn_decode_t_kernel(const AttnParams p) {
+// NT column tiles of 8 columns: NT = 1 for groups of one or two query rows (4 CTAs per SM), NT = 2
+// for three or four (3 CTAs per SM). Column c = 4 j + hl stands for (query row j, head hl).
+template <int NT>
+__global__ void __launch_bounds__(kWarps * 32, NT == 1 ? kCtasPerSmT : kCtasPerSm)
+    attn_decode_t_kernel(const AttnParams p) {
   pdl_begin();
   extern __shared__ __align__(128) unsigned char s_dyn[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, hkv = blockIdx.y, grp = blockIdx.z;
   const int r0 = grp * p.group_rows;
-  const int nrows = min(p.group_rows, p.rows - r0);  // 1 or 2
+  const int nrows = min(p.group_rows, p.rows - r0);  // at most 2 NT
   unsigned char* wsm = s_dyn + static_cast<size_t>(warp) * kWarpSmemT;
   unsigned char* raw_k = wsm;
   unsigned char* raw_v = wsm + kStagesT * kRawTile;
 
-  // column c = 4 j + hl stands for (query row j, head hl). As accumulator owner a thread has columns
-  // 2 t and 2 t + 1 (both of query row t / 2); as B-operand owner it has column g.
-  int pos_col = -1, pos_max = -1, pos_min = INT_MAX;
+  // As accumulator owner a thread has columns 8 nt + 2 t and 8 nt + 2 t + 1 of every tile nt (both of
+  // query row 2 nt + t / 2); as B-operand owner it has column 8 nt + g.
+  int pos_col[NT], pos_max = -1, pos_min = INT_MAX;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) pos_col[nt] = -1;
   for (int j = 0; j < nrows; ++j) {
     int pj = __ldg(p.row_pos + r0 + j);
     pj = pj < 0 ? -1 : min(pj, p.max_len - 1);
     pos_max = max(pos_max, pj);
     pos_min = min(pos_min, pj);
-    if (j == (t >> 1)) pos_col = pj;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+      if (j == 2 * nt + (t >> 1)) pos_col[nt] = pj;
   }
   const int* pt = p.row_pt != nullptr ? p.row_pt[r0] : p.pt;
   const int t_begin = split * p.split_len;
   const int t_end = min(t_begin + p.split_len, pos_max + 1);
 
-  // ---- q as the B operand: (dims 16 kk + 4 t .. + 3 of column g), fp16, scaled by a power of two
-  uint32_t qb[8][2];
+  // ---- q as the B operand: (dims 16 kk + 4 t .. + 3 of column 8 nt + g), fp16, scaled by a power of two
+  uint32_t qb[NT][8][2];
   float logit_scale;
-  float q_off[2];  // 1152 x the sum of q over the dims, for the accumulator's columns 2 t, 2 t + 1
+  float q_off[NT][2];  // 1152 x the sum of q over the dims, for the accumulator's columns
   {
-    const int j = g >> 2, hl = g & 3;
-    const bool live = j < nrows;
-    const uint16_t* qrow = p.q + (static_cast<size_t>(r0 + (live ? j : 0)) * p.Hq + hkv * kGqa + hl) * kAD;
-    float qf[8][4];
+    float qf[NT][8][4];
     float qmax = 0.0f;
 #pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      const uint2 w = live ? __ldg(reinterpret_cast<const uint2*>(qrow + kk * 16 + 4 * t)) : make_uint2(0u, 0u);
-      qf[kk][0] = bf16_to_f32(w.x & 0xffffu), qf[kk][1] = bf16_to_f32(w.x >> 16);
-      qf[kk][2] = bf16_to_f32(w.y & 0xffffu), qf[kk][3] = bf16_to_f32(w.y >> 16);
+    for (int nt = 0; nt < NT; ++nt) {
+      const int j = 2 * nt + (g >> 2), hl = g & 3;
+      const bool live = j < nrows;
+      const uint16_t* qrow = p.q + (static_cast<size_t>(r0 + (live ? j : 0)) * p.Hq + hkv * kGqa + hl) * kAD;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) qmax = fmaxf(qmax, fabsf(qf[kk][i]));
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint2 w = live ? __ldg(reinterpret_cast<const uint2*>(qrow + kk * 16 + 4 * t)) : make_uint2(0u, 0u);
+        qf[nt][kk][0] = bf16_to_f32(w.x & 0xffffu), qf[nt][kk][1] = bf16_to_f32(w.x >> 16);
+        qf[nt][kk][2] = bf16_to_f32(w.y & 0xffffu), qf[nt][kk][3] = bf16_to_f32(w.y >> 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qmax = fmaxf(qmax, fabsf(qf[nt][kk][i]));
+      }
     }
     qmax = warp_max(qmax);
     int qexp = 0;
@@ -530,27 +244,36 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSmT) attn_decode_t_kernel
       qexp = min(max(((__float_as_int(qmax) >> 23) & 0xff) - 127 - 10, -100), 100);
     const float qdown = __int_as_float((127 - qexp) << 23);
     logit_scale = p.scale_log2 * __int_as_float((127 + qexp) << 23);
-    float sum = 0.0f;
 #pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      qb[kk][0] = pack_half2(qf[kk][0] * qdown, qf[kk][1] * qdown);
-      qb[kk][1] = pack_half2(qf[kk][2] * qdown, qf[kk][3] * qdown);
-      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qb[kk][0]));
-      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qb[kk][1]));
-      sum += (a.x + a.y) + (b.x + b.y);
+    for (int nt = 0; nt < NT; ++nt) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        qb[nt][kk][0] = pack_half2(qf[nt][kk][0] * qdown, qf[nt][kk][1] * qdown);
+        qb[nt][kk][1] = pack_half2(qf[nt][kk][2] * qdown, qf[nt][kk][3] * qdown);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qb[nt][kk][0]));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qb[nt][kk][1]));
+        sum += (a.x + a.y) + (b.x + b.y);
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);  // the whole row of column 8 nt + g, in all four lanes of quad g
+      q_off[nt][0] = kCodeBias * __shfl_sync(0xffffffffu, sum, (2 * t) * 4);
+      q_off[nt][1] = kCodeBias * __shfl_sync(0xffffffffu, sum, (2 * t + 1) * 4);
     }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);  // the whole row of column g, in all four lanes of quad g
-    q_off[0] = kCodeBias * __shfl_sync(0xffffffffu, sum, (2 * t) * 4);
-    q_off[1] = kCodeBias * __shfl_sync(0xffffffffu, sum, (2 * t + 1) * 4);
   }
 
-  // O^T accumulators: block b, rows g / g + 8 = dims 16 b + 2 g / 16 b + 2 g + 1, columns 2 t, 2 t + 1
-  float o[8][4];
+  // O^T accumulators: tile nt, block b, rows g / g + 8 = dims 16 b + 2 g / 16 b + 2 g + 1, columns 2 t, 2 t + 1
+  float o[NT][8][4];
+  float osum[NT][4];
+  float m_run[NT][2], l_run[NT][2];
 #pragma unroll
-  for (int b = 0; b < 8; ++b) o[b][0] = o[b][1] = o[b][2] = o[b][3] = 0.0f;
-  float osum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int b = 0; b < 8; ++b) o[nt][b][0] = o[nt][b][1] = o[nt][b][2] = o[nt][b][3] = 0.0f;
+    osum[nt][0] = osum[nt][1] = osum[nt][2] = osum[nt][3] = 0.0f;
+    m_run[nt][0] = m_run[nt][1] = -INFINITY;
+    l_run[nt][0] = l_run[nt][1] = 0.0f;
+  }
   const size_t head_row0 = static_cast<size_t>(hkv) * p.stride;
 
   constexpr int kStep = kTile * kWarps;
@@ -599,8 +322,13 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSmT) attn_decode_t_kernel
     const unsigned char* vstage = raw_v + stage * kRawTile;
     stage = (stage + 1) % kStagesT;
 
-    // ---- S^T = K Q^T: rows = positions g and g + 8, columns 2 t, 2 t + 1
-    float sa[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // ---- S^T = K Q^T: rows = positions g and g + 8; the K operand is converted once per k-step and
+    // serves every column tile
+    float sa[NT][4], sb[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sa[nt][i] = sb[nt][i] = 0.0f;
     const unsigned char* k_lo = kstage + g * kPitch + 4 * t;
     const unsigned char* k_hi = k_lo + 8 * kPitch;
 #pragma unroll
@@ -608,46 +336,63 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSmT) attn_decode_t_kernel
       uint32_t a[4];
       codes4_to_half(*reinterpret_cast<const uint32_t*>(k_lo + kk * 16), a[0], a[2]);
       codes4_to_half(*reinterpret_cast<const uint32_t*>(k_hi + kk * 16), a[1], a[3]);
-      mma_f16((kk & 1) ? sb : sa, a, qb[kk][0], qb[kk][1]);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) mma_f16((kk & 1) ? sb[nt] : sa[nt], a, qb[nt][kk][0], qb[nt][kk][1]);
     }
     // ---- scale, mask, online softmax down the lanes
     const float f_lo = __shfl_sync(0xffffffffu, sk_cur, g) * logit_scale;
     const float f_hi = __shfl_sync(0xffffffffu, sk_cur, g + 8) * logit_scale;
     const float sv_lo = __shfl_sync(0xffffffffu, sv_cur, g), sv_hi = __shfl_sync(0xffffffffu, sv_cur, g + 8);
     const bool unmasked = t0 + kTile <= t_end && t0 + kTile - 1 <= pos_min;  // warp-uniform
-    const bool ok_lo = unmasked || (t0 + g <= pos_col && t0 + g < t_end);
-    const bool ok_hi = unmasked || (t0 + g + 8 <= pos_col && t0 + g + 8 < t_end);
-    float pr[4], corr[2];
+    uint32_t b0[NT], b1[NT];
+    bool rescale = false;
+    float corr[NT][2];
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const float x_lo = ok_lo ? (sa[e] + sb[e] - q_off[e]) * f_lo : -INFINITY;
-      const float x_hi = ok_hi ? (sa[2 + e] + sb[2 + e] - q_off[e]) * f_hi : -INFINITY;
-      float mx = fmaxf(x_lo, x_hi);
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-      const float m_new = fmaxf(m_run[e], mx);
-      corr[e] = (m_new == -INFINITY) ? 1.0f : ex2_approx(m_run[e] - m_new);
-      const float base = (m_new == -INFINITY) ? 0.0f : m_new;
-      pr[e] = ex2_approx(x_lo - base);      // position g
-      pr[2 + e] = ex2_approx(x_hi - base);  // position g + 8
-      l_run[e] = l_run[e] * corr[e] + pr[e] + pr[2 + e];  // this lane's two positions; lanes are summed at the end
-      m_run[e] = m_new;
-    }
-    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+    for (int nt = 0; nt < NT; ++nt) {
+      const bool ok_lo = unmasked || (t0 + g <= pos_col[nt] && t0 + g < t_end);
+      const bool ok_hi = unmasked || (t0 + g + 8 <= pos_col[nt] && t0 + g + 8 < t_end);
+      float pr[4];
 #pragma unroll
-      for (int b = 0; b < 8; ++b) {
-        o[b][0] *= corr[0], o[b][1] *= corr[1];
-        o[b][2] *= corr[0], o[b][3] *= corr[1];
+      for (int e = 0; e < 2; ++e) {
+        const float x_lo = ok_lo ? (sa[nt][e] + sb[nt][e] - q_off[nt][e]) * f_lo : -INFINITY;
+        const float x_hi = ok_hi ? (sa[nt][2 + e] + sb[nt][2 + e] - q_off[nt][e]) * f_hi : -INFINITY;
+        float mx = fmaxf(x_lo, x_hi);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m_run[nt][e], mx);
+        corr[nt][e] = (m_new == -INFINITY) ? 1.0f : ex2_approx(m_run[nt][e] - m_new);
+        const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+        pr[e] = ex2_approx(x_lo - base);      // position g
+        pr[2 + e] = ex2_approx(x_hi - base);  // position g + 8
+        l_run[nt][e] = l_run[nt][e] * corr[nt][e] + pr[e] + pr[2 + e];  // this lane's two positions
+        m_run[nt][e] = m_new;
+        rescale |= corr[nt][e] != 1.0f;
       }
-      osum[0] *= corr[0], osum[1] *= corr[1], osum[2] *= corr[0], osum[3] *= corr[1];
+      // P^T as the B operand: the accumulator fragments (position g: columns 2 t, 2 t + 1) transposed
+      b0[nt] = movmatrix_trans(pack_half2(pr[0] * sv_lo, pr[1] * sv_lo));  // positions 0-7
+      b1[nt] = movmatrix_trans(pack_half2(pr[2] * sv_hi, pr[3] * sv_hi));  // positions 8-15
     }
-    // ---- P^T as the B operand: the accumulator fragments (position g: columns 2 t, 2 t + 1) transposed
-    const uint32_t b0 = movmatrix_trans(pack_half2(pr[0] * sv_lo, pr[1] * sv_lo));  // positions 0-7
-    const uint32_t b1 = movmatrix_trans(pack_half2(pr[2] * sv_hi, pr[3] * sv_hi));  // positions 8-15
-    // ---- O^T += V^T P^T, V operand from the raw bytes (see the kernel above)
+    if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          o[nt][b][0] *= corr[nt][0], o[nt][b][1] *= corr[nt][1];
+          o[nt][b][2] *= corr[nt][0], o[nt][b][3] *= corr[nt][1];
+        }
+        osum[nt][0] *= corr[nt][0], osum[nt][1] *= corr[nt][1];
+        osum[nt][2] *= corr[nt][0], osum[nt][3] *= corr[nt][1];
+      }
+    }
+    // ---- O^T += V^T P^T. V operand straight from the raw bytes: the tile is read as 16-bit elements
+    // (two adjacent dims of one position), transposed by ldmatrix; a register then holds positions
+    // 2 t, 2 t + 1 for dims 2 g and 2 g + 1 of a 16-dim block, and one byte permute each picks the
+    // (position pair, dim) halves, already in fp16 form (code + 1152). Converted once per block, used
+    // by every column tile.
 #pragma unroll
     for (int blk = 0; blk < 8; blk += 2) {
+      // matrices: (pos 0-7, block blk), (pos 8-15, block blk), (pos 0-7, block blk + 1), (pos 8-15, ..)
       uint32_t r[4];
       ldmatrix_x4_trans(r, vstage + (lane & 15) * kPitch + (blk + (lane >> 4)) * 16);
 #pragma unroll
@@ -658,36 +403,40 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSmT) attn_decode_t_kernel
         // rows g / g + 8 = dims 2 g / 2 g + 1 of the block; k = positions 2 t, 2 t + 1 | 2 t + 8, 2 t + 9
         const uint32_t a[4] = {__byte_perm(lo, 0x64646464u, 0x4240), __byte_perm(lo, 0x64646464u, 0x4341),
                                __byte_perm(hi, 0x64646464u, 0x4240), __byte_perm(hi, 0x64646464u, 0x4341)};
-        mma_f16(o[blk + u], a, b0, b1);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_f16(o[nt][blk + u], a, b0[nt], b1[nt]);
       }
     }
     const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
-    mma_f16(osum, ones, b0, b1);  // every row: the sum over the positions of P^T's columns
-  }
 #pragma unroll
-  for (int b = 0; b < 8; ++b) {
-    o[b][0] -= kCodeBias * osum[0], o[b][1] -= kCodeBias * osum[1];
-    o[b][2] -= kCodeBias * osum[0], o[b][3] -= kCodeBias * osum[1];
+    for (int nt = 0; nt < NT; ++nt) mma_f16(osum[nt], ones, b0[nt], b1[nt]);  // sum over the positions of P^T's columns
   }
 
   cp_async_wait<0>();
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 4);
-    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 8);
-    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 16);
-  }
   __syncwarp();
   float* wo = reinterpret_cast<float*>(wsm);  // [16][128]; only the rows of live columns are read
   float* wml = wo + 16 * kAD;
 #pragma unroll
-  for (int b = 0; b < 8; ++b) {
-    *reinterpret_cast<float2*>(wo + (2 * t) * kAD + b * 16 + 2 * g) = make_float2(o[b][0], o[b][2]);
-    *reinterpret_cast<float2*>(wo + (2 * t + 1) * kAD + b * 16 + 2 * g) = make_float2(o[b][1], o[b][3]);
-  }
-  if (g == 0) {
-    wml[(2 * t) * 2] = m_run[0], wml[(2 * t) * 2 + 1] = l_run[0];
-    wml[(2 * t + 1) * 2] = m_run[1], wml[(2 * t + 1) * 2 + 1] = l_run[1];
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      l_run[nt][e] += __shfl_xor_sync(0xffffffffu, l_run[nt][e], 4);
+      l_run[nt][e] += __shfl_xor_sync(0xffffffffu, l_run[nt][e], 8);
+      l_run[nt][e] += __shfl_xor_sync(0xffffffffu, l_run[nt][e], 16);
+    }
+    const int c0 = 8 * nt + 2 * t;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      // take the code offset out: O = O_mma - 1152 * sum(p)
+      *reinterpret_cast<float2*>(wo + c0 * kAD + b * 16 + 2 * g) =
+          make_float2(o[nt][b][0] - kCodeBias * osum[nt][0], o[nt][b][2] - kCodeBias * osum[nt][0]);
+      *reinterpret_cast<float2*>(wo + (c0 + 1) * kAD + b * 16 + 2 * g) =
+          make_float2(o[nt][b][1] - kCodeBias * osum[nt][1], o[nt][b][3] - kCodeBias * osum[nt][1]);
+    }
+    if (g == 0) {
+      wml[c0 * 2] = m_run[nt][0], wml[c0 * 2 + 1] = l_run[nt][0];
+      wml[(c0 + 1) * 2] = m_run[nt][1], wml[(c0 + 1) * 2 + 1] = l_run[nt][1];
+    }
   }
   __syncthreads();
   merge_warps(p, s_dyn, kWarpSmemT, grp, hkv, split, r0, nrows);
@@ -833,19 +582,18 @@ int granite4_kernel_attn_decode_int8_paged(const uint16_t* d_q, const int8_t* d_
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      G4_CUDA_TRY(fn, cudaFuncSetAttribute(g4::attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(g4::kAttnSmemBytes)));
-      G4_CUDA_TRY(fn, cudaFuncSetAttribute(g4::attn_decode_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(g4::attn_decode_t_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(g4::kAttnSmemBytesT)));
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(g4::attn_decode_t_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(g4::kAttnSmemBytesT)));
       attr_set[dev] = true;
     }
   }
   const dim3 grid(static_cast<unsigned>(s.splits), static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups));
-  const char* force = std::getenv("G4_ATTN_TRANSPOSED");  // 0: the 16-row kernel for every group size (A/B runs)
-  if (rows_per_group <= 2 && !(force != nullptr && force[0] == '0'))
-    G4_LAUNCH_PDL(fn, g4::attn_decode_t_kernel, grid, dim3(g4::kWarps * 32), g4::kAttnSmemBytesT, st, p);
+  if (rows_per_group <= 2)
+    G4_LAUNCH_PDL(fn, g4::attn_decode_t_kernel<1>, grid, dim3(g4::kWarps * 32), g4::kAttnSmemBytesT, st, p);
   else
-    G4_LAUNCH_PDL(fn, g4::attn_decode_kernel, grid, dim3(g4::kWarps * 32), g4::kAttnSmemBytes, st, p);
+    G4_LAUNCH_PDL(fn, g4::attn_decode_t_kernel<2>, grid, dim3(g4::kWarps * 32), g4::kAttnSmemBytesT, st, p);
   if (s.splits > 1)
     G4_LAUNCH_PDL(fn, g4::attn_combine_kernel,
                   dim3(static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups), 4u * rows_per_group),

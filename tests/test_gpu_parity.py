@@ -1354,12 +1354,9 @@ def test_pool_tables_drive_kv_write_attention_and_moves(K, port):
     t.close()
 
 
-@pytest.mark.parametrize("transposed", ["1", "0"])
-def test_attention_pairs_of_rows_both_kernels(K, port, transposed, monkeypatch):
-    """Groups of two rows (and a ragged last group of one) run on the transposed kernel (cache
-    positions on the 16-row side of the mma); G4_ATTN_TRANSPOSED=0 forces the 16-row kernel. Both
-    against the golden pipeline and the unrounded evaluation."""
-    monkeypatch.setenv("G4_ATTN_TRANSPOSED", transposed)
+def test_attention_pairs_of_rows(K, port):
+    """Groups of two rows and a ragged last group of one (one column tile of the kernel), against
+    the golden pipeline and the unrounded evaluation."""
     stride, max_len = 1024, 900
     ck, cv, ks, vs = _att_pool(71, stride)
     pos = np.array([500, 501, 17, 18, 899], np.int32)
