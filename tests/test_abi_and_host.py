@@ -169,3 +169,23 @@ def test_glue_byte_counts(g4):
     assert b == {"embed": 16388, "add_rmsnorm_fp8": 28672, "rope_kv_int8": 23108,
                  "swiglu_fp8": 64000, "final_norm": 16384}
     assert glue.bytes_per_token(s) == 5794464
+
+
+def test_a_plain_c99_program_includes_the_header_and_links_the_library(g4, tmp_path):
+    """The boundary is a C ABI: a strict C99 translation unit includes include/granite4_b200.h,
+    links libgranite4_b200.so and runs (only entry points that need no GPU)."""
+    import shutil
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    lib_dir = os.path.dirname(g4._build.LIB_PATH)
+    exe = str(tmp_path / "abi_smoke")
+    src = os.path.join(ROOT, "tests", "c_abi", "abi_smoke.c")
+    build = subprocess.run([cc, "-std=c99", "-pedantic", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+                            src, "-o", exe, "-L", lib_dir, "-lgranite4_b200", "-Wl,-rpath," + lib_dir],
+                           capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    run = subprocess.run([exe], capture_output=True, text=True)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "granite-4.2-8b sm_100a layers=40" in run.stdout
+    assert "pool ok=1 rows 12 13 8 11 | 2" in run.stdout  # pages are handed out from the top of the free stack
