@@ -395,7 +395,7 @@ def small_shapes_and_embed(seq, rows, device, stream):
     and 8 rows replayed from a CUDA graph, one 500-row prefill layer - latency-bound shapes,
     reported in microseconds, not against the bandwidth roofline."""
     import torch
-    from granite4_b200 import glue, kernels as k
+    from granite4_b200 import capi, glue, kernels as k
     s = seq.shapes
     peak, _ = load_peaks()
 
@@ -465,6 +465,13 @@ def small_shapes_and_embed(seq, rows, device, stream):
                                   sq.scales[0, 0])
             entry["add_rmsnorm_f32_fp8_us"] = timed(c1, 50)
             entry["add_rmsnorm_f32_fp8_graph_us"] = graph_replay_us(c1)
+            # the same call straight through the C ABI (no Python wrapper around it): what a C host pays
+            lib = capi.lib()
+            c_args = (f32y.data_ptr(), 1, f32r.data_ptr(), 1, sq.w[0, 0].data_ptr(), s.eps, s.residual_multiplier,
+                      1, s.hidden, hb.data_ptr(), nb.data_ptr(), sq.n_fp8.data_ptr(), sq.scales[0, 0].data_ptr(),
+                      None)
+            c_fn = lib.granite4_kernel_add_rmsnorm_fp8
+            entry["add_rmsnorm_f32_fp8_c_abi_us"] = timed(lambda: c_fn(*c_args), 200)
         small[f"rows_{n}"] = entry
         del sq
     del table
@@ -516,7 +523,6 @@ def small_shapes_and_embed(seq, rows, device, stream):
     # A whole decode step (one layer's glue + attention at ~4096 positions + final norm + greedy
     # pick with the token scatter folded in) of n sessions, captured into a CUDA graph and replayed: everything that
     # changes between steps is read from the device descriptor, so the replays chain by themselves.
-    from granite4_b200 import capi
     decode_step = {}
     emb_small = (0.02 * torch.randn(4096, s.hidden, generator=g, device=device)).to(torch.bfloat16)
     logits_small = torch.randn(16, 4096, generator=g, device=device).to(torch.bfloat16)
