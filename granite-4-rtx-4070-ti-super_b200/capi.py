@@ -85,6 +85,7 @@ SIGNATURES = {
     "granite4_kernel_attn_decode_int8_paged": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int,
                                                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                                          C.c_int, C.c_float, _vp, C.c_longlong, _vp]),
+    "granite4_kernel_gemm_fp8": (C.c_int, [C.c_int, _vp, C.c_longlong, _vp, C.c_int, C.c_int, C.c_int, _vp]),
     "granite4_prefill_silu_mul": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "granite4_kernel_swiglu_fp8": (C.c_int, [_vp, _vp, C.c_int, C.c_longlong, C.c_int, C.c_int,
                                              _vp, _vp, _vp]),
@@ -117,6 +118,15 @@ class HostLayerIO(C.Structure):
         "hidden_in", "hidden_out", "n_attn_fp8", "n_mlp_fp8", "q_rot", "act_fp8", "scales")] + [
             ("rows", C.c_int), ("eps", C.c_float), ("resid_mult", C.c_float)]
 
+
+class GemmFp8Epilogue(C.Structure):
+    """granite4_gemm_fp8_epilogue (the FP8 counterpart of GemmEpilogue, engine/src/prefill_gemm.h:21-30)."""
+    _fields_ = [("d_a_scale", _vp), ("w_scale0", C.c_float), ("w_scale1", C.c_float), ("w_scale2", C.c_float),
+                ("seg1", C.c_int), ("seg2", C.c_int), ("d_out_bf16", _vp), ("d_out_f32", _vp),
+                ("d_residual", _vp), ("resid_scale", C.c_float), ("ldc", C.c_int)]
+
+
+GEMM_OUT_BF16, GEMM_OUT_F32, GEMM_OUT_RESIDUAL = 0, 1, 2
 MAX_VERIFY_ROWS = 16
 MAX_TREE_DEPTH = 8
 

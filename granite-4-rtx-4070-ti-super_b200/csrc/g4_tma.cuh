@@ -97,6 +97,7 @@ enum DeviceStatusBits : unsigned int {
   kStatusNormWaitTimeout = 1u << 1,
   kStatusSwigluWaitTimeout = 1u << 2,
   kStatusRopeWaitTimeout = 1u << 3,
+  kStatusGemmWaitTimeout = 1u << 4,
 };
 
 }  // namespace g4

@@ -315,6 +315,39 @@ def attn_decode_int8_paged(q, cache_k, cache_v, k_scale, v_scale, row_pos, Hq, H
         _p(scratch, torch.uint8), 0 if scratch is None else scratch.numel(), _p(out, *_BF16_OK))
 
 
+# ---- FP8 x FP8 GEMM -----------------------------------------------------------------------
+def gemm_fp8(a_fp8, w_fp8, out, a_scale=None, w_scales=(1.0,), segs=(), residual=None, resid_scale=1.0):
+    """granite4_kernel_gemm_fp8: out[M][N] = a_scale * w_scale(n) * a_fp8[M][K] x w_fp8[N][K]^T.
+    a_fp8 / w_fp8: uint8 e4m3 codes (a_fp8 may be a row-strided view); a_scale: float32 CUDA tensor
+    whose element 0 is the activation scale; w_scales: up to three per-segment weight scales with
+    the segment ends in segs; out: bf16 or float32 [M][N] (row-strided allowed); residual: bf16,
+    same pitch as out (GemmOut::kResidual, engine/src/prefill_gemm.h:12-16)."""
+    lib = _enter(a_fp8)
+    M, K = a_fp8.shape
+    N = w_fp8.shape[0]
+    ws = list(w_scales) + [w_scales[-1]] * (3 - len(w_scales))
+    sg = list(segs) + [2 ** 31 - 1] * (2 - len(segs))
+    ep = capi.GemmFp8Epilogue()
+    ep.d_a_scale = _p(a_scale, torch.float32)
+    ep.w_scale0, ep.w_scale1, ep.w_scale2 = ws
+    ep.seg1, ep.seg2 = sg
+    ep.resid_scale = resid_scale
+    ep.ldc = out.stride(0)
+    if out.dtype == torch.float32:
+        kind, ep.d_out_f32 = capi.GEMM_OUT_F32, out.data_ptr()
+    else:
+        kind = capi.GEMM_OUT_BF16 if residual is None else capi.GEMM_OUT_RESIDUAL
+        ep.d_out_bf16 = out.data_ptr()
+        if residual is not None:
+            if residual.stride(0) != out.stride(0):
+                raise ValueError("the residual must have the output's row pitch")
+            ep.d_residual = residual.data_ptr()
+    if w_fp8.dtype != torch.uint8 or a_fp8.dtype != torch.uint8 or not w_fp8.is_contiguous() or a_fp8.stride(1) != 1:
+        raise ValueError("a_fp8 / w_fp8 must be uint8 code matrices with unit column stride")
+    return lib.granite4_kernel_gemm_fp8(kind, a_fp8.data_ptr(), a_fp8.stride(0), w_fp8.data_ptr(), M, N, K,
+                                        C.byref(ep))
+
+
 # ---- a4 -----------------------------------------------------------------------------------
 def prefill_silu_mul(gu, I, rows, act):
     """engine/src/prefill_gemm.h:105: gu float32 [rows][2 I] -> act bf16 [rows][I]."""

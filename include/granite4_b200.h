@@ -525,6 +525,35 @@ int granite4_host_glue_sync(granite4_host_glue* ctx);
 long long granite4_host_glue_h2d_bytes(const granite4_host_glue* ctx, int rows);
 long long granite4_host_glue_d2h_bytes(const granite4_host_glue* ctx, int rows);
 
+/* ------------------------------------------------------------------------ */
+/* FP8 x FP8 GEMM consuming the glue's FP8 outputs                            */
+/* ------------------------------------------------------------------------ */
+/* Added; the FP8-activation counterpart of granite4::prefill_gemm
+ * (engine/src/prefill_gemm.h:12-36). C[M][N] = a_scale * w_scale(n) * A[M][K] x
+ * W[N][K]^T with A e4m3 codes of row pitch lda bytes (what
+ * granite4_kernel_add_rmsnorm_fp8 / _swiglu_fp8 write), W e4m3 row-major (the
+ * reference's weight layout) and f32 accumulation on the tensor cores. The
+ * activation scale is read from DEVICE memory (d_a_scale, slot 0 of the glue's
+ * {scale, amax} pair; NULL = 1), the weight scales are passed by value like the
+ * reference's GemmEpilogue: w_scale(n) = w_scale0 for n < seg1, w_scale1 for
+ * n < seg2, else w_scale2. Output kinds as GemmOut: bf16(y), f32 y, or
+ * bf16(residual + resid_scale * y) (d_residual may alias d_out_bf16).
+ * Needs K % 16 == 0, lda % 16 == 0, 16-byte aligned A and W; any M >= 0, any N.
+ * Returns 0, or -1 on bad arguments or a launch error. */
+enum { GRANITE4_GEMM_OUT_BF16 = 0, GRANITE4_GEMM_OUT_F32 = 1, GRANITE4_GEMM_OUT_RESIDUAL = 2 };
+typedef struct granite4_gemm_fp8_epilogue {
+  const float* d_a_scale;
+  float w_scale0, w_scale1, w_scale2;
+  int seg1, seg2;
+  uint16_t* d_out_bf16;
+  float* d_out_f32;
+  const uint16_t* d_residual;
+  float resid_scale;
+  int ldc; /* output (and residual) row pitch, elements */
+} granite4_gemm_fp8_epilogue;
+int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long long lda, const uint8_t* d_w, int M,
+                             int N, int K, const granite4_gemm_fp8_epilogue* ep);
+
 #ifdef __cplusplus
 }
 #endif
