@@ -327,6 +327,7 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, long long ld,
 extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long long lda, const uint8_t* d_w, int M,
                                         int N, int K, const granite4_gemm_fp8_epilogue* ep) {
   static const char* fn = "granite4_kernel_gemm_fp8";
+  if (M == 0 && N > 0 && K > 0 && ep != nullptr) return 0;  // no rows (an empty shard): nothing to do
   if (d_a == nullptr || d_w == nullptr || ep == nullptr) return fail(fn, "null argument");
   if (M < 0 || N <= 0 || K <= 0 || K % 16 != 0 || lda < K || lda % 16 != 0 || !aligned16(d_a) || !aligned16(d_w))
     return fail(fn, "needs K % 16 == 0, lda % 16 == 0, lda >= K and 16-byte aligned A and W");
@@ -336,7 +337,6 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
   if (out_kind == GRANITE4_GEMM_OUT_F32 ? ep->d_out_f32 == nullptr : ep->d_out_bf16 == nullptr)
     return fail(fn, "the output of the requested kind is null");
   if (out_kind == GRANITE4_GEMM_OUT_RESIDUAL && ep->d_residual == nullptr) return fail(fn, "null residual");
-  if (M == 0) return 0;
 
   CUtensorMap map_a, map_w;
   if (!make_map(&map_a, d_a, M, K, lda, kBM) || !make_map(&map_w, d_w, N, K, K, kBN))

@@ -366,3 +366,31 @@ void g4o_attn_decode_int8(const uint16_t* q, const int8_t* ck, const int8_t* cv,
     }
   }
 }
+
+/* ------------------------------------------------------------------------ */
+/* FP8 x FP8 GEMM (checker for the "next" row f2)                             */
+/* ------------------------------------------------------------------------ */
+void g4o_gemm_fp8(const uint8_t* a, long lda, const uint8_t* w, long M, long N, long K,
+                  float a_scale, float s0, float s1, float s2, long seg1, long seg2, int out_kind,
+                  const uint16_t* residual, float resid_scale, long ldc, uint16_t* out_bf16,
+                  float* out_f32) {
+  float lut[256];
+  for (int c = 0; c < 256; ++c) lut[c] = g4o_fp8_e4m3_decode((uint8_t)c);
+  for (long m = 0; m < M; ++m)
+    for (long n = 0; n < N; ++n) {
+      const uint8_t* ar = a + (size_t)m * lda;
+      const uint8_t* wr = w + (size_t)n * K;
+      float acc = 0.0f;
+      for (long k = 0; k < K; ++k) acc += lut[wr[k]] * lut[ar[k]];
+      const float ws = n < seg1 ? s0 : (n < seg2 ? s1 : s2);
+      const float y = (a_scale * ws) * acc;
+      const size_t off = (size_t)m * ldc + n;
+      if (out_kind == 1) {
+        out_f32[off] = y;
+      } else if (out_kind == 0) {
+        out_bf16[off] = g4o_f32_to_bf16(y);
+      } else {
+        out_bf16[off] = g4o_f32_to_bf16(g4o_bf16_to_f32(residual[off]) + resid_scale * y);
+      }
+    }
+}

@@ -124,6 +124,19 @@ void g4o_attn_decode_int8(const uint16_t* q, const int8_t* ck, const int8_t* cv,
                           long rows, int Hq, int Hk, int d, long stride, float scale,
                           uint16_t* out);
 
+/* FP8 x FP8 GEMM with the reference's epilogue. The contraction is the reference's
+ * golden GEMM (engine/src/kernel_math.h:250-262: every element decoded exactly,
+ * products accumulated in float in k order) applied to A given as e4m3 codes
+ * (their decoded values are exact in bf16, the type that golden takes);
+ * y = (a_scale * w_scale(n)) * acc with w_scale(n) = s0 for n < seg1, s1 for
+ * n < seg2, else s2, and the three output kinds of
+ * engine/src/prefill_gemm.cu:65-88: 0 bf16(y), 1 f32 y, 2 bf16(residual +
+ * resid_scale * y). out / residual rows have pitch ldc elements. */
+void g4o_gemm_fp8(const uint8_t* a, long lda, const uint8_t* w, long M, long N, long K,
+                  float a_scale, float s0, float s1, float s2, long seg1, long seg2, int out_kind,
+                  const uint16_t* residual, float resid_scale, long ldc, uint16_t* out_bf16,
+                  float* out_f32);
+
 #ifdef __cplusplus
 }
 #endif

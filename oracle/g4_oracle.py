@@ -70,6 +70,8 @@ class Oracle:
         f("argmax_rows", None, [_P, C.c_long, C.c_int, _P])
         f("attn_decode_int8", None, [_P, _P, _P, _P, _P, _P, _P, C.c_long, C.c_int, C.c_int, C.c_int,
                                      C.c_long, C.c_float, _P])
+        f("gemm_fp8", None, [_P, C.c_long, _P, C.c_long, C.c_long, C.c_long, C.c_float, C.c_float, C.c_float,
+                             C.c_float, C.c_long, C.c_long, C.c_int, _P, C.c_float, C.c_long, _P, _P])
 
     def _fn(self, name, res, args):
         fn = getattr(self._lib, self._p + name)
@@ -218,6 +220,22 @@ class Oracle:
             tables = (C.c_void_p * rows)(*[t.ctypes.data for t in keep])
         self._c_attn_decode_int8(_ptr(q), _ptr(ck), _ptr(cv), _ptr(ks), _ptr(vs), _ptr(pos), tables,
                                  rows, Hq, Hk, d, stride, scale, _ptr(out))
+        return out
+
+    def gemm_fp8(self, a, w, a_scale=1.0, w_scales=(1.0,), segs=(), kind="bf16", residual=None,
+                 resid_scale=1.0):
+        """a [M][K], w [N][K] e4m3 codes (uint8). kind "bf16" / "f32"; a bf16-bits residual [M][N]
+        selects bf16(residual + resid_scale * y). Returns [M][N] bf16 bits or float32."""
+        a, w = np.ascontiguousarray(a, np.uint8), np.ascontiguousarray(w, np.uint8)
+        (M, K), N = a.shape, w.shape[0]
+        ws = list(w_scales) + [w_scales[-1]] * (3 - len(w_scales))
+        sg = list(segs) + [2 ** 31 - 1] * (2 - len(segs))
+        out_kind = 1 if kind == "f32" else (0 if residual is None else 2)
+        out = np.empty((M, N), np.float32 if kind == "f32" else np.uint16)
+        res = None if residual is None else np.ascontiguousarray(residual, np.uint16)
+        self._c_gemm_fp8(_ptr(a), K, _ptr(w), M, N, K, a_scale, ws[0], ws[1], ws[2], sg[0], sg[1], out_kind,
+                         None if res is None else _ptr(res), resid_scale, N,
+                         _ptr(out) if kind != "f32" else None, _ptr(out) if kind == "f32" else None)
         return out
 
     # ---- the whole per-layer glue sequence over a slice of rows, for timing ---------

@@ -230,4 +230,31 @@ void g4ref_argmax_rows(const std::uint16_t* logits, long rows, int V, std::int32
   }
 }
 
+// The reference's golden GEMM (gemm_dequant_f32, kernel_math.h:250-262) on activations given as
+// e4m3 codes: their decoded values are exact in bf16, the type the golden takes. scale 1 leaves
+// the float accumulator as it is; the epilogue is prefill_gemm.cu:65-88 restated.
+void g4ref_gemm_fp8(const std::uint8_t* a, long lda, const std::uint8_t* w, long M, long N, long K,
+                    float a_scale, float s0, float s1, float s2, long seg1, long seg2, int out_kind,
+                    const std::uint16_t* residual, float resid_scale, long ldc,
+                    std::uint16_t* out_bf16, float* out_f32) {
+  std::vector<std::uint16_t> A(static_cast<std::size_t>(M) * K);
+  for (long m = 0; m < M; ++m)
+    for (long k = 0; k < K; ++k)
+      A[static_cast<std::size_t>(m) * K + k] = f32_to_bf16_host(fp8_to_f32_host(a[static_cast<std::size_t>(m) * lda + k]));
+  std::vector<float> acc;
+  gemm_dequant_f32(A.data(), w, 1.0f, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), &acc);
+  for (long m = 0; m < M; ++m)
+    for (long n = 0; n < N; ++n) {
+      const float ws = n < seg1 ? s0 : (n < seg2 ? s1 : s2);
+      const float y = (a_scale * ws) * acc[static_cast<std::size_t>(m) * N + n];
+      const std::size_t off = static_cast<std::size_t>(m) * ldc + n;
+      if (out_kind == 1)
+        out_f32[off] = y;
+      else if (out_kind == 0)
+        out_bf16[off] = f32_to_bf16_host(y);
+      else
+        out_bf16[off] = f32_to_bf16_host(bf16_to_f32_host(residual[off]) + resid_scale * y);
+    }
+}
+
 }  // extern "C"

@@ -128,6 +128,20 @@ def main():
     dec = np.array([ref.fp8_decode(c) for c in range(256)], np.float32)
     out["fp8_codec"] = dict(encode_all_bf16=enc, decode_all=dec)
 
+    # -- FP8 x FP8 GEMM with the reference's epilogue kinds: codes of values in [-2, 2) as the
+    #    reference's device fixture draws its weights (engine/tests/test_kernels.cu:1120-1129),
+    #    three weight segments, K over two 128-byte blocks and a ragged M / N
+    grng = np.random.default_rng(0xdead)
+    ga = np.array([ref.fp8_encode(v) for v in grng.uniform(-2, 2, 40 * 256)], np.uint8).reshape(40, 256)
+    gw = np.array([ref.fp8_encode(v) for v in grng.uniform(-2, 2, 72 * 256)], np.uint8).reshape(72, 256)
+    gres = f32_to_bf16_bits(ref, grng.standard_normal((40, 72)).astype(np.float32))
+    kw = dict(a_scale=0.125, w_scales=(0.001, 0.002, 0.0005), segs=(32, 48))
+    out["gemm_fp8_40x72x256"] = dict(
+        a=ga, w=gw, residual=gres, a_scale=np.float32(kw["a_scale"]), w_scales=np.array(kw["w_scales"], np.float32),
+        segs=np.array(kw["segs"], np.int32), resid_scale=np.float32(0.22),
+        out_bf16=ref.gemm_fp8(ga, gw, **kw), out_f32=ref.gemm_fp8(ga, gw, kind="f32", **kw),
+        out_residual=ref.gemm_fp8(ga, gw, residual=gres, resid_scale=0.22, **kw))
+
     for name, arrays in out.items():
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **arrays)

@@ -1593,3 +1593,143 @@ def test_attention_over_a_short_prefill_chunk_as_row_groups(K, port):
                                  [table] * len(sel), Hq, Hk, D, scale)
     assert np.abs(_bf16_to_f32_np(host(out)[sel]) - _bf16_to_f32_np(want)).max() < ATT_TOL
     t.close()
+
+
+# =========================================================================== FP8 x FP8 GEMM
+def _fp8_values(codes):
+    return golden("fp8_codec")["decode_all"].astype(np.float64)[codes]
+
+
+def _gemm_f64(a, w, a_scale, w_scales, segs, N):
+    """(exact product sums, sum of magnitudes) in float64, with the per-column scale applied."""
+    af, wf = _fp8_values(a), _fp8_values(w)
+    ws = list(w_scales) + [w_scales[-1]] * (3 - len(w_scales))
+    bounds = [0] + [min(s, N) for s in segs] + [N] * (3 - len(segs))
+    col = np.empty(N)
+    for i in range(3):
+        col[bounds[i]:bounds[i + 1]] = np.float32(a_scale) * np.float32(ws[i])
+    return (af @ wf.T) * col, (np.abs(af) @ np.abs(wf).T) * np.abs(col)
+
+
+def _gemm_close_bf16(got_bits, want_f64, mag, ref_bits=None):
+    """Within 4 bf16 steps of the rounded exact value (the reference's own bar for its GEMM,
+    engine/tests/test_kernels.cu:1146-1151) or within 2e-4 of the sum of magnitudes where the
+    products cancel."""
+    want_bits = ((want_f64.astype(np.float32).view(np.uint32) + 0x7FFF +
+                  ((want_f64.astype(np.float32).view(np.uint32) >> 16) & 1)) >> 16).astype(np.uint16)
+    ok = bf16_ulp_distance(got_bits, want_bits) <= 4
+    ok |= np.abs(_bf16_to_f32_np(got_bits).astype(np.float64) - want_f64) <= 2e-4 * mag
+    return ok.all()
+
+
+def _codes(rng, shape):
+    c = rng.integers(0, 256, shape, dtype=np.uint8)
+    c[(c & 0x7F) == 0x7F] = 0x38  # no NaN codes
+    return c
+
+
+def test_gemm_fp8_golden_fixture(K):
+    g = golden("gemm_fp8_40x72x256")
+    a, w = dev(g["a"]), dev(g["w"])
+    a_scale = torch.tensor([float(g["a_scale"]), 0.0], device=DEV)
+    kw = dict(a_scale=a_scale, w_scales=tuple(float(x) for x in g["w_scales"]), segs=tuple(int(x) for x in g["segs"]))
+    exact, mag = _gemm_f64(g["a"], g["w"], float(g["a_scale"]), kw["w_scales"], kw["segs"], 72)
+    out = empty_bf16(40, 72)
+    assert K.gemm_fp8(a, w, out, **kw) == 0
+    assert bf16_ulp_distance(host(out), g["out_bf16"]).max() <= 4
+    assert _gemm_close_bf16(host(out), exact, mag)
+    f32 = torch.empty(40, 72, dtype=torch.float32, device=DEV)
+    assert K.gemm_fp8(a, w, f32, **kw) == 0
+    assert (np.abs(host(f32) - g["out_f32"]) <= 1e-5 * mag + 1e-12).all()
+    res = dev(g["residual"])
+    assert K.gemm_fp8(a, w, out, residual=res, resid_scale=float(g["resid_scale"]), **kw) == 0
+    assert bf16_ulp_distance(host(out), g["out_residual"]).max() <= 1
+    # in place on the residual, as the reference's decode epilogue is used
+    assert K.gemm_fp8(a, w, res, residual=res, resid_scale=float(g["resid_scale"]), **kw) == 0
+    assert (host(res) == host(out)).all()
+
+
+@pytest.mark.parametrize("M,N,Kd,lda,ldc", [(200, 520, 384, 384, 520), (129, 257, 144, 160, 264), (1, 8, 16, 16, 8),
+                                            (77, 250, 96, 96, 251)])
+def test_gemm_fp8_matches_oracle(K, port, M, N, Kd, lda, ldc):
+    rng = np.random.default_rng(M * 1000 + N)
+    a_full, w = _codes(rng, (M, lda)), _codes(rng, (N, Kd))
+    a = a_full[:, :Kd]
+    segs, ws, a_s = (N // 3 // 2 * 2, N // 2), (0.01, 0.02, 0.005), 0.3
+    res = rand_bf16(M + N, (M, N))
+    a_scale = torch.tensor([a_s, 123.0], device=DEV)
+    exact, mag = _gemm_f64(a, w, a_s, ws, segs, N)
+    a_t = dev(a_full)[:, :Kd]
+    for kind in ("bf16", "f32", "residual"):
+        buf = torch.zeros(M, ldc, dtype=torch.float32 if kind == "f32" else torch.int16, device=DEV)
+        out = buf[:, :N]
+        rbuf = torch.zeros(M, ldc, dtype=torch.int16, device=DEV)
+        rbuf[:, :N] = dev(res)
+        assert K.gemm_fp8(a_t, dev(w), out, a_scale=a_scale, w_scales=ws, segs=segs,
+                          residual=rbuf[:, :N] if kind == "residual" else None, resid_scale=0.22) == 0
+        want = port.gemm_fp8(a, w, a_scale=a_s, w_scales=ws, segs=segs, kind="f32" if kind == "f32" else "bf16",
+                             residual=res if kind == "residual" else None, resid_scale=0.22)
+        got = host(out)
+        if kind == "f32":
+            assert (np.abs(got - want) <= 1e-5 * mag + 1e-12).all()
+            assert (np.abs(got - exact) <= 1e-5 * mag + 1e-12).all()
+        elif kind == "bf16":
+            assert _gemm_close_bf16(got, exact, mag)
+            assert ((bf16_ulp_distance(got, want) <= 4) | (np.abs(_bf16_to_f32_np(got) - _bf16_to_f32_np(want)) <= 4e-4 * mag)).all()
+        else:
+            full = _bf16_to_f32_np(res).astype(np.float64) + np.float32(0.22) * exact
+            assert _gemm_close_bf16(got, full, np.abs(_bf16_to_f32_np(res)) + mag)
+        if ldc > N:
+            assert (host(buf)[:, N:] == 0).all()  # nothing written past column N
+
+
+def test_gemm_fp8_full_size_selects_and_sums_exactly(K):
+    """Granite's QKV shape over every tile of the persistent schedule. One-hot weight rows turn
+    the GEMM into a column gather, whose results are exact; an all-ones activation makes every
+    output row the same weight-row sum."""
+    M, N, Kd = 8192, 6144, 4096
+    g = torch.Generator(device=DEV).manual_seed(9)
+    a = torch.randint(0, 256, (M, Kd), generator=g, device=DEV, dtype=torch.uint8)
+    a[(a & 0x7F) == 0x7F] = 0x38
+    w = torch.zeros(N, Kd, dtype=torch.uint8, device=DEV)
+    cols = (torch.arange(N, device=DEV) * 7 + 3) % Kd
+    w[torch.arange(N, device=DEV), cols] = 0x38  # 1.0
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    a_scale = torch.tensor([0.5, 0.0], device=DEV)
+    assert K.gemm_fp8(a, w, out, a_scale=a_scale) == 0
+    want = (a.view(torch.float8_e4m3fn)[:, cols].float() * 0.5).to(torch.bfloat16)
+    assert torch.equal(out, want)
+    # all-ones activations x random weights: C[m][n] = sum_k w[n][k] for every m
+    w2 = torch.randint(0, 256, (N, Kd), generator=g, device=DEV, dtype=torch.uint8)
+    w2[(w2 & 0x78) == 0x78] = 0x38  # keep magnitudes below 256 so sums stay well inside f32
+    a.fill_(0x38)
+    f32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    assert K.gemm_fp8(a, w2, f32) == 0
+    sums = w2.view(torch.float8_e4m3fn).double().sum(1)
+    mags = w2.view(torch.float8_e4m3fn).double().abs().sum(1)
+    assert ((f32.double() - sums[None, :]).abs() <= 1e-5 * mags[None, :]).all()
+    assert torch.equal(f32, f32[:1].expand_as(f32))  # the same instruction sequence for every row: identical bits
+
+
+def test_gemm_fp8_consumes_the_norm_kernels_codes_and_device_scale(K, port):
+    """add + RMSNorm -> FP8 feeds the GEMM through device memory only (codes + scale slot)."""
+    rows, H, N = 96, 4096, 512
+    y, r, w_norm = rand_bf16(1, (rows, H)), rand_bf16(2, (rows, H)), rand_bf16(3, (H,), 0.1)
+    h_out, codes, sa = empty_bf16(rows, H), torch.empty(rows, H, dtype=torch.uint8, device=DEV), \
+        torch.zeros(2, dtype=torch.float32, device=DEV)
+    assert K.add_rmsnorm_fp8(dev(y), dev(r), dev(w_norm), 1e-5, 0.22, h_out=h_out, n_fp8=codes, scale_amax=sa) == 0
+    wq = _codes(np.random.default_rng(4), (N, H))
+    out = torch.empty(rows, N, dtype=torch.float32, device=DEV)
+    assert K.gemm_fp8(codes, dev(wq), out, a_scale=sa, w_scales=(0.01,)) == 0
+    scale = float(host(sa)[0])
+    exact, mag = _gemm_f64(host(codes), wq, scale, (0.01,), (), N)
+    assert (np.abs(host(out) - exact) <= 1e-5 * mag).all()
+
+
+def test_gemm_fp8_rejects_bad_arguments(K):
+    a = torch.zeros(8, 64, dtype=torch.uint8, device=DEV)
+    w = torch.zeros(16, 64, dtype=torch.uint8, device=DEV)
+    out = empty_bf16(8, 16)
+    assert K.gemm_fp8(a[:, :40], w[:, :40].contiguous(), out) == -1       # K % 16
+    assert K.gemm_fp8(a[:, 8:24], w[:, :16].contiguous(), out) == -1      # A not 16-byte aligned
+    assert K.gemm_fp8(a[:0], w, out[:0]) == 0                              # no rows: nothing to do

@@ -333,3 +333,33 @@ def test_attention_oracle_matches_reference_golden_pipeline(port, ref):
     # no cache positions (negative position): zeros
     z = port.attn_decode_int8(q[:1], ck, cv, ks, vs, np.array([-1], np.int32), None, Hq, Hk, d, scale)
     assert (z == 0).all()
+
+
+def _gemm_kw(g):
+    return dict(a_scale=float(g["a_scale"]), w_scales=tuple(float(x) for x in g["w_scales"]),
+                segs=tuple(int(x) for x in g["segs"]))
+
+
+def test_gemm_known_answers_golden_and_reference(port, ref):
+    # engine/tests/test_kernel_math.cc:700-720: A [[1, 2], [3, 4]], B [[1, -1], [2, 0.5]], scale 2
+    a = np.array([[port.fp8_encode(v) for v in r] for r in ((1, 2), (3, 4))], np.uint8)
+    b = np.array([[port.fp8_encode(v) for v in r] for r in ((1, -1), (2, 0.5))], np.uint8)
+    # K must not matter for the restatement: pad K to 16 with zero codes
+    a16, b16 = np.zeros((2, 16), np.uint8), np.zeros((2, 16), np.uint8)
+    a16[:, :2], b16[:, :2] = a, b
+    c = port.gemm_fp8(a16, b16, a_scale=1.0, w_scales=(2.0,), kind="f32")
+    assert np.abs(c - np.array([[-2, 6], [-2, 16]], np.float32)).max() < 1e-4
+    g = golden("gemm_fp8_40x72x256")
+    kw = _gemm_kw(g)
+    assert (port.gemm_fp8(g["a"], g["w"], **kw) == g["out_bf16"]).all()
+    assert (port.gemm_fp8(g["a"], g["w"], kind="f32", **kw) == g["out_f32"]).all()
+    assert (port.gemm_fp8(g["a"], g["w"], residual=g["residual"], resid_scale=float(g["resid_scale"]), **kw)
+            == g["out_residual"]).all()
+    if ref is not None:
+        rng = np.random.default_rng(5)
+        a = rng.integers(0, 256, (9, 96), dtype=np.uint8)
+        w = rng.integers(0, 256, (11, 96), dtype=np.uint8)
+        a[(a & 0x7f) == 0x7f] = 0x30
+        w[(w & 0x7f) == 0x7f] = 0x30
+        assert (port.gemm_fp8(a, w, a_scale=0.01, w_scales=(0.5, 0.25), segs=(4,), kind="f32")
+                == ref.gemm_fp8(a, w, a_scale=0.01, w_scales=(0.5, 0.25), segs=(4,), kind="f32")).all()
