@@ -29,6 +29,8 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
+#include <map>
 #include <mutex>
 
 #include "../../include/granite4_b200.h"
@@ -41,17 +43,34 @@ namespace {
 using namespace g4;
 
 constexpr int kBM = 128, kBN = 256, kBK = 128;  // kBK in bytes = e4m3 elements
-constexpr int kStages = 4, kAccs = 2;
-constexpr uint32_t kABytes = kBM * kBK, kWBytes = kBN * kBK, kStageBytes = kABytes + kWBytes;
+constexpr int kAccs = 2;
+constexpr uint32_t kABytes = kBM * kBK;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = kAccs * kBN;  // 512: the whole tensor memory of the SM
+constexpr int kMaxStages = 6;
+
+// kPair = false: one CTA owns a 128 x 256 output tile and both operand blocks.
+// kPair = true: the two CTAs of a cluster own a 256 x 256 tile; each loads its 128 rows of A and
+// its 128 rows of W, and one thread of the leader CTA issues MMAs that run on both SMs
+// (cta_group::2), so each SM reads half as many W bytes from shared memory per flop.
+template <bool kPair>
+struct Cfg {
+  static constexpr int kWRows = kPair ? kBN / 2 : kBN;
+  static constexpr uint32_t kWBytes = kWRows * kBK;
+  static constexpr uint32_t kStageBytes = kABytes + kWBytes;
+  static constexpr int kStages = kPair ? 6 : 4;
+  static constexpr int kTileM = kPair ? 2 * kBM : kBM;
+  static constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + 256;
+  // Instruction descriptor: f32 accumulator, e4m3 x e4m3, both operands K-major, N 256, M 128 / 256.
+  static constexpr uint32_t kIdesc = (1u << 4) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+};
 
 struct Ring {
-  uint64_t full[kStages], empty[kStages], acc_full[kAccs], acc_empty[kAccs];
+  uint64_t full[kMaxStages], empty[kMaxStages], acc_full[kAccs], acc_empty[kAccs];
   uint32_t tmem_base;
   int abort;
 };
-constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + sizeof(Ring);
+static_assert(sizeof(Ring) <= 256, "the ring's bookkeeping has 256 bytes after the tiles");
 
 struct GemmParams {
   int M, N, K, ldc, out_kind, seg1, seg2, vec;
@@ -64,36 +83,90 @@ struct GemmParams {
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
+// Tiled TMA load of one box into this CTA's shared memory. In the pair form the completion is
+// counted on the leader CTA's barrier (`bar` is then a cluster-window address).
+template <bool kPair>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
-      : "memory");
+  if constexpr (kPair) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+  }
 }
+template <bool kPair>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if constexpr (kPair) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  } else {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
 }
+template <bool kPair>
 __device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+  if constexpr (kPair)
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+  else
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // D (tensor memory) (+)= A (smem) x B (smem)^T, both K-major; accumulate = 0 overwrites D.
+template <bool kPair>
 __device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+  if constexpr (kPair) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
 }
-// The mbarrier gets one arrival when every MMA this thread issued so far has completed.
+// The (issuing CTA's) mbarrier gets one arrival when every MMA this thread issued so far has
+// completed - on both SMs in the pair form.
+template <bool kPair>
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  if constexpr (kPair)
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  else
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Address, in the cluster's shared window, of the word at `addr` in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// One arrival on the same-named barrier of CTA `rank` of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t rank) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr(bar, rank)) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Hardware barrier over every thread of the cluster (no spin loop of ours).
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
@@ -118,8 +191,6 @@ __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
   return uint64_t((smem_addr & 0x3ffffu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
          (uint64_t(1) << 46) | (uint64_t(2) << 61);
 }
-// Instruction descriptor: f32 accumulator, e4m3 x e4m3, both operands K-major, N 256, M 128.
-constexpr uint32_t kIdesc = (1u << 4) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ring* ring, unsigned int* status) {
   volatile int* ab = &ring->abort;
@@ -137,146 +208,174 @@ __device__ __forceinline__ float seg_scale(const GemmParams& p, int n) {
   return n < p.seg1 ? p.s0 : (n < p.seg2 ? p.s1 : p.s2);
 }
 
+// One warp's 32 rows x 256 columns of a finished accumulator: tensor memory -> scale -> convert
+// -> global. Every lane executes the tensor-memory loads; lanes past row M skip the stores.
+__device__ __forceinline__ void store_accumulator(const GemmParams& p, uint32_t taddr, int row, int n0, float a_scale) {
+  const bool vec = p.vec != 0;
+#pragma unroll 1
+  for (int c = 0; c < kBN / 32; ++c) {
+    const int n = n0 + c * 32;
+    if (n >= p.N) break;  // uniform over the warp
+    uint32_t v[32];
+    __syncwarp();  // the load below is a warp-wide instruction: rejoin lanes that skipped the stores
+    tmem_ld32(taddr + c * 32, v);
+    tmem_ld_wait();
+    if (row >= p.M) continue;
+    const bool one_scale = (n >= p.seg1 || n + 32 <= p.seg1) && (n >= p.seg2 || n + 32 <= p.seg2);
+    const float sc0 = a_scale * seg_scale(p, n);
+    float y[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = (one_scale ? sc0 : a_scale * seg_scale(p, n + j)) * __uint_as_float(v[j]);
+    const size_t off = size_t(row) * p.ldc + n;
+    const bool full = vec && n + 32 <= p.N;
+    if (p.out_kind == GRANITE4_GEMM_OUT_F32) {
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(p.out_f32 + off + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+      } else {
+        for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_f32[off + j] = y[j];
+      }
+    } else {
+      if (p.out_kind == GRANITE4_GEMM_OUT_RESIDUAL) {
+        if (full) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            float r[8];
+            unpack8(*reinterpret_cast<const uint4*>(p.residual + off + j), r);  // may alias the output: plain load
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[j + e] = __fadd_rn(r[e], __fmul_rn(p.resid_scale, y[j + e]));
+          }
+        } else {
+          for (int j = 0; j < 32 && n + j < p.N; ++j)
+            y[j] = __fadd_rn(bf16_to_f32(p.residual[off + j]), __fmul_rn(p.resid_scale, y[j]));
+        }
+      }
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8)
+          *reinterpret_cast<uint4*>(p.out_bf16 + off + j) =
+              make_uint4(pack_bf16x2(y[j], y[j + 1]), pack_bf16x2(y[j + 2], y[j + 3]),
+                         pack_bf16x2(y[j + 4], y[j + 5]), pack_bf16x2(y[j + 6], y[j + 7]));
+      } else {
+        for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_bf16[off + j] = uint16_t(f32_to_bf16_bits(y[j]));
+      }
+    }
+  }
+}
+
+template <bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                 const GemmParams p) {
+  using C = Cfg<kPair>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw + 1023u) & ~1023u;  // swizzled tiles sit on 1024-byte boundaries
   uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw);
-  Ring* ring = reinterpret_cast<Ring*>(tiles_ptr + size_t(kStages) * kStageBytes);
+  Ring* ring = reinterpret_cast<Ring*>(tiles_ptr + size_t(C::kStages) * C::kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = kPair ? cluster_rank() : 0u;  // CTA of the pair; 0 leads
+  const bool leader = rank == 0u;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) mbar_init(&ring->full[s], 1), mbar_init(&ring->empty[s], 1);
-    for (int a = 0; a < kAccs; ++a) mbar_init(&ring->acc_full[a], 1), mbar_init(&ring->acc_empty[a], 4);
+    for (int s = 0; s < C::kStages; ++s) mbar_init(&ring->full[s], 1), mbar_init(&ring->empty[s], 1);
+    // a finished accumulator is released by the four epilogue warps of every CTA that reads it;
+    // in the pair form only the leader's barriers of this kind are waited on
+    for (int a = 0; a < kAccs; ++a) mbar_init(&ring->acc_full[a], 1), mbar_init(&ring->acc_empty[a], kPair ? 8 : 4);
     ring->abort = 0;
     mbar_init_fence();
     fence_async_smem();
   }
-  if (warp == 1) tmem_alloc(smem_u32(&ring->tmem_base), kTmemCols);
+  if (warp == 1) tmem_alloc<kPair>(smem_u32(&ring->tmem_base), kTmemCols);
   tc_fence_before();
-  __syncthreads();
+  __syncwarp();  // the cluster barrier is a warp-wide instruction
+  if constexpr (kPair) cluster_sync(); else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = ring->tmem_base;
 
   pdl_begin();  // everything above touches no global memory
 
-  const int mt = (p.M + kBM - 1) / kBM, nt = (p.N + kBN - 1) / kBN;
+  const int mt = (p.M + C::kTileM - 1) / C::kTileM, nt = (p.N + kBN - 1) / kBN;
   const int tiles = mt * nt, kblocks = (p.K + kBK - 1) / kBK;
+  const int first = kPair ? int(blockIdx.x >> 1) : int(blockIdx.x);
+  const int step = kPair ? int(gridDim.x >> 1) : int(gridDim.x);
 
   if (warp == 0) {
     if (lane == 0) {
+      // Pair form: both CTAs load their own halves; every completion is counted on the leader's
+      // `full` barrier, which the leader arms for both halves. The peer may refill a stage when
+      // the leader has seen the MMAs that read it complete, which the leader passes on.
+      const uint32_t full0 = kPair ? cluster_addr(smem_u32(&ring->full[0]), 0) : smem_u32(&ring->full[0]);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int m0 = (t % mt) * kBM, n0 = (t / mt) * kBN;
+      for (int t = first; t < tiles && ok; t += step) {
+        const int m0 = (t % mt) * C::kTileM + int(rank) * kBM, n0 = (t / mt) * kBN + int(rank) * C::kWRows;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          if (!(ok = wait_or_abort(&ring->empty[s], ph ^ 1u, ring, p.status))) break;
-          mbar_arrive_expect_tx(&ring->full[s], kStageBytes);
-          const uint32_t dst = tiles_addr + s * kStageBytes;
-          tma_load_2d(dst, &map_a, kb * kBK, m0, smem_u32(&ring->full[s]));
-          tma_load_2d(dst + kABytes, &map_w, kb * kBK, n0, smem_u32(&ring->full[s]));
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          if (!(ok = wait_or_abort(&ring->empty[s], (kPair && !leader) ? ph : (ph ^ 1u), ring, p.status))) break;
+          if (leader) {
+            mbar_arrive_expect_tx(&ring->full[s], (kPair ? 2u : 1u) * C::kStageBytes);
+            if constexpr (kPair) mbar_arrive_remote(smem_u32(&ring->empty[s]), 1);
+          }
+          const uint32_t dst = tiles_addr + s * C::kStageBytes, bar = full0 + s * uint32_t(sizeof(uint64_t));
+          tma_load_2d<kPair>(dst, &map_a, kb * kBK, m0, bar);
+          tma_load_2d<kPair>(dst + kABytes, &map_w, kb * kBK, n0, bar);
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+      for (int t = first; t < tiles && ok; t += step, ++local) {
         const uint32_t acc = local & 1u, aph = (local >> 1) & 1u;
         if (!(ok = wait_or_abort(&ring->acc_empty[acc], aph ^ 1u, ring, p.status))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
           if (!(ok = wait_or_abort(&ring->full[s], ph, ring, p.status))) break;
           tc_fence_after();
-          const uint32_t a_addr = tiles_addr + s * kStageBytes;
+          const uint32_t a_addr = tiles_addr + s * C::kStageBytes;
           const uint64_t a_desc = smem_desc_k128(a_addr), w_desc = smem_desc_k128(a_addr + kABytes);
 #pragma unroll
           for (int k = 0; k < kBK / 32; ++k)  // 32 bytes of K per instruction: +2 in 16-byte units
-            mma_f8(d_tmem, a_desc + uint64_t(2 * k), w_desc + uint64_t(2 * k), kIdesc, (kb | k) != 0);
-          mma_commit(smem_u32(&ring->empty[s]));
+            mma_f8<kPair>(d_tmem, a_desc + uint64_t(2 * k), w_desc + uint64_t(2 * k), C::kIdesc, (kb | k) != 0);
+          mma_commit<kPair>(smem_u32(&ring->empty[s]));
         }
-        if (ok) mma_commit(smem_u32(&ring->acc_full[acc]));
+        if (ok) mma_commit<kPair>(smem_u32(&ring->acc_full[acc]));
       }
     }
   } else {
     const int q = warp & 3;  // the 32 tensor-memory lanes this warp may read
     const float a_scale = p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f;
-    const bool vec = p.vec != 0;
     uint32_t local = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+    for (int t = first; t < tiles && ok; t += step, ++local) {
       const uint32_t acc = local & 1u, aph = (local >> 1) & 1u;
-      const int m0 = (t % mt) * kBM, n0 = (t / mt) * kBN;
+      const int m0 = (t % mt) * C::kTileM + int(rank) * kBM, n0 = (t / mt) * kBN;
       if (!(ok = wait_or_abort(&ring->acc_full[acc], aph, ring, p.status))) break;
+      // the leader learns from its own barrier that both halves of the accumulator are complete
+      // and tells the peer
+      if (kPair && leader && warp == 2 && lane == 0) mbar_arrive_remote(smem_u32(&ring->acc_full[acc]), 1);
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
-      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * kBN;
-#pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        const int n = n0 + c * 32;
-        if (n >= p.N) break;  // uniform over the warp
-        uint32_t v[32];
-        __syncwarp();  // the load below is a warp-wide instruction: rejoin lanes that skipped the stores
-        tmem_ld32(taddr + c * 32, v);
-        tmem_ld_wait();
-        if (row >= p.M) continue;
-        const bool one_scale = (n >= p.seg1 || n + 32 <= p.seg1) && (n >= p.seg2 || n + 32 <= p.seg2);
-        const float sc0 = a_scale * seg_scale(p, n);
-        float y[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = (one_scale ? sc0 : a_scale * seg_scale(p, n + j)) * __uint_as_float(v[j]);
-        const size_t off = size_t(row) * p.ldc + n;
-        const bool full = vec && n + 32 <= p.N;
-        if (p.out_kind == GRANITE4_GEMM_OUT_F32) {
-          if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(p.out_f32 + off + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
-          } else {
-            for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_f32[off + j] = y[j];
-          }
-        } else {
-          if (p.out_kind == GRANITE4_GEMM_OUT_RESIDUAL) {
-            if (full) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float r[8];
-                unpack8(__ldg(reinterpret_cast<const uint4*>(p.residual + off + j)), r);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) y[j + e] = __fadd_rn(r[e], __fmul_rn(p.resid_scale, y[j + e]));
-              }
-            } else {
-              for (int j = 0; j < 32 && n + j < p.N; ++j)
-                y[j] = __fadd_rn(bf16_to_f32(p.residual[off + j]), __fmul_rn(p.resid_scale, y[j]));
-            }
-          }
-          if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8)
-              *reinterpret_cast<uint4*>(p.out_bf16 + off + j) =
-                  make_uint4(pack_bf16x2(y[j], y[j + 1]), pack_bf16x2(y[j + 2], y[j + 3]),
-                             pack_bf16x2(y[j + 4], y[j + 5]), pack_bf16x2(y[j + 6], y[j + 7]));
-          } else {
-            for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_bf16[off + j] = uint16_t(f32_to_bf16_bits(y[j]));
-          }
-        }
-      }
+      store_accumulator(p, tmem_base + (uint32_t(q * 32) << 16) + acc * kBN, m0 + q * 32 + lane, n0, a_scale);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ring->acc_empty[acc]));
+      if (lane == 0) {
+        if (kPair && !leader) mbar_arrive_remote(smem_u32(&ring->acc_empty[acc]), 0);
+        else mbar_arrive(smem_u32(&ring->acc_empty[acc]));
+      }
     }
   }
 
   // Wind down. On the normal path the epilogue has seen the last accumulator
   // complete, so no MMA and no copy is in flight. After an abort, give copies
   // and MMAs already issued a bounded time to land before the tensor memory and
-  // the shared memory go away.
+  // the shared memory go away. In the pair form neither CTA leaves (or frees
+  // tensor memory) before both are here: each reads or signals the other's
+  // shared memory until then.
   __syncwarp();
   tc_fence_before();
   __syncthreads();
@@ -284,11 +383,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000) {
     }
-    __syncthreads();
   }
+  __syncwarp();
+  if constexpr (kPair) cluster_sync(); else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc<kPair>(tmem_base, kTmemCols);
   }
 }
 
@@ -322,6 +422,46 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, long long ld,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+
+bool pair_enabled() {
+  const char* v = std::getenv("G4_GEMM_PAIR");  // read per call: tests compare the two forms
+  return !(v != nullptr && v[0] == '0');
+}
+
+cudaLaunchConfig_t pair_config(int clusters) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2u * unsigned(clusters));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = Cfg<true>::kSmemBytes;
+  return cfg;
+}
+
+// How many two-CTA clusters of the pair kernel the current device runs at once (0: none, or the
+// query failed); asked once per device.
+int pair_clusters() {
+  static std::mutex mu;
+  static std::map<int, int> known;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  const auto it = known.find(dev);
+  if (it != known.end()) return it->second;
+  int fit = 0;
+  if (cudaFuncSetAttribute(gemm_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           int(Cfg<true>::kSmemBytes)) == cudaSuccess) {
+    cudaLaunchConfig_t cfg = pair_config(sm_count() / 2);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&fit, gemm_fp8_kernel<true>, &cfg) != cudaSuccess) fit = 0;
+  }
+  (void)cudaGetLastError();
+  known[dev] = fit;
+  return fit;
+}
+
 }  // namespace
 
 extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long long lda, const uint8_t* d_w, int M,
@@ -338,16 +478,12 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
     return fail(fn, "the output of the requested kind is null");
   if (out_kind == GRANITE4_GEMM_OUT_RESIDUAL && ep->d_residual == nullptr) return fail(fn, "null residual");
 
+  // The pair form needs more than one 128-row block of A to be worth its 256-row tiles and a
+  // device that co-schedules two-CTA clusters of this size; G4_GEMM_PAIR=0 keeps the single form.
+  const bool pair = M > kBM && pair_enabled() && pair_clusters() > 0;
   CUtensorMap map_a, map_w;
-  if (!make_map(&map_a, d_a, M, K, lda, kBM) || !make_map(&map_w, d_w, N, K, K, kBN))
+  if (!make_map(&map_a, d_a, M, K, lda, kBM) || !make_map(&map_w, d_w, N, K, K, pair ? Cfg<true>::kWRows : kBN))
     return fail(fn, "the tensor map could not be encoded");
-
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes));
-  });
-  G4_CUDA_TRY(fn, attr_err);
 
   GemmParams p{};
   p.M = M, p.N = N, p.K = K, p.ldc = ep->ldc, p.out_kind = out_kind;
@@ -359,8 +495,32 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
                                                       : static_cast<const void*>(ep->d_out_bf16)) &&
           (out_kind != GRANITE4_GEMM_OUT_RESIDUAL || aligned16(ep->d_residual));
   p.status = device_status_ptr();
-  const int tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+  const int nt = (N + kBN - 1) / kBN;
+  if (pair) {
+    const int tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * nt;
+    const int clusters = tiles < pair_clusters() ? tiles : pair_clusters();
+    cudaLaunchConfig_t cfg = pair_config(clusters);
+    cfg.stream = current_stream();
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2u : 1u;
+    G4_CUDA_TRY(fn, cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<true>, map_a, map_w, p));
+    return 0;
+  }
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    int(Cfg<false>::kSmemBytes));
+  });
+  G4_CUDA_TRY(fn, attr_err);
+  const int tiles = ((M + kBM - 1) / kBM) * nt;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  G4_LAUNCH_PDL(fn, gemm_fp8_kernel, dim3(grid), dim3(kThreads), kSmemBytes, current_stream(), map_a, map_w, p);
+  G4_LAUNCH_PDL(fn, gemm_fp8_kernel<false>, dim3(grid), dim3(kThreads), Cfg<false>::kSmemBytes, current_stream(), map_a,
+                map_w, p);
   return 0;
 }
