@@ -85,7 +85,9 @@ SIGNATURES = {
     "granite4_kernel_attn_decode_int8_paged": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int,
                                                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                                          C.c_int, C.c_float, _vp, C.c_longlong, _vp]),
-    "granite4_kernel_gemm_fp8": (C.c_int, [C.c_int, _vp, C.c_longlong, _vp, C.c_int, C.c_int, C.c_int, _vp]),
+    "granite4_gemm_fp8_workspace_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
+    "granite4_kernel_gemm_fp8": (C.c_int, [C.c_int, _vp, C.c_longlong, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp,
+                                           C.c_longlong]),
     "granite4_prefill_silu_mul": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "granite4_kernel_swiglu_fp8": (C.c_int, [_vp, _vp, C.c_int, C.c_longlong, C.c_int, C.c_int,
                                              _vp, _vp, _vp]),

@@ -44,31 +44,44 @@ using namespace g4;
 
 constexpr int kBM = 128, kBN = 256, kBK = 128;  // kBK in bytes = e4m3 elements
 constexpr int kAccs = 2;
-constexpr uint32_t kABytes = kBM * kBK;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = kAccs * kBN;  // 512: the whole tensor memory of the SM
 constexpr int kMaxStages = 6;
+constexpr int kMaxSplits = 16;
 
-// kPair = false: one CTA owns a 128 x 256 output tile and both operand blocks.
+// Forms of the kernel; all compute 256 output columns per tile, because one MMA takes the same
+// time whatever its N and only N = 256 moves enough weight bytes per MMA to keep up with HBM.
 // kPair = true: the two CTAs of a cluster own a 256 x 256 tile; each loads its 128 rows of A and
-// its 128 rows of W, and one thread of the leader CTA issues MMAs that run on both SMs
-// (cta_group::2), so each SM reads half as many W bytes from shared memory per flop.
-template <bool kPair>
+//   its 128 rows of W, and one thread of the leader CTA issues MMAs that run on both SMs
+//   (cta_group::2), so each SM reads half as many W bytes from shared memory per flop.
+// kPair = false: one CTA owns a 128 x 256 tile and both operand blocks. kARows = 16 loads only 16
+//   rows of A per block (decode and verify steps): the MMA still reads 128 rows of shared
+//   memory, the rest being whatever lies behind the 16 (rows of D that nobody reads).
+// With at most 128 rows of A the GEMM is a stream of the weights and N / 256 tiles are too few to
+// occupy the SMs; the single forms then also split K (see plan_split).
+template <bool kPair, int kARows_, int kStages_>
 struct Cfg {
+  static constexpr int kARows = kARows_, kStages = kStages_;
   static constexpr int kWRows = kPair ? kBN / 2 : kBN;
-  static constexpr uint32_t kWBytes = kWRows * kBK;
+  static constexpr uint32_t kABytes = kARows * kBK, kWBytes = kWRows * kBK;
   static constexpr uint32_t kStageBytes = kABytes + kWBytes;
-  static constexpr int kStages = kPair ? 6 : 4;
   static constexpr int kTileM = kPair ? 2 * kBM : kBM;
-  static constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + 256;
+  // the MMA reads kBM rows of A wherever kARows ends: keep that inside the allocation
+  static constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + (kBM - kARows) * kBK + 256;
   // Instruction descriptor: f32 accumulator, e4m3 x e4m3, both operands K-major, N 256, M 128 / 256.
   static constexpr uint32_t kIdesc = (1u << 4) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+  static_assert(kStages <= kMaxStages && kSmemBytes <= 227 * 1024, "ring too large");
+  static_assert(!kPair || kARows == kBM, "the pair form loads whole A blocks");
 };
+using CfgPair = Cfg<true, 128, 6>;
+using CfgWide = Cfg<false, 128, 4>;
+using CfgSkinny = Cfg<false, 16, 5>;
 
 struct Ring {
   uint64_t full[kMaxStages], empty[kMaxStages], acc_full[kAccs], acc_empty[kAccs];
   uint32_t tmem_base;
   int abort;
+  int last;  // split K: whether this CTA delivered the last partial of the current tile
 };
 static_assert(sizeof(Ring) <= 256, "the ring's bookkeeping has 256 bytes after the tiles");
 
@@ -80,6 +93,11 @@ struct GemmParams {
   float* out_f32;
   const uint16_t* residual;
   unsigned int* status;
+  // split K: unit u covers k blocks [(u % splits) * kb_per, ...) of tile u / splits; partial sums go
+  // to ws [tile][split][rows kept][256] and the CTA that brings a tile's count to `splits` adds them
+  int splits, kb_per, ws_rows;
+  float* ws;
+  unsigned int* counters;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -204,14 +222,74 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ri
   return false;
 }
 
+// AND of `ok` over the 128 epilogue threads (named barrier 1); every one of them calls it.
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+  uint32_t all;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(all)
+      : "r"(uint32_t(ok))
+      : "memory");
+  return all != 0;
+}
+
 __device__ __forceinline__ float seg_scale(const GemmParams& p, int n) {
   return n < p.seg1 ? p.s0 : (n < p.seg2 ? p.s1 : p.s2);
 }
 
-// One warp's 32 rows x 256 columns of a finished accumulator: tensor memory -> scale -> convert
-// -> global. Every lane executes the tensor-memory loads; lanes past row M skip the stores.
-__device__ __forceinline__ void store_accumulator(const GemmParams& p, uint32_t taddr, int row, int n0, float a_scale) {
-  const bool vec = p.vec != 0;
+// Epilogue of 32 consecutive columns n .. n + 31 of one output row from the f32 sums v: scale,
+// add the residual where asked, convert, store (engine/src/prefill_gemm.cu:65-88).
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[32], int row, int n, float a_scale) {
+  const bool one_scale = (n >= p.seg1 || n + 32 <= p.seg1) && (n >= p.seg2 || n + 32 <= p.seg2);
+  const float sc0 = a_scale * seg_scale(p, n);
+  float y[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) y[j] = (one_scale ? sc0 : a_scale * seg_scale(p, n + j)) * v[j];
+  const size_t off = size_t(row) * p.ldc + n;
+  const bool full = p.vec != 0 && n + 32 <= p.N;
+  if (p.out_kind == GRANITE4_GEMM_OUT_F32) {
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(p.out_f32 + off + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+    } else {
+      for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_f32[off + j] = y[j];
+    }
+    return;
+  }
+  if (p.out_kind == GRANITE4_GEMM_OUT_RESIDUAL) {
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        float r[8];
+        unpack8(*reinterpret_cast<const uint4*>(p.residual + off + j), r);  // may alias the output: plain load
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[j + e] = __fadd_rn(r[e], __fmul_rn(p.resid_scale, y[j + e]));
+      }
+    } else {
+      for (int j = 0; j < 32 && n + j < p.N; ++j)
+        y[j] = __fadd_rn(bf16_to_f32(p.residual[off + j]), __fmul_rn(p.resid_scale, y[j]));
+    }
+  }
+  if (full) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+      *reinterpret_cast<uint4*>(p.out_bf16 + off + j) =
+          make_uint4(pack_bf16x2(y[j], y[j + 1]), pack_bf16x2(y[j + 2], y[j + 3]),
+                     pack_bf16x2(y[j + 4], y[j + 5]), pack_bf16x2(y[j + 6], y[j + 7]));
+  } else {
+    for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_bf16[off + j] = uint16_t(f32_to_bf16_bits(y[j]));
+  }
+}
+
+// One warp's 32 rows x 256 columns of a finished accumulator: tensor memory -> epilogue -> global,
+// or (partial != NULL, split K) tensor memory -> this unit's f32 partial rows [.][256].
+// Every lane executes the tensor-memory loads; lanes past row M skip the stores.
+__device__ __forceinline__ void store_accumulator(const GemmParams& p, uint32_t taddr, int row, int n0, float a_scale,
+                                                  float* partial_row) {
 #pragma unroll 1
   for (int c = 0; c < kBN / 32; ++c) {
     const int n = n0 + c * 32;
@@ -221,54 +299,25 @@ __device__ __forceinline__ void store_accumulator(const GemmParams& p, uint32_t 
     tmem_ld32(taddr + c * 32, v);
     tmem_ld_wait();
     if (row >= p.M) continue;
-    const bool one_scale = (n >= p.seg1 || n + 32 <= p.seg1) && (n >= p.seg2 || n + 32 <= p.seg2);
-    const float sc0 = a_scale * seg_scale(p, n);
-    float y[32];
+    if (partial_row != nullptr) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) y[j] = (one_scale ? sc0 : a_scale * seg_scale(p, n + j)) * __uint_as_float(v[j]);
-    const size_t off = size_t(row) * p.ldc + n;
-    const bool full = vec && n + 32 <= p.N;
-    if (p.out_kind == GRANITE4_GEMM_OUT_F32) {
-      if (full) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(p.out_f32 + off + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
-      } else {
-        for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_f32[off + j] = y[j];
-      }
+      for (int j = 0; j < 32; j += 4)
+        __stcg(reinterpret_cast<uint4*>(partial_row + c * 32 + j), make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]));
     } else {
-      if (p.out_kind == GRANITE4_GEMM_OUT_RESIDUAL) {
-        if (full) {
+      float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            float r[8];
-            unpack8(*reinterpret_cast<const uint4*>(p.residual + off + j), r);  // may alias the output: plain load
-#pragma unroll
-            for (int e = 0; e < 8; ++e) y[j + e] = __fadd_rn(r[e], __fmul_rn(p.resid_scale, y[j + e]));
-          }
-        } else {
-          for (int j = 0; j < 32 && n + j < p.N; ++j)
-            y[j] = __fadd_rn(bf16_to_f32(p.residual[off + j]), __fmul_rn(p.resid_scale, y[j]));
-        }
-      }
-      if (full) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 8)
-          *reinterpret_cast<uint4*>(p.out_bf16 + off + j) =
-              make_uint4(pack_bf16x2(y[j], y[j + 1]), pack_bf16x2(y[j + 2], y[j + 3]),
-                         pack_bf16x2(y[j + 4], y[j + 5]), pack_bf16x2(y[j + 6], y[j + 7]));
-      } else {
-        for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_bf16[off + j] = uint16_t(f32_to_bf16_bits(y[j]));
-      }
+      for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+      store_chunk(p, f, row, n, a_scale);
     }
   }
 }
 
-template <bool kPair>
+template <class C>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                 const GemmParams p) {
-  using C = Cfg<kPair>;
+  constexpr bool kPair = C::kTileM == 2 * kBM;
+  constexpr uint32_t kABytes = C::kABytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw + 1023u) & ~1023u;  // swizzled tiles sit on 1024-byte boundaries
@@ -298,6 +347,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   const int mt = (p.M + C::kTileM - 1) / C::kTileM, nt = (p.N + kBN - 1) / kBN;
   const int tiles = mt * nt, kblocks = (p.K + kBK - 1) / kBK;
+  const int units = tiles * p.splits;  // splits == 1 unless K is split
   const int first = kPair ? int(blockIdx.x >> 1) : int(blockIdx.x);
   const int step = kPair ? int(gridDim.x >> 1) : int(gridDim.x);
 
@@ -309,9 +359,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t full0 = kPair ? cluster_addr(smem_u32(&ring->full[0]), 0) : smem_u32(&ring->full[0]);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = first; t < tiles && ok; t += step) {
+      for (int u = first; u < units && ok; u += step) {
+        const int t = u / p.splits, kb0 = (u % p.splits) * p.kb_per, kb1 = min(kblocks, kb0 + p.kb_per);
         const int m0 = (t % mt) * C::kTileM + int(rank) * kBM, n0 = (t / mt) * kBN + int(rank) * C::kWRows;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
           if (!(ok = wait_or_abort(&ring->empty[s], (kPair && !leader) ? ph : (ph ^ 1u), ring, p.status))) break;
           if (leader) {
@@ -328,12 +379,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0 && leader) {
       uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int t = first; t < tiles && ok; t += step, ++local) {
+      for (int u = first; u < units && ok; u += step, ++local) {
+        const int kb0 = (u % p.splits) * p.kb_per, kb1 = min(kblocks, kb0 + p.kb_per);
         const uint32_t acc = local & 1u, aph = (local >> 1) & 1u;
         if (!(ok = wait_or_abort(&ring->acc_empty[acc], aph ^ 1u, ring, p.status))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
           if (!(ok = wait_or_abort(&ring->full[s], ph, ring, p.status))) break;
           tc_fence_after();
@@ -341,7 +393,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint64_t a_desc = smem_desc_k128(a_addr), w_desc = smem_desc_k128(a_addr + kABytes);
 #pragma unroll
           for (int k = 0; k < kBK / 32; ++k)  // 32 bytes of K per instruction: +2 in 16-byte units
-            mma_f8<kPair>(d_tmem, a_desc + uint64_t(2 * k), w_desc + uint64_t(2 * k), C::kIdesc, (kb | k) != 0);
+            mma_f8<kPair>(d_tmem, a_desc + uint64_t(2 * k), w_desc + uint64_t(2 * k), C::kIdesc, (kb > kb0) || k != 0);
           mma_commit<kPair>(smem_u32(&ring->empty[s]));
         }
         if (ok) mma_commit<kPair>(smem_u32(&ring->acc_full[acc]));
@@ -350,22 +402,61 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else {
     const int q = warp & 3;  // the 32 tensor-memory lanes this warp may read
     const float a_scale = p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f;
+    const int et = int(threadIdx.x) - 64;  // 0..127 among the epilogue threads
     uint32_t local = 0;
     bool ok = true;
-    for (int t = first; t < tiles && ok; t += step, ++local) {
+    for (int u = first; u < units && ok; u += step, ++local) {
+      const int t = u / p.splits, sl = u % p.splits;
       const uint32_t acc = local & 1u, aph = (local >> 1) & 1u;
       const int m0 = (t % mt) * C::kTileM + int(rank) * kBM, n0 = (t / mt) * kBN;
-      if (!(ok = wait_or_abort(&ring->acc_full[acc], aph, ring, p.status))) break;
+      ok = wait_or_abort(&ring->acc_full[acc], aph, ring, p.status);
+      if (p.splits > 1) ok = epilogue_all(ok);  // the split path below has barriers: leave it together or not at all
+      if (!ok) break;
       // the leader learns from its own barrier that both halves of the accumulator are complete
       // and tells the peer
       if (kPair && leader && warp == 2 && lane == 0) mbar_arrive_remote(smem_u32(&ring->acc_full[acc]), 1);
       tc_fence_after();
-      store_accumulator(p, tmem_base + (uint32_t(q * 32) << 16) + acc * kBN, m0 + q * 32 + lane, n0, a_scale);
+      float* partial = p.splits > 1 ? p.ws + (size_t(t) * p.splits + sl) * p.ws_rows * kBN : nullptr;
+      if (m0 + q * 32 < p.M)  // uniform over the warp: a warp whose rows are all past M has nothing to read
+        store_accumulator(p, tmem_base + (uint32_t(q * 32) << 16) + acc * kBN, m0 + q * 32 + lane, n0, a_scale,
+                          partial != nullptr ? partial + size_t(q * 32 + lane) * kBN : nullptr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
         if (kPair && !leader) mbar_arrive_remote(smem_u32(&ring->acc_empty[acc]), 0);
         else mbar_arrive(smem_u32(&ring->acc_empty[acc]));
+      }
+      if (partial != nullptr) {
+        // Deterministic split-K sum: every unit publishes its partial, then counts itself in; the
+        // unit that completes the count adds the partials in split order. Nobody waits.
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) ring->last = atomicAdd(p.counters + t, 1u) == unsigned(p.splits - 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ring->last) {
+          __threadfence();
+          const int rows = min(p.ws_rows, p.M - m0);
+          const float* base = p.ws + size_t(t) * p.splits * p.ws_rows * kBN;
+          for (int g = et; g < rows * (kBN / 32); g += 128) {  // 32-column groups of the tile
+            const int r = g / (kBN / 32), c = g % (kBN / 32);
+            if (n0 + c * 32 >= p.N) continue;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+            for (int s2 = 0; s2 < p.splits; ++s2) {
+              const float4* src = reinterpret_cast<const float4*>(base + (size_t(s2) * p.ws_rows + r) * kBN + c * 32);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 x = __ldcg(src + j);
+                v[4 * j] = __fadd_rn(v[4 * j], x.x), v[4 * j + 1] = __fadd_rn(v[4 * j + 1], x.y);
+                v[4 * j + 2] = __fadd_rn(v[4 * j + 2], x.z), v[4 * j + 3] = __fadd_rn(v[4 * j + 3], x.w);
+              }
+            }
+            store_chunk(p, v, m0 + r, n0 + c * 32, a_scale);
+          }
+          if (et == 0) p.counters[t] = 0u;  // the workspace is ready for the next call
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // ring->last is rewritten by the next unit
       }
     }
   }
@@ -428,11 +519,19 @@ bool pair_enabled() {
   return !(v != nullptr && v[0] == '0');
 }
 
+// The dynamic shared memory opt-in of one form, once per process; the error of that call.
+template <class C>
+cudaError_t smem_opt_in() {
+  static const cudaError_t err =
+      cudaFuncSetAttribute(gemm_fp8_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(C::kSmemBytes));
+  return err;
+}
+
 cudaLaunchConfig_t pair_config(int clusters) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(2u * unsigned(clusters));
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = Cfg<true>::kSmemBytes;
+  cfg.dynamicSmemBytes = CfgPair::kSmemBytes;
   return cfg;
 }
 
@@ -447,25 +546,86 @@ int pair_clusters() {
   const auto it = known.find(dev);
   if (it != known.end()) return it->second;
   int fit = 0;
-  if (cudaFuncSetAttribute(gemm_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           int(Cfg<true>::kSmemBytes)) == cudaSuccess) {
+  if (smem_opt_in<CfgPair>() == cudaSuccess) {
     cudaLaunchConfig_t cfg = pair_config(sm_count() / 2);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaOccupancyMaxActiveClusters(&fit, gemm_fp8_kernel<true>, &cfg) != cudaSuccess) fit = 0;
+    if (cudaOccupancyMaxActiveClusters(&fit, gemm_fp8_kernel<CfgPair>, &cfg) != cudaSuccess) fit = 0;
   }
   (void)cudaGetLastError();
   known[dev] = fit;
   return fit;
 }
 
+// Split of K for at most 16 rows of A. With T = ceil(N / 256) tiles and S slices of K there are
+// T * S units for `sms` persistent CTAs; the busiest CTA gets ceil(T S / sms) of them. The plan is
+// the smallest S whose units keep the SMs at least 85 % busy, else the S that keeps them busiest;
+// slices are whole 128-byte blocks of K, at least 4 of them. rows: rows of the partials kept (16
+// or 128). Depends on the shape and the SM count only, so the workspace query and the launch agree.
+struct SplitPlan {
+  int splits, kb_per, rows;
+  size_t counter_bytes, bytes;
+};
+SplitPlan plan_split(int M, int N, int K, int sms) {
+  SplitPlan pl{1, (K + kBK - 1) / kBK, M <= 16 ? 16 : kBM, 0, 0};
+  if (M > 16 || sms <= 0) return pl;  // the last unit of a tile adds the partials alone: worth it for few rows only
+  const int tiles = (N + kBN - 1) / kBN, kblocks = pl.kb_per;
+  double best = 0.0;
+  for (int s = 1; s <= kMaxSplits && (s == 1 || kblocks / s >= 4); ++s) {
+    const int per = (kblocks + s - 1) / s, real = (kblocks + per - 1) / per;
+    const long long units = 1ll * tiles * real;
+    const double busy = double(units) / double(((units + sms - 1) / sms) * sms);
+    if (busy > best + 1e-9) best = busy, pl.splits = real, pl.kb_per = per;
+    if (busy >= 0.85) break;
+  }
+  if (pl.splits > 1) {
+    pl.counter_bytes = (size_t(tiles) * sizeof(unsigned int) + 255) / 256 * 256;
+    pl.bytes = pl.counter_bytes + size_t(tiles) * pl.splits * pl.rows * kBN * sizeof(float);
+  }
+  return pl;
+}
+
+// Encodes the two tensor maps of form C and launches it over min(units, SMs) CTAs (CTA pairs).
+template <class C>
+int launch(const char* fn, const uint8_t* d_a, long long lda, const uint8_t* d_w, const GemmParams& p) {
+  constexpr bool kPair = C::kTileM == 2 * kBM;
+  CUtensorMap map_a, map_w;
+  if (!make_map(&map_a, d_a, p.M, p.K, lda, C::kARows) || !make_map(&map_w, d_w, p.N, p.K, p.K, C::kWRows))
+    return fail(fn, "the tensor map could not be encoded");
+  G4_CUDA_TRY(fn, smem_opt_in<C>());
+  const int units = ((p.M + C::kTileM - 1) / C::kTileM) * ((p.N + kBN - 1) / kBN) * p.splits;
+  if constexpr (kPair) {
+    const int clusters = units < pair_clusters() ? units : pair_clusters();
+    cudaLaunchConfig_t cfg = pair_config(clusters);
+    cfg.stream = current_stream();
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2u : 1u;
+    G4_CUDA_TRY(fn, cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<C>, map_a, map_w, p));
+  } else {
+    const int grid = units < sm_count() ? units : sm_count();
+    G4_LAUNCH_PDL(fn, gemm_fp8_kernel<C>, dim3(grid), dim3(kThreads), C::kSmemBytes, current_stream(), map_a, map_w, p);
+  }
+  return 0;
+}
+
 }  // namespace
 
+extern "C" long long granite4_gemm_fp8_workspace_bytes(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return static_cast<long long>(plan_split(M, N, K, sm_count()).bytes);
+}
+
 extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long long lda, const uint8_t* d_w, int M,
-                                        int N, int K, const granite4_gemm_fp8_epilogue* ep) {
+                                        int N, int K, const granite4_gemm_fp8_epilogue* ep, void* d_ws,
+                                        long long ws_bytes) {
   static const char* fn = "granite4_kernel_gemm_fp8";
   if (M == 0 && N > 0 && K > 0 && ep != nullptr) return 0;  // no rows (an empty shard): nothing to do
   if (d_a == nullptr || d_w == nullptr || ep == nullptr) return fail(fn, "null argument");
@@ -477,13 +637,7 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
   if (out_kind == GRANITE4_GEMM_OUT_F32 ? ep->d_out_f32 == nullptr : ep->d_out_bf16 == nullptr)
     return fail(fn, "the output of the requested kind is null");
   if (out_kind == GRANITE4_GEMM_OUT_RESIDUAL && ep->d_residual == nullptr) return fail(fn, "null residual");
-
-  // The pair form needs more than one 128-row block of A to be worth its 256-row tiles and a
-  // device that co-schedules two-CTA clusters of this size; G4_GEMM_PAIR=0 keeps the single form.
-  const bool pair = M > kBM && pair_enabled() && pair_clusters() > 0;
-  CUtensorMap map_a, map_w;
-  if (!make_map(&map_a, d_a, M, K, lda, kBM) || !make_map(&map_w, d_w, N, K, K, pair ? Cfg<true>::kWRows : kBN))
-    return fail(fn, "the tensor map could not be encoded");
+  if (d_ws != nullptr && !aligned16(d_ws)) return fail(fn, "the workspace must be 16-byte aligned");
 
   GemmParams p{};
   p.M = M, p.N = N, p.K = K, p.ldc = ep->ldc, p.out_kind = out_kind;
@@ -495,32 +649,19 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
                                                       : static_cast<const void*>(ep->d_out_bf16)) &&
           (out_kind != GRANITE4_GEMM_OUT_RESIDUAL || aligned16(ep->d_residual));
   p.status = device_status_ptr();
-  const int nt = (N + kBN - 1) / kBN;
-  if (pair) {
-    const int tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * nt;
-    const int clusters = tiles < pair_clusters() ? tiles : pair_clusters();
-    cudaLaunchConfig_t cfg = pair_config(clusters);
-    cfg.stream = current_stream();
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2u : 1u;
-    G4_CUDA_TRY(fn, cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<true>, map_a, map_w, p));
-    return 0;
+  p.splits = 1, p.kb_per = (K + kBK - 1) / kBK;
+  if (M <= kBM) {
+    // a stream of the weights: split K where the workspace allows it
+    const SplitPlan pl = plan_split(M, N, K, sm_count());
+    if (pl.splits > 1 && d_ws != nullptr && ws_bytes >= static_cast<long long>(pl.bytes)) {
+      p.splits = pl.splits, p.kb_per = pl.kb_per, p.ws_rows = pl.rows;
+      p.counters = static_cast<unsigned int*>(d_ws);
+      p.ws = reinterpret_cast<float*>(static_cast<char*>(d_ws) + pl.counter_bytes);
+    }
+    return M <= 16 ? launch<CfgSkinny>(fn, d_a, lda, d_w, p) : launch<CfgWide>(fn, d_a, lda, d_w, p);
   }
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    int(Cfg<false>::kSmemBytes));
-  });
-  G4_CUDA_TRY(fn, attr_err);
-  const int tiles = ((M + kBM - 1) / kBM) * nt;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  G4_LAUNCH_PDL(fn, gemm_fp8_kernel<false>, dim3(grid), dim3(kThreads), Cfg<false>::kSmemBytes, current_stream(), map_a,
-                map_w, p);
-  return 0;
+  // 256-row tiles on CTA pairs where the device co-schedules two-CTA clusters of this size
+  // (G4_GEMM_PAIR=0 keeps the single form)
+  if (pair_enabled() && pair_clusters() > 0) return launch<CfgPair>(fn, d_a, lda, d_w, p);
+  return launch<CfgWide>(fn, d_a, lda, d_w, p);
 }

@@ -316,12 +316,20 @@ def attn_decode_int8_paged(q, cache_k, cache_v, k_scale, v_scale, row_pos, Hq, H
 
 
 # ---- FP8 x FP8 GEMM -----------------------------------------------------------------------
-def gemm_fp8(a_fp8, w_fp8, out, a_scale=None, w_scales=(1.0,), segs=(), residual=None, resid_scale=1.0):
+def gemm_fp8_workspace(M, N, K, device):
+    """A zeroed workspace that lets gemm_fp8 split K for an M x N x K GEMM (None: no split wanted)."""
+    need = capi.lib().granite4_gemm_fp8_workspace_bytes(M, N, K)
+    return torch.zeros(need, dtype=torch.uint8, device=device) if need > 0 else None
+
+
+def gemm_fp8(a_fp8, w_fp8, out, a_scale=None, w_scales=(1.0,), segs=(), residual=None, resid_scale=1.0,
+             workspace=None):
     """granite4_kernel_gemm_fp8: out[M][N] = a_scale * w_scale(n) * a_fp8[M][K] x w_fp8[N][K]^T.
     a_fp8 / w_fp8: uint8 e4m3 codes (a_fp8 may be a row-strided view); a_scale: float32 CUDA tensor
     whose element 0 is the activation scale; w_scales: up to three per-segment weight scales with
     the segment ends in segs; out: bf16 or float32 [M][N] (row-strided allowed); residual: bf16,
-    same pitch as out (GemmOut::kResidual, engine/src/prefill_gemm.h:12-16)."""
+    same pitch as out (GemmOut::kResidual, engine/src/prefill_gemm.h:12-16). workspace: uint8 CUDA
+    tensor from gemm_fp8_workspace (zeroed once; reusable call after call)."""
     lib = _enter(a_fp8)
     M, K = a_fp8.shape
     N = w_fp8.shape[0]
@@ -345,7 +353,8 @@ def gemm_fp8(a_fp8, w_fp8, out, a_scale=None, w_scales=(1.0,), segs=(), residual
     if w_fp8.dtype != torch.uint8 or a_fp8.dtype != torch.uint8 or not w_fp8.is_contiguous() or a_fp8.stride(1) != 1:
         raise ValueError("a_fp8 / w_fp8 must be uint8 code matrices with unit column stride")
     return lib.granite4_kernel_gemm_fp8(kind, a_fp8.data_ptr(), a_fp8.stride(0), w_fp8.data_ptr(), M, N, K,
-                                        C.byref(ep))
+                                        C.byref(ep), _p(workspace, torch.uint8),
+                                        0 if workspace is None else workspace.numel())
 
 
 # ---- a4 -----------------------------------------------------------------------------------

@@ -539,7 +539,14 @@ long long granite4_host_glue_d2h_bytes(const granite4_host_glue* ctx, int rows);
  * n < seg2, else w_scale2. Output kinds as GemmOut: bf16(y), f32 y, or
  * bf16(residual + resid_scale * y) (d_residual may alias d_out_bf16).
  * Needs K % 16 == 0, lda % 16 == 0, 16-byte aligned A and W; any M >= 0, any N.
- * Returns 0, or -1 on bad arguments or a launch error. */
+ * d_ws / ws_bytes, as the ws / ws_bytes of prefill_gemm: with at most 128 rows a
+ * GEMM has too few output tiles to occupy the card and splits K across CTAs,
+ * which add their partial sums in a fixed order (the result does not depend on
+ * scheduling). granite4_gemm_fp8_workspace_bytes(M, N, K) is the size that
+ * allows the planned split (0: none wanted); the buffer must be zeroed once
+ * before its first use (every call leaves its first bytes, the tile counters,
+ * zero again) and belongs to one call at a time. NULL or a smaller buffer: no
+ * split. Returns 0, or -1 on bad arguments or a launch error. */
 enum { GRANITE4_GEMM_OUT_BF16 = 0, GRANITE4_GEMM_OUT_F32 = 1, GRANITE4_GEMM_OUT_RESIDUAL = 2 };
 typedef struct granite4_gemm_fp8_epilogue {
   const float* d_a_scale;
@@ -551,8 +558,10 @@ typedef struct granite4_gemm_fp8_epilogue {
   float resid_scale;
   int ldc; /* output (and residual) row pitch, elements */
 } granite4_gemm_fp8_epilogue;
+long long granite4_gemm_fp8_workspace_bytes(int M, int N, int K);
 int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long long lda, const uint8_t* d_w, int M,
-                             int N, int K, const granite4_gemm_fp8_epilogue* ep);
+                             int N, int K, const granite4_gemm_fp8_epilogue* ep, void* d_ws,
+                             long long ws_bytes);
 
 #ifdef __cplusplus
 }

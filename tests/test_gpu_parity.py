@@ -1733,3 +1733,52 @@ def test_gemm_fp8_rejects_bad_arguments(K):
     assert K.gemm_fp8(a[:, :40], w[:, :40].contiguous(), out) == -1       # K % 16
     assert K.gemm_fp8(a[:, 8:24], w[:, :16].contiguous(), out) == -1      # A not 16-byte aligned
     assert K.gemm_fp8(a[:0], w, out[:0]) == 0                              # no rows: nothing to do
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 6144, 4096), (16, 4096, 1536), (5, 1000, 4096 + 64), (8, 520, 12800)])
+def test_gemm_fp8_decode_rows_split_k_is_deterministic_and_reusable(K, port, M, N, Kd):
+    """At most 16 rows: K is split over CTAs that add their partial sums in a fixed order through
+    the workspace, which is handed from call to call without being cleared again."""
+    rng = np.random.default_rng(N + Kd)
+    a, w = _codes(rng, (M, Kd)), _codes(rng, (N, Kd))
+    res = rand_bf16(M, (M, N))
+    ws = K.gemm_fp8_workspace(M, N, Kd, DEV)
+    assert ws is not None  # these shapes have too few tiles for the SMs
+    exact, mag = _gemm_f64(a, w, 0.3, (0.01,), (), N)
+    a_scale = torch.tensor([0.3, 0.0], device=DEV)
+    f32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    runs = []
+    for _ in range(3):  # the same workspace three times
+        f32.zero_()
+        assert K.gemm_fp8(dev(a), dev(w), f32, a_scale=a_scale, w_scales=(0.01,), workspace=ws) == 0
+        runs.append(host(f32).copy())
+    assert (runs[0] == runs[1]).all() and (runs[1] == runs[2]).all()
+    assert (np.abs(runs[0] - exact) <= 1e-5 * mag + 1e-12).all()
+    # without a workspace: no split, same values up to the order of the f32 additions
+    assert K.gemm_fp8(dev(a), dev(w), f32, a_scale=a_scale, w_scales=(0.01,)) == 0
+    assert (np.abs(host(f32) - runs[0]) <= 2e-5 * mag + 1e-12).all()
+    # the residual epilogue in place, through the split path
+    out = dev(res)
+    assert K.gemm_fp8(dev(a), dev(w), out, a_scale=a_scale, w_scales=(0.01,), residual=out, resid_scale=0.22,
+                      workspace=ws) == 0
+    full = _bf16_to_f32_np(res).astype(np.float64) + np.float32(0.22) * exact
+    assert _gemm_close_bf16(host(out), full, np.abs(_bf16_to_f32_np(res)) + mag)
+    if M * N * Kd <= 2e8:
+        want = port.gemm_fp8(a, w, a_scale=0.3, w_scales=(0.01,), residual=res, resid_scale=0.22)
+        assert ((bf16_ulp_distance(host(out), want) <= 4) |
+                (np.abs(_bf16_to_f32_np(host(out)) - _bf16_to_f32_np(want)) <= 4e-4 * mag)).all()
+
+
+def test_gemm_fp8_pair_and_single_forms_agree(K, monkeypatch):
+    """The CTA-pair form (cta_group::2 MMAs) and the single-CTA form add the same products in the
+    same order."""
+    rng = np.random.default_rng(31)
+    M, N, Kd = 700, 1100, 1024
+    a, w = dev(_codes(rng, (M, Kd))), dev(_codes(rng, (N, Kd)))
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("G4_GEMM_PAIR", flag)
+        o = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+        assert K.gemm_fp8(a, w, o, w_scales=(0.01,)) == 0
+        outs.append(o)
+    assert torch.equal(outs[0], outs[1])
