@@ -362,6 +362,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "argmax": extras["argmax"],
             "attention_decode": extras["attention"],
             "decode_step": extras["decode_step"],
+            "gemm_fp8": extras["gemm"],
             "clocks": clocks,
             "gpu_launches": launches,
             "device_status": status,
@@ -569,7 +570,62 @@ def small_shapes_and_embed(seq, rows, device, stream):
         decode_step[f"sessions_{n}"] = {"kernels": 9, "graph_replay_us": graph_replay_us(step)}
     del ck, cv, ksc, vsc, table
     torch.cuda.empty_cache()
-    return {"embed": embed, "small": small, "argmax": argmax, "attention": attention, "decode_step": decode_step}
+
+    # The FP8 x FP8 GEMMs on either side of the glue (tensor-core bound at prefill sizes, a stream
+    # of the weights at decode sizes). Codes of N(0, 1) values scaled the way the glue's per-tensor
+    # amax scales them (amax ~ 5 sigma -> 448). Prefill: one 8192-row chunk per projection, against
+    # twice the measured bf16 GEMM rate (there is no measured FP8 figure) and the nominal dense FP8
+    # peak. Decode: the four projections of a layer back to back in a CUDA graph over two rotated
+    # weight sets (2 x 199 MB, larger than L2), against the HBM roofline on the weight bytes.
+    mp = {}
+    if os.path.isfile(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp = json.load(f)
+    bf16_burst, bf16_sust = float(mp.get("bf16_tflops", 1590.0)), float(mp.get("bf16_tflops_sustained", 1400.0))
+
+    def fp8_codes(r, c):
+        return (torch.randn(r, c, generator=g, device=device) * (448.0 / 5.0)).to(torch.float8_e4m3fn).view(torch.uint8)
+    H, I, QKV = s.hidden, s.intermediate, (s.q_heads + 2 * s.kv_heads) * s.head_dim
+    proj = (("qkv", QKV, H), ("o", H, H), ("gate_up", 2 * I, H), ("down", H, I))
+    wsets = [{name: fp8_codes(N, Kd) for name, N, Kd in proj} for _ in range(2)]
+    g_rows = min(rows, 8192)
+    a_h, a_i = fp8_codes(g_rows, H), fp8_codes(g_rows, I)
+    a_sc = torch.tensor([5.0 / 448.0, 5.0], device=device)
+    gemm = {"prefill_rows": g_rows, "peaks": {"bf16_tflops_measured": bf16_burst,
+                                              "bf16_tflops_sustained_measured": bf16_sust, "fp8_tflops_nominal": 4500.0}}
+    for name, N, Kd in proj:
+        a_in = a_i if Kd == I else a_h
+        o = torch.empty(g_rows, N, dtype=torch.bfloat16, device=device)
+        flip = [0]
+
+        def run():
+            flip[0] ^= 1
+            k.gemm_fp8(a_in, wsets[flip[0]][name], o, a_scale=a_sc, w_scales=(0.01,))
+        us = timed(run, 20)
+        tf = 2.0 * g_rows * N * Kd / (us * 1e-6) / 1e12
+        gemm[name] = {"M": g_rows, "N": N, "K": Kd, "mean_us": us, "tflops": tf,
+                      "frac_of_2x_measured_bf16_sustained": tf / (2 * bf16_sust),
+                      "frac_of_2x_measured_bf16_burst": tf / (2 * bf16_burst), "frac_of_nominal_4500": tf / 4500.0}
+        del o
+    wbytes = sum(N * Kd for _, N, Kd in proj)
+    for n in (1, 8):
+        outs = {name: torch.empty(n, N, dtype=torch.bfloat16, device=device) for name, N, _ in proj}
+        wsp = {name: k.gemm_fp8_workspace(n, N, Kd, device) for name, N, Kd in proj}
+
+        def layer_gemms():
+            for ws_ in wsets:
+                for name, N, Kd in proj:
+                    k.gemm_fp8((a_i if Kd == I else a_h)[:n], ws_[name], outs[name], a_scale=a_sc, w_scales=(0.01,),
+                               workspace=wsp[name])
+        us = graph_replay_us(layer_gemms, 20) / 2
+        gemm[f"decode_rows_{n}_layer_graph_us"] = us
+        gemm[f"decode_rows_{n}_weight_gbs"] = wbytes / (us * 1e-6) / 1e9
+        gemm[f"decode_rows_{n}_frac"] = wbytes / (us * 1e-6) / 1e9 / peak
+    gemm["decode_weight_bytes_per_layer"] = wbytes
+    del wsets, a_h, a_i
+    torch.cuda.empty_cache()
+    return {"embed": embed, "small": small, "argmax": argmax, "attention": attention, "decode_step": decode_step,
+            "gemm": gemm}
 
 
 def run_e2e(seq, rows, device, steps):
