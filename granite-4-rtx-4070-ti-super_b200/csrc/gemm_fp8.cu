@@ -96,6 +96,7 @@ struct GemmParams {
   // split K: unit u covers k blocks [(u % splits) * kb_per, ...) of tile u / splits; partial sums go
   // to ws [tile][split][rows kept][256] and the CTA that brings a tile's count to `splits` adds them
   int splits, kb_per, ws_rows;
+  int early;  // decode-size launch: see the dependent-launch note in the kernel
   float* ws;
   unsigned int* counters;
 };
@@ -285,6 +286,38 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
   }
 }
 
+// The same epilogue for four consecutive columns n .. n + 3 (n a multiple of 4) of one row.
+__device__ __forceinline__ void store4(const GemmParams& p, float4 v, int row, int n, float a_scale) {
+  float y[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) y[j] = (a_scale * seg_scale(p, n + j)) * y[j];
+  const size_t off = size_t(row) * p.ldc + n;
+  const bool full = p.vec != 0 && n + 4 <= p.N;
+  if (p.out_kind == GRANITE4_GEMM_OUT_F32) {
+    if (full) {
+      *reinterpret_cast<float4*>(p.out_f32 + off) = make_float4(y[0], y[1], y[2], y[3]);
+    } else {
+      for (int j = 0; j < 4 && n + j < p.N; ++j) p.out_f32[off + j] = y[j];
+    }
+    return;
+  }
+  if (p.out_kind == GRANITE4_GEMM_OUT_RESIDUAL) {
+    if (full) {
+      const uint2 r = *reinterpret_cast<const uint2*>(p.residual + off);  // may alias the output: plain load
+      y[0] = __fadd_rn(bf16_lo(r.x), __fmul_rn(p.resid_scale, y[0])), y[1] = __fadd_rn(bf16_hi(r.x), __fmul_rn(p.resid_scale, y[1]));
+      y[2] = __fadd_rn(bf16_lo(r.y), __fmul_rn(p.resid_scale, y[2])), y[3] = __fadd_rn(bf16_hi(r.y), __fmul_rn(p.resid_scale, y[3]));
+    } else {
+      for (int j = 0; j < 4 && n + j < p.N; ++j)
+        y[j] = __fadd_rn(bf16_to_f32(p.residual[off + j]), __fmul_rn(p.resid_scale, y[j]));
+    }
+  }
+  if (full) {
+    *reinterpret_cast<uint2*>(p.out_bf16 + off) = make_uint2(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]));
+  } else {
+    for (int j = 0; j < 4 && n + j < p.N; ++j) p.out_bf16[off + j] = uint16_t(f32_to_bf16_bits(y[j]));
+  }
+}
+
 // One warp's 32 rows x 256 columns of a finished accumulator: tensor memory -> epilogue -> global,
 // or (partial != NULL, split K) tensor memory -> this unit's f32 partial rows [.][256].
 // Every lane executes the tensor-memory loads; lanes past row M skip the stores.
@@ -343,7 +376,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = ring->tmem_base;
 
-  pdl_begin();  // everything above touches no global memory
+  // Programmatic dependent launch. Everything above touches no global memory. The weights are
+  // constants of the model, not products of the kernel before this one on the stream, so the
+  // loader thread of the decode-size forms (p.early) fetches the first stages' W blocks before it
+  // waits for that kernel; whatever reads activations, residuals, scales or the workspace, and
+  // everything that writes, comes after the wait. Those forms also let the kernel after them
+  // start as soon as CTAs of this one retire: with a few microseconds of work per launch, the
+  // ramps of consecutive GEMMs are most of the time otherwise.
+  const bool loader = warp == 0 && lane == 0;
+  if (p.early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (!(loader && p.early)) pdl_begin();
 
   const int mt = (p.M + C::kTileM - 1) / C::kTileM, nt = (p.N + kBN - 1) / kBN;
   const int tiles = mt * nt, kblocks = (p.K + kBK - 1) / kBK;
@@ -357,19 +399,34 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       // `full` barrier, which the leader arms for both halves. The peer may refill a stage when
       // the leader has seen the MMAs that read it complete, which the leader passes on.
       const uint32_t full0 = kPair ? cluster_addr(smem_u32(&ring->full[0]), 0) : smem_u32(&ring->full[0]);
-      uint32_t it = 0;
+      uint32_t it = 0, ahead = 0;  // ahead: stages whose W block was fetched before the dependency wait
+      if (!kPair && p.early) {
+        for (int u = first; u < units && ahead < uint32_t(C::kStages); u += step) {
+          const int t = u / p.splits, kb0 = (u % p.splits) * p.kb_per, kb1 = min(kblocks, kb0 + p.kb_per);
+          for (int kb = kb0; kb < kb1 && ahead < uint32_t(C::kStages); ++kb, ++ahead) {
+            mbar_arrive_expect_tx(&ring->full[ahead], C::kStageBytes);  // first use of every stage: it is empty
+            tma_load_2d<kPair>(tiles_addr + ahead * C::kStageBytes + kABytes, &map_w, kb * kBK, (t / mt) * kBN,
+                               smem_u32(&ring->full[ahead]));
+          }
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+      }
       bool ok = true;
       for (int u = first; u < units && ok; u += step) {
         const int t = u / p.splits, kb0 = (u % p.splits) * p.kb_per, kb1 = min(kblocks, kb0 + p.kb_per);
         const int m0 = (t % mt) * C::kTileM + int(rank) * kBM, n0 = (t / mt) * kBN + int(rank) * C::kWRows;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          const uint32_t dst = tiles_addr + s * C::kStageBytes, bar = full0 + s * uint32_t(sizeof(uint64_t));
+          if (it < ahead) {  // armed and half loaded above
+            tma_load_2d<kPair>(dst, &map_a, kb * kBK, m0, bar);
+            continue;
+          }
           if (!(ok = wait_or_abort(&ring->empty[s], (kPair && !leader) ? ph : (ph ^ 1u), ring, p.status))) break;
           if (leader) {
             mbar_arrive_expect_tx(&ring->full[s], (kPair ? 2u : 1u) * C::kStageBytes);
             if constexpr (kPair) mbar_arrive_remote(smem_u32(&ring->empty[s]), 1);
           }
-          const uint32_t dst = tiles_addr + s * C::kStageBytes, bar = full0 + s * uint32_t(sizeof(uint64_t));
           tma_load_2d<kPair>(dst, &map_a, kb * kBK, m0, bar);
           tma_load_2d<kPair>(dst + kABytes, &map_w, kb * kBK, n0, bar);
         }
@@ -437,22 +494,22 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           __threadfence();
           const int rows = min(p.ws_rows, p.M - m0);
           const float* base = p.ws + size_t(t) * p.splits * p.ws_rows * kBN;
-          for (int g = et; g < rows * (kBN / 32); g += 128) {  // 32-column groups of the tile
-            const int r = g / (kBN / 32), c = g % (kBN / 32);
-            if (n0 + c * 32 >= p.N) continue;
-            float v[32];
+          // four columns per thread and step: the loads of all splits are in flight together (one
+          // round trip to L2), the additions then run in split order
+          for (int g = et; g < rows * (kBN / 4); g += 128) {
+            const int r = g / (kBN / 4), c = (g % (kBN / 4)) * 4;
+            if (n0 + c >= p.N) continue;
+            float4 x[kMaxSplits];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-            for (int s2 = 0; s2 < p.splits; ++s2) {
-              const float4* src = reinterpret_cast<const float4*>(base + (size_t(s2) * p.ws_rows + r) * kBN + c * 32);
+            for (int s2 = 0; s2 < kMaxSplits; ++s2)
+              if (s2 < p.splits) x[s2] = __ldcg(reinterpret_cast<const float4*>(base + (size_t(s2) * p.ws_rows + r) * kBN + c));
+            float4 v = x[0];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 x = __ldcg(src + j);
-                v[4 * j] = __fadd_rn(v[4 * j], x.x), v[4 * j + 1] = __fadd_rn(v[4 * j + 1], x.y);
-                v[4 * j + 2] = __fadd_rn(v[4 * j + 2], x.z), v[4 * j + 3] = __fadd_rn(v[4 * j + 3], x.w);
-              }
-            }
-            store_chunk(p, v, m0 + r, n0 + c * 32, a_scale);
+            for (int s2 = 1; s2 < kMaxSplits; ++s2)
+              if (s2 < p.splits)
+                v.x = __fadd_rn(v.x, x[s2].x), v.y = __fadd_rn(v.y, x[s2].y), v.z = __fadd_rn(v.z, x[s2].z),
+                v.w = __fadd_rn(v.w, x[s2].w);
+            store4(p, v, m0 + r, n0 + c, a_scale);
           }
           if (et == 0) p.counters[t] = 0u;  // the workspace is ready for the next call
         }
@@ -651,6 +708,7 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
   p.status = device_status_ptr();
   p.splits = 1, p.kb_per = (K + kBK - 1) / kBK;
   if (M <= kBM) {
+    p.early = 1;
     // a stream of the weights: split K where the workspace allows it
     const SplitPlan pl = plan_split(M, N, K, sm_count());
     if (pl.splits > 1 && d_ws != nullptr && ws_bytes >= static_cast<long long>(pl.bytes)) {

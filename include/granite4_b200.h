@@ -546,7 +546,10 @@ long long granite4_host_glue_d2h_bytes(const granite4_host_glue* ctx, int rows);
  * allows the planned split (0: none wanted); the buffer must be zeroed once
  * before its first use (every call leaves its first bytes, the tile counters,
  * zero again) and belongs to one call at a time. NULL or a smaller buffer: no
- * split. Returns 0, or -1 on bad arguments or a launch error. */
+ * split. d_w must not be written by the operation just before this call on
+ * the stream: with at most 128 rows the kernel starts fetching weights while
+ * that operation drains (weights are constants of a loaded model). Returns 0,
+ * or -1 on bad arguments or a launch error. */
 enum { GRANITE4_GEMM_OUT_BF16 = 0, GRANITE4_GEMM_OUT_F32 = 1, GRANITE4_GEMM_OUT_RESIDUAL = 2 };
 typedef struct granite4_gemm_fp8_epilogue {
   const float* d_a_scale;
