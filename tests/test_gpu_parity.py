@@ -1782,3 +1782,93 @@ def test_gemm_fp8_pair_and_single_forms_agree(K, monkeypatch):
         assert K.gemm_fp8(a, w, o, w_scales=(0.01,)) == 0
         outs.append(o)
     assert torch.equal(outs[0], outs[1])
+
+
+# =========================================================================== a whole layer
+def test_whole_layer_forward_glue_gemms_and_attention(K, port):
+    """One Granite layer over a 48-token prefill chunk, everything on the device and nothing but
+    device buffers between the steps: add + norm -> FP8 -> QKV GEMM (three weight segments) -> RoPE
+    + int8 paged KV -> attention over the pool -> FP8 -> O GEMM with the residual epilogue -> norm
+    -> FP8 -> gate|up GEMM -> SwiGLU -> FP8 -> down GEMM with the residual epilogue. Every step is
+    checked against the oracle (glue: exact) or a float64 evaluation (GEMMs, attention: their
+    tolerances) applied to the device's own inputs of that step."""
+    rows, H, I, stride, max_pos = 48, 4096, 12800, 64, 64
+    eps, rm = 1e-5, 0.22
+    rng = np.random.default_rng(2024)
+    h0, d0 = rand_bf16(1, (rows, H)), rand_bf16(2, (rows, H))
+    w_attn, w_mlp = rand_bf16(3, (H,), 0.1), rand_bf16(4, (H,), 0.1)
+
+    def weights(N, Kd):  # codes of N(0, 1/3) values, finite
+        return np.array(golden("fp8_codec")["encode_all_bf16"])[rand_bf16(N * 7 + Kd, (N, Kd), 0.33)]
+    Wqkv, Wo, Wgu, Wd = weights(6144, H), weights(H, H), weights(2 * I, H), weights(H, I)
+    qkv_scales, segs = (0.05, 0.04, 0.06), (4096, 5120)
+    table = rng.permutation(stride).astype(np.int32)
+    pos = np.arange(rows, dtype=np.int32)
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+
+    def f32buf(n):
+        return torch.zeros(n, dtype=torch.float32, device=DEV)
+
+    # 1. h1 = h0 + rm d0, n1 = norm(h1) -> FP8
+    h1, n1 = empty_bf16(rows, H), torch.empty(rows, H, dtype=torch.uint8, device=DEV)
+    s1 = f32buf(2)
+    assert K.add_rmsnorm_fp8(dev(d0), dev(h0), dev(w_attn), eps, rm, h_out=h1, n_fp8=n1, scale_amax=s1) == 0
+    o_h1, o_n1 = port.add_rmsnorm(d0, h0, w_attn, eps, rm)
+    o_c1, o_s1, _ = port.quant_fp8(o_n1)
+    assert (host(h1) == o_h1).all() and (host(n1) == o_c1).all()
+    assert_scale(host(s1)[0], o_s1)
+    # 2. qkv = n1 Wqkv^T
+    qkv = empty_bf16(rows, 6144)
+    assert K.gemm_fp8(n1, dev(Wqkv), qkv, a_scale=s1, w_scales=qkv_scales, segs=segs) == 0
+    exact, mag = _gemm_f64(host(n1), Wqkv, float(host(s1)[0]), qkv_scales, segs, 6144)
+    assert _gemm_close_bf16(host(qkv), exact, mag)
+    # 3. RoPE + int8 paged KV write
+    ck, cv, ks, vs = _pool(stride)
+    q_rot = empty_bf16(rows, Hq * D)
+    kvr = np.ascontiguousarray(table[:rows])
+    assert K.rope_kv_int8_paged(qkv, t.cos, t.sin, dev(pos), dev(kvr), Hq, Hk, D, stride, max_pos, 0, q_rot,
+                                ck, cv, ks, vs) == 0
+    c, sn = port.rope_tables(1e7, D, max_pos)
+    o_q, o_ck, o_cv, o_ks, o_vs = port.rope_kv_int8(host(qkv), c, sn, pos, kvr, Hq, Hk, D, stride, 0)
+    assert (host(q_rot) == o_q).all() and (host(ck)[:, kvr] == o_ck[:, kvr]).all()
+    assert (host(cv)[:, kvr] == o_cv[:, kvr]).all() and (host(ks)[:, kvr] == o_ks[:, kvr]).all()
+    # 4. causal attention over the pool (groups of four consecutive rows)
+    att = empty_bf16(rows, Hq * D)
+    assert K.attn_decode_int8_paged(q_rot, ck, cv, ks, vs, dev(pos), Hq, Hk, D, stride, max_pos, 1.0 / 128, att,
+                                    rows_per_group=4, pt=dev(table)) == 0
+    want = port.attn_decode_int8(host(q_rot), host(ck), host(cv), host(ks), host(vs), pos, [table] * rows, Hq, Hk, D,
+                                 1.0 / 128)
+    assert np.abs(_bf16_to_f32_np(host(att)) - _bf16_to_f32_np(want)).max() < ATT_TOL
+    # 5. FP8 of the attention output, O projection with the residual epilogue: h2 = h1 + rm (att Wo^T)
+    a8, s2 = torch.empty(rows, H, dtype=torch.uint8, device=DEV), f32buf(2)
+    assert K.fp8_quant(att, a8, s2) == 0
+    o_c, o_s, _ = port.quant_fp8(host(att))
+    assert (host(a8) == o_c).all()
+    h2 = empty_bf16(rows, H)
+    assert K.gemm_fp8(a8, dev(Wo), h2, a_scale=s2, w_scales=(0.05,), residual=h1, resid_scale=rm) == 0
+    exact, mag = _gemm_f64(host(a8), Wo, float(host(s2)[0]), (0.05,), (), H)
+    h1f = _bf16_to_f32_np(host(h1)).astype(np.float64)
+    assert _gemm_close_bf16(host(h2), h1f + np.float32(rm) * exact, np.abs(h1f) + mag)
+    # 6. n2 = norm(h2) -> FP8, gate|up projection
+    n2, s3 = torch.empty(rows, H, dtype=torch.uint8, device=DEV), f32buf(2)
+    assert K.add_rmsnorm_fp8(h2, None, dev(w_mlp), eps, rm, n_fp8=n2, scale_amax=s3) == 0
+    _, o_n2 = port.add_rmsnorm(host(h2), None, w_mlp, eps, rm, want_h=False)
+    assert (host(n2) == port.quant_fp8(o_n2)[0]).all()
+    gu = empty_bf16(rows, 2 * I)
+    assert K.gemm_fp8(n2, dev(Wgu), gu, a_scale=s3, w_scales=(0.05,)) == 0
+    exact, mag = _gemm_f64(host(n2), Wgu, float(host(s3)[0]), (0.05,), (), 2 * I)
+    assert _gemm_close_bf16(host(gu), exact, mag)
+    # 7. SwiGLU -> FP8 on the two halves of the one buffer, down projection with the residual epilogue
+    act8, s4 = torch.empty(rows, I, dtype=torch.uint8, device=DEV), f32buf(2)
+    assert K.swiglu_fp8(gu[:, :I], gu[:, I:], None, act8, s4, ld=2 * I) == 0
+    g_h = host(gu)
+    o_act = port.swiglu(g_h[:, :I], g_h[:, I:])
+    got_act = _fp8_values(host(act8)) * float(host(s4)[0])
+    assert np.abs(got_act - _bf16_to_f32_np(o_act)).max() <= float(host(s4)[0]) * 32 + 1e-6  # one FP8 step at the top binade
+    h3 = empty_bf16(rows, H)
+    assert K.gemm_fp8(act8, dev(Wd), h3, a_scale=s4, w_scales=(0.05,), residual=h2, resid_scale=rm) == 0
+    exact, mag = _gemm_f64(host(act8), Wd, float(host(s4)[0]), (0.05,), (), H)
+    h2f = _bf16_to_f32_np(host(h2)).astype(np.float64)
+    assert _gemm_close_bf16(host(h3), h2f + np.float32(rm) * exact, np.abs(h2f) + mag)
+    assert np.isfinite(_bf16_to_f32_np(host(h3))).all() and np.abs(_bf16_to_f32_np(host(h3))).max() > 0.5
+    t.close()
