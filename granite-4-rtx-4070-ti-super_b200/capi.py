@@ -88,6 +88,8 @@ SIGNATURES = {
     "granite4_gemm_fp8_workspace_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
     "granite4_kernel_gemm_fp8": (C.c_int, [C.c_int, _vp, C.c_longlong, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp,
                                            C.c_longlong]),
+    "granite4_prefill_attention_int8": (C.c_int, [_vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                  C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_longlong]),
     "granite4_prefill_silu_mul": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "granite4_kernel_swiglu_fp8": (C.c_int, [_vp, _vp, C.c_int, C.c_longlong, C.c_int, C.c_int,
                                              _vp, _vp, _vp]),

@@ -65,7 +65,8 @@ struct AttnParams {
   const int8_t* cv;
   const float* ks;
   const float* vs;
-  const int* row_pos;
+  const int* row_pos;        // per-row positions, or NULL: row r is at position base_pos + r
+  int base_pos;
   const int* const* row_pt;  // per-row tables, or NULL
   const int* pt;             // one table for every row, or NULL (identity)
   float* part_o;             // [groups][Hk][splits][16][128]
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(kWarps * 32, NT == 1 ? kCtasPerSmT : kCtasPerS
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) pos_col[nt] = -1;
   for (int j = 0; j < nrows; ++j) {
-    int pj = __ldg(p.row_pos + r0 + j);
+    int pj = p.row_pos != nullptr ? __ldg(p.row_pos + r0 + j) : p.base_pos + r0 + j;
     pj = pj < 0 ? -1 : min(pj, p.max_len - 1);
     pos_max = max(pos_max, pj);
     pos_min = min(pos_min, pj);
@@ -536,6 +537,72 @@ SplitPlan plan_splits(int rows, int group_rows, int Hk, int max_len) {
 }  // namespace
 }  // namespace g4
 
+extern "C" long long granite4_attn_decode_scratch_bytes(int rows, int rows_per_group, int Hk, int max_len);
+
+namespace g4 {
+// Validation, split plan and launches shared by the entry points. d_row_pos NULL: row r is at
+// base_pos + r. single_split_without_scratch: a caller that has no scratch to give (the reference's
+// prefill signature) gets one split over the whole range instead of an error.
+int attn_launch(const char* fn, const uint16_t* d_q, const int8_t* d_cache_k, const int8_t* d_cache_v,
+                const float* d_k_scale, const float* d_v_scale, const int* d_row_pos, int base_pos,
+                const int* const* d_row_pt, const int* d_pt, int rows, int rows_per_group, int Hq, int Hk, int d,
+                int stride, int max_len, float scale, void* d_scratch, long long scratch_bytes, uint16_t* d_out,
+                bool single_split_without_scratch) {
+  if (d_q == nullptr || d_cache_k == nullptr || d_cache_v == nullptr || d_k_scale == nullptr ||
+      d_v_scale == nullptr || d_out == nullptr || rows <= 0 ||
+      rows_per_group <= 0 || rows_per_group > kGroupRows || stride <= 0 || max_len <= 0 ||
+      max_len > stride || !std::isfinite(scale))
+    return fail(fn, "invalid arguments");
+  if (d != kAD || Hk <= 0 || Hq != kGqa * Hk) return -1;  // engine/src/attention_gpu.h:18-19
+  if (!aligned16(d_cache_k) || !aligned16(d_cache_v) || !aligned16(d_q))
+    return fail(fn, "q and the caches must be 16-byte aligned");
+  SplitPlan s = plan_splits(rows, rows_per_group, Hk, max_len);
+  if (s.splits > 1 && single_split_without_scratch &&
+      (d_scratch == nullptr || scratch_bytes < granite4_attn_decode_scratch_bytes(rows, rows_per_group, Hk, max_len))) {
+    s.splits = 1;
+    s.split_len = (max_len + kSplitAlign - 1) / kSplitAlign * kSplitAlign;
+  }
+  if (s.groups > 65535) return fail(fn, "too many row groups");
+  AttnParams p{};
+  p.q = d_q, p.ck = d_cache_k, p.cv = d_cache_v, p.ks = d_k_scale, p.vs = d_v_scale;
+  p.row_pos = d_row_pos, p.base_pos = base_pos, p.row_pt = d_row_pt, p.pt = d_pt, p.out = d_out;
+  p.rows = rows, p.group_rows = rows_per_group, p.Hq = Hq, p.Hk = Hk, p.stride = stride;
+  p.splits = s.splits, p.split_len = s.split_len, p.max_len = max_len;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  if (s.splits > 1) {
+    const long long need = granite4_attn_decode_scratch_bytes(rows, rows_per_group, Hk, max_len);
+    if (d_scratch == nullptr || scratch_bytes < need || !aligned16(d_scratch))
+      return fail(fn, "scratch missing or smaller than granite4_attn_decode_scratch_bytes()");
+    p.part_o = static_cast<float*>(d_scratch);
+    p.part_ml = p.part_o + static_cast<size_t>(s.groups) * Hk * s.splits * 16 * kAD;
+  }
+  cudaStream_t st = current_stream();
+  {
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(kAttnSmemBytesT)));
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(kAttnSmemBytesT)));
+      attr_set[dev] = true;
+    }
+  }
+  const dim3 grid(static_cast<unsigned>(s.splits), static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups));
+  if (rows_per_group <= 2)
+    G4_LAUNCH_PDL(fn, attn_decode_t_kernel<1>, grid, dim3(kWarps * 32), kAttnSmemBytesT, st, p);
+  else
+    G4_LAUNCH_PDL(fn, attn_decode_t_kernel<2>, grid, dim3(kWarps * 32), kAttnSmemBytesT, st, p);
+  if (s.splits > 1)
+    G4_LAUNCH_PDL(fn, attn_combine_kernel,
+                  dim3(static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups), 4u * rows_per_group),
+                  dim3(kAD), 0, st, p);
+  return 0;
+}
+
+}  // namespace g4
+
 extern "C" {
 
 long long granite4_attn_decode_scratch_bytes(int rows, int rows_per_group, int Hk, int max_len) {
@@ -553,52 +620,36 @@ int granite4_kernel_attn_decode_int8_paged(const uint16_t* d_q, const int8_t* d_
                                            int max_len, float scale, void* d_scratch,
                                            long long scratch_bytes, uint16_t* d_out) {
   const char* fn = "granite4_kernel_attn_decode_int8_paged";
-  if (d_q == nullptr || d_cache_k == nullptr || d_cache_v == nullptr || d_k_scale == nullptr ||
-      d_v_scale == nullptr || d_row_pos == nullptr || d_out == nullptr || rows <= 0 ||
-      rows_per_group <= 0 || rows_per_group > g4::kGroupRows || stride <= 0 || max_len <= 0 ||
-      max_len > stride || !std::isfinite(scale))
-    return g4::fail(fn, "invalid arguments");
-  if (d != g4::kAD || Hk <= 0 || Hq != g4::kGqa * Hk) return -1;  // engine/src/attention_gpu.h:18-19
-  if (!g4::aligned16(d_cache_k) || !g4::aligned16(d_cache_v) || !g4::aligned16(d_q))
-    return g4::fail(fn, "q and the caches must be 16-byte aligned");
-  const g4::SplitPlan s = g4::plan_splits(rows, rows_per_group, Hk, max_len);
-  if (s.groups > 65535) return g4::fail(fn, "too many row groups");
-  g4::AttnParams p{};
-  p.q = d_q, p.ck = d_cache_k, p.cv = d_cache_v, p.ks = d_k_scale, p.vs = d_v_scale;
-  p.row_pos = d_row_pos, p.row_pt = d_row_pt, p.pt = d_pt, p.out = d_out;
-  p.rows = rows, p.group_rows = rows_per_group, p.Hq = Hq, p.Hk = Hk, p.stride = stride;
-  p.splits = s.splits, p.split_len = s.split_len, p.max_len = max_len;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  if (s.splits > 1) {
-    const long long need = granite4_attn_decode_scratch_bytes(rows, rows_per_group, Hk, max_len);
-    if (d_scratch == nullptr || scratch_bytes < need || !g4::aligned16(d_scratch))
-      return g4::fail(fn, "scratch missing or smaller than granite4_attn_decode_scratch_bytes()");
-    p.part_o = static_cast<float*>(d_scratch);
-    p.part_ml = p.part_o + static_cast<size_t>(s.groups) * Hk * s.splits * 16 * g4::kAD;
-  }
-  cudaStream_t st = g4::current_stream();
-  {
-    static bool attr_set[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      G4_CUDA_TRY(fn, cudaFuncSetAttribute(g4::attn_decode_t_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(g4::kAttnSmemBytesT)));
-      G4_CUDA_TRY(fn, cudaFuncSetAttribute(g4::attn_decode_t_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(g4::kAttnSmemBytesT)));
-      attr_set[dev] = true;
-    }
-  }
-  const dim3 grid(static_cast<unsigned>(s.splits), static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups));
-  if (rows_per_group <= 2)
-    G4_LAUNCH_PDL(fn, g4::attn_decode_t_kernel<1>, grid, dim3(g4::kWarps * 32), g4::kAttnSmemBytesT, st, p);
-  else
-    G4_LAUNCH_PDL(fn, g4::attn_decode_t_kernel<2>, grid, dim3(g4::kWarps * 32), g4::kAttnSmemBytesT, st, p);
-  if (s.splits > 1)
-    G4_LAUNCH_PDL(fn, g4::attn_combine_kernel,
-                  dim3(static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups), 4u * rows_per_group),
-                  dim3(g4::kAD), 0, st, p);
-  return 0;
+  if (d_row_pos == nullptr) return g4::fail(fn, "invalid arguments");
+  return g4::attn_launch(fn, d_q, d_cache_k, d_cache_v, d_k_scale, d_v_scale, d_row_pos, 0, d_row_pt, d_pt, rows,
+                         rows_per_group, Hq, Hk, d, stride, max_len, scale, d_scratch, scratch_bytes, d_out, false);
+}
+
+int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq, int Hk, int d, int base_pos,
+                                    int rows, int stride, uint16_t* d_out, const int8_t* d_cache_k8,
+                                    const int8_t* d_cache_v8, const float* d_k_scale, const float* d_v_scale,
+                                    const int* d_pt, void* d_scratch, long long scratch_bytes) {
+  const char* fn = "granite4_prefill_attention_int8";
+  if (base_pos < 0 || rows <= 0 || base_pos > INT_MAX - rows) return g4::fail(fn, "invalid arguments");
+  return g4::attn_launch(fn, d_q_rot, d_cache_k8, d_cache_v8, d_k_scale, d_v_scale, nullptr, base_pos, nullptr, d_pt,
+                         rows, g4::kGroupRows, Hq, Hk, d, stride, base_pos + rows, scale, d_scratch, scratch_bytes,
+                         d_out, true);
 }
 
 }  // extern "C"
+
+// The reference's C++ entry point (engine/src/prefill_gemm.h:86-101), same mangled name. Only the
+// int8 cache is built; the other formats and the sliding window return -1, which the reference's
+// caller treats as "take the other attention path" (engine/src/forward_gpu.cu:2800-2830).
+namespace granite4 {
+int prefill_attention(const std::uint16_t* q_rot, const std::uint16_t* cache_k, const std::uint16_t* cache_v,
+                      float scale, int Hq, int Hk, int d, int base_pos, int rows, int stride, std::uint16_t* out,
+                      const std::int8_t* cache_k8, const std::int8_t* cache_v8, const float* k_scale,
+                      const float* v_scale, bool int8, const std::uint8_t* cache_k4, const std::uint8_t* cache_v4,
+                      bool int4, const int* d_pt, bool k5, int window) {
+  (void)cache_k, (void)cache_v, (void)cache_k4, (void)cache_v4;
+  if (!int8 || int4 || k5 || window > 0) return -1;
+  return granite4_prefill_attention_int8(q_rot, scale, Hq, Hk, d, base_pos, rows, stride, out, cache_k8, cache_v8,
+                                         k_scale, v_scale, d_pt, nullptr, 0);
+}
+}  // namespace granite4

@@ -315,6 +315,17 @@ def attn_decode_int8_paged(q, cache_k, cache_v, k_scale, v_scale, row_pos, Hq, H
         _p(scratch, torch.uint8), 0 if scratch is None else scratch.numel(), _p(out, *_BF16_OK))
 
 
+def prefill_attention_int8(q_rot, scale, Hq, Hk, d, base_pos, stride, out, cache_k, cache_v, k_scale, v_scale,
+                           pt=None, scratch=None):
+    """granite4_prefill_attention_int8 (engine/src/prefill_gemm.h:86-101 with the int8 cache): causal
+    attention of q_rot's rows at positions base_pos, base_pos + 1, ... of one sequence."""
+    lib = _enter(q_rot)
+    return lib.granite4_prefill_attention_int8(
+        _p(q_rot, *_BF16_OK), scale, Hq, Hk, d, base_pos, q_rot.shape[0], stride, _p(out, *_BF16_OK),
+        _p(cache_k, torch.int8), _p(cache_v, torch.int8), _p(k_scale, torch.float32), _p(v_scale, torch.float32),
+        _p(pt, torch.int32), _p(scratch, torch.uint8), 0 if scratch is None else scratch.numel())
+
+
 # ---- FP8 x FP8 GEMM -----------------------------------------------------------------------
 def gemm_fp8_workspace(M, N, K, device):
     """A zeroed workspace that lets gemm_fp8 split K for an M x N x K GEMM (None: no split wanted)."""

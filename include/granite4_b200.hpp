@@ -40,6 +40,14 @@ int prefill_rope_split_append_int8(const std::uint16_t* qkv, const float* cos_tb
                                    int d, int stride, std::uint16_t* q_rot, std::int8_t* cache_k,
                                    std::int8_t* cache_v, float* cache_k_scale,
                                    float* cache_v_scale, const int* d_pt = nullptr);
+// engine/src/prefill_gemm.h:86-101. Only int8 == true (and no int4 / k5 / window) is built; anything
+// else returns -1, the reference's "take the other attention path".
+int prefill_attention(const std::uint16_t* q_rot, const std::uint16_t* cache_k, const std::uint16_t* cache_v,
+                      float scale, int Hq, int Hk, int d, int base_pos, int rows, int stride,
+                      std::uint16_t* out, const std::int8_t* cache_k8, const std::int8_t* cache_v8,
+                      const float* k_scale, const float* v_scale, bool int8, const std::uint8_t* cache_k4,
+                      const std::uint8_t* cache_v4, bool int4, const int* d_pt = nullptr, bool k5 = false,
+                      int window = 0);
 // engine/src/prefill_gemm.h:105
 int prefill_silu_mul(const float* gu, int I, int rows, std::uint16_t* act);
 // engine/src/forward_gpu_api.h:224-227

@@ -58,11 +58,13 @@ def test_cpp_entry_points_keep_the_reference_mangled_names(g4):
                 "_ZN8granite421gpu_multi_rope_appendEPKtS1_S1_PKfS3_PKNS_12GpuMultiRowsEiiiiiPvS7_PfS8_iPt",
                 "_ZN8granite414gpu_multi_ropeEPKtPKfS3_PKNS_12GpuMultiRowsEiiiPt",
                 "_ZN8granite419gpu_multi_kv_appendEPKtS1_iPvS2_PfS3_PKNS_12GpuMultiRowsEiiii",
-                "_ZN8granite425prefill_rope_split_appendEPKtPKfS3_iiiiiiPtS4_S4_PKi"):
+                "_ZN8granite425prefill_rope_split_appendEPKtPKfS3_iiiiiiPtS4_S4_PKi",
+                "_ZN8granite417prefill_attentionEPKtS1_S1_fiiiiiiPtPKaS4_PKfS6_bPKhS8_bPKibi"):
         assert sym in out
     hpp = open(HEADER_CPP).read()
     for fn in ("prefill_embed_rows", "prefill_rope_split_append_int8", "prefill_silu_mul",
-               "gpu_multi_rope_append", "gpu_multi_rope(", "gpu_multi_kv_append", "prefill_rope_split_append("):
+               "gpu_multi_rope_append", "gpu_multi_rope(", "gpu_multi_kv_append", "prefill_rope_split_append(",
+               "prefill_attention("):
         assert fn in hpp
 
 

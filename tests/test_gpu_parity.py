@@ -1595,6 +1595,44 @@ def test_attention_over_a_short_prefill_chunk_as_row_groups(K, port):
     t.close()
 
 
+def test_prefill_attention_entry_point_second_chunk_through_a_page_table(K, port):
+    """granite4_prefill_attention_int8 (the reference's prefill_attention contract with the int8
+    cache): the second chunk of a prompt, 150 rows at positions 300..449 over a pool the RoPE + KV
+    kernel filled for positions 0..449 through a permuted table; with and without scratch."""
+    n, base, stride, max_pos = 450, 300, 512, 512
+    qkv = rand_bf16(2900, (n, 48 * D), 1.0)
+    table = np.random.default_rng(82).permutation(stride).astype(np.int32)
+    pos = np.arange(n, dtype=np.int32)
+    t = K.RopeTables(1e7, D, max_pos, DEV)
+    ck, cv, ks, vs = _pool(stride)
+    q_rot = empty_bf16(n, Hq * D)
+    assert K.rope_kv_int8_paged(dev(qkv), t.cos, t.sin, dev(pos), dev(np.ascontiguousarray(table[:n])), Hq, Hk, D,
+                                stride, max_pos, 0, q_rot, ck, cv, ks, vs) == 0
+    q2 = q_rot[base:].contiguous()
+    rows = n - base
+    scale = 1.0 / 128
+    out = empty_bf16(rows, Hq * D)
+    assert K.prefill_attention_int8(q2, scale, Hq, Hk, D, base, stride, out, ck, cv, ks, vs, pt=dev(table)) == 0
+    sel = np.r_[0:6, 70:78, 140:150]
+    want = port.attn_decode_int8(host(q2)[sel], host(ck), host(cv), host(ks), host(vs), pos[base:][sel],
+                                 [table] * len(sel), Hq, Hk, D, scale)
+    assert np.abs(_bf16_to_f32_np(host(out)[sel]) - _bf16_to_f32_np(want)).max() < ATT_TOL
+    # a short chunk: the context may be split over CTAs when scratch is given; same result either way
+    few = empty_bf16(6, Hq * D)
+    few2 = empty_bf16(6, Hq * D)
+    need = K.attn_decode_scratch_bytes(6, 4, Hk, base + 6)
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=DEV)
+    assert K.prefill_attention_int8(q2[:6].contiguous(), scale, Hq, Hk, D, base, stride, few, ck, cv, ks, vs,
+                                    pt=dev(table), scratch=scratch) == 0
+    assert K.prefill_attention_int8(q2[:6].contiguous(), scale, Hq, Hk, D, base, stride, few2, ck, cv, ks, vs,
+                                    pt=dev(table)) == 0
+    assert np.abs(_bf16_to_f32_np(host(few)) - _bf16_to_f32_np(host(out)[:6])).max() < 0.01
+    assert np.abs(_bf16_to_f32_np(host(few2)) - _bf16_to_f32_np(host(out)[:6])).max() < 0.01
+    # head shapes the reference's kernel also refuses
+    assert K.prefill_attention_int8(q2, scale, Hq, Hk, 64, base, stride, out, ck, cv, ks, vs) == -1
+    t.close()
+
+
 # =========================================================================== FP8 x FP8 GEMM
 def _fp8_values(codes):
     return golden("fp8_codec")["decode_all"].astype(np.float64)[codes]
