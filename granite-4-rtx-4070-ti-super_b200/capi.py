@@ -90,6 +90,7 @@ SIGNATURES = {
                                            C.c_longlong]),
     "granite4_prefill_attention_int8": (C.c_int, [_vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                                   C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_longlong]),
+    "granite4_kernel_fp8_encode_with_amax": (C.c_int, [_vp, C.c_longlong, _vp, _vp]),
     "granite4_prefill_silu_mul": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "granite4_kernel_swiglu_fp8": (C.c_int, [_vp, _vp, C.c_int, C.c_longlong, C.c_int, C.c_int,
                                              _vp, _vp, _vp]),
@@ -127,10 +128,11 @@ class GemmFp8Epilogue(C.Structure):
     """granite4_gemm_fp8_epilogue (the FP8 counterpart of GemmEpilogue, engine/src/prefill_gemm.h:21-30)."""
     _fields_ = [("d_a_scale", _vp), ("w_scale0", C.c_float), ("w_scale1", C.c_float), ("w_scale2", C.c_float),
                 ("seg1", C.c_int), ("seg2", C.c_int), ("d_out_bf16", _vp), ("d_out_f32", _vp),
-                ("d_residual", _vp), ("resid_scale", C.c_float), ("ldc", C.c_int)]
+                ("d_residual", _vp), ("resid_scale", C.c_float), ("ldc", C.c_int),
+                ("d_out_scale_amax", _vp)]
 
 
-GEMM_OUT_BF16, GEMM_OUT_F32, GEMM_OUT_RESIDUAL = 0, 1, 2
+GEMM_OUT_BF16, GEMM_OUT_F32, GEMM_OUT_RESIDUAL, GEMM_OUT_SWIGLU = 0, 1, 2, 3
 MAX_VERIFY_ROWS = 16
 MAX_TREE_DEPTH = 8
 

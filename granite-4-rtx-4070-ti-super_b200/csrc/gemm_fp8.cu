@@ -97,6 +97,10 @@ struct GemmParams {
   // to ws [tile][split][rows kept][256] and the CTA that brings a tile's count to `splits` adds them
   int splits, kb_per, ws_rows;
   int early;  // decode-size launch: see the dependent-launch note in the kernel
+  // fused SwiGLU (out_kind SWIGLU): W is gate rows [0, I) then up rows [I, 2 I); a tile is 128 output
+  // columns whose accumulator holds gate in columns 0..127 and up in 128..255
+  int swiglu_i;      // I, or 0 when the epilogue is not the fused SwiGLU
+  float* amax_slot;  // {scale, amax} of the activations: the epilogue maxes |a| into [1]
   float* ws;
   unsigned int* counters;
 };
@@ -318,6 +322,53 @@ __device__ __forceinline__ void store4(const GemmParams& p, float4 v, int row, i
   }
 }
 
+// Fused SwiGLU epilogue of one warp's 32 rows: gate from columns 0..127 and up from columns 128..255 of
+// the accumulator, a = bf16(silu(g) u) (the arithmetic of the standalone kernel, g4_math.cuh swiglu) for
+// output columns n0 .. n0 + 127, and the running max |a| of what was stored (packed bf16 pairs).
+__device__ __forceinline__ uint32_t store_accumulator_swiglu(const GemmParams& p, uint32_t taddr, int row, int n0,
+                                                             float a_scale) {
+  uint32_t amax = 0u;
+  const int I = p.swiglu_i;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    const int n = n0 + c * 32;
+    if (n >= I) break;  // uniform over the warp
+    uint32_t gv[32], uv[32];
+    __syncwarp();
+    tmem_ld32(taddr + c * 32, gv);
+    tmem_ld32(taddr + 128 + c * 32, uv);
+    tmem_ld_wait();
+    if (row >= p.M) continue;
+    const bool one_scale = (n >= p.seg1 || n + 32 <= p.seg1) && (n >= p.seg2 || n + 32 <= p.seg2) &&
+                           (I + n >= p.seg1 || I + n + 32 <= p.seg1) && (I + n >= p.seg2 || I + n + 32 <= p.seg2);
+    const float sg0 = a_scale * seg_scale(p, n), su0 = a_scale * seg_scale(p, I + n);
+    uint32_t w[16];
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const float sg_a = one_scale ? sg0 : a_scale * seg_scale(p, n + j), sg_b = one_scale ? sg0 : a_scale * seg_scale(p, n + j + 1);
+      const float su_a = one_scale ? su0 : a_scale * seg_scale(p, I + n + j), su_b = one_scale ? su0 : a_scale * seg_scale(p, I + n + j + 1);
+      const float a0 = swiglu(__fmul_rn(sg_a, __uint_as_float(gv[j])), __fmul_rn(su_a, __uint_as_float(uv[j])));
+      const float a1 = swiglu(__fmul_rn(sg_b, __uint_as_float(gv[j + 1])), __fmul_rn(su_b, __uint_as_float(uv[j + 1])));
+      w[j / 2] = pack_bf16x2(a0, a1);
+    }
+    const size_t off = size_t(row) * p.ldc + n;
+    if (p.vec != 0 && n + 32 <= I) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        *reinterpret_cast<uint4*>(p.out_bf16 + off + 2 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
+        amax = amax_acc(amax, make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]));
+      }
+    } else {
+      for (int j = 0; j < 32 && n + j < I; ++j) {
+        const uint32_t bits = (j & 1) ? (w[j / 2] >> 16) : (w[j / 2] & 0xffffu);
+        p.out_bf16[off + j] = uint16_t(bits);
+        amax = amax_acc(amax, bits);
+      }
+    }
+  }
+  return amax;
+}
+
 // One warp's 32 rows x 256 columns of a finished accumulator: tensor memory -> epilogue -> global,
 // or (partial != NULL, split K) tensor memory -> this unit's f32 partial rows [.][256].
 // Every lane executes the tensor-memory loads; lanes past row M skip the stores.
@@ -387,7 +438,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (p.early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (!(loader && p.early)) pdl_begin();
 
-  const int mt = (p.M + C::kTileM - 1) / C::kTileM, nt = (p.N + kBN - 1) / kBN;
+  const int tile_cols = p.swiglu_i ? kBN / 2 : kBN;  // output columns of a tile
+  const int mt = (p.M + C::kTileM - 1) / C::kTileM, nt = ((p.swiglu_i ? p.swiglu_i : p.N) + tile_cols - 1) / tile_cols;
   const int tiles = mt * nt, kblocks = (p.K + kBK - 1) / kBK;
   const int units = tiles * p.splits;  // splits == 1 unless K is split
   const int first = kPair ? int(blockIdx.x >> 1) : int(blockIdx.x);
@@ -405,8 +457,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int t = u / p.splits, kb0 = (u % p.splits) * p.kb_per, kb1 = min(kblocks, kb0 + p.kb_per);
           for (int kb = kb0; kb < kb1 && ahead < uint32_t(C::kStages); ++kb, ++ahead) {
             mbar_arrive_expect_tx(&ring->full[ahead], C::kStageBytes);  // first use of every stage: it is empty
-            tma_load_2d<kPair>(tiles_addr + ahead * C::kStageBytes + kABytes, &map_w, kb * kBK, (t / mt) * kBN,
-                               smem_u32(&ring->full[ahead]));
+            const uint32_t wdst = tiles_addr + ahead * C::kStageBytes + kABytes;
+            if (p.swiglu_i) {  // two boxes of 128 rows: gate rows, then up rows
+              tma_load_2d<kPair>(wdst, &map_w, kb * kBK, (t / mt) * tile_cols, smem_u32(&ring->full[ahead]));
+              tma_load_2d<kPair>(wdst + C::kWBytes / 2, &map_w, kb * kBK, p.swiglu_i + (t / mt) * tile_cols,
+                                 smem_u32(&ring->full[ahead]));
+            } else {
+              tma_load_2d<kPair>(wdst, &map_w, kb * kBK, (t / mt) * kBN, smem_u32(&ring->full[ahead]));
+            }
           }
         }
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -414,7 +472,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool ok = true;
       for (int u = first; u < units && ok; u += step) {
         const int t = u / p.splits, kb0 = (u % p.splits) * p.kb_per, kb1 = min(kblocks, kb0 + p.kb_per);
-        const int m0 = (t % mt) * C::kTileM + int(rank) * kBM, n0 = (t / mt) * kBN + int(rank) * C::kWRows;
+        const int m0 = (t % mt) * C::kTileM + int(rank) * kBM;
+        // W rows of this CTA's block: its half (pair) or all (single) of the tile's 256 columns; with the
+        // fused SwiGLU, columns 0..127 are gate rows n0.. and columns 128..255 are up rows I + n0..
+        const int n0 = p.swiglu_i ? (t / mt) * tile_cols + (kPair && rank ? p.swiglu_i : 0)
+                                  : (t / mt) * kBN + int(rank) * C::kWRows;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
           const uint32_t dst = tiles_addr + s * C::kStageBytes, bar = full0 + s * uint32_t(sizeof(uint64_t));
@@ -429,6 +491,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
           tma_load_2d<kPair>(dst, &map_a, kb * kBK, m0, bar);
           tma_load_2d<kPair>(dst + kABytes, &map_w, kb * kBK, n0, bar);
+          if (!kPair && p.swiglu_i)
+            tma_load_2d<kPair>(dst + kABytes + C::kWBytes / 2, &map_w, kb * kBK, p.swiglu_i + n0, bar);
         }
       }
     }
@@ -465,7 +529,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     for (int u = first; u < units && ok; u += step, ++local) {
       const int t = u / p.splits, sl = u % p.splits;
       const uint32_t acc = local & 1u, aph = (local >> 1) & 1u;
-      const int m0 = (t % mt) * C::kTileM + int(rank) * kBM, n0 = (t / mt) * kBN;
+      const int m0 = (t % mt) * C::kTileM + int(rank) * kBM, n0 = (t / mt) * tile_cols;
       ok = wait_or_abort(&ring->acc_full[acc], aph, ring, p.status);
       if (p.splits > 1) ok = epilogue_all(ok);  // the split path below has barriers: leave it together or not at all
       if (!ok) break;
@@ -474,7 +538,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (kPair && leader && warp == 2 && lane == 0) mbar_arrive_remote(smem_u32(&ring->acc_full[acc]), 1);
       tc_fence_after();
       float* partial = p.splits > 1 ? p.ws + (size_t(t) * p.splits + sl) * p.ws_rows * kBN : nullptr;
-      if (m0 + q * 32 < p.M)  // uniform over the warp: a warp whose rows are all past M has nothing to read
+      if (p.swiglu_i) {
+        if (m0 + q * 32 < p.M) {
+          const uint32_t amax = amax_warp(store_accumulator_swiglu(p, tmem_base + (uint32_t(q * 32) << 16) + acc * kBN,
+                                                                   m0 + q * 32 + lane, n0, a_scale));
+          if (lane == 0 && amax != 0u) atomic_amax(p.amax_slot + 1, amax_value(amax));
+        }
+      } else if (m0 + q * 32 < p.M)  // uniform over the warp: a warp whose rows are all past M has nothing to read
         store_accumulator(p, tmem_base + (uint32_t(q * 32) << 16) + acc * kBN, m0 + q * 32 + lane, n0, a_scale,
                           partial != nullptr ? partial + size_t(q * 32 + lane) * kBN : nullptr);
       tc_fence_before();
@@ -650,10 +720,13 @@ template <class C>
 int launch(const char* fn, const uint8_t* d_a, long long lda, const uint8_t* d_w, const GemmParams& p) {
   constexpr bool kPair = C::kTileM == 2 * kBM;
   CUtensorMap map_a, map_w;
-  if (!make_map(&map_a, d_a, p.M, p.K, lda, C::kARows) || !make_map(&map_w, d_w, p.N, p.K, p.K, C::kWRows))
+  // the fused SwiGLU fetches a single CTA's 256 W rows as two boxes of 128 (gate rows, up rows)
+  const int w_box = (p.swiglu_i && !kPair) ? kBN / 2 : C::kWRows;
+  if (!make_map(&map_a, d_a, p.M, p.K, lda, C::kARows) || !make_map(&map_w, d_w, p.N, p.K, p.K, w_box))
     return fail(fn, "the tensor map could not be encoded");
   G4_CUDA_TRY(fn, smem_opt_in<C>());
-  const int units = ((p.M + C::kTileM - 1) / C::kTileM) * ((p.N + kBN - 1) / kBN) * p.splits;
+  const int nt = p.swiglu_i ? (p.swiglu_i + kBN / 2 - 1) / (kBN / 2) : (p.N + kBN - 1) / kBN;
+  const int units = ((p.M + C::kTileM - 1) / C::kTileM) * nt * p.splits;
   if constexpr (kPair) {
     const int clusters = units < pair_clusters() ? units : pair_clusters();
     cudaLaunchConfig_t cfg = pair_config(clusters);
@@ -688,9 +761,13 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
   if (d_a == nullptr || d_w == nullptr || ep == nullptr) return fail(fn, "null argument");
   if (M < 0 || N <= 0 || K <= 0 || K % 16 != 0 || lda < K || lda % 16 != 0 || !aligned16(d_a) || !aligned16(d_w))
     return fail(fn, "needs K % 16 == 0, lda % 16 == 0, lda >= K and 16-byte aligned A and W");
-  if (out_kind != GRANITE4_GEMM_OUT_BF16 && out_kind != GRANITE4_GEMM_OUT_F32 && out_kind != GRANITE4_GEMM_OUT_RESIDUAL)
+  if (out_kind != GRANITE4_GEMM_OUT_BF16 && out_kind != GRANITE4_GEMM_OUT_F32 && out_kind != GRANITE4_GEMM_OUT_RESIDUAL &&
+      out_kind != GRANITE4_GEMM_OUT_SWIGLU)
     return fail(fn, "unknown output kind");
-  if (ep->ldc < N) return fail(fn, "ldc < N");
+  const bool fused_swiglu = out_kind == GRANITE4_GEMM_OUT_SWIGLU;
+  if (fused_swiglu && (N % 2 != 0 || ep->d_out_scale_amax == nullptr))
+    return fail(fn, "the fused SwiGLU needs an even N (gate rows, then up rows) and d_out_scale_amax");
+  if (ep->ldc < (fused_swiglu ? N / 2 : N)) return fail(fn, "ldc smaller than the output row");
   if (out_kind == GRANITE4_GEMM_OUT_F32 ? ep->d_out_f32 == nullptr : ep->d_out_bf16 == nullptr)
     return fail(fn, "the output of the requested kind is null");
   if (out_kind == GRANITE4_GEMM_OUT_RESIDUAL && ep->d_residual == nullptr) return fail(fn, "null residual");
@@ -707,6 +784,11 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
           (out_kind != GRANITE4_GEMM_OUT_RESIDUAL || aligned16(ep->d_residual));
   p.status = device_status_ptr();
   p.splits = 1, p.kb_per = (K + kBK - 1) / kBK;
+  if (fused_swiglu) {
+    p.swiglu_i = N / 2, p.amax_slot = ep->d_out_scale_amax;
+    if (!amax_prezeroed()) G4_CUDA_TRY(fn, cudaMemsetAsync(p.amax_slot, 0, 2 * sizeof(float), current_stream()));
+    if (M <= kBM) return launch<CfgWide>(fn, d_a, lda, d_w, p);  // no split of K under this epilogue
+  }
   if (M <= kBM) {
     p.early = 1;
     // a stream of the weights: split K where the workspace allows it

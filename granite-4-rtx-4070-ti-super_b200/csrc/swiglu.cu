@@ -251,6 +251,21 @@ int granite4_kernel_swiglu_fp8(const void* d_gate, const void* d_up, int in_is_f
   return in_is_f32 ? g4::launch_swiglu<true>(fn, p) : g4::launch_swiglu<false>(fn, p);
 }
 
+int granite4_kernel_fp8_encode_with_amax(const uint16_t* d_x, long long n, uint8_t* d_codes,
+                                         float* d_scale_amax) {
+  const char* fn = "granite4_kernel_fp8_encode_with_amax";
+  if (d_x == nullptr || d_codes == nullptr || d_scale_amax == nullptr || n <= 0 || n % 8 != 0 ||
+      n / 8 >= (1ll << 32) || !g4::aligned16(d_x) || !g4::aligned16(d_codes))
+    return g4::fail(fn, "needs n % 8 == 0 and 16-byte aligned buffers");
+  g4::SwigluParams p{};
+  p.act_bf16 = const_cast<uint16_t*>(d_x), p.act_fp8 = d_codes, p.scale_amax = d_scale_amax;
+  p.items = n / 8, p.ipr = 1, p.contiguous = 1, p.ld = 8;
+  const long long tiles = (p.items + g4::kThreads * g4::kUnroll - 1) / (g4::kThreads * g4::kUnroll);
+  G4_LAUNCH_PDL(fn, (g4::swiglu_kernel<false, g4::kEncode, true>), dim3(static_cast<unsigned>(tiles)),
+                dim3(g4::kThreads), 0, g4::current_stream(), p);
+  return 0;
+}
+
 int granite4_prefill_silu_mul(const float* gu, int I, int rows, uint16_t* act) {
   const char* fn = "prefill_silu_mul";
   if (rows <= 0 || I <= 0) return -1;  // engine/src/prefill_gemm.cu:1469

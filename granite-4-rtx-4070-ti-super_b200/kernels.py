@@ -333,14 +333,24 @@ def gemm_fp8_workspace(M, N, K, device):
     return torch.zeros(need, dtype=torch.uint8, device=device) if need > 0 else None
 
 
+def fp8_encode_with_amax(x, codes, scale_amax):
+    """granite4_kernel_fp8_encode_with_amax: codes of a bf16 tensor whose max |x| is already in
+    scale_amax[1] (the fused SwiGLU epilogue of gemm_fp8 leaves it there)."""
+    lib = _enter(x)
+    return lib.granite4_kernel_fp8_encode_with_amax(_p(x, *_BF16_OK), x.numel(), _p(codes, torch.uint8),
+                                                    _p(scale_amax, torch.float32))
+
+
 def gemm_fp8(a_fp8, w_fp8, out, a_scale=None, w_scales=(1.0,), segs=(), residual=None, resid_scale=1.0,
-             workspace=None):
+             workspace=None, swiglu_scale_amax=None):
     """granite4_kernel_gemm_fp8: out[M][N] = a_scale * w_scale(n) * a_fp8[M][K] x w_fp8[N][K]^T.
     a_fp8 / w_fp8: uint8 e4m3 codes (a_fp8 may be a row-strided view); a_scale: float32 CUDA tensor
     whose element 0 is the activation scale; w_scales: up to three per-segment weight scales with
     the segment ends in segs; out: bf16 or float32 [M][N] (row-strided allowed); residual: bf16,
     same pitch as out (GemmOut::kResidual, engine/src/prefill_gemm.h:12-16). workspace: uint8 CUDA
-    tensor from gemm_fp8_workspace (zeroed once; reusable call after call)."""
+    tensor from gemm_fp8_workspace (zeroed once; reusable call after call). swiglu_scale_amax: float32[2];
+    when given, w_fp8 is gate rows then up rows and out [M][N / 2] gets bf16(silu(gate) * up), its
+    max |.| going to swiglu_scale_amax[1] (GRANITE4_GEMM_OUT_SWIGLU)."""
     lib = _enter(a_fp8)
     M, K = a_fp8.shape
     N = w_fp8.shape[0]
@@ -352,7 +362,10 @@ def gemm_fp8(a_fp8, w_fp8, out, a_scale=None, w_scales=(1.0,), segs=(), residual
     ep.seg1, ep.seg2 = sg
     ep.resid_scale = resid_scale
     ep.ldc = out.stride(0)
-    if out.dtype == torch.float32:
+    if swiglu_scale_amax is not None:
+        kind, ep.d_out_bf16 = capi.GEMM_OUT_SWIGLU, out.data_ptr()
+        ep.d_out_scale_amax = _p(swiglu_scale_amax, torch.float32)
+    elif out.dtype == torch.float32:
         kind, ep.d_out_f32 = capi.GEMM_OUT_F32, out.data_ptr()
     else:
         kind = capi.GEMM_OUT_BF16 if residual is None else capi.GEMM_OUT_RESIDUAL

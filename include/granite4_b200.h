@@ -421,6 +421,13 @@ int granite4_prefill_silu_mul(const float* gu, int I, int rows, uint16_t* act);
  * d_scale_amax: float[2] = {scale, amax}, required with d_act_fp8. I must be
  * a multiple of 8, rows 16-byte aligned. With d_act_fp8 this enqueues an 8-byte
  * memset and two kernels. */
+/* Added. The second half of a per-tensor FP8 quantisation whose first half (the
+ * max |x|) another kernel already did: d_scale_amax[1] holds the max |x| of
+ * the bf16 tensor d_x (n elements, n % 8 == 0, 16-byte aligned), the call
+ * writes the scale to d_scale_amax[0] and the e4m3 codes to d_codes. One sweep:
+ * 2 bytes read, 1 written per element. */
+int granite4_kernel_fp8_encode_with_amax(const uint16_t* d_x, long long n, uint8_t* d_codes,
+                                         float* d_scale_amax);
 int granite4_kernel_swiglu_fp8(const void* d_gate, const void* d_up, int in_is_f32, long long ld,
                                int rows, int I, uint16_t* d_act_bf16, uint8_t* d_act_fp8,
                                float* d_scale_amax);
@@ -555,6 +562,14 @@ int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq
  * reference's GemmEpilogue: w_scale(n) = w_scale0 for n < seg1, w_scale1 for
  * n < seg2, else w_scale2. Output kinds as GemmOut: bf16(y), f32 y, or
  * bf16(residual + resid_scale * y) (d_residual may alias d_out_bf16).
+ * GRANITE4_GEMM_OUT_SWIGLU folds prefill_silu_mul (engine/src/prefill_gemm.h:105)
+ * into the epilogue of the gate|up projection: W holds the I = N / 2 gate rows,
+ * then the I up rows (the reference's stacked layout), d_out_bf16 [M][I] gets
+ * a = bf16(silu(y_gate) * y_up) computed from the f32 sums (as the reference
+ * does from its f32 GEMM output), and max |a| is written to
+ * d_out_scale_amax[1] (cleared by the call), so that
+ * granite4_kernel_fp8_encode_with_amax turns a into FP8 codes in one sweep;
+ * the 4 I bytes per row of gate|up output never exist.
  * Needs K % 16 == 0, lda % 16 == 0, 16-byte aligned A and W; any M >= 0, any N.
  * d_ws / ws_bytes, as the ws / ws_bytes of prefill_gemm: with at most 128 rows a
  * GEMM has too few output tiles to occupy the card and splits K across CTAs,
@@ -567,7 +582,12 @@ int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq
  * the stream: with at most 128 rows the kernel starts fetching weights while
  * that operation drains (weights are constants of a loaded model). Returns 0,
  * or -1 on bad arguments or a launch error. */
-enum { GRANITE4_GEMM_OUT_BF16 = 0, GRANITE4_GEMM_OUT_F32 = 1, GRANITE4_GEMM_OUT_RESIDUAL = 2 };
+enum {
+  GRANITE4_GEMM_OUT_BF16 = 0,
+  GRANITE4_GEMM_OUT_F32 = 1,
+  GRANITE4_GEMM_OUT_RESIDUAL = 2,
+  GRANITE4_GEMM_OUT_SWIGLU = 3
+};
 typedef struct granite4_gemm_fp8_epilogue {
   const float* d_a_scale;
   float w_scale0, w_scale1, w_scale2;
@@ -577,6 +597,7 @@ typedef struct granite4_gemm_fp8_epilogue {
   const uint16_t* d_residual;
   float resid_scale;
   int ldc; /* output (and residual) row pitch, elements */
+  float* d_out_scale_amax; /* GRANITE4_GEMM_OUT_SWIGLU only: {scale, amax} of the activations */
 } granite4_gemm_fp8_epilogue;
 long long granite4_gemm_fp8_workspace_bytes(int M, int N, int K);
 int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long long lda, const uint8_t* d_w, int M,

@@ -1910,3 +1910,38 @@ def test_whole_layer_forward_glue_gemms_and_attention(K, port):
     assert _gemm_close_bf16(host(h3), h2f + np.float32(rm) * exact, np.abs(h2f) + mag)
     assert np.isfinite(_bf16_to_f32_np(host(h3))).all() and np.abs(_bf16_to_f32_np(host(h3))).max() > 0.5
     t.close()
+
+
+@pytest.mark.parametrize("M,I,Kd", [(300, 640, 512), (100, 200, 256), (1000, 1536, 1024), (9, 128, 128)])
+def test_gemm_fp8_fused_swiglu_epilogue_and_one_sweep_encode(K, port, M, I, Kd):
+    """gate|up projection with SwiGLU folded into the epilogue (pair form, single form, ragged I):
+    the activations equal SwiGLU of the same GEMM's f32 output, the amax slot is their maximum,
+    and the one-sweep encode gives the oracle quantiser's codes for them."""
+    rng = np.random.default_rng(M + I)
+    a, w = _codes(rng, (M, Kd)), _codes(rng, (2 * I, Kd))
+    w[(w & 0x7F) > 0x50] = 0x41  # keep |w| <= 8 so that the gate stays in the range where silu varies
+    a_scale = torch.tensor([0.6 / Kd ** 0.5, 0.0], device=DEV)
+    ws = (0.01, 0.02)  # gate and up tensors have their own scales
+    gu = torch.empty(M, 2 * I, dtype=torch.float32, device=DEV)
+    assert K.gemm_fp8(dev(a), dev(w), gu, a_scale=a_scale, w_scales=ws, segs=(I,)) == 0
+    ldc = (I + 7) // 8 * 8
+    buf = torch.zeros(M, ldc, dtype=torch.int16, device=DEV)
+    act = buf[:, :I]
+    slot = torch.full((2,), 7.0, dtype=torch.float32, device=DEV)  # the call clears it
+    assert K.gemm_fp8(dev(a), dev(w), act, a_scale=a_scale, w_scales=ws, segs=(I,), swiglu_scale_amax=slot) == 0
+    g_h = host(gu)
+    want = port.swiglu(np.ascontiguousarray(g_h[:, :I]), np.ascontiguousarray(g_h[:, I:]))
+    got = host(act)
+    assert bf16_ulp_distance(got, want).max() <= 1
+    assert np.abs(_bf16_to_f32_np(got)).max() > 0.05  # the case exercises the non-linear range
+    amax = float(host(slot)[1])
+    assert amax == float(np.abs(_bf16_to_f32_np(got)).max())
+    if ldc > I:
+        assert (host(buf)[:, I:] == 0).all()
+    if I % 8 == 0:
+        codes = torch.empty(M, I, dtype=torch.uint8, device=DEV)
+        dense = act.contiguous()
+        assert K.fp8_encode_with_amax(dense, codes, slot) == 0
+        scale = port.fp8_scale_from_amax(amax)
+        assert_scale(host(slot)[0], scale)
+        assert (host(codes) == port.quant_fp8_with_scale(host(dense), float(host(slot)[0]))).all()
