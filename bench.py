@@ -618,6 +618,27 @@ def small_shapes_and_embed(seq, rows, device, stream):
                       "frac_of_2x_measured_bf16_sustained": tf / (2 * bf16_sust),
                       "frac_of_2x_measured_bf16_burst": tf / (2 * bf16_burst), "frac_of_nominal_4500": tf / 4500.0}
         del o
+    # gate|up projection -> SwiGLU -> FP8, two ways: the projection writing gate|up (bf16) and the
+    # standalone two-sweep SwiGLU kernel after it, or SwiGLU folded into the projection's epilogue
+    # (which also leaves max |a| in the device slot) and the one-sweep encode after it.
+    gu_o = torch.empty(g_rows, 2 * I, dtype=torch.bfloat16, device=device)
+    act_b = torch.empty(g_rows, I, dtype=torch.bfloat16, device=device)
+    act_8 = torch.empty(g_rows, I, dtype=torch.uint8, device=device)
+    slot = torch.zeros(2, dtype=torch.float32, device=device)
+    flip = [0]
+
+    def unfused():
+        flip[0] ^= 1
+        k.gemm_fp8(a_h, wsets[flip[0]]["gate_up"], gu_o, a_scale=a_sc, w_scales=(0.01,))
+        k.swiglu_fp8(gu_o[:, :I], gu_o[:, I:], None, act_8, slot, ld=2 * I)
+
+    def fused():
+        flip[0] ^= 1
+        k.gemm_fp8(a_h, wsets[flip[0]]["gate_up"], act_b, a_scale=a_sc, w_scales=(0.01,), swiglu_scale_amax=slot)
+        k.fp8_encode_with_amax(act_b, act_8, slot)
+    gemm["gate_up_swiglu_fp8"] = {"M": g_rows, "unfused_us": timed(unfused, 10), "fused_epilogue_us": timed(fused, 10),
+                                  "bytes_per_row_unfused": 2 * (2 * I) + 9 * I, "bytes_per_row_fused": 2 * I + 3 * I}
+    del gu_o, act_b, act_8
     wbytes = sum(N * Kd for _, N, Kd in proj)
     for n in (1, 8):
         outs = {name: torch.empty(n, N, dtype=torch.bfloat16, device=device) for name, N, _ in proj}
