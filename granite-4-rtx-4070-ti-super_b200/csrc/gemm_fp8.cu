@@ -1,4 +1,4 @@
-// FP8 x FP8 prefill GEMM on the 5th-generation tensor cores (sm_100a).
+// FP8 x FP8 GEMM on the 5th-generation tensor cores (sm_100a).
 //
 //   C[m][n] = a_scale * w_scale(n) * sum_k A[m][k] * W[n][k]
 //
@@ -11,8 +11,10 @@
 // / kResidual and the three-segment weight scale) is the reference's
 // (engine/src/prefill_gemm.cu:65-88).
 //
-// Shape of the kernel: persistent, one CTA per SM, 128 x 256 output tiles,
-// K consumed in 128-byte blocks. Roles by warp:
+// Shape of the kernel (its single-CTA form; the CTA-pair form for more than 128
+// rows, the 16-row form with split K and the fused SwiGLU epilogue are described
+// at Cfg, plan_split and store_accumulator_swiglu): persistent, one CTA per SM,
+// 128 x 256 output tiles, K consumed in 128-byte blocks. Roles by warp:
 //   warp 0   one thread issues the tiled TMA loads (128-byte swizzle) of the A
 //            and W blocks into a 4-stage shared-memory ring;
 //   warp 1   allocates tensor memory; one thread issues tcgen05.mma
