@@ -654,6 +654,84 @@ def small_shapes_and_embed(seq, rows, device, stream):
         gemm[f"decode_rows_{n}_weight_gbs"] = wbytes / (us * 1e-6) / 1e9
         gemm[f"decode_rows_{n}_frac"] = wbytes / (us * 1e-6) / 1e9 / peak
     gemm["decode_weight_bytes_per_layer"] = wbytes
+
+    # A complete decode step of a two-layer model with real projections, one CUDA graph: embedding of
+    # the newest tokens, per layer {norm -> FP8, QKV GEMM, RoPE + int8 KV append, attention over
+    # ~4100 cached positions, FP8 of the attention output, O GEMM + residual, norm -> FP8, gate|up
+    # GEMM, SwiGLU -> FP8, down GEMM + residual}, final norm -> FP8, lm_head GEMM (100352 x 4096),
+    # greedy pick + token scatter. 809 MB of weights per replay (two layer sets + lm_head).
+    stride_d, page_d = 16384, 16
+    ck = torch.zeros(s.kv_heads, stride_d, s.head_dim, device=device, dtype=torch.int8)
+    cv = torch.zeros_like(ck)
+    ksc = torch.full((s.kv_heads, stride_d), 0.01, device=device)
+    vsc = torch.full((s.kv_heads, stride_d), 0.01, device=device)
+    ck.random_(-127, 128, generator=g), cv.random_(-127, 128, generator=g)
+    w_lm = fp8_codes(s.vocab, H)
+    wn = (1.0 + 0.02 * torch.randn(3, H, generator=g, device=device)).to(torch.bfloat16)
+    emb_d = (0.02 * torch.randn(4096, H, generator=g, device=device)).to(torch.bfloat16)
+    full = {}
+    for n in (1, 8):
+        tables = [(torch.randperm(stride_d // 8 // page_d, generator=g, device=device).repeat_interleave(page_d) * page_d
+                   + torch.arange(stride_d // 8, device=device) % page_d + r * (stride_d // 8)).to(torch.int32)
+                  for r in range(n)]
+        toks = [torch.zeros(stride_d // 8, dtype=torch.int32, device=device) for _ in range(n)]
+        desc = capi.MultiRows()
+        desc.n = n
+        for r in range(n):
+            desc.pos[r] = 1900 + 3 * r
+            desc.pt[r] = tables[r].data_ptr()
+            desc.tok[r] = toks[r].data_ptr()
+        d_rows = k.multi_rows_to_device(desc, device)
+        row_pos = d_rows[capi.MultiRows.pos.offset:capi.MultiRows.pos.offset + 4 * n].view(torch.int32)
+        row_pt = d_rows[capi.MultiRows.pt.offset:capi.MultiRows.pt.offset + 8 * n].view(torch.int64)
+        kv_rows = torch.stack([tables[r][1900 + 3 * r] for r in range(n)]).to(torch.int32)
+        hid = torch.empty(n, H, dtype=torch.bfloat16, device=device)
+        nf8 = torch.empty(n, H, dtype=torch.uint8, device=device)
+        a8 = torch.empty(n, H, dtype=torch.uint8, device=device)
+        act8 = torch.empty(n, I, dtype=torch.uint8, device=device)
+        qkv = torch.empty(n, QKV, dtype=torch.bfloat16, device=device)
+        qr = torch.empty(n, H, dtype=torch.bfloat16, device=device)
+        ao = torch.empty_like(qr)
+        gu = torch.empty(n, 2 * I, dtype=torch.bfloat16, device=device)
+        logits = torch.empty(n, s.vocab, dtype=torch.bfloat16, device=device)
+        sc = torch.zeros(12, 2, dtype=torch.float32, device=device)
+        idv = torch.zeros(n, dtype=torch.int32, device=device)
+        scr = torch.empty(max(k.attn_decode_scratch_bytes(n, 1, s.kv_heads, 2048), 16), dtype=torch.uint8, device=device)
+        wsp = {name: k.gemm_fp8_workspace(n, N, Kd, device) for name, N, Kd in proj}
+        wsp["lm"] = k.gemm_fp8_workspace(n, s.vocab, H, device)
+        count = [0]
+
+        def step():
+            c = 0
+            k.gpu_multi_embed(d_rows, n, emb_d, s.embedding_multiplier, hid)
+            c += 1
+            for li, ws_ in enumerate(wsets):
+                b = 5 * li
+                k.add_rmsnorm_fp8(hid, None, wn[0], s.eps, s.residual_multiplier, n_fp8=nf8, scale_amax=sc[b])
+                k.gemm_fp8(nf8, ws_["qkv"], qkv, a_scale=sc[b], w_scales=(0.01,), workspace=wsp["qkv"])
+                k.rope_kv_int8_paged(qkv, seq.tables.cos, seq.tables.sin, row_pos, kv_rows, s.q_heads, s.kv_heads,
+                                     s.head_dim, stride_d, seq.max_pos, 0, qr, ck, cv, ksc, vsc)
+                k.attn_decode_int8_paged(qr, ck, cv, ksc, vsc, row_pos, s.q_heads, s.kv_heads, s.head_dim, stride_d,
+                                         2048, 1.0 / 128, ao, rows_per_group=1, row_pt=row_pt, scratch=scr)
+                k.fp8_quant(ao, a8, sc[b + 1])
+                k.gemm_fp8(a8, ws_["o"], hid, a_scale=sc[b + 1], w_scales=(0.01,), residual=hid,
+                           resid_scale=s.residual_multiplier, workspace=wsp["o"])
+                k.add_rmsnorm_fp8(hid, None, wn[1], s.eps, s.residual_multiplier, n_fp8=nf8, scale_amax=sc[b + 2])
+                k.gemm_fp8(nf8, ws_["gate_up"], gu, a_scale=sc[b + 2], w_scales=(0.01,), workspace=wsp["gate_up"])
+                k.swiglu_fp8(gu[:, :I], gu[:, I:], None, act8, sc[b + 3], ld=2 * I)
+                k.gemm_fp8(act8, ws_["down"], hid, a_scale=sc[b + 3], w_scales=(0.01,), residual=hid,
+                           resid_scale=s.residual_multiplier, workspace=wsp["down"])
+                c += 11
+            k.add_rmsnorm_fp8(hid, None, wn[2], s.eps, s.residual_multiplier, n_fp8=nf8, scale_amax=sc[10])
+            k.gemm_fp8(nf8, w_lm, logits, a_scale=sc[10], w_scales=(0.01,), workspace=wsp["lm"])
+            k.argmax_advance(logits, d_rows, idv)
+            count[0] = c + 3
+        us = graph_replay_us(step, 20)
+        wb = 2 * wbytes + s.vocab * H
+        full[f"sessions_{n}"] = {"layers": 2, "launches": count[0], "graph_replay_us": us, "weight_bytes": wb,
+                                 "weight_gbs": wb / (us * 1e-6) / 1e9, "frac": wb / (us * 1e-6) / 1e9 / peak}
+    gemm["decode_step_two_layers_lm_head"] = full
+    del ck, cv, ksc, vsc, w_lm, logits
     del wsets, a_h, a_i
     torch.cuda.empty_cache()
     return {"embed": embed, "small": small, "argmax": argmax, "attention": attention, "decode_step": decode_step,
