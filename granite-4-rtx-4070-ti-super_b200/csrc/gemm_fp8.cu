@@ -51,8 +51,10 @@ constexpr uint32_t kTmemCols = kAccs * kBN;  // 512: the whole tensor memory of 
 constexpr int kMaxStages = 6;
 constexpr int kMaxSplits = 16;
 
-// Forms of the kernel; all compute 256 output columns per tile, because one MMA takes the same
-// time whatever its N and only N = 256 moves enough weight bytes per MMA to keep up with HBM.
+// Forms of the kernel; all compute 256 output columns per tile: a stage costs the loader thread
+// about 0.3 us of issue (barrier wait, expect_tx, two TMA instructions) whatever its size, so only
+// 256-row W blocks (32 KB per stage) carry enough bytes per stage to keep up with HBM; 32- and
+// 64-column tiles were measured at a quarter and a half of that rate.
 // kPair = true: the two CTAs of a cluster own a 256 x 256 tile; each loads its 128 rows of A and
 //   its 128 rows of W, and one thread of the leader CTA issues MMAs that run on both SMs
 //   (cta_group::2), so each SM reads half as many W bytes from shared memory per flop.
