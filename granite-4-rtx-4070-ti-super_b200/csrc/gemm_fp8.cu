@@ -650,11 +650,20 @@ bool pair_enabled() {
   return !(v != nullptr && v[0] == '0');
 }
 
-// The dynamic shared memory opt-in of one form, once per process; the error of that call.
+// The dynamic shared memory opt-in of one form, once per device (function attributes are per
+// device); the error of that call.
 template <class C>
 cudaError_t smem_opt_in() {
-  static const cudaError_t err =
+  static std::mutex mu;
+  static std::map<int, cudaError_t> done;
+  int dev = 0;
+  if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  const auto it = done.find(dev);
+  if (it != done.end()) return it->second;
+  const cudaError_t err =
       cudaFuncSetAttribute(gemm_fp8_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(C::kSmemBytes));
+  done[dev] = err;
   return err;
 }
 
