@@ -101,6 +101,9 @@ struct GemmParams {
   // to ws [tile][split][rows kept][256] and the CTA that brings a tile's count to `splits` adds them
   int splits, kb_per, ws_rows;
   int early;  // decode-size launch: see the dependent-launch note in the kernel
+  // stream form (gemm_fp8_stream_kernel): tile columns, k blocks per stage, rows of A fetched, ring depth
+  int bn, kc, a_rows, stages;
+  int box3d;  // one TMA box spans the kc k-blocks of a stage (needs K % 128 == 0)
   // fused SwiGLU (out_kind SWIGLU): W is gate rows [0, I) then up rows [I, 2 I); a tile is 128 output
   // columns whose accumulator holds gate in columns 0..127 and up in 128..255
   int swiglu_i;      // I, or 0 when the epilogue is not the fused SwiGLU
@@ -125,6 +128,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
         : "memory");
   }
+}
+// 3-D box {128 bytes, rows, k-blocks}: lands as consecutive K-major 128-byte-swizzled blocks [k-block][row][128].
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
 }
 template <bool kPair>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t cols) {
@@ -251,21 +261,23 @@ __device__ __forceinline__ float seg_scale(const GemmParams& p, int n) {
 
 // Epilogue of 32 consecutive columns n .. n + 31 of one output row from the f32 sums v: scale,
 // add the residual where asked, convert, store (engine/src/prefill_gemm.cu:65-88).
-__device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[32], int row, int n, float a_scale) {
+// n_end: first column that is not this call's to write (the tile's end or N).
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[32], int row, int n, float a_scale,
+                                            int n_end) {
   const bool one_scale = (n >= p.seg1 || n + 32 <= p.seg1) && (n >= p.seg2 || n + 32 <= p.seg2);
   const float sc0 = a_scale * seg_scale(p, n);
   float y[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) y[j] = (one_scale ? sc0 : a_scale * seg_scale(p, n + j)) * v[j];
   const size_t off = size_t(row) * p.ldc + n;
-  const bool full = p.vec != 0 && n + 32 <= p.N;
+  const bool full = p.vec != 0 && n + 32 <= n_end;
   if (p.out_kind == GRANITE4_GEMM_OUT_F32) {
     if (full) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4)
         *reinterpret_cast<float4*>(p.out_f32 + off + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
     } else {
-      for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_f32[off + j] = y[j];
+      for (int j = 0; j < 32 && n + j < n_end; ++j) p.out_f32[off + j] = y[j];
     }
     return;
   }
@@ -279,7 +291,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
         for (int e = 0; e < 8; ++e) y[j + e] = __fadd_rn(r[e], __fmul_rn(p.resid_scale, y[j + e]));
       }
     } else {
-      for (int j = 0; j < 32 && n + j < p.N; ++j)
+      for (int j = 0; j < 32 && n + j < n_end; ++j)
         y[j] = __fadd_rn(bf16_to_f32(p.residual[off + j]), __fmul_rn(p.resid_scale, y[j]));
     }
   }
@@ -290,7 +302,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
           make_uint4(pack_bf16x2(y[j], y[j + 1]), pack_bf16x2(y[j + 2], y[j + 3]),
                      pack_bf16x2(y[j + 4], y[j + 5]), pack_bf16x2(y[j + 6], y[j + 7]));
   } else {
-    for (int j = 0; j < 32 && n + j < p.N; ++j) p.out_bf16[off + j] = uint16_t(f32_to_bf16_bits(y[j]));
+    for (int j = 0; j < 32 && n + j < n_end; ++j) p.out_bf16[off + j] = uint16_t(f32_to_bf16_bits(y[j]));
   }
 }
 
@@ -395,7 +407,7 @@ __device__ __forceinline__ void store_accumulator(const GemmParams& p, uint32_t 
       float f[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-      store_chunk(p, f, row, n, a_scale);
+      store_chunk(p, f, row, n, a_scale, p.N);
     }
   }
 }
@@ -614,6 +626,187 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
+// ---- at most 128 rows: a stream of the weights ---------------------------------------------------
+// With few rows the GEMM is one pass over W and the question is only how to keep every SM fetching.
+// A tile is p.bn output columns (a multiple of 16, chosen by the host so that the tiles are about
+// one per SM) times ALL of K: no split of K, no partial sums, no workspace. A stage of the ring holds
+// p.kc k-blocks; lanes 0 .. kc - 1 of the loader warp each issue the two TMA loads of one k-block,
+// because one thread gets through only about three loads per microsecond and a 32-column block is
+// just 4 KB. The MMA thread issues 4 p.kc MMAs (M 128, N p.bn, K 32) per stage; an MMA of up to 32
+// columns takes ~46 cycles (measured; 64 -> 48, 128 -> 64, 256 -> 128), so a 32-column tile
+// consumes 22 weight bytes per cycle, just under an SM's share of HBM. p.a_rows = 16 fetches only
+// 16 rows of A per block (the MMA reads 128 rows of shared memory wherever the 16 end: rows of D
+// nobody reads). Roles, barriers and the bounded waits are those of gemm_fp8_kernel.
+constexpr int kStreamMaxStages = 8;
+struct StreamRing {
+  uint64_t full[kStreamMaxStages], empty[kStreamMaxStages], acc_full[kAccs], acc_empty[kAccs];
+  uint32_t tmem_base;
+  int abort;
+};
+constexpr size_t kStreamTileBytes = 192 * 1024;  // the ring
+constexpr size_t kStreamSmemBytes = 1024 + kStreamTileBytes + (kBM - 16) * kBK + 256;
+
+__device__ __forceinline__ bool stream_wait(uint64_t* bar, uint32_t parity, StreamRing* ring, unsigned int* status) {
+  volatile int* ab = &ring->abort;
+  for (uint32_t i = 0; i < kMbarWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*ab) return false;
+    if (i > 256) __nanosleep(64);
+  }
+  *ab = 1;
+  if (status != nullptr) atomicOr(status, kStatusGemmWaitTimeout);
+  return false;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fp8_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                       const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw + 1023u) & ~1023u;
+  StreamRing* ring = reinterpret_cast<StreamRing*>(smem_raw + (tiles_addr - raw) + kStreamTileBytes + (kBM - 16) * kBK);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t a_blk = uint32_t(p.a_rows) * kBK, w_blk = uint32_t(p.bn) * kBK;
+  const uint32_t stage_bytes = uint32_t(p.kc) * (a_blk + w_blk);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) mbar_init(&ring->full[s], 1), mbar_init(&ring->empty[s], 1);
+    for (int a = 0; a < kAccs; ++a) mbar_init(&ring->acc_full[a], 1), mbar_init(&ring->acc_empty[a], 4);
+    ring->abort = 0;
+    mbar_init_fence();
+    fence_async_smem();
+  }
+  if (warp == 1) tmem_alloc<false>(smem_u32(&ring->tmem_base), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ring->tmem_base;
+
+  // Programmatic dependent launch as in the 16-row form of gemm_fp8_kernel: the loader warp fetches
+  // W (a constant of the model) before it waits for the kernel ahead of it on the stream.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (warp != 0) pdl_begin();
+
+  const int tiles = (p.N + p.bn - 1) / p.bn, kblocks = (p.K + kBK - 1) / kBK;
+  const int stages_per_tile = (kblocks + p.kc - 1) / p.kc;
+
+  if (warp == 0) {
+    // stage it (counted over this CTA's tiles) covers k-blocks [kc (it % spt), ...) of tile
+    // blockIdx.x + gridDim.x (it / spt); lane j loads block j of the stage
+    const long long total = (long long)stages_per_tile * ((tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x));
+    auto issue = [&](long long it, bool load_a, bool load_w) {
+      const int t = int(blockIdx.x) + int(gridDim.x) * int(it / stages_per_tile);
+      const int kb = int(it % stages_per_tile) * p.kc + (p.box3d ? 0 : lane), nblk = min(p.kc, kblocks - int(it % stages_per_tile) * p.kc);
+      const uint32_t s = uint32_t(it % p.stages);
+      const uint32_t dst = tiles_addr + s * stage_bytes, bar = smem_u32(&ring->full[s]);
+      if (p.box3d) {  // one box per operand and stage; k-blocks past K are filled with zeros
+        if (lane == 0) {
+          if (load_a) tma_load_3d(dst, &map_a, 0, 0, kb, bar);
+          if (load_w) tma_load_3d(dst + p.kc * a_blk, &map_w, 0, t * p.bn, kb, bar);
+        }
+      } else if (lane < nblk) {
+        if (load_a) tma_load_2d<false>(dst + lane * a_blk, &map_a, kb * kBK, 0, bar);
+        if (load_w) tma_load_2d<false>(dst + p.kc * a_blk + lane * w_blk, &map_w, kb * kBK, t * p.bn, bar);
+      }
+      return nblk;
+    };
+    long long ahead = 0;
+    for (; ahead < total && ahead < p.stages; ++ahead) {  // first use of every stage: it is empty
+      const int nblk = p.box3d ? p.kc : min(p.kc, kblocks - int(ahead % stages_per_tile) * p.kc);
+      if (lane == 0) mbar_arrive_expect_tx(&ring->full[ahead], uint32_t(nblk) * (a_blk + w_blk));
+      __syncwarp();
+      issue(ahead, false, true);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    bool ok = true;
+    for (long long it = 0; it < total && ok; ++it) {
+      if (it < ahead) {
+        issue(it, true, false);
+        continue;
+      }
+      const uint32_t s = uint32_t(it % p.stages), ph = uint32_t(it / p.stages) & 1u;
+      if (lane == 0) ok = stream_wait(&ring->empty[s], ph ^ 1u, ring, p.status);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const int nblk = p.box3d ? p.kc : min(p.kc, kblocks - int(it % stages_per_tile) * p.kc);
+      if (lane == 0) mbar_arrive_expect_tx(&ring->full[s], uint32_t(nblk) * (a_blk + w_blk));
+      __syncwarp();
+      issue(it, true, true);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (uint32_t(p.bn >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+      long long it = 0;
+      uint32_t local = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+        const uint32_t acc = local & 1u, aph = (local >> 1) & 1u;
+        if (!(ok = stream_wait(&ring->acc_empty[acc], aph ^ 1u, ring, p.status))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int st = 0; st < stages_per_tile; ++st, ++it) {
+          const uint32_t s = uint32_t(it % p.stages), ph = uint32_t(it / p.stages) & 1u;
+          if (!(ok = stream_wait(&ring->full[s], ph, ring, p.status))) break;
+          tc_fence_after();
+          const uint32_t base = tiles_addr + s * stage_bytes;
+          const int nblk = min(p.kc, kblocks - st * p.kc);
+          for (int j = 0; j < nblk; ++j) {
+            const uint64_t a_desc = smem_desc_k128(base + j * a_blk), w_desc = smem_desc_k128(base + p.kc * a_blk + j * w_blk);
+#pragma unroll
+            for (int k = 0; k < kBK / 32; ++k)
+              mma_f8<false>(d_tmem, a_desc + uint64_t(2 * k), w_desc + uint64_t(2 * k), idesc, (st | j | k) != 0);
+          }
+          mma_commit<false>(smem_u32(&ring->empty[s]));
+        }
+        if (ok) mma_commit<false>(smem_u32(&ring->acc_full[acc]));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const float a_scale = p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f;
+    uint32_t local = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+      const uint32_t acc = local & 1u, aph = (local >> 1) & 1u;
+      const int n0 = t * p.bn, n_end = min(p.N, n0 + p.bn), row = q * 32 + lane;
+      if (!(ok = stream_wait(&ring->acc_full[acc], aph, ring, p.status))) break;
+      tc_fence_after();
+      if (q * 32 < p.M) {  // uniform over the warp
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * kBN;
+#pragma unroll 1
+        for (int c = 0; n0 + c * 32 < n_end; ++c) {
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld_wait();
+          if (row >= p.M) continue;
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          store_chunk(p, f, row, n0 + c * 32, a_scale, n_end);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ring->acc_empty[acc]));
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (ring->abort) {  // give copies and MMAs already issued a bounded time to land
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<false>(tmem_base, kTmemCols);
+  }
+}
+
 // ---- host ---------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -644,6 +837,16 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, long long ld,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+
+bool box3d_enabled() {
+  const char* v = std::getenv("G4_GEMM_BOX3D");
+  return !(v != nullptr && v[0] == '0');
+}
+
+bool stream_enabled() {
+  const char* v = std::getenv("G4_GEMM_STREAM");  // G4_GEMM_STREAM=0: at most 128 rows take the tiled forms
+  return !(v != nullptr && v[0] == '0');
+}
 
 bool pair_enabled() {
   const char* v = std::getenv("G4_GEMM_PAIR");  // read per call: tests compare the two forms
@@ -728,6 +931,73 @@ SplitPlan plan_split(int M, int N, int K, int sms) {
   return pl;
 }
 
+// Tile width and ring shape of the stream form. A round of tiles over `sms` CTAs costs what its
+// slowest resource costs: the MMA thread (4 MMAs per k-block at ~max(46, bn / 2) cycles) or the SM's
+// share of HBM (bn x K bytes at ~44 bytes per ns); the plan is the width with the cheapest total.
+// Ties go to the wider tile (fewer A blocks and loader steps per weight byte).
+struct StreamPlan {
+  int bn, kc, stages;
+};
+StreamPlan plan_stream(int N, int K, int a_rows, int sms) {
+  const int kblocks = (K + kBK - 1) / kBK;
+  double best = 1e300;
+  StreamPlan pl{kBN, 1, 4};
+  for (int bn = 32; bn <= kBN; bn += 16) {
+    const int tiles = (N + bn - 1) / bn, rounds = (tiles + sms - 1) / sms;
+    const double mma_ns = 4.0 * kblocks * (bn / 2 > 46 ? bn / 2 : 46) / 1.85;
+    const double hbm_ns = double(bn) * K / 44.0;
+    const double cost = rounds * (mma_ns > hbm_ns ? mma_ns : hbm_ns) + 500.0 * rounds;
+    if (cost <= best * 1.0001) best = cost, pl.bn = bn;
+  }
+  const int blk = (a_rows + pl.bn) * kBK;  // bytes of one k-block of a stage
+  pl.kc = 48 * 1024 / blk;
+  pl.kc = pl.kc < 1 ? 1 : (pl.kc > 8 ? 8 : pl.kc);
+  if (pl.kc > kblocks) pl.kc = kblocks;
+  pl.stages = int(kStreamTileBytes / (size_t(pl.kc) * blk));
+  if (pl.stages > kStreamMaxStages) pl.stages = kStreamMaxStages;
+  return pl;
+}
+
+// The same matrix as {128 bytes, rows, K / 128 k-blocks} with a box of kc k-blocks (K % 128 == 0).
+bool make_map3d(CUtensorMap* map, const void* base, int rows, int K, long long ld, int box_rows, int kc) {
+  EncodeTiledFn enc = encode_tiled();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[3] = {cuuint64_t(kBK), cuuint64_t(rows), cuuint64_t(K / kBK)};
+  const cuuint64_t strides[2] = {cuuint64_t(ld), cuuint64_t(kBK)};
+  const cuuint32_t box[3] = {cuuint32_t(kBK), cuuint32_t(box_rows), cuuint32_t(kc)};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_stream(const char* fn, const uint8_t* d_a, long long lda, const uint8_t* d_w, GemmParams p) {
+  p.a_rows = p.M <= 16 ? 16 : kBM;
+  const StreamPlan pl = plan_stream(p.N, p.K, p.a_rows, sm_count());
+  p.bn = pl.bn, p.kc = pl.kc, p.stages = pl.stages;
+  CUtensorMap map_a, map_w;
+  p.box3d = p.K % kBK == 0 && p.kc > 1 && box3d_enabled() && make_map3d(&map_a, d_a, p.M, p.K, lda, p.a_rows, p.kc) &&
+            make_map3d(&map_w, d_w, p.N, p.K, p.K, p.bn, p.kc);
+  if (!p.box3d && (!make_map(&map_a, d_a, p.M, p.K, lda, p.a_rows) || !make_map(&map_w, d_w, p.N, p.K, p.K, p.bn)))
+    return fail(fn, "the tensor map could not be encoded");
+  static std::mutex mu;
+  static std::map<int, cudaError_t> done;
+  int dev = 0;
+  G4_CUDA_TRY(fn, cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.find(dev) == done.end())
+      done[dev] = cudaFuncSetAttribute(gemm_fp8_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(kStreamSmemBytes));
+    G4_CUDA_TRY(fn, done[dev]);
+  }
+  const int tiles = (p.N + p.bn - 1) / p.bn;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  G4_LAUNCH_PDL(fn, gemm_fp8_stream_kernel, dim3(grid), dim3(kThreads), kStreamSmemBytes, current_stream(), map_a,
+                map_w, p);
+  return 0;
+}
+
 // Encodes the two tensor maps of form C and launches it over min(units, SMs) CTAs (CTA pairs).
 template <class C>
 int launch(const char* fn, const uint8_t* d_a, long long lda, const uint8_t* d_w, const GemmParams& p) {
@@ -803,10 +1073,15 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
     if (M <= kBM) return launch<CfgWide>(fn, d_a, lda, d_w, p);  // no split of K under this epilogue
   }
   if (M <= kBM) {
-    p.early = 1;
-    // a stream of the weights: split K where the workspace allows it
+    // A stream of the weights. Measured per layer of four projections (one CUDA graph): the split of
+    // K through the workspace wins at one and two rows (63 us against 70), the full-K stream form
+    // from three rows on (70 us flat up to 16 rows against 74 - 126; 100 - 109 us for 32 - 128 rows
+    // against 121 - 128).
     const SplitPlan pl = plan_split(M, N, K, sm_count());
-    if (pl.splits > 1 && d_ws != nullptr && ws_bytes >= static_cast<long long>(pl.bytes)) {
+    const bool can_split = pl.splits > 1 && d_ws != nullptr && ws_bytes >= static_cast<long long>(pl.bytes);
+    if (stream_enabled() && !(M <= 2 && can_split)) return launch_stream(fn, d_a, lda, d_w, p);
+    p.early = 1;
+    if (can_split) {
       p.splits = pl.splits, p.kb_per = pl.kb_per, p.ws_rows = pl.rows;
       p.counters = static_cast<unsigned int*>(d_ws);
       p.ws = reinterpret_cast<float*>(static_cast<char*>(d_ws) + pl.counter_bytes);

@@ -1773,15 +1773,20 @@ def test_gemm_fp8_rejects_bad_arguments(K):
     assert K.gemm_fp8(a[:0], w, out[:0]) == 0                              # no rows: nothing to do
 
 
-@pytest.mark.parametrize("M,N,Kd", [(1, 6144, 4096), (16, 4096, 1536), (5, 1000, 4096 + 64), (8, 520, 12800)])
-def test_gemm_fp8_decode_rows_split_k_is_deterministic_and_reusable(K, port, M, N, Kd):
-    """At most 16 rows: K is split over CTAs that add their partial sums in a fixed order through
-    the workspace, which is handed from call to call without being cleared again."""
+@pytest.mark.parametrize("stream", ["1", "0"])
+@pytest.mark.parametrize("M,N,Kd", [(1, 6144, 4096), (16, 4096, 1536), (5, 1000, 4096 + 64), (8, 520, 12800),
+                                    (2, 4096, 4096), (40, 1000, 2048), (128, 6144, 1024)])
+def test_gemm_fp8_decode_rows_split_k_is_deterministic_and_reusable(K, port, monkeypatch, M, N, Kd, stream):
+    """At most 128 rows, both ways of streaming the weights. stream = 1: full-K tiles of a planned
+    width (3-D TMA boxes where K is a multiple of 128; one and two rows still split K). stream = 0:
+    256-column tiles, and up to 16 rows K split over CTAs that add their partial sums in a fixed
+    order through the workspace, which is handed from call to call without being cleared again."""
+    monkeypatch.setenv("G4_GEMM_STREAM", stream)
     rng = np.random.default_rng(N + Kd)
     a, w = _codes(rng, (M, Kd)), _codes(rng, (N, Kd))
     res = rand_bf16(M, (M, N))
     ws = K.gemm_fp8_workspace(M, N, Kd, DEV)
-    assert ws is not None  # these shapes have too few tiles for the SMs
+    assert ws is not None or M > 16  # up to 16 rows these shapes have too few tiles for the SMs
     exact, mag = _gemm_f64(a, w, 0.3, (0.01,), (), N)
     a_scale = torch.tensor([0.3, 0.0], device=DEV)
     f32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
