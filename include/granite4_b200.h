@@ -571,7 +571,7 @@ int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq
  * granite4_kernel_fp8_encode_with_amax turns a into FP8 codes in one sweep;
  * the 4 I bytes per row of gate|up output never exist.
  * Needs K % 16 == 0, lda % 16 == 0, 16-byte aligned A and W; any M >= 0, any N.
- * d_ws / ws_bytes, as the ws / ws_bytes of prefill_gemm: with at most 128 rows a
+ * d_ws / ws_bytes, as the ws / ws_bytes of prefill_gemm: with one or two rows a
  * GEMM has too few output tiles to occupy the card and splits K across CTAs,
  * which add their partial sums in a fixed order (the result does not depend on
  * scheduling). granite4_gemm_fp8_workspace_bytes(M, N, K) is the size that
