@@ -640,6 +640,10 @@ def small_shapes_and_embed(seq, rows, device, stream):
                                   "bytes_per_row_unfused": 2 * (2 * I) + 9 * I, "bytes_per_row_fused": 2 * I + 3 * I}
     del gu_o, act_b, act_8
     wbytes = sum(N * Kd for _, N, Kd in proj)
+    # the prefill projections above ran under the power cap; a decode step does not follow such a burst,
+    # so let the clocks come back before the latency-sized measurements
+    torch.cuda.synchronize()
+    time.sleep(1.0)
     for n in (1, 8):
         outs = {name: torch.empty(n, N, dtype=torch.bfloat16, device=device) for name, N, _ in proj}
         wsp = {name: k.gemm_fp8_workspace(n, N, Kd, device) for name, N, Kd in proj}
