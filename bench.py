@@ -735,7 +735,53 @@ def small_shapes_and_embed(seq, rows, device, stream):
         full[f"sessions_{n}"] = {"layers": 2, "launches": count[0], "graph_replay_us": us, "weight_bytes": wb,
                                  "weight_gbs": wb / (us * 1e-6) / 1e9, "frac": wb / (us * 1e-6) / 1e9 / peak}
     gemm["decode_step_two_layers_lm_head"] = full
-    del ck, cv, ksc, vsc, w_lm, logits
+    del w_lm, logits
+
+    # One whole prefill layer on device buffers only (the first chunk of a prompt, positions 0..n-1):
+    # norm -> FP8, QKV GEMM, RoPE + int8 KV write, causal attention over the pool, FP8 of its output,
+    # O GEMM + residual, norm -> FP8, gate|up GEMM with the fused SwiGLU epilogue, one-sweep encode,
+    # down GEMM + residual. Event-timed per step to show where a layer's time goes.
+    layer = {}
+    for n_pf in (2048, 8192):
+        if n_pf > stride_d:
+            continue
+        hid = torch.randn(n_pf, H, generator=g, device=device).to(torch.bfloat16)
+        nf8 = torch.empty(n_pf, H, dtype=torch.uint8, device=device)
+        a8 = torch.empty(n_pf, H, dtype=torch.uint8, device=device)
+        qkv = torch.empty(n_pf, QKV, dtype=torch.bfloat16, device=device)
+        qr = torch.empty(n_pf, H, dtype=torch.bfloat16, device=device)
+        ao = torch.empty_like(qr)
+        act_b = torch.empty(n_pf, I, dtype=torch.bfloat16, device=device)
+        act8 = torch.empty(n_pf, I, dtype=torch.uint8, device=device)
+        sc = torch.zeros(4, 2, dtype=torch.float32, device=device)
+        pos = torch.arange(n_pf, dtype=torch.int32, device=device)
+        ws_ = wsets[0]
+        steps = (
+            ("norm_fp8", lambda: k.add_rmsnorm_fp8(hid, None, wn[0], s.eps, s.residual_multiplier, n_fp8=nf8, scale_amax=sc[0])),
+            ("qkv_gemm", lambda: k.gemm_fp8(nf8, ws_["qkv"], qkv, a_scale=sc[0], w_scales=(0.01,))),
+            ("rope_kv", lambda: k.rope_kv_int8_paged(qkv, seq.tables.cos, seq.tables.sin, pos, pos, s.q_heads, s.kv_heads,
+                                                      s.head_dim, stride_d, seq.max_pos, 0, qr, ck, cv, ksc, vsc)),
+            ("attention", lambda: k.prefill_attention_int8(qr, 1.0 / 128, s.q_heads, s.kv_heads, s.head_dim, 0, stride_d, ao,
+                                                           ck, cv, ksc, vsc)),
+            ("attn_fp8", lambda: k.fp8_quant(ao, a8, sc[1])),
+            ("o_gemm_residual", lambda: k.gemm_fp8(a8, ws_["o"], hid, a_scale=sc[1], w_scales=(0.01,), residual=hid,
+                                                   resid_scale=s.residual_multiplier)),
+            ("norm_fp8_2", lambda: k.add_rmsnorm_fp8(hid, None, wn[1], s.eps, s.residual_multiplier, n_fp8=nf8, scale_amax=sc[2])),
+            ("gate_up_gemm_swiglu", lambda: k.gemm_fp8(nf8, ws_["gate_up"], act_b, a_scale=sc[2], w_scales=(0.01,),
+                                                       swiglu_scale_amax=sc[3])),
+            ("act_fp8_encode", lambda: k.fp8_encode_with_amax(act_b, act8, sc[3])),
+            ("down_gemm_residual", lambda: k.gemm_fp8(act8, ws_["down"], hid, a_scale=sc[3], w_scales=(0.0001,), residual=hid,
+                                                      resid_scale=s.residual_multiplier)),
+        )
+
+        def whole():
+            for _, fn in steps:
+                fn()
+        total = timed(whole, 5)
+        per = {name: timed(fn, 5) for name, fn in steps}
+        layer[f"rows_{n_pf}"] = {"total_us": total, "steps_us": per}
+    gemm["prefill_layer"] = layer
+    del ck, cv, ksc, vsc
     del wsets, a_h, a_i
     torch.cuda.empty_cache()
     return {"embed": embed, "small": small, "argmax": argmax, "attention": attention, "decode_step": decode_step,

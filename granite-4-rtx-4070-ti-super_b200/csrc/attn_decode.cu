@@ -540,6 +540,13 @@ SplitPlan plan_splits(int rows, int group_rows, int Hk, int max_len) {
 extern "C" long long granite4_attn_decode_scratch_bytes(int rows, int rows_per_group, int Hk, int max_len);
 
 namespace g4 {
+// csrc/attn_prefill.cu
+int attn_prefill_flash(const char* fn, const uint16_t* d_q, float scale, int Hq, int Hk, int base_pos, int rows,
+                       int stride, uint16_t* d_out, const int8_t* d_ck, const int8_t* d_cv, const float* d_ks,
+                       const float* d_vs, const int* d_pt);
+}  // namespace g4
+
+namespace g4 {
 // Validation, split plan and launches shared by the entry points. d_row_pos NULL: row r is at
 // base_pos + r. single_split_without_scratch: a caller that has no scratch to give (the reference's
 // prefill signature) gets one split over the whole range instead of an error.
@@ -631,6 +638,20 @@ int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq
                                     const int* d_pt, void* d_scratch, long long scratch_bytes) {
   const char* fn = "granite4_prefill_attention_int8";
   if (base_pos < 0 || rows <= 0 || base_pos > INT_MAX - rows) return g4::fail(fn, "invalid arguments");
+  // A chunk of 32 rows or more takes the flash form (one K / V tile serves 16 positions x 4 heads);
+  // shorter ones the decode kernel as groups of four rows, which can also split a long context
+  // over CTAs. G4_PREFILL_FLASH=0 keeps every chunk on the decode kernel.
+  const char* flash_env = std::getenv("G4_PREFILL_FLASH");
+  if (rows >= 32 && !(flash_env != nullptr && flash_env[0] == '0')) {
+    if (d_q_rot == nullptr || d_cache_k8 == nullptr || d_cache_v8 == nullptr || d_k_scale == nullptr ||
+        d_v_scale == nullptr || d_out == nullptr || stride <= 0 || base_pos + rows > stride || !std::isfinite(scale))
+      return g4::fail(fn, "invalid arguments");
+    if (d != g4::kAD || Hk <= 0 || Hq != g4::kGqa * Hk) return -1;  // engine/src/attention_gpu.h:18-19
+    if (!g4::aligned16(d_cache_k8) || !g4::aligned16(d_cache_v8) || !g4::aligned16(d_q_rot))
+      return g4::fail(fn, "q and the caches must be 16-byte aligned");
+    return g4::attn_prefill_flash(fn, d_q_rot, scale, Hq, Hk, base_pos, rows, stride, d_out, d_cache_k8, d_cache_v8,
+                                  d_k_scale, d_v_scale, d_pt);
+  }
   return g4::attn_launch(fn, d_q_rot, d_cache_k8, d_cache_v8, d_k_scale, d_v_scale, nullptr, base_pos, nullptr, d_pt,
                          rows, g4::kGroupRows, Hq, Hk, d, stride, base_pos + rows, scale, d_scratch, scratch_bytes,
                          d_out, true);
