@@ -521,8 +521,8 @@ def small_shapes_and_embed(seq, rows, device, stream):
         nbytes = groups * s.kv_heads * ctx * (2 * s.head_dim + 8)
         attention[name] = {"mean_us": us, "achieved_gbs": nbytes / (us * 1e-6) / 1e9,
                            "frac": nbytes / (us * 1e-6) / 1e9 / peak, "bytes": nbytes}
-    # Causal attention of a whole prefill chunk on the same kernels (groups of four rows, each
-    # reading its own prefix; K/V of the chunk stay in L2): 4 d Hq n^2 / 2 flops.
+    # Causal attention of a whole prefill chunk (the flash kernel over the same pool; K/V of the chunk
+    # stay in L2): 4 d Hq n^2 / 2 flops.
     for n_pf in (2048, 8192):
         qa = torch.randn(n_pf, s.q_heads * s.head_dim, generator=g, device=device).to(torch.bfloat16)
         oa = torch.empty_like(qa)
@@ -530,7 +530,7 @@ def small_shapes_and_embed(seq, rows, device, stream):
                                                     ck, cv, ksc, vsc, pt=table), 5)
         flops = 4.0 * s.head_dim * s.q_heads * n_pf * (n_pf + 1) / 2
         attention[f"prefill_{n_pf}_rows"] = {"mean_us": us, "tflops": flops / (us * 1e-6) / 1e12,
-                                             "kv_bytes_read_per_group_of_4": "prefix x 2112 B"}
+                                             "form": "flash, 32 positions x 4 heads per CTA"}
         del qa, oa
     # A whole decode step (one layer's glue + attention at ~4096 positions + final norm + greedy
     # pick with the token scatter folded in) of n sessions, captured into a CUDA graph and replayed: everything that

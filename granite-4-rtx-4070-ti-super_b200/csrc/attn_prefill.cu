@@ -30,6 +30,7 @@
 #include <climits>
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 
 #include "g4_host.h"
 #include "g4_math.cuh"
@@ -281,6 +282,206 @@ __global__ void __launch_bounds__(kPfWarps * 32, 3) attn_prefill_kernel(const Pr
   }
 }
 
+// The same with 32 query positions per CTA: every warp owns two 16-row tiles of its head, so a K or V
+// fragment fetched from shared memory feeds four MMAs instead of two and the conversion is shared by 128
+// query rows. The accumulators of two tiles leave no registers for Q and a 64-column S, so Q (fp16) lives
+// in shared memory and a tile of 64 positions is consumed as two halves of 32.
+constexpr int kQRows2 = 32;
+struct PrefillSmem2 {
+  PrefillSmem t;
+  __half qh[kPfWarps][kQRows2][kHPitch];
+};
+
+__global__ void __launch_bounds__(kPfWarps * 32, 2) attn_prefill2_kernel(const PrefillParams p) {
+  extern __shared__ __align__(16) unsigned char pf_smem[];
+  PrefillSmem2& sm2 = *reinterpret_cast<PrefillSmem2*>(pf_smem);
+  PrefillSmem& sm = sm2.t;
+  pdl_begin();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int qb = static_cast<int>(gridDim.x - 1 - blockIdx.x);
+  const int hkv = blockIdx.y, head = hkv * kPfWarps + warp;
+  const int r0 = qb * kQRows2;
+  const int nrows = min(kQRows2, p.rows - r0);
+  const int kv_len = p.base_pos + r0 + nrows;
+  const int ntiles = (kv_len + kTileP - 1) / kTileP;
+  const size_t head_row0 = static_cast<size_t>(hkv) * p.stride;
+  int pos_row[2][2];  // [tile of 16 rows][row g / g + 8]
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) pos_row[mt][e] = p.base_pos + r0 + min(mt * 16 + g + 8 * e, nrows - 1);
+
+  const int crow = tid >> 1, chalf = tid & 1;
+  auto gather = [&](int stage, int tile) {
+    const int pos = tile * kTileP + crow;
+    const bool have = pos < kv_len;
+    int prow = have ? (p.pt != nullptr ? __ldg(p.pt + pos) : pos) : 0;
+    prow = min(max(prow, 0), static_cast<int>(p.stride) - 1);
+    const size_t off = (head_row0 + prow) * kD + chalf * 64;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      pf_cp16(&sm.raw_k[stage][crow][chalf * 64 + 16 * i], p.ck + off + 16 * i, have);
+      pf_cp16(&sm.raw_v[stage][crow][chalf * 64 + 16 * i], p.cv + off + 16 * i, have);
+    }
+    if (chalf == 0) pf_cp4(&sm.ks[stage][crow], p.ks + head_row0 + prow, have);
+    else pf_cp4(&sm.vs[stage][crow], p.vs + head_row0 + prow, have);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  gather(0, 0);
+
+  // this warp's 32 Q rows -> fp16 in shared memory (rows past the chunk repeat the last row)
+  for (int i = lane; i < kQRows2 * (kD / 8); i += 32) {
+    const int row = i >> 4, piece = i & 15;
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(r0 + min(row, nrows - 1)) * p.Hq + head) * kD) + piece);
+    uint4 h;
+    h.x = pf_pack(bf16_lo(w.x), bf16_hi(w.x)), h.y = pf_pack(bf16_lo(w.y), bf16_hi(w.y));
+    h.z = pf_pack(bf16_lo(w.z), bf16_hi(w.z)), h.w = pf_pack(bf16_lo(w.w), bf16_hi(w.w));
+    *reinterpret_cast<uint4*>(&sm2.qh[warp][row][piece * 8]) = h;
+  }
+  __syncwarp();
+
+  float o[2][16][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nb = 0; nb < 16; ++nb) o[mt][nb][0] = o[mt][nb][1] = o[mt][nb][2] = o[mt][nb][3] = 0.0f;
+  float m_run[2][2], l_run[2][2];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) m_run[mt][0] = m_run[mt][1] = -INFINITY, l_run[mt][0] = l_run[mt][1] = 0.0f;
+
+  for (int tile = 0; tile < ntiles; ++tile) {
+    const int stage = tile & 1;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (tile + 1 < ntiles) gather(stage ^ 1, tile + 1);
+#pragma unroll
+    for (int it = 0; it < kTileP * 16 / (kPfWarps * 32); ++it) {
+      const int item = it * (kPfWarps * 32) + tid, row = item >> 4, piece = item & 15;
+      const uint2 rk = *reinterpret_cast<const uint2*>(&sm.raw_k[stage][row][piece * 8]);
+      const uint2 rv = *reinterpret_cast<const uint2*>(&sm.raw_v[stage][row][piece * 8]);
+      const __half2 vs2 = __float2half2_rn(sm.vs[stage][row]);
+      __half2 kh2[4], vh2[4];
+      pf_codes4(rk.x, kh2[0], kh2[1]), pf_codes4(rk.y, kh2[2], kh2[3]);
+      pf_codes4(rv.x, vh2[0], vh2[1]), pf_codes4(rv.y, vh2[2], vh2[3]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) vh2[j] = __hmul2(vh2[j], vs2);
+      *reinterpret_cast<uint4*>(&sm.kh[row][piece * 8]) = *reinterpret_cast<const uint4*>(&kh2[0]);
+      *reinterpret_cast<uint4*>(&sm.vh[row][piece * 8]) = *reinterpret_cast<const uint4*>(&vh2[0]);
+    }
+    if (tid < kTileP) sm.ks[stage][tid] *= p.scale_log2;
+    __syncthreads();
+
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {  // 32 positions at a time
+      const int c0 = tile * kTileP + half * 32;
+      if (c0 >= kv_len) break;  // uniform over the CTA
+      // ---- S = Q K^T: two 16 x 32 tiles; a K fragment serves both
+      float s[2][4][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < 8; kk += 2) {
+        uint32_t qa[2][2][4];  // [row tile][k-step kk, kk + 1]
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int u = 0; u < 2; ++u)
+            pf_ldmatrix_x4(qa[mt][u], &sm2.qh[warp][mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][(kk + u) * 16 + (lane >> 4) * 8]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t b[4];
+          pf_ldmatrix_x4(b, &sm.kh[half * 32 + j * 8 + (lane & 7)][kk * 16 + (lane >> 3) * 8]);
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            pf_mma(s[mt][j], qa[mt][0], b[0], b[1]);
+            pf_mma(s[mt][j], qa[mt][1], b[2], b[3]);
+          }
+        }
+      }
+      // ---- scale, mask, online softmax; P fragments
+      const bool diag = c0 + 31 > p.base_pos + r0;
+      uint32_t pa[2][2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = *reinterpret_cast<const float2*>(&sm.ks[stage][half * 32 + j * 8 + 2 * t]);
+          s[mt][j][0] *= f.x, s[mt][j][1] *= f.y, s[mt][j][2] *= f.x, s[mt][j][3] *= f.y;
+          if (diag) {
+            const int col = c0 + j * 8 + 2 * t;
+            if (col > pos_row[mt][0]) s[mt][j][0] = -INFINITY;
+            if (col + 1 > pos_row[mt][0]) s[mt][j][1] = -INFINITY;
+            if (col > pos_row[mt][1]) s[mt][j][2] = -INFINITY;
+            if (col + 1 > pos_row[mt][1]) s[mt][j][3] = -INFINITY;
+          }
+          mx[0] = fmaxf(mx[0], fmaxf(s[mt][j][0], s[mt][j][1]));
+          mx[1] = fmaxf(mx[1], fmaxf(s[mt][j][2], s[mt][j][3]));
+        }
+        float corr[2], base[2], rsum[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
+          mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 2));
+          const float m_new = fmaxf(m_run[mt][e], mx[e]);
+          corr[e] = m_new == -INFINITY ? 1.0f : pf_ex2(m_run[mt][e] - m_new);
+          base[e] = m_new == -INFINITY ? 0.0f : m_new;
+          m_run[mt][e] = m_new;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float p0 = pf_ex2(s[mt][j][0] - base[0]), p1 = pf_ex2(s[mt][j][1] - base[0]);
+          const float p2 = pf_ex2(s[mt][j][2] - base[1]), p3 = pf_ex2(s[mt][j][3] - base[1]);
+          rsum[0] += p0 + p1, rsum[1] += p2 + p3;
+          pa[mt][j >> 1][(j & 1) * 2] = pf_pack(p0, p1);
+          pa[mt][j >> 1][(j & 1) * 2 + 1] = pf_pack(p2, p3);
+        }
+        l_run[mt][0] = l_run[mt][0] * corr[0] + rsum[0], l_run[mt][1] = l_run[mt][1] * corr[1] + rsum[1];
+        if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+          for (int nb = 0; nb < 16; ++nb)
+            o[mt][nb][0] *= corr[0], o[mt][nb][1] *= corr[0], o[mt][nb][2] *= corr[1], o[mt][nb][3] *= corr[1];
+        }
+      }
+      // ---- O += P V: a V fragment serves both row tiles
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+        for (int nb = 0; nb < 16; nb += 2) {
+          uint32_t b[4];
+          pf_ldmatrix_x4_trans(b, &sm.vh[half * 32 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][nb * 8 + (lane >> 4) * 8]);
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            pf_mma(o[mt][nb], pa[mt][kk], b[0], b[1]);
+            pf_mma(o[mt][nb + 1], pa[mt][kk], b[2], b[3]);
+          }
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      l_run[mt][e] += __shfl_xor_sync(0xffffffffu, l_run[mt][e], 1);
+      l_run[mt][e] += __shfl_xor_sync(0xffffffffu, l_run[mt][e], 2);
+    }
+    const float inv_a = l_run[mt][0] > 0.0f ? 1.0f / l_run[mt][0] : 0.0f;
+    const float inv_b = l_run[mt][1] > 0.0f ? 1.0f / l_run[mt][1] : 0.0f;
+    const int ra = mt * 16 + g, rb = ra + 8;
+    uint16_t* out_a = p.out + (static_cast<size_t>(r0 + ra) * p.Hq + head) * kD + 2 * t;
+    uint16_t* out_b = p.out + (static_cast<size_t>(r0 + rb) * p.Hq + head) * kD + 2 * t;
+#pragma unroll
+    for (int nb = 0; nb < 16; ++nb) {
+      if (ra < nrows) *reinterpret_cast<uint32_t*>(out_a + nb * 8) = pack_bf16x2(o[mt][nb][0] * inv_a, o[mt][nb][1] * inv_a);
+      if (rb < nrows) *reinterpret_cast<uint32_t*>(out_b + nb * 8) = pack_bf16x2(o[mt][nb][2] * inv_b, o[mt][nb][3] * inv_b);
+    }
+  }
+}
+
 }  // namespace
 
 // Launch of the flash form for a whole chunk; arguments as granite4_prefill_attention_int8 (validated there).
@@ -293,12 +494,20 @@ int attn_prefill_flash(const char* fn, const uint16_t* d_q, float scale, int Hq,
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(sizeof(PrefillSmem))));
+    G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_prefill2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(sizeof(PrefillSmem2))));
     attr_set[dev] = true;
   }
   PrefillParams p{};
   p.q = d_q, p.ck = d_ck, p.cv = d_cv, p.ks = d_ks, p.vs = d_vs, p.pt = d_pt, p.out = d_out;
   p.rows = rows, p.base_pos = base_pos, p.Hq = Hq, p.Hk = Hk, p.stride = stride;
   p.scale_log2 = scale * 1.4426950408889634f;
+  const char* v = std::getenv("G4_PREFILL_ROWS32");  // 0: 16 query positions per CTA
+  if (!(v != nullptr && v[0] == '0')) {
+    const dim3 grid(static_cast<unsigned>((rows + kQRows2 - 1) / kQRows2), static_cast<unsigned>(Hk));
+    G4_LAUNCH_PDL(fn, attn_prefill2_kernel, grid, dim3(kPfWarps * 32), sizeof(PrefillSmem2), current_stream(), p);
+    return 0;
+  }
   const dim3 grid(static_cast<unsigned>((rows + kQRows - 1) / kQRows), static_cast<unsigned>(Hk));
   G4_LAUNCH_PDL(fn, attn_prefill_kernel, grid, dim3(kPfWarps * 32), sizeof(PrefillSmem), current_stream(), p);
   return 0;

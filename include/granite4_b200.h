@@ -536,11 +536,11 @@ long long granite4_host_glue_d2h_bytes(const granite4_host_glue* ctx, int rows);
  * as a C entry point: causal attention of the query rows at positions
  * [base_pos, base_pos + rows) of ONE sequence (d_q_rot [rows][Hq 128] bf16, as
  * the RoPE kernels write it) over cache positions [0, position], position t in
- * pool row d_pt[t] (NULL: t). It runs on the decode kernel as groups of four
- * consecutive rows, each reading its own causal prefix: the same arithmetic
- * as a flash kernel, K/V re-read once per group (from L2 for chunks whose K/V
- * fit there). d_scratch / scratch_bytes: optional,
- * granite4_attn_decode_scratch_bytes(rows, 4, Hk, base_pos + rows) bytes let a
+ * pool row d_pt[t] (NULL: t). Chunks of 32 rows or more run as a flash kernel
+ * (32 query positions x 4 heads per CTA share each K / V tile; no scratch);
+ * shorter ones on the decode kernel as groups of four consecutive rows, where
+ * d_scratch / scratch_bytes (optional,
+ * granite4_attn_decode_scratch_bytes(rows, 4, Hk, base_pos + rows) bytes) let a
  * short chunk at a long context split the context over CTAs; without it the
  * range is walked in one piece. -1 as granite4_kernel_attn_decode_int8_paged. */
 int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq, int Hk, int d,
