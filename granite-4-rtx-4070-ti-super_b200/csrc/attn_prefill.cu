@@ -201,11 +201,14 @@ __global__ void __launch_bounds__(kPfWarps * 32, 3) attn_prefill_kernel(const Pr
 #pragma unroll
     for (int kk = 0; kk < 8; kk += 2) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint32_t b[4];
-        pf_ldmatrix_x4(b, &sm.kh[j * 8 + (lane & 7)][kk * 16 + (lane >> 3) * 8]);
-        pf_mma(s[j], qa[kk], b[0], b[1]);
-        pf_mma(s[j], qa[kk + 1], b[2], b[3]);
+      for (int jj = 0; jj < 8; jj += 4) {  // four fragments in flight; no two consecutive MMAs share an accumulator
+        uint32_t b[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pf_ldmatrix_x4(b[j], &sm.kh[(jj + j) * 8 + (lane & 7)][kk * 16 + (lane >> 3) * 8]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pf_mma(s[jj + j], qa[kk], b[j][0], b[j][1]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pf_mma(s[jj + j], qa[kk + 1], b[j][2], b[j][3]);
       }
     }
 
@@ -390,15 +393,15 @@ __global__ void __launch_bounds__(kPfWarps * 32, 2) attn_prefill2_kernel(const P
           for (int u = 0; u < 2; ++u)
             pf_ldmatrix_x4(qa[mt][u], &sm2.qh[warp][mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][(kk + u) * 16 + (lane >> 4) * 8]);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t b[4];
-          pf_ldmatrix_x4(b, &sm.kh[half * 32 + j * 8 + (lane & 7)][kk * 16 + (lane >> 3) * 8]);
+        uint32_t b[4][4];
 #pragma unroll
-          for (int mt = 0; mt < 2; ++mt) {
-            pf_mma(s[mt][j], qa[mt][0], b[0], b[1]);
-            pf_mma(s[mt][j], qa[mt][1], b[2], b[3]);
-          }
-        }
+        for (int j = 0; j < 4; ++j) pf_ldmatrix_x4(b[j], &sm.kh[half * 32 + j * 8 + (lane & 7)][kk * 16 + (lane >> 3) * 8]);
+#pragma unroll
+        for (int u = 0; u < 2; ++u)  // no two consecutive MMAs share an accumulator
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) pf_mma(s[mt][j], qa[mt][u], b[j][2 * u], b[j][2 * u + 1]);
       }
       // ---- scale, mask, online softmax; P fragments
       const bool diag = c0 + 31 > p.base_pos + r0;
