@@ -312,7 +312,7 @@ void g4o_argmax_rows(const uint16_t* logits, long rows, int V, int32_t* out) {
 }
 
 /* ------------------------------------------------------------------------ */
-/* Decode attention over the int8 pool (checker for the "next" row f1)        */
+/* Decode attention over the int8 pool                                        */
 /* ------------------------------------------------------------------------ */
 /* The reference's golden pipeline, engine/src/kernel_math.h:265-331, on cache rows
  * dequantised the way its kernels do (engine/src/attention_split.cu:229-234:
@@ -368,7 +368,7 @@ void g4o_attn_decode_int8(const uint16_t* q, const int8_t* ck, const int8_t* cv,
 }
 
 /* ------------------------------------------------------------------------ */
-/* FP8 x FP8 GEMM (checker for the "next" row f2)                             */
+/* FP8 x FP8 GEMM                                                            */
 /* ------------------------------------------------------------------------ */
 void g4o_gemm_fp8(const uint8_t* a, long lda, const uint8_t* w, long M, long N, long K,
                   float a_scale, float s0, float s1, float s2, long seg1, long seg2, int out_kind,
