@@ -1033,6 +1033,7 @@ int launch(const char* fn, const uint8_t* d_a, long long lda, const uint8_t* d_w
 
 extern "C" long long granite4_gemm_fp8_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M > 2 && stream_enabled()) return 0;  // the stream form needs none
   return static_cast<long long>(plan_split(M, N, K, sm_count()).bytes);
 }
 

@@ -575,7 +575,7 @@ int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq
  * GEMM has too few output tiles to occupy the card and splits K across CTAs,
  * which add their partial sums in a fixed order (the result does not depend on
  * scheduling). granite4_gemm_fp8_workspace_bytes(M, N, K) is the size that
- * allows the planned split (0: none wanted); the buffer must be zeroed once
+ * allows the planned split (0: none wanted, e.g. from three rows on); the buffer must be zeroed once
  * before its first use (every call leaves its first bytes, the tile counters,
  * zero again) and belongs to one call at a time. NULL or a smaller buffer: no
  * split. d_w must not be written by the operation just before this call on

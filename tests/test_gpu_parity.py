@@ -1786,7 +1786,7 @@ def test_gemm_fp8_decode_rows_split_k_is_deterministic_and_reusable(K, port, mon
     a, w = _codes(rng, (M, Kd)), _codes(rng, (N, Kd))
     res = rand_bf16(M, (M, N))
     ws = K.gemm_fp8_workspace(M, N, Kd, DEV)
-    assert ws is not None or M > 16  # up to 16 rows these shapes have too few tiles for the SMs
+    assert ws is not None or M > (2 if stream == "1" else 16)  # no workspace is wanted where no form would use one
     exact, mag = _gemm_f64(a, w, 0.3, (0.01,), (), N)
     a_scale = torch.tensor([0.3, 0.0], device=DEV)
     f32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
