@@ -1775,7 +1775,7 @@ def test_gemm_fp8_rejects_bad_arguments(K):
 
 @pytest.mark.parametrize("stream", ["1", "0"])
 @pytest.mark.parametrize("M,N,Kd", [(1, 6144, 4096), (16, 4096, 1536), (5, 1000, 4096 + 64), (8, 520, 12800),
-                                    (2, 4096, 4096), (40, 1000, 2048), (128, 6144, 1024)])
+                                    (2, 4096, 4096), (40, 1000, 2048), (128, 6144, 1024), (40, 520, 4096 + 64)])
 def test_gemm_fp8_decode_rows_split_k_is_deterministic_and_reusable(K, port, monkeypatch, M, N, Kd, stream):
     """At most 128 rows, both ways of streaming the weights. stream = 1: full-K tiles of a planned
     width (3-D TMA boxes where K is a multiple of 128; one and two rows still split K). stream = 0:
