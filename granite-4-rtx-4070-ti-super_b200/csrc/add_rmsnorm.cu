@@ -432,6 +432,36 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The same for a decode-size tensor (up to 16 rows of 4096): one CTA keeps the tensor in registers,
+// finds max |x| through shared memory and encodes - one launch instead of a memset and two sweeps.
+constexpr int kQuantSmallThreads = 1024, kQuantSmallItems = 8;
+__global__ void __launch_bounds__(kQuantSmallThreads)
+    quant_small_kernel(const uint4* x, int n8, uint2* codes, float* scale_amax) {
+  pdl_begin();
+  __shared__ uint32_t s[kQuantSmallThreads / 32];
+  uint4 v[kQuantSmallItems];
+  uint32_t amax = 0u;
+#pragma unroll
+  for (int k = 0; k < kQuantSmallItems; ++k) {
+    const int i = k * kQuantSmallThreads + threadIdx.x;
+    v[k] = i < n8 ? __ldg(x + i) : make_uint4(0, 0, 0, 0);
+    amax = amax_acc(amax, v[k]);
+  }
+  amax = amax_warp(amax);
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  uint32_t m = s[threadIdx.x & 31];
+  m = amax_warp(m);
+  const float a = amax_value(m);
+  const Fp8Scale fs = fp8_scale_from_amax(a);
+  if (threadIdx.x == 0) scale_amax[0] = fs.scale, scale_amax[1] = a;
+#pragma unroll
+  for (int k = 0; k < kQuantSmallItems; ++k) {
+    const int i = k * kQuantSmallThreads + threadIdx.x;
+    if (i < n8) codes[i] = fp8x8_quant(v[k], fs);
+  }
+}
+
 int env_int(const char* name, int fallback) {
   const char* v = std::getenv(name);
   return (v != nullptr && *v != '\0') ? std::atoi(v) : fallback;
@@ -621,6 +651,12 @@ int granite4_kernel_fp8_quant(const uint16_t* d_x, long long n, uint8_t* d_codes
   const long long n8 = n / 8;
   const long long grid = g4::quant_grid(n8);
   if (grid > INT_MAX) return g4::fail(fn, "tensor too large");
+  if (n8 <= g4::kQuantSmallThreads * g4::kQuantSmallItems && g4::cluster_enabled()) {  // G4_CLUSTER=0: the two-sweep form
+    G4_LAUNCH_PDL(fn, g4::quant_small_kernel, dim3(1), dim3(g4::kQuantSmallThreads), 0, st,
+                  reinterpret_cast<const uint4*>(d_x), static_cast<int>(n8), reinterpret_cast<uint2*>(d_codes),
+                  d_scale_amax);
+    return 0;
+  }
   G4_CUDA_TRY(fn, cudaMemsetAsync(d_scale_amax, 0, 2 * sizeof(float), st));
   G4_LAUNCH_PDL(fn, g4::amax_bf16_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, st,
                 reinterpret_cast<const uint4*>(d_x), n8, d_scale_amax);

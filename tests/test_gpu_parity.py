@@ -273,6 +273,14 @@ def test_fp8_quant_matches_oracle_including_double_rounding_cases(K, port):
     cz = torch.empty(64, dtype=torch.uint8, device=DEV)
     assert K.fp8_quant(dev(zb), cz, sa) == 0
     assert sa[0].item() == 0.0 and host(cz)[1] == 0x80 and host(cz)[0] == 0
+    # decode-size tensors (one launch, the tensor in the registers of one CTA): same codes and scale
+    for m in (4096, 8 * 4096 + 64, 16 * 4096):
+        sub = bits[1000:1000 + m]
+        cw, sw, aw = port.quant_fp8(sub)
+        cs = torch.empty(m, dtype=torch.uint8, device=DEV)
+        sa.fill_(7.0)
+        assert K.fp8_quant(dev(sub), cs, sa) == 0
+        assert sa[1].item() == aw and sa[0].item() == sw and (host(cs) == cw).all()
 
 
 # =========================================================================== a3 RoPE + paged KV
