@@ -14,6 +14,12 @@ prints ONE JSON line (rank 0). `value` is whole-job tokens/s with inputs residen
 sequence through the host-buffer C-ABI entry point (host<->device copies inside the timed
 region); `cpu_baseline` is the reference's CPU formulation on this box's cores.
 `--impl reference` times only that CPU formulation and prints the reference arm's line.
+After the timed regions every rank's outputs are checked (`check` in the line): the ranks
+all_gather a fingerprint of what their last step left behind, and rank 0 rebuilds every other
+rank's shard from its seed, runs it alone and compares bit for bit.
+`--sweep-only` leaves out the other shapes (short profiler captures); `--traffic-from-ncu CSV`
+is a converter, not a benchmark: it condenses an ncu raw CSV into the DRAM-traffic file the
+roofline's `traffic` is read from.
 """
 from __future__ import annotations
 
@@ -306,22 +312,27 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     status = capi.lib().device_status()
 
     # ---- the embedding gather (a1; not part of the sweep) and the small, latency-bound shapes ----
-    extras = small_shapes_and_embed(seq, rows, device, stream) if rank == 0 else None
+    extras = small_shapes_and_embed(seq, rows, device, stream) if rank == 0 and not args.sweep_only else None
 
     # ---- end to end through the host-buffer entry points ------------------------------------
     e2e = None
     if not args.no_e2e:
-        e2e_ms, h2d, d2h, e2e_steps = run_e2e(seq, rows, device, min(args.steps, 2))
-        e2e_ms = max_over_ranks(e2e_ms, device)
+        e2e_ms_own, h2d, d2h, e2e_steps, placement = run_e2e(seq, rows, device, min(args.steps, 2))
+        e2e_ms = max_over_ranks(e2e_ms_own, device)
         e2e = {"value": total_tokens * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": e2e_steps,
+               "rank0_h2d_gbs": h2d * e2e_steps / (e2e_ms_own * 1e-3) / 1e9,
+               "rank0_d2h_gbs": d2h * e2e_steps / (e2e_ms_own * 1e-3) / 1e9, "placement": placement,
                "timing": "host clock around enqueue + granite4_host_glue_sync, max over ranks",
                "api": "granite4_host_glue_layer x layers + granite4_host_glue_final_norm, pinned "
                       "host buffers; the residual stream and the KV pool stay on the device"}
 
+    check = check_outputs(seq, rows, rank, world, device, shapes, prof_layers, workspace)
+
     if rank == 0:
         peak, peak_src = load_peaks()
         bpr = glue.bytes_per_row(shapes)
+        traffic = load_traffic()
         ops = {}
         for name, evs in op_events.items():
             dur = [a.elapsed_time(b) for a, b in evs]
@@ -332,7 +343,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                          "achieved_gbs": per_row * rows / (mean_ms * 1e-3) / 1e9,
                          "frac": per_row * rows / (mean_ms * 1e-3) / 1e9 / peak,
                          "frac_of_nominal_8000": per_row * rows / (mean_ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
-                         "bytes_per_row": per_row}
+                         "bytes_per_row": per_row,
+                         "dram_bytes_per_row": traffic.get(name)}
         dominant = max(ops, key=lambda k: ops[k]["share"])
         tokens_per_s = total_tokens * args.steps / (ms_max * 1e-3)
         per_token = (seq.layers * (2 * bpr["add_rmsnorm_fp8"] + bpr["rope_kv_int8"] + bpr["swiglu_fp8"]) +
@@ -349,20 +361,16 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                        "bytes_per_token": per_token},
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": ops[dominant]["achieved_gbs"],
                          "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                         "frac": ops[dominant]["frac"], "traffic": TRAFFIC_PER_ROW.get(dominant, 0) * rows
-                         if TRAFFIC_PER_ROW.get(dominant) else None,
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the op's "
-                                           "kernels at 8192 rows, scaled by rows (profiles/)",
+                         "frac": ops[dominant]["frac"],
+                         "traffic": traffic[dominant] * rows if dominant in traffic else None,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the op's kernels "
+                                           "from the committed profiler launch list, scaled by rows"
+                                           if dominant in traffic else None,
                          "algorithmic_bytes_per_launch": ops[dominant]["bytes_per_row"] * rows,
                          "timing": f"event pair around each op, {op_steps} steps after the main region"},
             "sequence_roofline": {"achieved": seq_gbs, "unit": "GB/s per GPU", "frac": seq_gbs / peak},
             "ops": ops,
-            "embed": extras["embed"],
-            "small_shapes": extras["small"],
-            "argmax": extras["argmax"],
-            "attention_decode": extras["attention"],
-            "decode_step": extras["decode_step"],
-            "gemm_fp8": extras["gemm"],
+            "check": check,
             "clocks": clocks,
             "gpu_launches": launches,
             "device_status": status,
@@ -376,18 +384,124 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                                     "sample": f"{c_rows} token rows through all 40 layers + final norm, "
                                               f"3 steps after 1 warm-up, {dt:.1f} s"}
         line["e2e"] = e2e
+        if extras is not None:
+            line.update({"embed": extras["embed"], "small_shapes": extras["small"], "argmax": extras["argmax"],
+                         "config2_decode_chain": extras["config2"], "config4_rope_kv": extras["config4"],
+                         "attention_decode": extras["attention"], "decode_step": extras["decode_step"],
+                         "gemm_fp8": extras["gemm"]})
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
+def check_outputs(seq, rows, rank, world, device, shapes, prof_layers, workspace):
+    """After the timed regions, outside every timer: are the outputs the ranks computed the right
+    ones? Each rank condenses what its last step left behind (GlueSequence.fingerprint: integer
+    sums over every output buffer in full, plus the raw bits of 64 sample rows) and the ranks
+    all_gather those fingerprints - the one data collective of the benchmark, and it carries
+    results for checking, not data of the path. Rank 0 then rebuilds every other rank's shard
+    from that rank's seed in buffers of its own, runs it alone, launch by launch instead of one
+    library call per layer, and compares fingerprints bit for bit (same shard => same per-shard
+    FP8 scales). With one GPU the rebuilt shard is rank 0's own."""
+    import torch
+    import torch.distributed as dist
+    from granite4_b200 import glue
+    seq.reset()
+    seq.run_fast()
+    torch.cuda.synchronize(device)
+    mine = seq.fingerprint()
+    prints = [mine]
+    if world > 1:
+        prints = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(prints, mine)
+        torch.cuda.synchronize(device)
+    if rank != 0:
+        return None
+    compared, equal = [], True
+    for r in (range(1, world) if world > 1 else (0,)):
+        other = glue.GlueSequence(rows, shapes, device=device, seed=r, sets=2,
+                                  layers=int(prof_layers) if prof_layers else None, workspace=workspace)
+        other.reset()
+        other.run()
+        torch.cuda.synchronize(device)
+        same = bool(torch.equal(other.fingerprint(), prints[r]))
+        compared.append(r)
+        equal = equal and same
+        del other
+        torch.cuda.empty_cache()
+    return {"ranks": world, "compared_ranks": compared, "rows": min(64, rows), "bytes_per_rank": mine.numel(),
+            "covers": "sums over all rows of h, out, n_fp8, act_fp8, q_rot, KV pool and scales; bits of the "
+                      "sample rows", "equal": equal}
+
+
 NOMINAL_HBM_GBS = 8000.0  # the data-sheet figure the reference's target is stated against
 
-# DRAM bytes per token row each op really moves (both sweeps of the FP8 ops), from the ncu
-# captures summarised under profiles/: the second sweep re-reads the bf16 intermediate.
-TRAFFIC_PER_ROW = {"add_rmsnorm_fp8": 26542, "rope_kv_int8": 16597, "swiglu_fp8": 104285,
-                   "final_norm": 10475}
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "layer_kernels_dram_traffic.txt")
+
+
+def op_of_kernel(kernel_name: str):
+    """The op of the sweep a kernel (as the profiler names it) belongs to, or None."""
+    if "add_rmsnorm_fast_kernel<0, 0>" in kernel_name:
+        return "final_norm"
+    if "add_rmsnorm" in kernel_name or "norm_encode_kernel" in kernel_name:
+        return "add_rmsnorm_fp8"
+    if "rope_kv" in kernel_name:
+        return "rope_kv_int8"
+    if "swiglu_kernel" in kernel_name:
+        return "swiglu_fp8"
+    return None
+
+
+def traffic_from_ncu(csv_path: str, rows: int, out_path: str = TRAFFIC_FILE) -> dict:
+    """Condense an `ncu --csv` launch list (one line per launch and metric; metrics
+    dram__bytes_read.sum and dram__bytes_write.sum) of a sweep of `rows` token rows into DRAM
+    bytes per launch of each op. Every kernel specialisation runs once per op, so an op's bytes
+    are the sum over its kernels of each kernel's mean over its launches."""
+    import csv
+    scale = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    launches = {}  # (kernel name, launch id) -> bytes
+    with open(csv_path, newline="") as f:
+        rd = csv.DictReader(l for l in f if l.startswith('"'))
+        for r in rd:
+            if r["Metric Name"] in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+                key = (r["Kernel Name"], r["ID"])
+                launches[key] = launches.get(key, 0.0) + float(r["Metric Value"].replace(",", "")) * scale[r["Metric Unit"]]
+    per_kernel = {}
+    for (name, _), v in launches.items():
+        per_kernel.setdefault(name, []).append(v)
+    ops = {}
+    for name, vals in per_kernel.items():
+        op = op_of_kernel(name)
+        if op is not None:
+            ops[op] = ops.get(op, 0.0) + sum(vals) / len(vals)
+    with open(out_path, "w") as f:
+        f.write("# DRAM bytes (read + written) per launch of each op of the layer sweep, from one profiler\n"
+                "# launch list; written by: python bench.py --traffic-from-ncu <csv> --traffic-rows <rows>\n")
+        f.write(f"rows {rows}\n")
+        for op in sorted(ops):
+            f.write(f"{op} {ops[op]:.0f}\n")
+    return ops
+
+
+def load_traffic():
+    """{op: DRAM bytes per token row} from the committed profiler summary, or {} when it is absent."""
+    if not os.path.isfile(TRAFFIC_FILE):
+        return {}
+    vals = {}
+    with open(TRAFFIC_FILE) as f:
+        for line in f:
+            if line.startswith("#") or not line.strip():
+                continue
+            k, v = line.split()
+            vals[k] = float(v)
+    rows = vals.pop("rows", 0)
+    return {k: v / rows for k, v in vals.items()} if rows else {}
+
+
+def kernels_rope_tables(s, max_pos, device):
+    from granite4_b200 import kernels
+    return kernels.RopeTables(s.rope_theta, s.head_dim, max_pos, device)
 
 
 def small_shapes_and_embed(seq, rows, device, stream):
@@ -475,7 +589,85 @@ def small_shapes_and_embed(seq, rows, device, stream):
             entry["add_rmsnorm_f32_fp8_c_abi_us"] = timed(lambda: c_fn(*c_args), 200)
         small[f"rows_{n}"] = entry
         del sq
-    del table
+    # Benchmark configuration 2 in its own shape: B decode sessions; gather from the Granite-size
+    # table (ids uniform, multiplier 12) -> add + RMSNorm -> FP8 -> RoPE of Q [32 x 128] / K [8 x 128]
+    # at positions uniform in [0, 8192) with the int8 KV append through per-session page tables
+    # (the reference's decode entry point: K rounded to bf16 first) -> SwiGLU of gate / up [12800]
+    # -> FP8. Four kernels, replayed from a CUDA graph.
+    config2 = {}
+    pool2 = 8 * 8192
+    ck2 = torch.zeros(s.kv_heads, pool2, s.head_dim, dtype=torch.int8, device=device)
+    cv2 = torch.zeros_like(ck2)
+    ks2 = torch.zeros(s.kv_heads, pool2, dtype=torch.float32, device=device)
+    vs2 = torch.zeros_like(ks2)
+    tables2 = [((torch.randperm(512, generator=g, device=device) + 512 * r).repeat_interleave(16) * 16
+                + torch.arange(8192, device=device) % 16).to(torch.int32) for r in range(8)]
+    tabs2 = kernels_rope_tables(s, 8192, device)
+    for n in (1, 2, 4, 8):
+        desc = capi.MultiRows()
+        desc.n = n
+        pos_n = torch.randint(0, 8192, (n,), generator=g, device=device).tolist()
+        for r in range(n):
+            desc.pos[r] = pos_n[r]
+            desc.pt[r] = tables2[r].data_ptr()
+        d_rows = k.multi_rows_to_device(desc, device)
+        b = {name: torch.randn(n, c, generator=g, device=device).to(torch.bfloat16)
+             for name, c in (("y", s.hidden), ("q", s.q_heads * s.head_dim), ("k", s.kv_heads * s.head_dim),
+                             ("v", s.kv_heads * s.head_dim), ("gate", s.intermediate), ("up", s.intermediate))}
+        hid = torch.empty(n, s.hidden, dtype=torch.bfloat16, device=device)
+        nf8 = torch.empty(n, s.hidden, dtype=torch.uint8, device=device)
+        af8 = torch.empty(n, s.intermediate, dtype=torch.uint8, device=device)
+        qr = torch.empty_like(b["q"])
+        sc = torch.zeros(2, 2, dtype=torch.float32, device=device)
+        tok = ids[:n].contiguous()
+        wn = seq.w[0, 0]
+
+        def chain2():
+            k.embed_gather(tok, table, s.embedding_multiplier, hid)
+            k.add_rmsnorm_fp8(b["y"], hid, wn, s.eps, s.residual_multiplier, h_out=hid, n_fp8=nf8, scale_amax=sc[0])
+            k.gpu_multi_rope_append(b["q"], b["k"], b["v"], tabs2.cos, tabs2.sin, d_rows, n, s.q_heads, s.kv_heads,
+                                    s.head_dim, 8, ck2, cv2, ks2, vs2, pool2, qr)
+            k.swiglu_fp8(b["gate"], b["up"], None, af8, sc[1])
+        config2[f"sessions_{n}"] = {"kernels": 4, "chain_eager_us": timed(chain2, 50),
+                                    "chain_graph_us": graph_replay_us(chain2)}
+    tabs2.close()
+    del table, ck2, cv2, ks2, vs2
+    torch.cuda.empty_cache()
+
+    # Benchmark configuration 4, the long-context write: 4 sequences x 8192 tokens at RoPE offsets up to
+    # 131071, K/V scattered into a 122880-row pool through a random permutation of its 7680
+    # 16-token pages, against the same rows written to consecutive pool rows.
+    from granite4_b200 import paging
+    c4_rows = min(rows, 32768)
+    per_seq = c4_rows // 4
+    pool4, max_pos4 = 7680 * 16, 131072
+    tabs4 = kernels_rope_tables(s, max_pos4, device)
+    bt = paging.permuted_block_tables(4, (per_seq + 15) // 16, 7680, seed=44)
+    pos4, kvr4 = paging.batch_rows(bt, [0, 40000, 90001, max_pos4 - per_seq], per_seq)
+    pos4_d, kvr4_d = torch.from_numpy(pos4).to(device), torch.from_numpy(kvr4).to(device)
+    ident = torch.arange(c4_rows, dtype=torch.int32, device=device)
+    ck4 = torch.zeros(s.kv_heads, pool4, s.head_dim, dtype=torch.int8, device=device)
+    cv4 = torch.zeros_like(ck4)
+    ks4 = torch.zeros(s.kv_heads, pool4, dtype=torch.float32, device=device)
+    vs4 = torch.zeros_like(ks4)
+    qr4 = torch.empty(c4_rows, s.q_heads * s.head_dim, dtype=torch.bfloat16, device=device)
+    flip4 = [0]
+
+    def rope4(pos_t, kv_t):
+        flip4[0] ^= 1  # rotate the two input sets: nothing is L2-hot
+        qkv = seq.sets[flip4[0] % len(seq.sets)]["qkv"][:c4_rows]
+        k.rope_kv_int8_paged(qkv, tabs4.cos, tabs4.sin, pos_t, kv_t, s.q_heads, s.kv_heads, s.head_dim, pool4,
+                             max_pos4, 0, qr4, ck4, cv4, ks4, vs4)
+    bpr4 = glue.bytes_per_row(s)["rope_kv_int8"]
+    us_id = timed(lambda: rope4(ident, ident), 20)
+    us_pg = timed(lambda: rope4(pos4_d, kvr4_d), 20)
+    config4 = {"rows": c4_rows, "pool_rows": pool4, "pages": 7680,
+               "consecutive_rows_us": us_id, "permuted_pages_us": us_pg,
+               "permuted_over_consecutive": us_pg / us_id,
+               "achieved_gbs": bpr4 * c4_rows / (us_pg * 1e-6) / 1e9,
+               "frac": bpr4 * c4_rows / (us_pg * 1e-6) / 1e9 / peak}
+    tabs4.close()
+    del ck4, cv4, ks4, vs4, qr4
     torch.cuda.empty_cache()
 
     # Greedy pick over the logits (the decode step's last glue op; 2 V bytes read per row): a
@@ -785,15 +977,48 @@ def small_shapes_and_embed(seq, rows, device, stream):
     del wsets, a_h, a_i
     torch.cuda.empty_cache()
     return {"embed": embed, "small": small, "argmax": argmax, "attention": attention, "decode_step": decode_step,
-            "gemm": gemm}
+            "gemm": gemm, "config2": config2, "config4": config4}
+
+
+def cpus_near_gpu(device):
+    """CPUs of the NUMA node the GPU hangs off (sysfs local_cpulist of its PCI function), cut down
+    to the ones this process may run on; an empty set when sysfs does not say."""
+    import torch
+    try:
+        pr = torch.cuda.get_device_properties(device)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/local_cpulist") as f:
+            text = f.read().strip()
+    except (OSError, AttributeError):
+        return set(), None
+    cpus = set()
+    for part in text.split(","):
+        if part:
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus & os.sched_getaffinity(0), bdf
 
 
 def run_e2e(seq, rows, device, steps):
     """The same sequence through the host-buffer C ABI: per step every layer's inputs are copied
-    from pinned host memory, its FP8 / q_rot outputs are copied back."""
+    from pinned host memory, its FP8 / q_rot outputs are copied back. For the duration of this leg
+    the process is bound to the CPUs next to its GPU, so the pinned buffers (allocated below, first
+    touched here) and the enqueueing thread sit on the GPU's NUMA node."""
     import torch
     from granite4_b200 import glue
     s = seq.shapes
+    before = os.sched_getaffinity(0)
+    near, bdf = cpus_near_gpu(device)
+    if near and os.environ.get("G4_BENCH_BIND", "1") != "0":
+        os.sched_setaffinity(0, near)
+    try:
+        ms, h2d, d2h, steps = _run_e2e_bound(seq, rows, device, steps, s, glue, torch)
+    finally:
+        os.sched_setaffinity(0, before)
+    return ms, h2d, d2h, steps, {"pci": bdf, "cpus_near_gpu": len(near), "bound": bool(near)}
+
+
+def _run_e2e_bound(seq, rows, device, steps, s, glue, torch):
     hg = glue.HostGlue(rows, s, device=device, layers=seq.layers, pool_rows=seq.pool_rows,
                        max_pos=seq.max_pos)
     src = seq.sets[0]
@@ -859,7 +1084,13 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--sweep-only", action="store_true", help="only the sweep (short profiler captures)")
+    ap.add_argument("--traffic-from-ncu", metavar="CSV", help="convert a profiler launch list; no benchmark")
+    ap.add_argument("--traffic-rows", type=int, default=8192, help="token rows of that capture")
     args = ap.parse_args()
+    if args.traffic_from_ncu:
+        print(json.dumps(traffic_from_ncu(args.traffic_from_ncu, args.traffic_rows)))
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -38,6 +38,7 @@
 #include "../../include/granite4_b200.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 namespace g4 {
@@ -58,6 +59,7 @@ struct NormParams {
   int cols8;  // cols / 8
   int cols;
   int reverse;  // walk rows from the last to the first
+  float keep_h;  // > 0: a second sweep re-reads h; fraction of its lines to hold in L2 (evict_last)
   double inv_cols;  // 1 / cols when cols is a power of two (the scaling is then exact), else 0
 };
 
@@ -85,6 +87,7 @@ template <bool Y_F32, bool RES_F32, int V, int PHASE>
 __global__ void __launch_bounds__(max_threads_for(V))
     add_rmsnorm_kernel(const NormParams p) {
   pdl_begin();
+  if (PHASE == kCluster) cluster_announce();
   const int T = blockDim.x;
   const int t = threadIdx.x;
   // A cluster is a power of two wide: its spare CTAs redo the last row without storing anything,
@@ -242,6 +245,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_fast_kernel(const NormParams 
   }
   float h[V][8];
   double acc = 0.0;
+  const bool keep = WANT_AMAX && p.keep_h > 0.0f;
+  const uint64_t pol = keep ? l2_policy_evict_last(p.keep_h) : 0ull;
 #pragma unroll
   for (int j = 0; j < V; ++j) {
     unpack8(yraw[j], h[j]);
@@ -253,7 +258,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_fast_kernel(const NormParams 
     }
     const uint4 hb = pack8(h[j]);
     unpack8(hb, h[j]);
-    if (p.h_out != nullptr) reinterpret_cast<uint4*>(p.h_out)[row_chunk0 + t + j * T] = hb;
+    if (p.h_out != nullptr) {
+      uint4* dst = reinterpret_cast<uint4*>(p.h_out) + row_chunk0 + t + j * T;
+      if (keep) st_l2_hint(dst, hb, pol); else *dst = hb;
+    }
   }
 #pragma unroll
   for (int j = 0; j < V; ++j)
@@ -324,6 +332,8 @@ __global__ void __launch_bounds__(kEncodeThreads) norm_encode_kernel(const NormP
   if (blockIdx.x == 0 && t == 0) p.scale_amax[0] = fs.scale;
   const uint4* h = reinterpret_cast<const uint4*>(p.h_out);
   uint2* out = reinterpret_cast<uint2*>(p.n_fp8);
+  const bool kept = p.keep_h > 0.0f;
+  const uint64_t pol = kept ? l2_policy_evict_first() : 0ull;  // h was held for this read: let go of it
   const int pass_cols = kEncodeThreads * kEncodeMaxIter;
   for (int c0 = 0; c0 < (FULL ? pass_cols : p.cols8); c0 += pass_cols) {
     uint4 hv[kRowsPerCta][kEncodeMaxIter];
@@ -336,8 +346,10 @@ __global__ void __launch_bounds__(kEncodeThreads) norm_encode_kernel(const NormP
         wv[k] = __ldg(reinterpret_cast<const uint4*>(p.w) + c);
 #pragma unroll
         for (int j = 0; j < kRowsPerCta; ++j)
-          if (FULL || row0 + j < p.rows)
-            hv[j][k] = ld_stream(h + static_cast<size_t>(row0 + j) * p.cols8 + c);
+          if (FULL || row0 + j < p.rows) {
+            const uint4* src = h + static_cast<size_t>(row0 + j) * p.cols8 + c;
+            hv[j][k] = kept ? ld_l2_hint(src, pol) : ld_stream(src);
+          }
       }
     }
 #pragma unroll
@@ -520,6 +532,9 @@ int add_rmsnorm_launch(const char* fn, const void* d_y, int y_is_f32, const void
   p.rstd = d_rstd;
   p.eps = eps, p.rm = rm, p.rows = rows, p.cols = cols, p.cols8 = cols / 8, p.reverse = 0;
   p.inv_cols = (cols & (cols - 1)) == 0 ? 1.0 / static_cast<double>(cols) : 0.0;
+  // the rstd form of the second sweep re-reads h: hold as much of it in L2 as is likely to fit
+  p.keep_h = (d_n_fp8 != nullptr && d_n_bf16 == nullptr && d_h_out != nullptr && d_rstd != nullptr)
+                 ? l2_keep_fraction(static_cast<double>(rows) * cols * 2.0) : 0.0f;
   if (d_n_fp8 != nullptr && rows <= kMaxClusterCtas && p.cols8 <= max_threads_for(1) && cluster_enabled()) {
     const int ctas = cluster_ctas_for(rows);
     const int threads = (p.cols8 + 31) / 32 * 32;
@@ -686,7 +701,7 @@ namespace {
 // Device address of g_noalloc_rstd on each device. In host code the array's name is only a
 // handle for the runtime, not an address a kernel can use; the address is looked up once per
 // device, with that device current, and cached.
-float* g_noalloc_rstd_ptr[64];
+std::atomic<float*> g_noalloc_rstd_ptr[64];  // relaxed: any thread may fill it, all with the same value
 
 float* noalloc_rstd_ptr(const char* fn) {
   int dev = -1;
@@ -694,7 +709,8 @@ float* noalloc_rstd_ptr(const char* fn) {
     fail(fn, "cannot identify the current device");
     return nullptr;
   }
-  if (g_noalloc_rstd_ptr[dev] == nullptr) {
+  float* known = g_noalloc_rstd_ptr[dev].load(std::memory_order_relaxed);
+  if (known == nullptr) {
     void* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_rstd);
     if (e != cudaSuccess || p == nullptr) {
@@ -702,9 +718,10 @@ float* noalloc_rstd_ptr(const char* fn) {
                    cudaGetErrorString(e));
       return nullptr;
     }
-    g_noalloc_rstd_ptr[dev] = static_cast<float*>(p);
+    known = static_cast<float*>(p);
+    g_noalloc_rstd_ptr[dev].store(known, std::memory_order_relaxed);
   }
-  return g_noalloc_rstd_ptr[dev];
+  return known;
 }
 }  // namespace
 }  // namespace g4

@@ -36,6 +36,7 @@
 
 #include "../../include/granite4_b200.h"
 
+#include <atomic>
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -585,15 +586,15 @@ int attn_launch(const char* fn, const uint16_t* d_q, const int8_t* d_cache_k, co
   }
   cudaStream_t st = current_stream();
   {
-    static bool attr_set[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    static std::atomic<bool> attr_set[64];  // per device; relaxed: setting the attribute twice is harmless
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(fn, "cannot identify the current device");
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_relaxed)) {
       G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(kAttnSmemBytesT)));
       G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(kAttnSmemBytesT)));
-      attr_set[dev] = true;
+      attr_set[dev].store(true, std::memory_order_relaxed);
     }
   }
   const dim3 grid(static_cast<unsigned>(s.splits), static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups));

@@ -58,6 +58,7 @@ __device__ __forceinline__ float pair_max(uint32_t m) {
 template <bool VEC, bool CLUSTER>
 __global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const ArgmaxParams p) {
   pdl_begin();
+  if (CLUSTER) cluster_announce();
   const int T = blockDim.x, t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = T >> 5;
   const int C = CLUSTER ? p.ctas_per_row : 1;
   const int row = CLUSTER ? static_cast<int>(blockIdx.x) / C : blockIdx.x;
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const Argma
   for (int o = 16; o > 0; o >>= 1) idx = min(idx, __shfl_xor_sync(0xffffffffu, idx, o));
   if (lane == 0) s_idx[warp] = idx;
   __syncthreads();
+  if (CLUSTER) cluster_all_started();  // before the stores into CTA 0's shared memory below
   __shared__ float s_cmax[kMaxClusterCtas];
   __shared__ int s_cidx[kMaxClusterCtas];
   if (t == 0) {

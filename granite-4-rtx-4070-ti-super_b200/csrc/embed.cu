@@ -24,6 +24,7 @@
 #include "../../include/granite4_b200.h"
 #include "../../include/granite4_b200.hpp"
 
+#include <atomic>
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -166,13 +167,13 @@ int embed_launch(const char* fn, const int32_t* d_tokens, long long start, long 
   const size_t smem = static_cast<size_t>(kStages) * H * 2 + kStages * sizeof(uint64_t);
   unsigned int* status = device_status_ptr();
   if (bulk_enabled() && smem <= 200 * 1024 && status != nullptr) {
-    static bool attr_set[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    static std::atomic<bool> attr_set[64];  // per device; relaxed: setting the attribute twice is harmless
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(fn, "cannot identify the current device");
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_relaxed)) {
       G4_CUDA_TRY(fn, cudaFuncSetAttribute(embed_bulk_kernel,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      attr_set[dev] = true;
+      attr_set[dev].store(true, std::memory_order_relaxed);
     }
     const long long per_sm = std::max<long long>(1, std::min<long long>(8, (200 * 1024) / smem));
     const unsigned grid = static_cast<unsigned>(std::min<long long>(rows, sm_count() * per_sm));

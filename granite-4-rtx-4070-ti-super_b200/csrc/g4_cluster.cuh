@@ -30,9 +30,23 @@ namespace g4 {
 
 constexpr int kMaxClusterCtas = 16;  // 8 is the portable limit, 16 needs the opt-in attribute
 
+// A CTA's shared memory may be written from another CTA of the cluster only once that CTA is
+// known to be executing. Every kernel that runs as one cluster therefore announces itself as its
+// first statement (after pdl_begin) with cluster_announce(), and waits with cluster_all_started()
+// just before its first store into a peer's shared memory: one split phase of the hardware cluster
+// barrier, whose wait is long over by the time the data for the store has been loaded. Every
+// thread of every CTA executes both, exactly once and in this order.
+__device__ __forceinline__ void cluster_announce() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_all_started() {
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
+
 // Max of `thread_amax` (packed sign-cleared bf16 pairs) over every thread of
 // every CTA in the cluster, as float bits. s_warp: one word per warp of the
-// CTA; s_slots: kMaxClusterCtas words. Called by all threads.
+// CTA; s_slots: kMaxClusterCtas words. Called by all threads, in a kernel that
+// began with cluster_announce().
 __device__ __forceinline__ uint32_t cluster_amax_bits(uint32_t thread_amax, uint32_t* s_warp,
                                                       uint32_t* s_slots) {
   namespace cg = cooperative_groups;
@@ -41,6 +55,7 @@ __device__ __forceinline__ uint32_t cluster_amax_bits(uint32_t thread_amax, uint
   thread_amax = amax_warp(thread_amax);
   if (lane == 0) s_warp[warp] = thread_amax;
   __syncthreads();
+  cluster_all_started();  // pairs with the cluster_announce() at the top of the calling kernel
   const unsigned n = cluster.num_blocks();
   if (warp == 0) {
     uint32_t m = 0u;

@@ -62,6 +62,12 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 bool amax_prezeroed();
 void set_amax_prezeroed(bool on);
 
+// Fraction of a `bytes`-large intermediate to mark evict_last in L2 between the two sweeps of an
+// FP8 op (g4_math.cuh, l2_policy_evict_last): all of it while it fits the share of L2 set aside
+// for it (G4_L2_KEEP_MB in the environment, read once; default 64 of the 126 MB; 0 turns the hints
+// off), else that share of it, spread evenly over the tensor.
+float l2_keep_fraction(double bytes);
+
 // Programmatic dependent launch: a kernel launched through launch_pdl may be staged on the GPU
 // while the kernel before it on the stream is still draining; it must (and every kernel launched
 // this way does, as its first statements, in every CTA) execute pdl_begin() from g4_math.cuh,

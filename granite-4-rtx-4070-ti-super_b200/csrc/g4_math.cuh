@@ -243,11 +243,24 @@ __device__ __forceinline__ void rope_pair(float a, float b, float c, float s, fl
 // that follows hides except for roughly one element in several thousand, where
 // the bf16 result is the neighbouring value (the stated tolerance is 1 bf16
 // ulp; the reference's own device kernels are tested to the same bound against
-// this host formula). For g < -87.3 the reciprocal underflows to zero and the
-// result is -0 where the host gives a number of magnitude < 1e-36.
+// this host formula).
+// For g below about -87.3 the sum 1 + e^-g passes 2^126 and its flushed reciprocal
+// is zero, while the host still divides by a finite number until expf(-g)
+// overflows at -g = 88.7228...: there the host's quotient is a normal float of
+// magnitude ~1e-36. Those few gate values (three bf16 values: -87.5, -88, -88.5)
+// take swiglu_tail, which forms g * 2^(64 - t) * 2^-64 with every factor in the
+// normal range; below the overflow point both sides give g / inf = -0.
+static __device__ __noinline__ float swiglu_tail(float g, float t, float u) {
+  if (g < -88.72283f) return __fmul_rn(__fmul_rn(g, 0.0f), u);
+  float r;
+  const float s = __fsub_rn(64.0f, t);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(s));
+  return __fmul_rn(__fmul_rn(__fmul_rn(g, r), 0x1p-64f), u);
+}
 __device__ __forceinline__ float swiglu(float g, float u) {
   float e, r;
   const float t = __fmul_rn(g, -1.4426950408889634f);
+  if (__builtin_expect(t > 126.0f, 0)) return swiglu_tail(g, t, u);
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
   const float d = __fadd_rn(1.0f, e);
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
@@ -262,6 +275,33 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
 __device__ __forceinline__ void st_stream(uint2* p, uint2 v) { __stcs(p, v); }
+
+// L2 eviction-priority hints on single loads and stores (an instruction-level policy operand;
+// nothing about the device or the context is configured). A tensor that one sweep writes and the
+// next sweep re-reads is stored with evict_last so that the read-once inputs streaming past it do
+// not push it out, and re-read with evict_first so that its lines are the first to go afterwards.
+// `fraction` of the lines touched get the priority, the rest the default (evict_first for the
+// store-side policy of a tensor larger than L2: see the callers).
+__device__ __forceinline__ uint64_t l2_policy_evict_last(float fraction) {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.L2::evict_first.b64 %0, %1;" : "=l"(pol) : "f"(fraction));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void st_l2_hint(uint4* p, uint4 v, uint64_t pol) {
+  asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;"
+               :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(pol) : "memory");
+}
+__device__ __forceinline__ uint4 ld_l2_hint(const uint4* p, uint64_t pol) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.b32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
+  return v;
+}
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

@@ -1041,8 +1041,8 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
                                         int N, int K, const granite4_gemm_fp8_epilogue* ep, void* d_ws,
                                         long long ws_bytes) {
   static const char* fn = "granite4_kernel_gemm_fp8";
-  if (M == 0 && N > 0 && K > 0 && ep != nullptr) return 0;  // no rows (an empty shard): nothing to do
-  if (d_a == nullptr || d_w == nullptr || ep == nullptr) return fail(fn, "null argument");
+  // M == 0 (an empty shard) is valid: every check below still applies, then nothing is launched
+  if (ep == nullptr || d_w == nullptr || (d_a == nullptr && M != 0)) return fail(fn, "null argument");
   if (M < 0 || N <= 0 || K <= 0 || K % 16 != 0 || lda < K || lda % 16 != 0 || !aligned16(d_a) || !aligned16(d_w))
     return fail(fn, "needs K % 16 == 0, lda % 16 == 0, lda >= K and 16-byte aligned A and W");
   if (out_kind != GRANITE4_GEMM_OUT_BF16 && out_kind != GRANITE4_GEMM_OUT_F32 && out_kind != GRANITE4_GEMM_OUT_RESIDUAL &&
@@ -1056,6 +1056,13 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
     return fail(fn, "the output of the requested kind is null");
   if (out_kind == GRANITE4_GEMM_OUT_RESIDUAL && ep->d_residual == nullptr) return fail(fn, "null residual");
   if (d_ws != nullptr && !aligned16(d_ws)) return fail(fn, "the workspace must be 16-byte aligned");
+  if (M == 0) {
+    // no rows: the only effect is on the fused epilogue's {scale, amax} slot, which must not keep a
+    // previous call's maximum for the encode step (or a GEMM reading the scale) that follows
+    if (fused_swiglu && !amax_prezeroed())
+      G4_CUDA_TRY(fn, cudaMemsetAsync(ep->d_out_scale_amax, 0, 2 * sizeof(float), current_stream()));
+    return 0;
+  }
 
   GemmParams p{};
   p.M = M, p.N = N, p.K = K, p.ldc = ep->ldc, p.out_kind = out_kind;

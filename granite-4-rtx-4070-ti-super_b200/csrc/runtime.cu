@@ -6,6 +6,7 @@
 
 #include "../../include/granite4_b200.h"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace g4 {
@@ -13,8 +14,10 @@ namespace g4 {
 namespace {
 thread_local cudaStream_t t_stream = cudaStreamPerThread;
 constexpr int kMaxDevices = 64;
-int g_sm_count[kMaxDevices];  // 0 = not queried yet
-unsigned int* g_status_ptr[kMaxDevices];
+// Per-device caches, filled on first use by whichever host thread gets there first (several may,
+// with the same value): relaxed atomics, no lock.
+std::atomic<int> g_sm_count[kMaxDevices];  // 0 = not queried yet
+std::atomic<unsigned int*> g_status_ptr[kMaxDevices];
 
 // One word per device that loads the library; zero until a kernel reports.
 __device__ unsigned int g_device_status;
@@ -23,12 +26,14 @@ __device__ unsigned int g_device_status;
 unsigned int* device_status_ptr() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-  if (g_status_ptr[dev] == nullptr) {
+  unsigned int* known = g_status_ptr[dev].load(std::memory_order_relaxed);
+  if (known == nullptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
-    g_status_ptr[dev] = static_cast<unsigned int*>(p);
+    known = static_cast<unsigned int*>(p);
+    g_status_ptr[dev].store(known, std::memory_order_relaxed);
   }
-  return g_status_ptr[dev];
+  return known;
 }
 
 cudaStream_t current_stream() { return t_stream; }
@@ -48,13 +53,23 @@ bool pdl_enabled() {
 int sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
-  if (g_sm_count[dev] == 0) {
-    int n = 0;
+  int n = g_sm_count[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
       n = 148;
-    g_sm_count[dev] = n;
+    g_sm_count[dev].store(n, std::memory_order_relaxed);
   }
-  return g_sm_count[dev];
+  return n;
+}
+
+float l2_keep_fraction(double bytes) {
+  static const int keep_mb = [] {
+    const char* v = std::getenv("G4_L2_KEEP_MB");
+    return (v != nullptr && *v != '\0') ? std::atoi(v) : 64;
+  }();
+  if (keep_mb <= 0 || bytes <= 0.0) return 0.0f;
+  const double f = static_cast<double>(keep_mb) * 1048576.0 / bytes;
+  return f >= 1.0 ? 1.0f : static_cast<float>(f);
 }
 
 }  // namespace g4

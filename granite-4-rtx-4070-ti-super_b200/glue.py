@@ -203,6 +203,34 @@ class GlueSequence:
         self._check(thunk(), name)
         self.launches += KERNELS_FINAL
 
+    def fingerprint(self, sample_rows: int = 64) -> torch.Tensor:
+        """Everything a finished step left behind, condensed into one uint8 tensor whose length
+        depends only on the shapes: the integer sums of the bit patterns of every output buffer
+        over ALL rows (hidden state, final norm, FP8 codes, q_rot, the int8 pool and its scales of
+        every layer, every {scale, amax} slot), followed by the raw bits of `sample_rows` evenly
+        spaced rows of the row-shaped outputs and of their K/V pool rows in the first and last
+        layer. Two runs of the same shard agree on it bit for bit; ranks exchange it after a timed
+        region to be compared with an independent re-run."""
+        def total(t):
+            flat = t.reshape(-1)
+            if flat.element_size() == 2:
+                flat = flat.view(torch.int16)
+            elif flat.element_size() == 4:
+                flat = flat.view(torch.int32)
+            return flat.sum(dtype=torch.int64).reshape(1)
+        sums = [total(t) for t in (self.h, self.out, self.n_fp8, self.act_fp8, self.q_rot, self.cache_k,
+                                   self.cache_v, self.k_scale, self.v_scale, self.scales)]
+        k = max(1, min(sample_rows, self.rows))
+        pick = torch.arange(k, device=self.device) * (self.rows // k)
+        pool = self.kv_rows[pick].long()
+        parts = [torch.cat(sums).view(torch.uint8), self.scales.reshape(-1).view(torch.uint8)]
+        for t in (self.h, self.out, self.n_fp8, self.act_fp8, self.q_rot):
+            parts.append(t[pick].reshape(-1).view(torch.uint8))
+        for layer in sorted({0, self.layers - 1}):
+            for t in (self.cache_k, self.cache_v, self.k_scale, self.v_scale):
+                parts.append(t[layer][:, pool].contiguous().reshape(-1).view(torch.uint8))
+        return torch.cat(parts)
+
     def run(self, wrap=None):
         """One step: all layers, then the final norm. Enqueues only; does not synchronise.
         `wrap(name, thunk)` may run the thunk itself (e.g. between two events) and must return

@@ -577,8 +577,12 @@ int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq
  * scheduling). granite4_gemm_fp8_workspace_bytes(M, N, K) is the size that
  * allows the planned split (0: none wanted, e.g. from three rows on); the buffer must be zeroed once
  * before its first use (every call leaves its first bytes, the tile counters,
- * zero again) and belongs to one call at a time. NULL or a smaller buffer: no
- * split. d_w must not be written by the operation just before this call on
+ * zero again) and belongs to one call at a time. The counters return to zero
+ * only when a call runs to completion: after granite4_b200_device_status
+ * reported a non-zero word (a bounded wait ran out and the kernel left early),
+ * or after a failed launch, zero the buffer again before reusing it, or later
+ * calls sum stale partials without reporting anything. NULL or a smaller
+ * buffer: no split. d_w must not be written by the operation just before this call on
  * the stream: with at most 128 rows the kernel starts fetching weights while
  * that operation drains (weights are constants of a loaded model). Returns 0,
  * or -1 on bad arguments or a launch error. */

@@ -31,10 +31,21 @@ def _ptr(a):
     return a.ctypes.data_as(_P)
 
 
-def build(ref_root: str = "/root/reference") -> None:
+def reference_root() -> str | None:
+    """Where a checkout of the reference engine lies, if anywhere: $G4_REFERENCE_ROOT, else a
+    directory named `reference` beside this repository."""
+    for cand in (os.environ.get("G4_REFERENCE_ROOT"),
+                 os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if cand and os.path.isfile(os.path.join(cand, "engine", "src", "kernel_math.h")):
+            return os.path.abspath(cand)
+    return None
+
+
+def build(ref_root: str | None = None) -> None:
     """(Re)build the port, and the reference-backed library when a reference tree is there."""
     subprocess.run(["make", "-s", "-C", _HERE, "all"], check=True)
-    if os.path.isfile(os.path.join(ref_root, "engine", "src", "kernel_math.h")):
+    ref_root = ref_root or reference_root()
+    if ref_root is not None:
         subprocess.run(["make", "-s", "-C", _HERE, "_ref", f"REF={ref_root}"], check=True)
 
 

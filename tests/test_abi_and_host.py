@@ -191,3 +191,34 @@ def test_a_plain_c99_program_includes_the_header_and_links_the_library(g4, tmp_p
     assert run.returncode == 0, run.stdout + run.stderr
     assert "granite-4.2-8b sm_100a layers=40" in run.stdout
     assert "pool ok=1 rows 12 13 8 11 | 2" in run.stdout  # pages are handed out from the top of the free stack
+
+
+def test_bench_condenses_a_profiler_launch_list_into_traffic_per_op(tmp_path):
+    """bench.py's converter: one line per launch and metric in, DRAM bytes per op launch out
+    (mean over the launches of each kernel, summed over the op's kernels), and the loader turns
+    the written file back into bytes per token row."""
+    import bench
+    head = '"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size",' \
+           '"Grid Size","Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"\n'
+
+    def line(i, kernel, metric, unit, value):
+        return f'"{i}","1","python","h","{kernel}","1","7","(128, 1, 1)","(8, 1, 1)","0","10.0","x","{metric}","{unit}","{value}"\n'
+    stats = "void unnamed>::add_rmsnorm_fast_kernel<1, 1>(unnamed>::NormParams)"
+    enc = "void unnamed>::norm_encode_kernel<1>(unnamed>::NormParams)"
+    fin = "void unnamed>::add_rmsnorm_fast_kernel<0, 0>(unnamed>::NormParams)"
+    text = "==PROF== Connected\n" + head
+    text += line(0, stats, "dram__bytes_read.sum", "Mbyte", "100") + line(0, stats, "dram__bytes_write.sum", "byte", "50,000,000")
+    text += line(1, enc, "dram__bytes_read.sum", "byte", "10000000") + line(1, enc, "dram__bytes_write.sum", "byte", "30000000")
+    text += line(2, stats, "dram__bytes_read.sum", "byte", "120000000") + line(2, stats, "dram__bytes_write.sum", "byte", "50000000")
+    text += line(2, stats, "gpu__time_duration.sum", "ns", "31040")
+    text += line(3, fin, "dram__bytes_read.sum", "byte", "64") + line(3, fin, "dram__bytes_write.sum", "byte", "36")
+    src, dst = tmp_path / "launches.csv", tmp_path / "traffic.txt"
+    src.write_text(text)
+    ops = bench.traffic_from_ncu(str(src), 1000, str(dst))
+    assert ops == {"add_rmsnorm_fp8": 160e6 + 40e6, "final_norm": 100.0}
+    old = bench.TRAFFIC_FILE
+    bench.TRAFFIC_FILE = str(dst)
+    try:
+        assert bench.load_traffic() == {"add_rmsnorm_fp8": 200e3, "final_norm": 0.1}
+    finally:
+        bench.TRAFFIC_FILE = old

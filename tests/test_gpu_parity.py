@@ -538,6 +538,40 @@ def test_swiglu_random_and_fused_layout(K, port):
     assert torch.equal(act, act2)
 
 
+@pytest.mark.parametrize("f32", [False, True])
+def test_swiglu_large_negative_and_positive_gates(K, port, f32):
+    """Gates where 1 + e^-g leaves the range whose reciprocal is a normal float (g below about -87.3:
+    the host still divides by a finite number until expf overflows at 88.72) and where the sigmoid is
+    1 to the last bit (g above 80). bf16 gates have three values in the first window (-87.5, -88,
+    -88.5); f32 gates cover it densely. Up values span 60 orders of magnitude so that the tiny
+    quotients come back into range. 1 bf16 ulp, as everywhere else for this op."""
+    rng = np.random.default_rng(77)
+    n = 8 * 4096
+    g32 = np.concatenate([rng.uniform(-100, -80, n // 2), rng.uniform(80, 100, n // 4),
+                          rng.uniform(-88.70, -87.2, n // 4)]).astype(np.float32)
+    g32[:6] = [-87.5, -88.0, -88.5, -89.0, -87.0, -126.0]
+    u32 = (rng.standard_normal(n) * np.exp(rng.uniform(-70, 70, n))).astype(np.float32)
+    keep = np.abs(np.abs(g32) - 88.7228) > 0.01  # expf's overflow point itself is one float wide: stay clear
+    g32, u32 = g32[keep][: (keep.sum() // 8) * 8], u32[keep][: (keep.sum() // 8) * 8]
+    if f32:
+        gate, up = g32.reshape(1, -1), u32.reshape(1, -1)
+        gd, ud = torch.from_numpy(gate).to(DEV), torch.from_numpy(up).to(DEV)
+    else:
+        to_bits = lambda a: np.array([port.f32_to_bf16(v) for v in a], np.uint16)
+        gate, up = to_bits(g32).reshape(1, -1), to_bits(u32).reshape(1, -1)
+        gd, ud = dev(gate), dev(up)
+    I = gate.shape[1]
+    act = empty_bf16(1, I)
+    assert K.swiglu_fp8(gd, ud, act, None, None) == 0
+    want = port.swiglu(gate, up)
+    got = host(act)
+    finite = ((want & 0x7F80) != 0x7F80)
+    assert bf16_ulp_distance(got[finite], want[finite]).max() <= 1
+    assert ((got[~finite] & 0x7F80) == 0x7F80).all()
+    assert (want[0, :3] & 0x7FFF != 0).all()  # the window values are not zero on the host ...
+    assert (got[0, :3] & 0x7FFF != 0).all()   # ... and neither here
+
+
 def test_swiglu_full_size_round_trip(K):
     """8192 x 12800 (one 8-GPU shard of the sweep): decode(code) * scale must sit within half an
     e4m3 step of the bf16 activation, and the scale must be amax / 448. Checked on the device."""
@@ -1770,6 +1804,28 @@ def test_gemm_fp8_consumes_the_norm_kernels_codes_and_device_scale(K, port):
     scale = float(host(sa)[0])
     exact, mag = _gemm_f64(host(codes), wq, scale, (0.01,), (), N)
     assert (np.abs(host(out) - exact) <= 1e-5 * mag).all()
+
+
+def test_gemm_fp8_empty_shard_still_validates_and_clears_the_fused_slot(K):
+    """M == 0 launches nothing, but the argument checks still run and the fused SwiGLU epilogue's
+    {scale, amax} slot does not keep the previous call's maximum."""
+    a = torch.zeros(8, 256, dtype=torch.uint8, device=DEV)[:0]
+    w = torch.zeros(64, 256, dtype=torch.uint8, device=DEV)
+    out = torch.empty(8, 32, dtype=torch.bfloat16, device=DEV)[:0]
+    slot = torch.tensor([3.0, 7.0], device=DEV)
+    assert K.gemm_fp8(a, w, out, w_scales=(1.0,), swiglu_scale_amax=slot) == 0
+    assert slot.tolist() == [0.0, 0.0]
+    out2 = torch.empty(8, 64, dtype=torch.bfloat16, device=DEV)[:0]
+    assert K.gemm_fp8(a, w, out2, w_scales=(1.0,)) == 0
+    from granite4_b200 import capi
+    ep = capi.GemmFp8Epilogue()
+    ep.w_scale0 = ep.w_scale1 = ep.w_scale2 = 1.0
+    ep.seg1 = ep.seg2 = 2 ** 31 - 1
+    ep.ldc = 64
+    import ctypes as C
+    lib = capi.lib()  # no output pointer of the requested kind: refused even with no rows
+    assert lib.granite4_kernel_gemm_fp8(capi.GEMM_OUT_BF16, None, 256, w.data_ptr(), 0, 64, 256, C.byref(ep), None, 0) == -1
+    assert lib.granite4_kernel_gemm_fp8(7, None, 256, w.data_ptr(), 0, 64, 256, C.byref(ep), None, 0) == -1
 
 
 def test_gemm_fp8_rejects_bad_arguments(K):

@@ -30,7 +30,7 @@ def _worker(rank, world, port, out_dir):
     w = lib.fill_bf16(3, 1.5, cols)
     h, n = lib.add_rmsnorm(y[lo:hi], res[lo:hi], w, 1e-5, 0.22)
     codes, scale, amax = lib.quant_fp8(n)
-    # gather for checking only (NCCL all_gather on the GPU box, after the timed region)
+    # gather for checking only: no collective belongs to the data path
     parts = [torch.empty(hi - lo, cols, dtype=torch.int32) for _ in range(world)]  # gloo has no int16
     dist.all_gather(parts, torch.from_numpy(h.astype(np.int32)))
     amaxes = [torch.zeros(1) for _ in range(world)]

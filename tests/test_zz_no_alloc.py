@@ -19,7 +19,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _run_both(K, rows, cols, seed, rm):
+def _bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _run_both(K, port, rows, cols, seed, rm):
     g = torch.Generator(device=DEV).manual_seed(seed)
     y = torch.randn(rows, cols, generator=g, device=DEV).to(torch.bfloat16)
     res = torch.randn(rows, cols, generator=g, device=DEV).to(torch.bfloat16)
@@ -43,16 +47,21 @@ def _run_both(K, rows, cols, seed, rm):
     assert torch.equal(c, c_ref)
     assert abs(sa[0].item() - sa_ref[0].item()) <= 1e-6 * abs(sa_ref[0].item())
     assert sa[1].item() == sa_ref[1].item()
+    # and, independently of the sibling entry point, against the CPU oracle
+    want_h, want_n = port.add_rmsnorm(_bits(y), _bits(res), _bits(w), 1e-5, rm)
+    codes, scale, amax = port.quant_fp8(want_n)
+    assert (_bits(h) == want_h).all() and (c.cpu().numpy() == codes).all()
+    assert sa[0].item() == scale and sa[1].item() == amax
 
 
-def test_noalloc_matches_the_regular_entry_point_twice_in_a_row():
+def test_noalloc_matches_the_regular_entry_point_twice_in_a_row(port):
     import granite4_b200  # noqa: F401
     from granite4_b200 import capi, kernels as K
     capi.lib()
     # two calls in a row share the library's scratch array; the second uses fewer rows, so stale
     # entries of the first remain in the array beyond its range and must not matter
-    _run_both(K, 700, 4096, seed=11, rm=0.22)
-    _run_both(K, 333, 4096, seed=12, rm=1.0)
+    _run_both(K, port, 700, 4096, seed=11, rm=0.22)
+    _run_both(K, port, 333, 4096, seed=12, rm=1.0)
     assert capi.lib().device_status() == 0
 
 
