@@ -81,6 +81,26 @@ SIGNATURES = {
     "granite4_kv_pool_ref_count": (C.c_int, [_vp, C.c_int]),
     "granite4_kv_pool_page_in_cache": (C.c_int, [_vp, C.c_int]),
     "granite4_kv_pool_move_rows": (C.c_int, [_vp, C.c_int, _vp, _vp, C.c_int, _vp, _vp]),
+    "granite4_kv_ctl_create": (_vp, [C.c_int, C.c_int]),
+    "granite4_kv_ctl_destroy": (None, [_vp]),
+    "granite4_kv_ctl_shutdown": (None, [_vp]),
+    "granite4_kv_ctl_pool": (_vp, [_vp]),
+    "granite4_kv_ctl_new_slot": (C.c_int, [_vp]),
+    "granite4_kv_ctl_release_slot": (None, [_vp, C.c_int]),
+    "granite4_kv_ctl_prefill": (C.c_int, [_vp, C.c_int, _vp, C.c_longlong, C.POINTER(C.c_int),
+                                          C.POINTER(C.c_longlong)]),
+    "granite4_kv_ctl_commit": (None, [_vp, C.c_int, _vp, C.c_longlong]),
+    "granite4_kv_ctl_open_slot": (C.c_int, [_vp]),
+    "granite4_kv_ctl_ensure": (C.c_int, [_vp, C.c_int, C.c_longlong]),
+    "granite4_kv_ctl_trim": (None, [_vp, C.c_int, C.c_longlong]),
+    "granite4_kv_ctl_drop": (None, [_vp, C.c_int]),
+    "granite4_kv_ctl_slot_pages": (C.c_longlong, [_vp, C.c_int]),
+    "granite4_kv_ctl_pages_missing": (C.c_longlong, [_vp, C.c_int, C.c_longlong]),
+    "granite4_kv_ctl_row_table": (C.c_int, [_vp, C.c_int, C.c_longlong, _vp]),
+    "granite4_kv_ctl_committed": (C.c_longlong, [_vp, C.c_int]),
+    "granite4_kv_ctl_last_reused": (C.c_longlong, [_vp, C.c_int]),
+    "granite4_kv_ctl_max_slots": (C.c_longlong, [_vp]),
+    "granite4_kv_ctl_count": (C.c_longlong, [_vp, C.c_int]),
     "granite4_attn_decode_scratch_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "granite4_kernel_attn_decode_int8_paged": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int,
                                                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

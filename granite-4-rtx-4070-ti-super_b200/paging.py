@@ -150,3 +150,84 @@ class KvPool:
         rc = self._lib.granite4_kv_pool_move_rows(self._p, seq, s.ctypes.data, d.ctypes.data, n, so.ctypes.data,
                                                   do.ctypes.data)
         return (so[:n], do[:n]) if rc == 0 else None
+
+
+class KvPoolController:
+    """The library's serve-loop controller over the pool (``granite4_kv_ctl_*``): the reference's
+    ``KvPoolController`` (``engine/src/kv_pool_controller.h:32-112``) behind the C ABI. Method
+    names and meanings are the reference's."""
+
+    def __init__(self, num_pages: int, tokens_per_page: int = TOKENS_PER_PAGE):
+        from . import capi
+        self._lib = capi.lib()
+        self._p = self._lib.granite4_kv_ctl_create(num_pages, tokens_per_page)
+        if not self._p:
+            raise ValueError("granite4_kv_ctl_create failed")
+        self.num_pages, self.tokens_per_page = num_pages, tokens_per_page
+
+    def close(self):
+        if getattr(self, "_p", None):
+            self._lib.granite4_kv_ctl_destroy(self._p)
+            self._p = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def new_slot(self) -> int:
+        return self._lib.granite4_kv_ctl_new_slot(self._p)
+
+    def release_slot(self, slot: int):
+        self._lib.granite4_kv_ctl_release_slot(self._p, slot)
+
+    def shutdown(self):
+        self._lib.granite4_kv_ctl_shutdown(self._p)
+
+    def prefill(self, slot: int, prompt):
+        """(ok, pool sequence id, page-aligned tokens already cached)."""
+        import ctypes as C
+        a, ptr, n = KvPool._tok(prompt)
+        seq, reused = C.c_int(-1), C.c_longlong(0)
+        ok = self._lib.granite4_kv_ctl_prefill(self._p, slot, ptr, n, C.byref(seq), C.byref(reused))
+        return bool(ok), seq.value, reused.value
+
+    def commit(self, slot: int, all_tokens):
+        a, ptr, n = KvPool._tok(all_tokens)
+        self._lib.granite4_kv_ctl_commit(self._p, slot, ptr, n)
+
+    def open_slot(self) -> int:
+        return self._lib.granite4_kv_ctl_open_slot(self._p)
+
+    def ensure(self, slot: int, n_tokens: int) -> bool:
+        return bool(self._lib.granite4_kv_ctl_ensure(self._p, slot, n_tokens))
+
+    def trim(self, slot: int, n_tokens: int):
+        self._lib.granite4_kv_ctl_trim(self._p, slot, n_tokens)
+
+    def drop(self, slot: int):
+        self._lib.granite4_kv_ctl_drop(self._p, slot)
+
+    def slot_pages(self, slot: int) -> int:
+        return self._lib.granite4_kv_ctl_slot_pages(self._p, slot)
+
+    def pages_missing(self, slot: int, n_tokens: int) -> int:
+        return self._lib.granite4_kv_ctl_pages_missing(self._p, slot, n_tokens)
+
+    def row_table(self, slot: int, n: int):
+        out = np.empty(max(n, 1), np.int32)
+        ok = self._lib.granite4_kv_ctl_row_table(self._p, slot, n, out.ctypes.data)
+        return out[:n] if ok else None
+
+    def committed(self, slot: int) -> int:
+        return self._lib.granite4_kv_ctl_committed(self._p, slot)
+
+    def last_reused(self, slot: int) -> int:
+        return self._lib.granite4_kv_ctl_last_reused(self._p, slot)
+
+    def max_slots(self) -> int:
+        return self._lib.granite4_kv_ctl_max_slots(self._p)
+
+    def count(self, name: str) -> int:
+        return self._lib.granite4_kv_ctl_count(self._p, KvPool.COUNTS[name])

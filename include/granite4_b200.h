@@ -379,6 +379,66 @@ int granite4_kv_pool_move_rows(const granite4_kv_pool* pool, int seq, const int*
                                const int* dst_pos, int n, int* src_rows, int* dst_rows);
 
 /* ------------------------------------------------------------------------ */
+/* Serve-loop controller over the pool: session slots (no device work)       */
+/* ------------------------------------------------------------------------ */
+/* Added; the reference's granite4::KvPoolController
+ * (engine/src/kv_pool_controller.h:32-112, engine/src/kv_pool_controller.cc)
+ * behind a C interface. It owns one pool and maps session slots (one per
+ * concurrent request; at most num_pages of them) to pool sequences. Same slot
+ * ids, return values, row tables and pool counts as the reference for the same
+ * sequence of calls.
+ *   new_slot      a slot id, or -1 when the pool has no sequence left. An idle
+ *                 slot (released earlier) is recycled first, lowest id first,
+ *                 and stays idle until prefill or open_slot puts it in use.
+ *   release_slot  ends a session: private pages freed, published pages stay
+ *                 cached; the id can be reused.
+ *   shutdown      frees everything and empties the cache; all slot ids die.
+ *   prefill       starts a request on a slot: drops what the slot held, adopts
+ *                 the cached page-aligned prefix of prompt[0..n), reserves the
+ *                 rest, publishes every full page. Returns 1 and writes the
+ *                 pool sequence id and the number of leading tokens whose KV
+ *                 is already in the pool rows the row table names (the GPU may
+ *                 skip them) to *seq_out / *reused_out (either may be NULL);
+ *                 0 when the pool cannot hold the prompt (the slot is left
+ *                 idle and clean, *seq_out = -1, *reused_out = 0).
+ *   commit        after a generated token, with the session's full id list:
+ *                 grows by a page at page boundaries, publishes pages as they
+ *                 fill; no effect when n does not exceed what is committed.
+ *   open_slot / ensure / trim / drop / pages_missing / slot_pages: resident
+ *                 sessions that never share pages - make a slot live, grow it
+ *                 to n_tokens (1, or 0 and nothing changed), hand back the
+ *                 pages past n_tokens, drop all pages, pages still needed for
+ *                 n_tokens, pages held.
+ *   row_table     out[p] = pool row of position p for p < n <= committed(slot):
+ *                 the d_pt / kv_rows table of the KV-write and attention entry
+ *                 points; rows of committed positions never move. 1 / 0.
+ *   count         granite4_kv_pool_count of the pool underneath (same enum);
+ *                 granite4_kv_ctl_pool exposes that pool for inspection and
+ *                 for granite4_kv_pool_move_rows (it stays owned by the
+ *                 controller). Not thread-safe. */
+typedef struct granite4_kv_ctl granite4_kv_ctl;
+granite4_kv_ctl* granite4_kv_ctl_create(int num_pages, int tokens_per_page);
+void granite4_kv_ctl_destroy(granite4_kv_ctl* ctl);
+void granite4_kv_ctl_shutdown(granite4_kv_ctl* ctl);
+granite4_kv_pool* granite4_kv_ctl_pool(granite4_kv_ctl* ctl);
+int granite4_kv_ctl_new_slot(granite4_kv_ctl* ctl);
+void granite4_kv_ctl_release_slot(granite4_kv_ctl* ctl, int slot);
+int granite4_kv_ctl_prefill(granite4_kv_ctl* ctl, int slot, const uint32_t* prompt, long long n,
+                            int* seq_out, long long* reused_out);
+void granite4_kv_ctl_commit(granite4_kv_ctl* ctl, int slot, const uint32_t* all_tokens, long long n);
+int granite4_kv_ctl_open_slot(granite4_kv_ctl* ctl);
+int granite4_kv_ctl_ensure(granite4_kv_ctl* ctl, int slot, long long n_tokens);
+void granite4_kv_ctl_trim(granite4_kv_ctl* ctl, int slot, long long n_tokens);
+void granite4_kv_ctl_drop(granite4_kv_ctl* ctl, int slot);
+long long granite4_kv_ctl_slot_pages(const granite4_kv_ctl* ctl, int slot);
+long long granite4_kv_ctl_pages_missing(const granite4_kv_ctl* ctl, int slot, long long n_tokens);
+int granite4_kv_ctl_row_table(const granite4_kv_ctl* ctl, int slot, long long n, int* out);
+long long granite4_kv_ctl_committed(const granite4_kv_ctl* ctl, int slot);
+long long granite4_kv_ctl_last_reused(const granite4_kv_ctl* ctl, int slot);
+long long granite4_kv_ctl_max_slots(const granite4_kv_ctl* ctl);
+long long granite4_kv_ctl_count(const granite4_kv_ctl* ctl, int which);
+
+/* ------------------------------------------------------------------------ */
 /* Decode / verify attention over the int8 paged pool                        */
 /* ------------------------------------------------------------------------ */
 /* Added; the int8 multi-sequence mode of granite4::attn_split
