@@ -105,6 +105,10 @@ SIGNATURES = {
     "granite4_kernel_attn_decode_int8_paged": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int,
                                                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                                          C.c_int, C.c_float, _vp, C.c_longlong, _vp]),
+    "granite4_attn_split_scratch_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
+    "granite4_attn_split_int8": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int,
+                                           _vp, C.c_int, C.c_int, _vp, C.c_longlong, _vp, _vp, C.c_int, _vp, _vp,
+                                           _vp, C.c_int, _vp, _vp, C.c_int]),
     "granite4_gemm_fp8_workspace_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
     "granite4_kernel_gemm_fp8": (C.c_int, [C.c_int, _vp, C.c_longlong, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp,
                                            C.c_longlong]),

@@ -51,6 +51,7 @@ constexpr int kGqa = 4;        // q heads per kv head
 constexpr int kGroupRows = 4;  // query rows of one sequence per CTA (two column tiles of 2 rows x 4 heads)
 constexpr int kSplitAlign = kTile * kWarps;
 constexpr int kCtasPerSm = 3;  // register budget with two column tiles (groups of three or four rows)
+constexpr int kTailStride = 8;  // engine/src/attention_gpu.h:52 (kAttnTailStride): a tree row has at most 8 ancestors
 
 // Shared memory of one warp: kStagesT tiles of raw K and V code rows, filled by 16-byte asynchronous
 // copies (cp.async), so the bytes in flight occupy no registers. Rows are padded to 144 bytes: the
@@ -66,10 +67,15 @@ struct AttnParams {
   const int8_t* cv;
   const float* ks;
   const float* vs;
-  const int* row_pos;        // per-row positions, or NULL: row r is at position base_pos + r
-  int base_pos;
+  const int* row_pos;        // per-row positions, or NULL: row r is at position base + r
+  int base_pos;              // base when d_pos is NULL
+  const int* d_pos;          // base read on the device, or NULL
   const int* const* row_pt;  // per-row tables, or NULL
   const int* pt;             // one table for every row, or NULL (identity)
+  const int* row_grp;        // per-group words r0 | nr << 8, or NULL: groups of group_rows consecutive rows
+  const int* row_tbase;      // tree rows: positions above row_tbase[r0] are the row's own ancestors' slots ...
+  const int* row_tail;       // ... row_tail[r * kTailStride + (position - tbase - 1)], both or neither
+  int window;                // > 0: a row attends to its last `window` positions only
   float* part_o;             // [groups][Hk][splits][16][128]
   float* part_ml;            // [groups][Hk][splits][16][2]
   uint16_t* out;
@@ -173,6 +179,19 @@ __device__ __forceinline__ void merge_warps(const AttnParams& p, const unsigned 
 // which is the S^T accumulator transposed by movmatrix). The softmax of a column runs down the
 // lanes (three xor shuffles over g). One column tile serves one or two query rows, two tiles
 // three or four; the K and V operands are converted once and feed every tile.
+// Rows [r0, r0 + nrows) of group `grp`: a row_grp word r0 | nr << 8 when the caller describes the
+// groups (engine/src/attention_split.cu:108-113), else group_rows consecutive rows.
+__device__ __forceinline__ void group_rows_of(const AttnParams& p, int grp, int cap, int& r0, int& nrows) {
+  if (p.row_grp != nullptr) {
+    const int w = __ldg(p.row_grp + grp);
+    r0 = w & 0xff;
+    nrows = max(0, min(min(w >> 8, cap), p.rows - r0));
+  } else {
+    r0 = grp * p.group_rows;
+    nrows = min(p.group_rows, p.rows - r0);
+  }
+}
+
 constexpr int kStagesT = 3;
 constexpr int kWarpSmemT = kStagesT * 2 * kRawTile;  // 13824
 constexpr size_t kAttnSmemBytesT = static_cast<size_t>(kWarps) * kWarpSmemT;
@@ -187,7 +206,8 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
 
 // NT column tiles of 8 columns: NT = 1 for groups of one or two query rows (4 CTAs per SM), NT = 2
 // for three or four (3 CTAs per SM). Column c = 4 j + hl stands for (query row j, head hl).
-template <int NT>
+// EXT: the launch has a window or tree rows; without it that code is compiled away.
+template <int NT, bool EXT>
 __global__ void __launch_bounds__(kWarps * 32, NT == 1 ? kCtasPerSmT : kCtasPerSm)
     attn_decode_t_kernel(const AttnParams p) {
   pdl_begin();
@@ -195,29 +215,41 @@ __global__ void __launch_bounds__(kWarps * 32, NT == 1 ? kCtasPerSmT : kCtasPerS
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, hkv = blockIdx.y, grp = blockIdx.z;
-  const int r0 = grp * p.group_rows;
-  const int nrows = min(p.group_rows, p.rows - r0);  // at most 2 NT
+  int r0, nrows;
+  group_rows_of(p, grp, 2 * NT, r0, nrows);
   unsigned char* wsm = s_dyn + static_cast<size_t>(warp) * kWarpSmemT;
   unsigned char* raw_k = wsm;
   unsigned char* raw_v = wsm + kStagesT * kRawTile;
 
   // As accumulator owner a thread has columns 8 nt + 2 t and 8 nt + 2 t + 1 of every tile nt (both of
   // query row 2 nt + t / 2); as B-operand owner it has column 8 nt + g.
-  int pos_col[NT], pos_max = -1, pos_min = INT_MAX;
+  // A column attends to logical positions [lo_col, pos_col]. Those up to `shared_max` (all of them
+  // unless the rows are tree rows) are the same pool rows for every row of the group and are walked
+  // as shared tiles; a tree row's positions above its tbase are its own ancestors' slots and come
+  // as one extra tile per row after the loop.
+  const int base = p.d_pos != nullptr ? __ldg(p.d_pos) : p.base_pos;
+  const int tb = (EXT && p.row_tbase != nullptr) ? __ldg(p.row_tbase + r0) : INT_MAX;
+  int pos_col[NT], lo_col[NT], pos_max = -1, pos_min = INT_MAX, lo_min = INT_MAX, lo_max = 0;
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) pos_col[nt] = -1;
+  for (int nt = 0; nt < NT; ++nt) pos_col[nt] = -1, lo_col[nt] = 0;
   for (int j = 0; j < nrows; ++j) {
-    int pj = p.row_pos != nullptr ? __ldg(p.row_pos + r0 + j) : p.base_pos + r0 + j;
+    int pj = p.row_pos != nullptr ? __ldg(p.row_pos + r0 + j) : base + r0 + j;
     pj = pj < 0 ? -1 : min(pj, p.max_len - 1);
+    const int lj = (EXT && p.window > 0) ? max(0, pj + 1 - p.window) : 0;
     pos_max = max(pos_max, pj);
     pos_min = min(pos_min, pj);
+    lo_min = min(lo_min, lj);
+    lo_max = max(lo_max, lj);
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
-      if (j == 2 * nt + (t >> 1)) pos_col[nt] = pj;
+      if (j == 2 * nt + (t >> 1)) pos_col[nt] = pj, lo_col[nt] = lj;
   }
+  const int shared_max = min(pos_max, tb);  // last logical position read through the shared tiles
   const int* pt = p.row_pt != nullptr ? p.row_pt[r0] : p.pt;
-  const int t_begin = split * p.split_len;
-  const int t_end = min(t_begin + p.split_len, pos_max + 1);
+  // whole 64-position steps below every row's window are skipped
+  const int t_begin = split * p.split_len +
+                      (EXT ? max(0, (lo_min - split * p.split_len) / (kTile * kWarps)) * (kTile * kWarps) : 0);
+  const int t_end = min(split * p.split_len + p.split_len, shared_max + 1);
 
   // ---- q as the B operand: (dims 16 kk + 4 t .. + 3 of column 8 nt + g), fp16, scaled by a power of two
   uint32_t qb[NT][8][2];
@@ -311,19 +343,12 @@ __global__ void __launch_bounds__(kWarps * 32, NT == 1 ? kCtasPerSmT : kCtasPerS
   int prow_next = table_row(t_first + 2 * kStep);
   int stage = 0;
 
-  for (int t0 = t_first; t0 < t_end; t0 += kStep) {
-    cp_async_wait<kStagesT - 2>();
-    __syncwarp();
-    gather((stage + kStagesT - 1) % kStagesT, t0 + (kStagesT - 1) * kStep, prow_next, sk_q[kStagesT - 1],
-           sv_q[kStagesT - 1]);
-    prow_next = table_row(t0 + kStagesT * kStep);
-    const float sk_cur = sk_q[0], sv_cur = sv_q[0];
-#pragma unroll
-    for (int i = 0; i + 1 < kStagesT; ++i) sk_q[i] = sk_q[i + 1], sv_q[i] = sv_q[i + 1];
-    const unsigned char* kstage = raw_k + stage * kRawTile;
-    const unsigned char* vstage = raw_v + stage * kRawTile;
-    stage = (stage + 1) % kStagesT;
-
+  // One tile of 16 positions (raw code rows at kstage / vstage, their scales in lanes 0-15 of sk_cur /
+  // sv_cur) against every column. ok_lo / ok_hi: whether position g / g + 8 of the tile counts for
+  // the accumulator columns of tile nt this thread owns; unmasked: every position counts for every
+  // column (warp-uniform).
+  auto attend = [&](const unsigned char* kstage, const unsigned char* vstage, float sk_cur, float sv_cur,
+                    bool unmasked, const bool (&okl)[NT], const bool (&okh)[NT]) {
     // ---- S^T = K Q^T: rows = positions g and g + 8; the K operand is converted once per k-step and
     // serves every column tile
     float sa[NT][4], sb[NT][4];
@@ -345,14 +370,13 @@ __global__ void __launch_bounds__(kWarps * 32, NT == 1 ? kCtasPerSmT : kCtasPerS
     const float f_lo = __shfl_sync(0xffffffffu, sk_cur, g) * logit_scale;
     const float f_hi = __shfl_sync(0xffffffffu, sk_cur, g + 8) * logit_scale;
     const float sv_lo = __shfl_sync(0xffffffffu, sv_cur, g), sv_hi = __shfl_sync(0xffffffffu, sv_cur, g + 8);
-    const bool unmasked = t0 + kTile <= t_end && t0 + kTile - 1 <= pos_min;  // warp-uniform
     uint32_t b0[NT], b1[NT];
     bool rescale = false;
     float corr[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const bool ok_lo = unmasked || (t0 + g <= pos_col[nt] && t0 + g < t_end);
-      const bool ok_hi = unmasked || (t0 + g + 8 <= pos_col[nt] && t0 + g + 8 < t_end);
+      const bool ok_lo = unmasked || okl[nt];
+      const bool ok_hi = unmasked || okh[nt];
       float pr[4];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
@@ -412,10 +436,72 @@ __global__ void __launch_bounds__(kWarps * 32, NT == 1 ? kCtasPerSmT : kCtasPerS
     const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) mma_f16(osum[nt], ones, b0[nt], b1[nt]);  // sum over the positions of P^T's columns
+  };
+
+  for (int t0 = t_first; t0 < t_end; t0 += kStep) {
+    cp_async_wait<kStagesT - 2>();
+    __syncwarp();
+    gather((stage + kStagesT - 1) % kStagesT, t0 + (kStagesT - 1) * kStep, prow_next, sk_q[kStagesT - 1],
+           sv_q[kStagesT - 1]);
+    prow_next = table_row(t0 + kStagesT * kStep);
+    const float sk_cur = sk_q[0], sv_cur = sv_q[0];
+#pragma unroll
+    for (int i = 0; i + 1 < kStagesT; ++i) sk_q[i] = sk_q[i + 1], sv_q[i] = sv_q[i + 1];
+    const unsigned char* kstage = raw_k + stage * kRawTile;
+    const unsigned char* vstage = raw_v + stage * kRawTile;
+    stage = (stage + 1) % kStagesT;
+    const bool unmasked = t0 + kTile <= t_end && t0 + kTile - 1 <= pos_min && (!EXT || t0 >= lo_max);  // warp-uniform
+    bool okl[NT], okh[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      okl[nt] = t0 + g <= pos_col[nt] && (!EXT || t0 + g >= lo_col[nt]) && t0 + g < t_end;
+      okh[nt] = t0 + g + 8 <= pos_col[nt] && (!EXT || t0 + g + 8 >= lo_col[nt]) && t0 + g + 8 < t_end;
+    }
+    attend(kstage, vstage, sk_cur, sv_cur, unmasked, okl, okh);
   }
 
   cp_async_wait<0>();
   __syncwarp();
+  // Tree rows: row j's positions tbase + 1 .. pos_j are the slots of its own ancestors (at most
+  // kTailStride of them). They form one more tile that only row j's columns attend to; warp j of
+  // the first split's CTA takes it (a group has at most four rows, a CTA four warps).
+  if (EXT && p.row_tail != nullptr && split == 0 && warp < nrows) {
+    const int j = warp;
+    int pj = __ldg(p.row_pos + r0 + j);
+    pj = pj < 0 ? -1 : min(pj, p.max_len - 1);
+    const int cnt = min(max(pj - tb, 0), kTailStride);
+    if (cnt > 0) {
+      const int n = lane & 15;
+      int prow = 0;
+      if (n < cnt) {
+        const int slot = __ldg(p.row_tail + static_cast<size_t>(r0 + j) * kTailStride + n);
+        prow = pt != nullptr ? __ldg(pt + slot) : slot;
+        prow = min(max(prow, 0), static_cast<int>(p.stride) - 1);
+      }
+      const int piece = (lane & 7) * 16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int nn = 4 * i + (lane >> 3);
+        const int pr = __shfl_sync(0xffffffffu, prow, nn);
+        const size_t off = (head_row0 + pr) * kAD + piece;
+        cp_async16(raw_k + nn * kPitch + piece, p.ck + off, nn < cnt);
+        cp_async16(raw_v + nn * kPitch + piece, p.cv + off, nn < cnt);
+      }
+      cp_async_commit();
+      const float sk_t = n < cnt ? __ldg(p.ks + head_row0 + prow) : 0.0f;
+      const float sv_t = n < cnt ? __ldg(p.vs + head_row0 + prow) : 0.0f;
+      cp_async_wait<0>();
+      __syncwarp();
+      bool okl[NT], okh[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        okl[nt] = j == 2 * nt + (t >> 1) && g < cnt && tb + 1 + g >= lo_col[nt];
+        okh[nt] = false;
+      }
+      attend(raw_k, raw_v, sk_t, sv_t, false, okl, okh);
+      __syncwarp();
+    }
+  }
   float* wo = reinterpret_cast<float*>(wsm);  // [16][128]; only the rows of live columns are read
   float* wml = wo + 16 * kAD;
 #pragma unroll
@@ -450,8 +536,8 @@ constexpr int kMaxSplits = 512;
 __global__ void __launch_bounds__(kAD) attn_combine_kernel(const AttnParams p) {
   pdl_begin();
   const int hkv = blockIdx.x, grp = blockIdx.y, m = blockIdx.z, dim = threadIdx.x;
-  const int r0 = grp * p.group_rows;
-  const int nrows = min(p.group_rows, p.rows - r0);
+  int r0, nrows;
+  group_rows_of(p, grp, kGroupRows, r0, nrows);
   if (m >= 4 * nrows) return;
   const int j = m >> 2, hl = m & 3;
   const size_t part0 = (static_cast<size_t>(grp) * p.Hk + hkv) * p.splits;
@@ -518,10 +604,10 @@ struct SplitPlan {
   int groups, splits, split_len;
 };
 
-SplitPlan plan_splits(int rows, int group_rows, int Hk, int max_len) {
+SplitPlan plan_splits_for_groups(int groups, int group_rows, int Hk, int max_len) {
   const int ctas_per_sm = group_rows <= 2 ? kCtasPerSmT : kCtasPerSm;
   SplitPlan s{};
-  s.groups = (rows + group_rows - 1) / group_rows;
+  s.groups = groups;
   const int tiles = (max_len + kSplitAlign - 1) / kSplitAlign;  // units of 64 positions
   // aim at one resident wave over the whole launch, at least 64 positions per split
   const long long ctas_wanted = static_cast<long long>(ctas_per_sm) * sm_count();
@@ -533,6 +619,15 @@ SplitPlan plan_splits(int rows, int group_rows, int Hk, int max_len) {
   s.split_len = tiles_per_split * kSplitAlign;
   s.splits = (tiles + tiles_per_split - 1) / tiles_per_split;
   return s;
+}
+
+SplitPlan plan_splits(int rows, int group_rows, int Hk, int max_len) {
+  return plan_splits_for_groups((rows + group_rows - 1) / group_rows, group_rows, Hk, max_len);
+}
+
+// Partial states of every (group, kv head, split): [16][128] O and [16][2] (max, sum), f32.
+long long scratch_bytes_of(const SplitPlan& s, int Hk) {
+  return static_cast<long long>(s.groups) * Hk * s.splits * 16 * (kAD + 2) * static_cast<long long>(sizeof(float));
 }
 
 }  // namespace
@@ -548,39 +643,59 @@ int attn_prefill_flash(const char* fn, const uint16_t* d_q, float scale, int Hq,
 }  // namespace g4
 
 namespace g4 {
-// Validation, split plan and launches shared by the entry points. d_row_pos NULL: row r is at
-// base_pos + r. single_split_without_scratch: a caller that has no scratch to give (the reference's
+// Everything the launch needs beyond the caches: the reference's attn_split arguments
+// (engine/src/attention_gpu.h:39-68) that select where each row sits and what it may see.
+struct AttnRows {
+  const int* d_row_pos = nullptr;        // per-row positions; NULL: row r is at base + r
+  int base_pos = 0;                      // base when d_pos is NULL
+  const int* d_pos = nullptr;            // base read on the device
+  const int* const* d_row_pt = nullptr;  // per-row (per-group) tables
+  const int* d_pt = nullptr;             // one table for every row
+  const int* d_row_grp = nullptr;        // group words r0 | nr << 8 ...
+  int ngroups = 0;                       // ... and how many
+  const int* d_row_tbase = nullptr;      // tree rows
+  const int* d_row_tail = nullptr;
+  int window = 0;
+};
+
+// Validation, split plan and launches shared by the entry points.
+// single_split_without_scratch: a caller that has no scratch to give (the reference's
 // prefill signature) gets one split over the whole range instead of an error.
 int attn_launch(const char* fn, const uint16_t* d_q, const int8_t* d_cache_k, const int8_t* d_cache_v,
-                const float* d_k_scale, const float* d_v_scale, const int* d_row_pos, int base_pos,
-                const int* const* d_row_pt, const int* d_pt, int rows, int rows_per_group, int Hq, int Hk, int d,
-                int stride, int max_len, float scale, void* d_scratch, long long scratch_bytes, uint16_t* d_out,
-                bool single_split_without_scratch) {
+                const float* d_k_scale, const float* d_v_scale, const AttnRows& r, int rows, int rows_per_group,
+                int Hq, int Hk, int d, int stride, int max_len, float scale, void* d_scratch, long long scratch_bytes,
+                uint16_t* d_out, bool single_split_without_scratch) {
   if (d_q == nullptr || d_cache_k == nullptr || d_cache_v == nullptr || d_k_scale == nullptr ||
       d_v_scale == nullptr || d_out == nullptr || rows <= 0 ||
       rows_per_group <= 0 || rows_per_group > kGroupRows || stride <= 0 || max_len <= 0 ||
-      max_len > stride || !std::isfinite(scale))
+      max_len > stride || !std::isfinite(scale) || r.window < 0)
     return fail(fn, "invalid arguments");
+  // the reference's own argument rules (engine/src/attention_split.cu:1098-1105)
+  if ((r.d_row_grp != nullptr && (r.d_row_pos == nullptr || r.ngroups <= 0 || r.ngroups > rows || rows > 256)) ||
+      ((r.d_row_tbase != nullptr) != (r.d_row_tail != nullptr)) || (r.d_row_tbase != nullptr && r.d_row_pos == nullptr))
+    return fail(fn, "row groups and tree rows need per-row positions; tbase and tail come together");
   if (d != kAD || Hk <= 0 || Hq != kGqa * Hk) return -1;  // engine/src/attention_gpu.h:18-19
   if (!aligned16(d_cache_k) || !aligned16(d_cache_v) || !aligned16(d_q))
     return fail(fn, "q and the caches must be 16-byte aligned");
   SplitPlan s = plan_splits(rows, rows_per_group, Hk, max_len);
-  if (s.splits > 1 && single_split_without_scratch &&
-      (d_scratch == nullptr || scratch_bytes < granite4_attn_decode_scratch_bytes(rows, rows_per_group, Hk, max_len))) {
+  if (r.d_row_grp != nullptr) s = plan_splits_for_groups(r.ngroups, rows_per_group, Hk, max_len);
+  const long long need = scratch_bytes_of(s, Hk);
+  if (s.splits > 1 && single_split_without_scratch && (d_scratch == nullptr || scratch_bytes < need)) {
     s.splits = 1;
     s.split_len = (max_len + kSplitAlign - 1) / kSplitAlign * kSplitAlign;
   }
   if (s.groups > 65535) return fail(fn, "too many row groups");
   AttnParams p{};
   p.q = d_q, p.ck = d_cache_k, p.cv = d_cache_v, p.ks = d_k_scale, p.vs = d_v_scale;
-  p.row_pos = d_row_pos, p.base_pos = base_pos, p.row_pt = d_row_pt, p.pt = d_pt, p.out = d_out;
+  p.row_pos = r.d_row_pos, p.base_pos = r.base_pos, p.d_pos = r.d_pos, p.row_pt = r.d_row_pt, p.pt = r.d_pt;
+  p.row_grp = r.d_row_grp, p.row_tbase = r.d_row_tbase, p.row_tail = r.d_row_tail, p.window = r.window;
+  p.out = d_out;
   p.rows = rows, p.group_rows = rows_per_group, p.Hq = Hq, p.Hk = Hk, p.stride = stride;
   p.splits = s.splits, p.split_len = s.split_len, p.max_len = max_len;
   p.scale_log2 = scale * 1.4426950408889634f;
   if (s.splits > 1) {
-    const long long need = granite4_attn_decode_scratch_bytes(rows, rows_per_group, Hk, max_len);
     if (d_scratch == nullptr || scratch_bytes < need || !aligned16(d_scratch))
-      return fail(fn, "scratch missing or smaller than granite4_attn_decode_scratch_bytes()");
+      return fail(fn, "scratch missing or smaller than the size the scratch query returns");
     p.part_o = static_cast<float*>(d_scratch);
     p.part_ml = p.part_o + static_cast<size_t>(s.groups) * Hk * s.splits * 16 * kAD;
   }
@@ -590,18 +705,23 @@ int attn_launch(const char* fn, const uint16_t* d_q, const int8_t* d_cache_k, co
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess) return fail(fn, "cannot identify the current device");
     if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_relaxed)) {
-      G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(kAttnSmemBytesT)));
-      G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(kAttnSmemBytesT)));
+      const int bytes = static_cast<int>(kAttnSmemBytesT);
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+      G4_CUDA_TRY(fn, cudaFuncSetAttribute(attn_decode_t_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
       attr_set[dev].store(true, std::memory_order_relaxed);
     }
   }
   const dim3 grid(static_cast<unsigned>(s.splits), static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups));
-  if (rows_per_group <= 2)
-    G4_LAUNCH_PDL(fn, attn_decode_t_kernel<1>, grid, dim3(kWarps * 32), kAttnSmemBytesT, st, p);
-  else
-    G4_LAUNCH_PDL(fn, attn_decode_t_kernel<2>, grid, dim3(kWarps * 32), kAttnSmemBytesT, st, p);
+  const bool ext = r.window > 0 || r.d_row_tail != nullptr;
+  if (rows_per_group <= 2) {
+    if (ext) G4_LAUNCH_PDL(fn, (attn_decode_t_kernel<1, true>), grid, dim3(kWarps * 32), kAttnSmemBytesT, st, p);
+    else G4_LAUNCH_PDL(fn, (attn_decode_t_kernel<1, false>), grid, dim3(kWarps * 32), kAttnSmemBytesT, st, p);
+  } else {
+    if (ext) G4_LAUNCH_PDL(fn, (attn_decode_t_kernel<2, true>), grid, dim3(kWarps * 32), kAttnSmemBytesT, st, p);
+    else G4_LAUNCH_PDL(fn, (attn_decode_t_kernel<2, false>), grid, dim3(kWarps * 32), kAttnSmemBytesT, st, p);
+  }
   if (s.splits > 1)
     G4_LAUNCH_PDL(fn, attn_combine_kernel,
                   dim3(static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups), 4u * rows_per_group),
@@ -616,8 +736,7 @@ extern "C" {
 long long granite4_attn_decode_scratch_bytes(int rows, int rows_per_group, int Hk, int max_len) {
   if (rows <= 0 || rows_per_group <= 0 || rows_per_group > g4::kGroupRows || Hk <= 0 || max_len <= 0)
     return -1;
-  const g4::SplitPlan s = g4::plan_splits(rows, rows_per_group, Hk, max_len);
-  return static_cast<long long>(s.groups) * Hk * s.splits * 16 * (g4::kAD + 2) * static_cast<long long>(sizeof(float));
+  return g4::scratch_bytes_of(g4::plan_splits(rows, rows_per_group, Hk, max_len), Hk);
 }
 
 int granite4_kernel_attn_decode_int8_paged(const uint16_t* d_q, const int8_t* d_cache_k,
@@ -629,8 +748,47 @@ int granite4_kernel_attn_decode_int8_paged(const uint16_t* d_q, const int8_t* d_
                                            long long scratch_bytes, uint16_t* d_out) {
   const char* fn = "granite4_kernel_attn_decode_int8_paged";
   if (d_row_pos == nullptr) return g4::fail(fn, "invalid arguments");
-  return g4::attn_launch(fn, d_q, d_cache_k, d_cache_v, d_k_scale, d_v_scale, d_row_pos, 0, d_row_pt, d_pt, rows,
-                         rows_per_group, Hq, Hk, d, stride, max_len, scale, d_scratch, scratch_bytes, d_out, false);
+  g4::AttnRows r;
+  r.d_row_pos = d_row_pos, r.d_row_pt = d_row_pt, r.d_pt = d_pt;
+  return g4::attn_launch(fn, d_q, d_cache_k, d_cache_v, d_k_scale, d_v_scale, r, rows, rows_per_group, Hq, Hk, d,
+                         stride, max_len, scale, d_scratch, scratch_bytes, d_out, false);
+}
+
+// Upper bound over every way the rows may be grouped (one group of up to four consecutive rows
+// per sequence, or one group per row), so that a caller can size the scratch before it knows the
+// grouping, as with the reference's attn_split_scratch_bytes(Hq, rows, stride).
+long long granite4_attn_split_scratch_bytes(int Hq, int rows, int max_len) {
+  if (Hq <= 0 || Hq % g4::kGqa != 0 || rows <= 0 || max_len <= 0) return -1;
+  const int Hk = Hq / g4::kGqa;
+  long long need = 0;
+  for (int groups = 1; groups <= rows; ++groups)
+    for (int per = 1; per <= g4::kGroupRows; per += 2)  // the two kernel forms plan differently
+      need = std::max(need, g4::scratch_bytes_of(g4::plan_splits_for_groups(groups, per == 1 ? 1 : g4::kGroupRows, Hk, max_len), Hk));
+  return need;
+}
+
+int granite4_attn_split_int8(const uint16_t* d_q, const int8_t* d_cache_k8, const int8_t* d_cache_v8,
+                             const float* d_k_scale, const float* d_v_scale, float scale, int Hq, int Hk, int d,
+                             int kv_base, const int* d_pos, int rows, int stride, void* d_scratch,
+                             long long scratch_bytes, uint16_t* d_out, const int* d_pt, int max_len,
+                             const int* d_row_pos, const int* const* d_row_pt, const int* d_row_grp, int ngroups,
+                             const int* d_row_tbase, const int* d_row_tail, int window) {
+  const char* fn = "granite4_attn_split_int8";
+  const int ml = max_len > 0 ? max_len : stride;
+  // engine/src/attention_split.cu:1096-1105
+  if (rows <= 0 || rows > GRANITE4_MAX_VERIFY_ROWS || stride <= 0 || ml > stride ||
+      (d_pos == nullptr && d_row_pos == nullptr && (kv_base < 0 || kv_base + rows > ml)) ||
+      ((d_row_pos == nullptr) != (d_row_pt == nullptr)))
+    return g4::fail(fn, "invalid arguments");
+  g4::AttnRows r;
+  r.d_row_pos = d_row_pos, r.base_pos = kv_base, r.d_pos = d_pos, r.d_row_pt = d_row_pt, r.d_pt = d_pt;
+  r.d_row_grp = d_row_grp, r.ngroups = ngroups, r.d_row_tbase = d_row_tbase, r.d_row_tail = d_row_tail;
+  r.window = window;
+  // rows of one sequence at consecutive positions share tiles in groups of four; rows that are
+  // sequences of their own are one group each unless the caller's group words say otherwise
+  const int per_group = (d_row_pos == nullptr || d_row_grp != nullptr) ? g4::kGroupRows : 1;
+  return g4::attn_launch(fn, d_q, d_cache_k8, d_cache_v8, d_k_scale, d_v_scale, r, rows, per_group, Hq, Hk, d, stride,
+                         ml, scale, d_scratch, scratch_bytes, d_out, false);
 }
 
 int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq, int Hk, int d, int base_pos,
@@ -653,9 +811,10 @@ int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq
     return g4::attn_prefill_flash(fn, d_q_rot, scale, Hq, Hk, base_pos, rows, stride, d_out, d_cache_k8, d_cache_v8,
                                   d_k_scale, d_v_scale, d_pt);
   }
-  return g4::attn_launch(fn, d_q_rot, d_cache_k8, d_cache_v8, d_k_scale, d_v_scale, nullptr, base_pos, nullptr, d_pt,
-                         rows, g4::kGroupRows, Hq, Hk, d, stride, base_pos + rows, scale, d_scratch, scratch_bytes,
-                         d_out, true);
+  g4::AttnRows r;
+  r.base_pos = base_pos, r.d_pt = d_pt;
+  return g4::attn_launch(fn, d_q_rot, d_cache_k8, d_cache_v8, d_k_scale, d_v_scale, r, rows, g4::kGroupRows, Hq, Hk, d,
+                         stride, base_pos + rows, scale, d_scratch, scratch_bytes, d_out, true);
 }
 
 }  // extern "C"
@@ -673,5 +832,30 @@ int prefill_attention(const std::uint16_t* q_rot, const std::uint16_t* cache_k, 
   if (!int8 || int4 || k5 || window > 0) return -1;
   return granite4_prefill_attention_int8(q_rot, scale, Hq, Hk, d, base_pos, rows, stride, out, cache_k8, cache_v8,
                                          k_scale, v_scale, d_pt, nullptr, 0);
+}
+}  // namespace granite4
+
+// The reference's split-KV entry points (engine/src/attention_gpu.h:13, :53-66), same mangled names.
+// Only the int8 cache is built: the bf16, int4 and K5 forms return -1, which the reference's callers
+// treat as "take the other attention path".
+namespace granite4 {
+std::size_t attn_split_scratch_bytes(int Hq, int rows, int stride) {
+  const long long n = granite4_attn_split_scratch_bytes(Hq, rows, stride);
+  return n < 0 ? 0 : static_cast<std::size_t>(n);
+}
+int attn_split(const std::uint16_t* q, const std::uint16_t* cache_k, const std::uint16_t* cache_v, float scale, int Hq,
+               int Hk, int d, int kv_base, const int* d_pos, int rows, int stride, void* scratch, std::uint16_t* out,
+               const std::int8_t* cache_k8, const std::int8_t* cache_v8, const float* cache_k_scale,
+               const float* cache_v_scale, bool int8, const std::uint8_t* cache_k4, const std::uint8_t* cache_v4,
+               bool int4, const int* d_pt, int max_len, const int* row_pos, const int* const* row_pt,
+               const int* row_grp, int ngroups, const int* row_tbase, const int* row_tail, int kv_hint, bool k5,
+               int window) {
+  (void)cache_k, (void)cache_v, (void)cache_k4, (void)cache_v4, (void)kv_hint;
+  if (!int8 || int4 || k5 || scratch == nullptr) return -1;
+  // the reference's callers size the scratch with attn_split_scratch_bytes(Hq, rows, stride)
+  const long long have = granite4_attn_split_scratch_bytes(Hq, rows, stride);
+  return granite4_attn_split_int8(q, cache_k8, cache_v8, cache_k_scale, cache_v_scale, scale, Hq, Hk, d, kv_base, d_pos,
+                                  rows, stride, scratch, have, out, d_pt, max_len, row_pos, row_pt, row_grp, ngroups,
+                                  row_tbase, row_tail, window);
 }
 }  // namespace granite4

@@ -1052,9 +1052,10 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
   if (fused_swiglu && (N % 2 != 0 || ep->d_out_scale_amax == nullptr))
     return fail(fn, "the fused SwiGLU needs an even N (gate rows, then up rows) and d_out_scale_amax");
   if (ep->ldc < (fused_swiglu ? N / 2 : N)) return fail(fn, "ldc smaller than the output row");
-  if (out_kind == GRANITE4_GEMM_OUT_F32 ? ep->d_out_f32 == nullptr : ep->d_out_bf16 == nullptr)
+  // (with no rows there is nothing to read or write: A, the output and the residual may be null)
+  if (M != 0 && (out_kind == GRANITE4_GEMM_OUT_F32 ? ep->d_out_f32 == nullptr : ep->d_out_bf16 == nullptr))
     return fail(fn, "the output of the requested kind is null");
-  if (out_kind == GRANITE4_GEMM_OUT_RESIDUAL && ep->d_residual == nullptr) return fail(fn, "null residual");
+  if (M != 0 && out_kind == GRANITE4_GEMM_OUT_RESIDUAL && ep->d_residual == nullptr) return fail(fn, "null residual");
   if (d_ws != nullptr && !aligned16(d_ws)) return fail(fn, "the workspace must be 16-byte aligned");
   if (M == 0) {
     // no rows: the only effect is on the fused epilogue's {scale, amax} slot, which must not keep a

@@ -65,7 +65,7 @@ int sm_count() {
 float l2_keep_fraction(double bytes) {
   static const int keep_mb = [] {
     const char* v = std::getenv("G4_L2_KEEP_MB");
-    return (v != nullptr && *v != '\0') ? std::atoi(v) : 64;
+    return (v != nullptr && *v != '\0') ? std::atoi(v) : 0;
   }();
   if (keep_mb <= 0 || bytes <= 0.0) return 0.0f;
   const double f = static_cast<double>(keep_mb) * 1048576.0 / bytes;

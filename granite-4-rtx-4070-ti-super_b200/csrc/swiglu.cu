@@ -48,7 +48,6 @@ struct SwigluParams {
   long long items;     // rows * I / 8
   unsigned ipr;        // items per row = I / 8
   int contiguous;      // ld == I: item index is the element offset / 8
-  float keep;          // > 0: fraction of the bf16 intermediate to hold in L2 for the encode sweep
 };
 
 enum { kAmax = 0, kEncode = 1, kPlain = 2 };
@@ -92,8 +91,6 @@ __global__ void __launch_bounds__(kThreads) swiglu_kernel(const SwigluParams p) 
     fs = fp8_scale_from_amax(__ldcg(p.scale_amax + 1));
     if (blockIdx.x == 0 && threadIdx.x == 0) p.scale_amax[0] = fs.scale;
   }
-  const bool keep = p.keep > 0.0f && (MODE == kAmax || FROM_BF16);
-  const uint64_t pol = !keep ? 0ull : (MODE == kAmax ? l2_policy_evict_last(p.keep) : l2_policy_evict_first());
   long long item[kUnroll];
   uint4 a[kUnroll];
   uint4 graw[kUnroll], uraw[kUnroll];  // bf16 inputs: every load is issued before any math
@@ -108,8 +105,7 @@ __global__ void __launch_bounds__(kThreads) swiglu_kernel(const SwigluParams p) 
     if (MODE == kEncode) it = p.items - 1 - it;  // backwards
     item[k] = it;
     if (FROM_BF16) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.act_bf16) + it;
-      a[k] = keep ? ld_l2_hint(src, pol) : ld_stream(src);
+      a[k] = ld_stream(reinterpret_cast<const uint4*>(p.act_bf16) + it);
     } else if (F32) {
       a[k] = swiglu8<true>(p.gate, p.up, item_offset(p, it));
     } else {
@@ -138,10 +134,7 @@ __global__ void __launch_bounds__(kThreads) swiglu_kernel(const SwigluParams p) 
     } else {
       if (p.act_bf16 != nullptr) {
         uint4* dst = reinterpret_cast<uint4*>(p.act_bf16) + item[k];
-        // kAmax: re-read by the encode sweep
-        if (MODE != kAmax) st_stream(dst, a[k]);
-        else if (keep) st_l2_hint(dst, a[k], pol);
-        else *dst = a[k];
+        if (MODE == kAmax) *dst = a[k]; else st_stream(dst, a[k]);  // kAmax: re-read by the encode sweep
       }
       if (MODE == kAmax) amax = amax_acc(amax, a[k]);
     }
@@ -205,17 +198,8 @@ __global__ void __launch_bounds__(256)
   act[idx] = static_cast<uint16_t>(f32_to_bf16_bits(swiglu(gu[r * 2 * I + i], gu[r * 2 * I + I + i])));
 }
 
-// G4_L2_KEEP_SWIGLU=0 leaves SwiGLU's bf16 intermediate on the default cache policy (A/B runs).
-bool swiglu_keep_enabled() {
-  static const bool on = [] {
-    const char* v = std::getenv("G4_L2_KEEP_SWIGLU");
-    return !(v != nullptr && v[0] == '0');
-  }();
-  return on;
-}
-
 template <bool F32>
-int launch_swiglu(const char* fn, SwigluParams p) {
+int launch_swiglu(const char* fn, const SwigluParams& p) {
   cudaStream_t st = current_stream();
   const long long tiles = (p.items + kThreads * kUnroll - 1) / (kThreads * kUnroll);
   if (tiles > INT_MAX || p.items > 0xffffffffLL) return fail(fn, "tensor too large");
@@ -235,7 +219,6 @@ int launch_swiglu(const char* fn, SwigluParams p) {
     // the device cannot place such a cluster: the multi-launch form below takes over
   }
   if (!amax_prezeroed()) G4_CUDA_TRY(fn, cudaMemsetAsync(p.scale_amax, 0, 2 * sizeof(float), st));
-  p.keep = (p.act_bf16 != nullptr && swiglu_keep_enabled()) ? l2_keep_fraction(static_cast<double>(p.items) * 16.0) : 0.0f;
   G4_LAUNCH_PDL(fn, swiglu_kernel<F32, kAmax, false>, dim3(grid), dim3(kThreads), 0, st, p);
   if (p.act_bf16 != nullptr)
     G4_LAUNCH_PDL(fn, swiglu_kernel<F32, kEncode, true>, dim3(grid), dim3(kThreads), 0, st, p);

@@ -315,6 +315,25 @@ def attn_decode_int8_paged(q, cache_k, cache_v, k_scale, v_scale, row_pos, Hq, H
         _p(scratch, torch.uint8), 0 if scratch is None else scratch.numel(), _p(out, *_BF16_OK))
 
 
+def attn_split_int8(q, cache_k, cache_v, k_scale, v_scale, scale, Hq, Hk, d, stride, out, kv_base=0, d_pos=None,
+                    pt=None, max_len=0, row_pos=None, row_pt=None, row_grp=None, row_tbase=None, row_tail=None,
+                    window=0, scratch=None):
+    """granite4_attn_split_int8: the reference's attn_split contract (engine/src/attention_gpu.h:39-68)
+    over the int8 pool. row_pt: int64 CUDA tensor of per-row table addresses; row_grp: int32 group
+    words r0 | nr << 8; row_tbase int32 [rows], row_tail int32 [rows][8]."""
+    lib = _enter(q)
+    rows = q.shape[0]
+    need = lib.granite4_attn_split_scratch_bytes(Hq, rows, max_len if max_len > 0 else stride)
+    if scratch is None:
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    return lib.granite4_attn_split_int8(
+        _p(q, *_BF16_OK), _p(cache_k, torch.int8), _p(cache_v, torch.int8), _p(k_scale, torch.float32),
+        _p(v_scale, torch.float32), scale, Hq, Hk, d, kv_base, _p(d_pos, torch.int32), rows, stride,
+        _p(scratch, torch.uint8), scratch.numel(), _p(out, *_BF16_OK), _p(pt, torch.int32), max_len,
+        _p(row_pos, torch.int32), _p(row_pt, torch.int64), _p(row_grp, torch.int32),
+        0 if row_grp is None else row_grp.numel(), _p(row_tbase, torch.int32), _p(row_tail, torch.int32), window)
+
+
 def prefill_attention_int8(q_rot, scale, Hq, Hk, d, base_pos, stride, out, cache_k, cache_v, k_scale, v_scale,
                            pt=None, scratch=None):
     """granite4_prefill_attention_int8 (engine/src/prefill_gemm.h:86-101 with the int8 cache): causal

@@ -467,6 +467,41 @@ int granite4_kernel_attn_decode_int8_paged(const uint16_t* d_q, const int8_t* d_
                                            int max_len, float scale, void* d_scratch,
                                            long long scratch_bytes, uint16_t* d_out);
 
+/* The reference's split-KV contract (granite4::attn_split, engine/src/attention_gpu.h:15-68)
+ * for the int8 cache, argument for argument (the bf16 / int4 cache pointers and
+ * flags of that signature are left out; the C++ symbol granite4::attn_split
+ * with the full signature is exported too and returns -1 for those formats):
+ *   rows 1..16 query rows d_q [rows][Hq 128].
+ *   d_row_pos NULL: the rows are consecutive positions p, p + 1, ... of ONE
+ *     sequence, p = *d_pos (read on the device) when d_pos is given, else
+ *     kv_base; position t lives in pool row d_pt[t] (NULL: t).
+ *   d_row_pos / d_row_pt (both or neither): row r is at position d_row_pos[r]
+ *     and reads through its own table d_row_pt[r]; every row is a sequence of
+ *     its own unless d_row_grp says otherwise.
+ *   d_row_grp / ngroups: group z owns rows [w & 0xff, + (w >> 8)) (at most 4)
+ *     of one sequence, which then read each cache tile once and share the
+ *     first row's table.
+ *   d_row_tbase / d_row_tail (both or neither; need d_row_pos): draft-tree
+ *     rows. Logical positions up to tbase = d_row_tbase[first row of the
+ *     group] are the sequence's own; position tbase + 1 + j of row r is the
+ *     slot d_row_tail[r * 8 + j] (an ancestor of r in the tree), looked up
+ *     through the table like any position; at most 8 such positions per row.
+ *   window > 0: a row attends to its last `window` positions only,
+ *     (pos - window, pos].
+ *   max_len (0 = stride) bounds every position + 1 and sizes the split of the
+ *     cache range; d_scratch must hold granite4_attn_split_scratch_bytes(Hq,
+ *     rows, max_len) bytes (an upper bound over every grouping of the rows).
+ * Results are those of one single-row call per row at its position. -1 on
+ * invalid arguments and for shapes other than d == 128, Hq == 4 Hk. */
+long long granite4_attn_split_scratch_bytes(int Hq, int rows, int max_len);
+int granite4_attn_split_int8(const uint16_t* d_q, const int8_t* d_cache_k8, const int8_t* d_cache_v8,
+                             const float* d_k_scale, const float* d_v_scale, float scale, int Hq,
+                             int Hk, int d, int kv_base, const int* d_pos, int rows, int stride,
+                             void* d_scratch, long long scratch_bytes, uint16_t* d_out, const int* d_pt,
+                             int max_len, const int* d_row_pos, const int* const* d_row_pt,
+                             const int* d_row_grp, int ngroups, const int* d_row_tbase,
+                             const int* d_row_tail, int window);
+
 /* ------------------------------------------------------------------------ */
 /* a4. SwiGLU, bf16 and FP8 outputs                                          */
 /* ------------------------------------------------------------------------ */

@@ -1824,9 +1824,12 @@ def test_gemm_fp8_empty_shard_still_validates_and_clears_the_fused_slot(K):
     ep.seg1 = ep.seg2 = 2 ** 31 - 1
     ep.ldc = 64
     import ctypes as C
-    lib = capi.lib()  # no output pointer of the requested kind: refused even with no rows
-    assert lib.granite4_kernel_gemm_fp8(capi.GEMM_OUT_BF16, None, 256, w.data_ptr(), 0, 64, 256, C.byref(ep), None, 0) == -1
-    assert lib.granite4_kernel_gemm_fp8(7, None, 256, w.data_ptr(), 0, 64, 256, C.byref(ep), None, 0) == -1
+    lib = capi.lib()  # the other argument checks still apply with no rows
+    assert lib.granite4_kernel_gemm_fp8(capi.GEMM_OUT_BF16, None, 256, w.data_ptr(), 0, 64, 256, C.byref(ep), None, 0) == 0
+    assert lib.granite4_kernel_gemm_fp8(7, None, 256, w.data_ptr(), 0, 64, 256, C.byref(ep), None, 0) == -1   # kind
+    assert lib.granite4_kernel_gemm_fp8(capi.GEMM_OUT_BF16, None, 256, w.data_ptr(), 0, 64, 250, C.byref(ep), None, 0) == -1  # K
+    ep.ldc = 8
+    assert lib.granite4_kernel_gemm_fp8(capi.GEMM_OUT_BF16, None, 256, w.data_ptr(), 0, 64, 256, C.byref(ep), None, 0) == -1  # ldc
 
 
 def test_gemm_fp8_rejects_bad_arguments(K):
