@@ -9,8 +9,8 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libgranite4_b200.so")
 
-SOURCES = ["runtime.cu", "embed.cu", "add_rmsnorm.cu", "rope_kv.cu", "rope_bf16.cu", "swiglu.cu", "decode_glue.cu", "attn_decode.cu", "attn_prefill.cu", "gemm_fp8.cu", "kv_pool.cc", "kv_pool_controller.cc", "host_glue.cu"]
-HEADERS = ["g4_host.h", "g4_math.cuh", "g4_tma.cuh", "g4_cluster.cuh"]
+SOURCES = ["runtime.cu", "embed.cu", "add_rmsnorm.cu", "rope_kv.cu", "rope_bf16.cu", "swiglu.cu", "decode_glue.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu", "gemm_fp8.cu", "kv_pool.cc", "kv_pool_controller.cc", "host_glue.cu"]
+HEADERS = ["g4_host.h", "g4_math.cuh", "g4_tma.cuh", "g4_cluster.cuh", "g4_tcgen05.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

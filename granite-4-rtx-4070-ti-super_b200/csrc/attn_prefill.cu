@@ -487,10 +487,22 @@ __global__ void __launch_bounds__(kPfWarps * 32, 2) attn_prefill2_kernel(const P
 
 }  // namespace
 
+// csrc/attn_prefill_tc.cu: the tcgen05 form (0 done, 1 not available here, -1 launch error)
+int attn_prefill_tc(const char* fn, const uint16_t* d_q, float scale, int Hq, int Hk, int base_pos, int rows,
+                    int stride, uint16_t* d_out, const int8_t* d_ck, const int8_t* d_cv, const float* d_ks,
+                    const float* d_vs, const int* d_pt);
+
 // Launch of the flash form for a whole chunk; arguments as granite4_prefill_attention_int8 (validated there).
+// Chunks of 64 rows or more run on the tcgen05 kernel (G4_PREFILL_TC=0 keeps them on the mma.sync
+// kernels below, for A/B runs and for tests that compare the two).
 int attn_prefill_flash(const char* fn, const uint16_t* d_q, float scale, int Hq, int Hk, int base_pos, int rows,
                        int stride, uint16_t* d_out, const int8_t* d_ck, const int8_t* d_cv, const float* d_ks,
                        const float* d_vs, const int* d_pt) {
+  const char* tc_env = std::getenv("G4_PREFILL_TC");
+  if (rows >= 64 && !(tc_env != nullptr && tc_env[0] == '0')) {
+    const int rc = attn_prefill_tc(fn, d_q, scale, Hq, Hk, base_pos, rows, stride, d_out, d_ck, d_cv, d_ks, d_vs, d_pt);
+    if (rc <= 0) return rc;
+  }
   static bool attr_set[64];
   int dev = 0;
   G4_CUDA_TRY(fn, cudaGetDevice(&dev));

@@ -98,6 +98,7 @@ enum DeviceStatusBits : unsigned int {
   kStatusSwigluWaitTimeout = 1u << 2,
   kStatusRopeWaitTimeout = 1u << 3,
   kStatusGemmWaitTimeout = 1u << 4,
+  kStatusAttnWaitTimeout = 1u << 5,
 };
 
 }  // namespace g4
