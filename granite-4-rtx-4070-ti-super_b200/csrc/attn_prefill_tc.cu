@@ -32,9 +32,10 @@
 //               tensor-memory lane): reads its 64 logits (tcgen05.ld), applies the column factor
 //               (K scale x softmax scale) and the causal mask, keeps the running maximum and sum,
 //               and writes the probabilities as f16 pairs back over the logits (tcgen05.st). The
-//               accumulator O is rescaled in tensor memory only when the maximum grew by more than
-//               2^8 (the final division uses the same maximum, so the result does not depend on
-//               when the rescale happens), and only then does a tile wait for the previous P V;
+//               accumulator O is rescaled in tensor memory only when a tile's maximum exceeds the
+//               running one by more than 2^12 (the final division uses the same maximum, so the
+//               result does not depend on when the rescale happens), and only then does a tile
+//               wait for the previous P V;
 //   warps 2-3, 12-13  converters: int8 codes -> f16, written as 128-byte-swizzled tiles
 //               ([position][64 dims] twice), three buffers: K as the exact codes, K-major for
 //               S = Q K^T; V as code x scale and, the same byte layout, N-major for P V.
@@ -412,7 +413,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
     }
     const int pos_first = __shfl_sync(0xffffffffu, pos, 0);  // lane 0 has the warp's earliest position
     const bool all_live = __all_sync(0xffffffffu, live);
-    float m_run = -INFINITY, l_run = 0.0f;
+    // Running maximum and sum of the row. A row without a position (past the chunk's end) starts at a
+    // finite maximum: all its logits are masked and it never looks for one.
+    float m_run = live ? -INFINITY : 0.0f, l_run = 0.0f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int sb = j & 1, b = j % kBufs;
@@ -420,80 +423,70 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
       tc_fence_after();
       const int kv0 = j * kTN;
       const uint32_t s_addr = lane_addr + s_col(t, sb);
-      // pass 1: the maximum of the row's 64 scaled, masked logits; only a tile that reaches past the
-      // warp's first position needs the causal mask (warp-uniform). The logits stay in tensor memory
-      // and are read again for the probabilities: 64 values would not fit the register budget twice.
+      // only a tile that reaches past the warp's first position needs the causal mask (warp-uniform)
       const bool masked = !all_live || kv0 + kTN - 1 > pos_first;
       const float4* cs4 = reinterpret_cast<const float4*>(sm->cs[b]);
-      float m_tile = -INFINITY;
+      // One sweep over the row's 64 logits computes the probabilities against the maximum the row has
+      // had so far, and the tile's own maximum on the side. The running maximum is replaced only when
+      // a tile exceeds it by more than 2^12 (always so in the first tile): then O and the sum are
+      // rescaled and the sweep is repeated against the new maximum. Probabilities therefore stay below
+      // 2^12, inside f16, and the final division uses the same maximum as every sum, so the result
+      // does not depend on when the maximum moved.
+      uint32_t pk[32];
+      float l_tile = 0.0f;
+#pragma unroll 1
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        const float base = m_run == -INFINITY ? 0.0f : m_run;
+        float m_tile = -INFINITY;
+        l_tile = 0.0f;
 #pragma unroll
-      for (int hc = 0; hc < 2; ++hc) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + hc * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float4 c4 = cs4[hc * 8 + (i >> 2)];
-          float y[4] = {__uint_as_float(v[i]) * c4.x, __uint_as_float(v[i + 1]) * c4.y, __uint_as_float(v[i + 2]) * c4.z,
-                        __uint_as_float(v[i + 3]) * c4.w};
-          if (masked) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (kv0 + hc * 32 + i + e > pos) y[e] = -INFINITY;
-          }
-          m_tile = fmaxf(fmaxf(m_tile, fmaxf(y[0], y[1])), fmaxf(y[2], y[3]));
-        }
-      }
-      // the running maximum moves only when it has to (first tile with a live column) or when the new
-      // one is more than 2^8 above it: the accumulated sums stay below 2^8 times their true scale
-      const bool grow = m_tile > m_run + 8.0f || (m_run == -INFINITY && m_tile > -INFINITY);
-      const float m_new = grow ? m_tile : m_run;
-      const float corr = (grow && m_run > -INFINITY) ? ex2_approx(m_run - m_new) : 1.0f;
-      l_run *= corr;
-      m_run = m_new;
-      const float base = m_run == -INFINITY ? 0.0f : m_run;
-      if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-        // O has to shrink: it is complete (and nobody adds to it) once the previous tile's P V is done
-        if (!(ok = wait_tc(&sm->pv_done[t], (j - 1) & 1, sm, p.status))) break;
-        tc_fence_after();
-#pragma unroll
-        for (int oc = 0; oc < 4; ++oc) {
+        for (int hc = 0; hc < 2; ++hc) {
           uint32_t v[32];
-          tmem_ld32(lane_addr + o_col(t) + oc * 32, v);
+          tmem_ld32(s_addr + hc * 32, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-          tmem_st32(lane_addr + o_col(t) + oc * 32, v);
-        }
-      }
-      // pass 2: probabilities as f16 pairs, written over the first 32 columns of the logits they came
-      // from (V carries its scale already). Both halves are read before the first is overwritten.
-      float l_tile = 0.0f;
-      uint32_t pk[32];
+          for (int i = 0; i < 32; i += 4) {
+            const float4 c4 = cs4[hc * 8 + (i >> 2)];
+            float y[4] = {__uint_as_float(v[i]) * c4.x, __uint_as_float(v[i + 1]) * c4.y, __uint_as_float(v[i + 2]) * c4.z,
+                          __uint_as_float(v[i + 3]) * c4.w};
+            if (masked) {
 #pragma unroll
-      for (int hc = 0; hc < 2; ++hc) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + hc * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float4 c4 = cs4[hc * 8 + (i >> 2)];
-          float y[4] = {__uint_as_float(v[i]) * c4.x, __uint_as_float(v[i + 1]) * c4.y, __uint_as_float(v[i + 2]) * c4.z,
-                        __uint_as_float(v[i + 3]) * c4.w};
-          if (masked) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (kv0 + hc * 32 + i + e > pos) y[e] = -INFINITY;
+              for (int e = 0; e < 4; ++e)
+                if (kv0 + hc * 32 + i + e > pos) y[e] = -INFINITY;
+            }
+            m_tile = fmaxf(fmaxf(m_tile, fmaxf(y[0], y[1])), fmaxf(y[2], y[3]));
+            const float p0 = ex2_approx(y[0] - base), p1 = ex2_approx(y[1] - base), p2 = ex2_approx(y[2] - base),
+                        p3 = ex2_approx(y[3] - base);
+            l_tile += (p0 + p1) + (p2 + p3);
+            const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+            pk[hc * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&h01);
+            pk[hc * 16 + (i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&h23);
           }
-          const float p0 = ex2_approx(y[0] - base), p1 = ex2_approx(y[1] - base), p2 = ex2_approx(y[2] - base),
-                      p3 = ex2_approx(y[3] - base);
-          l_tile += (p0 + p1) + (p2 + p3);
-          const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
-          pk[hc * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&h01);
-          pk[hc * 16 + (i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+        }
+        const bool grow = m_tile > m_run + 12.0f;  // also true for the first live logits (m_run = -inf)
+        if (attempt == 1 || !__any_sync(0xffffffffu, grow)) break;
+        const float m_new = grow ? m_tile : m_run;
+        const float corr = (grow && m_run > -INFINITY) ? ex2_approx(m_run - m_new) : 1.0f;
+        l_run *= corr;
+        m_run = m_new;
+        if (j > 0) {
+          // O has to shrink: it is complete (and nobody adds to it) once the previous tile's P V is done
+          if (!(ok = wait_tc(&sm->pv_done[t], (j - 1) & 1, sm, p.status))) break;
+          tc_fence_after();
+#pragma unroll 1
+          for (int oc = 0; oc < 4; ++oc) {
+            uint32_t v[32];
+            tmem_ld32(lane_addr + o_col(t) + oc * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+            tmem_st32(lane_addr + o_col(t) + oc * 32, v);
+          }
         }
       }
+      if (!ok) break;
       l_run += l_tile;
+      // the probabilities go over the first 32 columns of the logits they came from
       tmem_st32(s_addr, pk);
       tmem_st_wait();
       tc_fence_before();
@@ -506,7 +499,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
       tc_fence_after();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
       uint16_t* dst = p.out + (static_cast<size_t>(live ? crow : 0) * p.Hq + hkv * 4 + hl) * kD;
-#pragma unroll
+#pragma unroll 1
       for (int oc = 0; oc < 4; ++oc) {
         uint32_t v[32];
         tmem_ld32(lane_addr + o_col(t) + oc * 32, v);
