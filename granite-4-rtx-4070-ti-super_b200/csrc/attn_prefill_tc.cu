@@ -486,6 +486,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
       }
       if (!ok) break;
       l_run += l_tile;
+      // Every phase of pv_done is observed, in order, whether or not this tile needed O: a parity wait
+      // cannot tell a phase from the one two before it. By now the previous P V finished long ago.
+      if (j > 0 && !(ok = wait_tc(&sm->pv_done[t], (j - 1) & 1, sm, p.status))) break;
       // the probabilities go over the first 32 columns of the logits they came from
       tmem_st32(s_addr, pk);
       tmem_st_wait();
