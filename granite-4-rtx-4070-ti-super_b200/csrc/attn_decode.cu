@@ -495,7 +495,7 @@ __global__ void __launch_bounds__(kWarps * 32, NT == 1 ? kCtasPerSmT : kCtasPerS
       bool okl[NT], okh[NT];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        okl[nt] = j == 2 * nt + (t >> 1) && g < cnt && tb + 1 + g >= lo_col[nt];
+        okl[nt] = j == 2 * nt + (t >> 1) && g < cnt && (EXT ? tb : 0) + 1 + g >= lo_col[nt];
         okh[nt] = false;
       }
       attend(raw_k, raw_v, sk_t, sv_t, false, okl, okh);

@@ -24,10 +24,11 @@
 //               rows are consecutive, else 128 bytes per row) and their scales with 4-byte
 //               cp.async, into a three-stage ring;
 //   warp 1      allocates the tensor memory; one thread issues every MMA and commits them to the
-//               barriers of whoever waits for the result. S of tile j + 1 is issued before P V of
-//               tile j, so the tensor cores work on the next logits while the softmax of this
-//               tile runs; MMAs execute in issue order, which is what lets P V of tile j - 1 (reading
-//               P from an S buffer) precede S of tile j + 1 (overwriting it) without a barrier;
+//               barriers of whoever waits for the result: P V of a row tile as soon as its P is
+//               written, directly followed by that row tile's S for the tile after next, which reuses
+//               the buffer the P V reads (MMAs execute in issue order, so no barrier is needed
+//               between them). The tensor cores thus work on tile j + 1's logits while the softmax
+//               of tile j runs;
 //   warps 4-7   softmax of row tile 0, warps 8-11 of row tile 1: a thread owns one row (its
 //               tensor-memory lane): reads its 64 logits (tcgen05.ld), applies the column factor
 //               (K scale x softmax scale) and the causal mask, keeps the running maximum and sum,
@@ -68,7 +69,8 @@ constexpr int kRowTiles = 2;
 constexpr int kCtaPos = kQPos * kRowTiles;  // 64 query positions per CTA
 constexpr int kTN = 64;      // cache positions per tile
 constexpr int kThreads = 448;  // 14 warps: four on two of the SM's sub-partitions, so 128 registers per thread
-constexpr int kBufs = 3;       // raw stages and converted K / V buffers
+constexpr int kBufs = 3;  // converted K / V buffers
+constexpr int kRaw = 3;   // raw stages
 
 constexpr uint32_t kQTileBytes = 128 * kD * 2;     // 32768: two 64-dim halves of [128 rows][128 bytes]
 constexpr uint32_t kKvTileBytes = kTN * kD * 2;    // 16384: two 64-dim halves of [64 positions][128 bytes]
@@ -80,12 +82,12 @@ struct TcSmem {
   uint8_t q16[kRowTiles][kQTileBytes];
   uint8_t k16[kBufs][kKvTileBytes];
   uint8_t v16[kBufs][kKvTileBytes];
-  uint8_t raw_k[kBufs][kRawBytes];
-  uint8_t raw_v[kBufs][kRawBytes];
-  float raw_ks[kBufs][kTN], raw_vs[kBufs][kTN];  // scales of the raw stages
+  uint8_t raw_k[kRaw][kRawBytes];
+  uint8_t raw_v[kRaw][kRawBytes];
+  float raw_ks[kRaw][kTN], raw_vs[kRaw][kTN];  // scales of the raw stages
   float cs[kBufs][kTN];  // per converted K tile: K scale x softmax scale x log2(e) x the power of two taken out of Q
-  uint64_t raw_full[kBufs], raw_empty[kBufs], kv_full[kBufs], kv_empty[kBufs];
-  uint64_t s_full[kRowTiles][2], p_full[kRowTiles], pv_done[kRowTiles];
+  uint64_t raw_full[kRaw], raw_empty[kRaw], kv_full[kBufs], kv_empty[kBufs];
+  uint64_t s_full[kRowTiles][2], p_full[kRowTiles][2], pv_done[kRowTiles][2];
   uint64_t q_ready;
   uint32_t q_amax;  // max |q| over the CTA's rows, as float bits
   uint32_t tmem_base;
@@ -126,6 +128,36 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Four MMAs of one accumulator in one statement: D (+)= A0 B0 + A1 B1 + A2 B2 + A3 B3; `accumulate` = 0
+// makes the first of them overwrite D.
+__device__ __forceinline__ void mma4_ss(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint64_t a1, uint64_t b1, uint64_t a2,
+                                        uint64_t b2, uint64_t a3, uint64_t b3, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %10, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %9, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %4, %9, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %6, %9, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %8, %9, q;\n\t}" ::"r"(d_tmem),
+      "l"(a0), "l"(b0), "l"(a1), "l"(b1), "l"(a2), "l"(b2), "l"(a3), "l"(b3), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same with A in tensor memory: k-step i reads the 8 columns from a_tmem + 8 i.
+__device__ __forceinline__ void mma4_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b0, uint64_t b1, uint64_t b2, uint64_t b3,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b32 a1, a2, a3;\n\t"
+      "setp.ne.b32 p, %7, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %6, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], %3, %6, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], %4, %6, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], %5, %6, q;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // A shared-memory descriptor from its two words (g4_tcgen05.cuh smem_desc_sw128): the low one holds the
@@ -209,16 +241,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
   const size_t head_row0 = static_cast<size_t>(hkv) * p.stride;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kBufs; ++i) {
+    for (int i = 0; i < kRaw; ++i) {
       mbar_init(&sm->raw_full[i], 1 + 32);  // the arming arrival + one per producer lane (its scale copies)
       mbar_init(&sm->raw_empty[i], 4);
+    }
+    for (int i = 0; i < kBufs; ++i) {
       mbar_init(&sm->kv_full[i], 4);
       mbar_init(&sm->kv_empty[i], 1);
     }
     for (int t = 0; t < kRowTiles; ++t) {
-      for (int i = 0; i < 2; ++i) mbar_init(&sm->s_full[t][i], 1);
-      mbar_init(&sm->p_full[t], 4);
-      mbar_init(&sm->pv_done[t], 1);
+      // one barrier of each kind per S buffer: the warps of a row tile may be a tile apart, never two
+      for (int i = 0; i < 2; ++i)
+        mbar_init(&sm->s_full[t][i], 1), mbar_init(&sm->pv_done[t][i], 1), mbar_init(&sm->p_full[t][i], 4);
     }
     mbar_init(&sm->q_ready, 8);
     sm->abort = 0;
@@ -245,8 +279,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
     rows_of(0, ra, rb);
     if (n_kv > 1) rows_of(1, na, nb);
     for (int j = 0; j < n_kv; ++j) {
-      const int s = j % kBufs;
-      if (!wait_tc(&sm->raw_empty[s], ((j / kBufs) & 1) ^ 1, sm, p.status)) break;
+      const int s = j % kRaw;
+      if (!wait_tc(&sm->raw_empty[s], ((j / kRaw) & 1) ^ 1, sm, p.status)) break;
       if (lane == 0) mbar_arrive_expect_tx(&sm->raw_full[s], 2u * kRawBytes);
       __syncwarp();
       // A group of 16 consecutive positions usually is one page of the pool, i.e. 16 consecutive pool
@@ -287,22 +321,32 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
     }
   } else if (warp == 1) {
     // ---- MMA issue ----------------------------------------------------------------------------
+    // One thread issues every MMA; it is the busiest thread of the CTA (29 MMAs and commits per
+    // tile), so its instruction count per MMA is kept at the minimum: the descriptors of Q are
+    // formed once, those of a tile's K and V once per tile (both row tiles use them), and four MMAs
+    // go out per asm statement.
     if (lane == 0) {
       bool ok = wait_tc(&sm->q_ready, 0, sm, p.status);
       const uint32_t q_lo = (smem_u32(sm->q16[0]) >> 4) | (1u << 16), k_lo = (smem_u32(sm->k16[0]) >> 4) | (1u << 16);
       const uint32_t v_lo = (smem_u32(sm->v16[0]) >> 4) | ((kKvTileBytes / 2 >> 4) << 16);  // 64-dim halves 8 KB apart
+      uint64_t qd[kRowTiles][8];
+#pragma unroll
+      for (int t = 0; t < kRowTiles; ++t)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)  // 16 dims = 32 bytes per instruction; dims 64.. in the second half tile
+          qd[t][kk] = desc_of(q_lo + ((t * kQTileBytes + (kk >> 2) * (kQTileBytes / 2) + (kk & 3) * 32) >> 4));
       auto issue_s = [&](int j) {
         const int b = j % kBufs, sb = j & 1;
         if (!(ok = ok && wait_tc(&sm->kv_full[b], (j / kBufs) & 1, sm, p.status))) return;
         tc_fence_after();
+        uint64_t kd[8];
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          kd[kk] = desc_of(k_lo + ((b * kKvTileBytes + (kk >> 2) * (kKvTileBytes / 2) + (kk & 3) * 32) >> 4));
 #pragma unroll
         for (int t = 0; t < kRowTiles; ++t) {
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {  // 16 dims = 32 bytes per instruction; dims 64.. in the second half tile
-            const uint32_t qo = (t * kQTileBytes + (kk >> 2) * (kQTileBytes / 2) + (kk & 3) * 32) >> 4;
-            const uint32_t ko = (b * kKvTileBytes + (kk >> 2) * (kKvTileBytes / 2) + (kk & 3) * 32) >> 4;
-            mma_f16_ss(tmem_base + s_col(t, sb), desc_of(q_lo + qo), desc_of(k_lo + ko), kIdescS, kk != 0);
-          }
+          mma4_ss(tmem_base + s_col(t, sb), qd[t][0], kd[0], qd[t][1], kd[1], qd[t][2], kd[2], qd[t][3], kd[3], kIdescS, 0u);
+          mma4_ss(tmem_base + s_col(t, sb), qd[t][4], kd[4], qd[t][5], kd[5], qd[t][6], kd[6], qd[t][7], kd[7], kIdescS, 1u);
           mma_commit<false>(smem_u32(&sm->s_full[t][sb]));
         }
       };
@@ -310,14 +354,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j + 1 < n_kv) issue_s(j + 1);
         const int b = j % kBufs, sb = j & 1;
-        for (int t = 0; t < kRowTiles && ok; ++t) {
-          if (!(ok = wait_tc(&sm->p_full[t], j & 1, sm, p.status))) break;
-          tc_fence_after();
+        uint64_t vd[4];
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // 16 positions per instruction: 8 columns of P, two 8-row groups of V
-            mma_f16_ts(tmem_base + o_col(t), tmem_base + s_col(t, sb) + kk * 8,
-                       desc_of(v_lo + ((b * kKvTileBytes + kk * 2048) >> 4)), kIdescPV, (j > 0) || kk != 0);
-          mma_commit<false>(smem_u32(&sm->pv_done[t]));
+        for (int kk = 0; kk < 4; ++kk)  // 16 positions per instruction: 8 columns of P, two 8-row groups of V
+          vd[kk] = desc_of(v_lo + ((b * kKvTileBytes + kk * 2048) >> 4));
+        for (int t = 0; t < kRowTiles && ok; ++t) {
+          if (!(ok = wait_tc(&sm->p_full[t][sb], (j >> 1) & 1, sm, p.status))) break;
+          tc_fence_after();
+          mma4_ts(tmem_base + o_col(t), tmem_base + s_col(t, sb), vd[0], vd[1], vd[2], vd[3], kIdescPV, j > 0 ? 1u : 0u);
+          mma_commit<false>(smem_u32(&sm->pv_done[t][sb]));
         }
         if (ok) mma_commit<false>(smem_u32(&sm->kv_empty[b]));
       }
@@ -330,10 +375,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
     bool okc = wait_tc(&sm->q_ready, 0, sm, p.status);
     const float col_scale = p.scale_log2 * q_up_factor(sm->q_amax);
     for (int j = 0; j < n_kv && okc; ++j) {
-      const int s = j % kBufs, b = s;
-      const uint32_t ph = (j / kBufs) & 1;
-      if (!wait_tc(&sm->raw_full[s], ph, sm, p.status)) break;
-      if (!wait_tc(&sm->kv_empty[b], ph ^ 1, sm, p.status)) break;
+      const int s = j % kRaw, b = j % kBufs;
+      if (!wait_tc(&sm->raw_full[s], (j / kRaw) & 1, sm, p.status)) break;
+      if (!wait_tc(&sm->kv_empty[b], ((j / kBufs) & 1) ^ 1, sm, p.status)) break;
       // unit u = (row, piece of 16 codes): a quarter warp reads one whole raw row; its stores land in
       // eight different 16-byte columns (the lanes of the second half tile write their two chunks in
       // the other order)
@@ -439,11 +483,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
         const float base = m_run == -INFINITY ? 0.0f : m_run;
         float m_tile = -INFINITY;
         l_tile = 0.0f;
+        uint32_t v2[2][32];  // both halves of the row are requested before the first is waited for
+        tmem_ld32(s_addr, v2[0]);
+        tmem_ld32(s_addr + 32, v2[1]);
+        tmem_ld_wait();
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + hc * 32, v);
-          tmem_ld_wait();
+          const uint32_t(&v)[32] = v2[hc];
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const float4 c4 = cs4[hc * 8 + (i >> 2)];
@@ -471,7 +517,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
         m_run = m_new;
         if (j > 0) {
           // O has to shrink: it is complete (and nobody adds to it) once the previous tile's P V is done
-          if (!(ok = wait_tc(&sm->pv_done[t], (j - 1) & 1, sm, p.status))) break;
+          if (!(ok = wait_tc(&sm->pv_done[t][(j - 1) & 1], ((j - 1) >> 1) & 1, sm, p.status))) break;
           tc_fence_after();
 #pragma unroll 1
           for (int oc = 0; oc < 4; ++oc) {
@@ -486,18 +532,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
       }
       if (!ok) break;
       l_run += l_tile;
-      // Every phase of pv_done is observed, in order, whether or not this tile needed O: a parity wait
-      // cannot tell a phase from the one two before it. By now the previous P V finished long ago.
-      if (j > 0 && !(ok = wait_tc(&sm->pv_done[t], (j - 1) & 1, sm, p.status))) break;
-      // the probabilities go over the first 32 columns of the logits they came from
+      // The probabilities go over the first 32 columns of the logits they came from. That buffer last
+      // held P of tile j - 2, and S of tile j, issued after that tile's P V, has completed: MMAs
+      // complete in issue order, so nothing reads the old P any more and no wait is needed here.
+      // (P V completions of even and odd tiles are counted on two barriers, so that a thread which
+      // has not looked at them for a tile or two still reads the right phase when it has to.)
       tmem_st32(s_addr, pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[t]));
+      if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[t][sb]));
     }
     // ---- the finished row: O / l -> bf16
-    if (ok && n_kv > 0) ok = wait_tc(&sm->pv_done[t], (n_kv - 1) & 1, sm, p.status);
+    if (ok && n_kv > 0) ok = wait_tc(&sm->pv_done[t][(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, sm, p.status);
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
