@@ -713,16 +713,29 @@ def small_shapes_and_embed(seq, rows, device, stream):
         nbytes = groups * s.kv_heads * ctx * (2 * s.head_dim + 8)
         attention[name] = {"mean_us": us, "achieved_gbs": nbytes / (us * 1e-6) / 1e9,
                            "frac": nbytes / (us * 1e-6) / 1e9 / peak, "bytes": nbytes}
-    # Causal attention of a whole prefill chunk (the flash kernel over the same pool; K/V of the chunk
-    # stay in L2): 4 d Hq n^2 / 2 flops.
+    # Causal attention of a whole prefill chunk over the same pool (K/V of the chunk stay in L2):
+    # 4 d Hq n^2 / 2 flops, against the measured bf16 GEMM rate. The tcgen05 kernel (default) and the
+    # mma.sync kernel it replaced for chunks of 64 rows or more, through the same entry point.
+    mp_attn = {}
+    if os.path.isfile(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp_attn = json.load(f)
+    bf16_peak = float(mp_attn.get("bf16_tflops", 1590.0))
     for n_pf in (2048, 8192):
         qa = torch.randn(n_pf, s.q_heads * s.head_dim, generator=g, device=device).to(torch.bfloat16)
         oa = torch.empty_like(qa)
-        us = timed(lambda: k.prefill_attention_int8(qa, 1.0 / 128, s.q_heads, s.kv_heads, s.head_dim, 0, stride, oa,
-                                                    ck, cv, ksc, vsc, pt=table), 5)
         flops = 4.0 * s.head_dim * s.q_heads * n_pf * (n_pf + 1) / 2
-        attention[f"prefill_{n_pf}_rows"] = {"mean_us": us, "tflops": flops / (us * 1e-6) / 1e12,
-                                             "form": "flash, 32 positions x 4 heads per CTA"}
+        entry = {}
+        for form, env in (("tcgen05", "1"), ("mma_sync", "0")):
+            os.environ["G4_PREFILL_TC"] = env
+            us = timed(lambda: k.prefill_attention_int8(qa, 1.0 / 128, s.q_heads, s.kv_heads, s.head_dim, 0, stride,
+                                                        oa, ck, cv, ksc, vsc, pt=table), 5)
+            entry[form] = {"mean_us": us, "tflops": flops / (us * 1e-6) / 1e12,
+                           "frac_of_measured_bf16": flops / (us * 1e-6) / 1e12 / bf16_peak}
+        os.environ.pop("G4_PREFILL_TC")
+        entry.update({"mean_us": entry["tcgen05"]["mean_us"], "tflops": entry["tcgen05"]["tflops"],
+                      "form": "tcgen05: S and O in tensor memory, 64 positions x 4 heads per CTA, K / V converted once per tile"})
+        attention[f"prefill_{n_pf}_rows"] = entry
         del qa, oa
     # A whole decode step (one layer's glue + attention at ~4096 positions + final norm + greedy
     # pick with the token scatter folded in) of n sessions, captured into a CUDA graph and replayed: everything that

@@ -35,6 +35,7 @@
 #include "../../include/granite4_b200.hpp"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <vector>
 
@@ -176,168 +177,205 @@ __global__ void __launch_bounds__(kHeadsPerCta * 8) rope_kv_int8_kernel(const Ro
 // ---- the same op with the inputs staged by bulk asynchronous copies ------------------------------
 // The per-row work above is short and every CTA starts with a dependent chain (row index ->
 // position -> table row), so at one CTA per row the kernel is latency-bound. Here persistent CTAs
-// stream their rows through a ring of shared-memory stages instead: one elected thread reads the
-// row's position and pool row and issues bulk asynchronous copies (TMA engine, cp.async.bulk +
-// mbarrier, no multicast) of the row's activations (one 12 KB copy for token-major qkv, three for
-// separate q / k / v) and of its cos and sin table rows (256 B each) kBulkAhead rows ahead; the
-// CTA computes row i out of shared memory while the copies of the next rows are in flight, and
-// stores results straight to global memory. Bytes in flight per SM are bounded by shared memory
-// (4 CTAs x 3 stages x 12.8 KB), not by registers or occupancy. The thread layout is the one of
-// rope_kv_int8_kernel (every thread gets two query heads and one key or value head of a Granite row). The arithmetic, and so every
-// output bit, is that of rope_kv_int8_kernel.
+// stream their rows through a ring of shared-memory stages instead. A producer warp (one elected
+// thread) reads each row's position and pool row - one row ahead of the one it is issuing, so that
+// the load's latency never sits between two issues - and issues bulk asynchronous copies (TMA engine,
+// cp.async.bulk + mbarrier, no multicast) of the row's activations (one 12 KB copy for token-major
+// qkv, three for separate q / k / v) and of its cos and sin table rows (256 B each) up to kBulkStages
+// rows ahead; four consumer warps compute row i out of shared memory while the copies of the next
+// rows are in flight, and store results straight to global memory. Stages go back to the producer
+// through a second set of mbarriers (one arrival per consumer warp), so the loop has no CTA-wide
+// barrier and the consumers never wait for anything but data. Bytes in flight per SM are bounded by
+// shared memory (4 CTAs x 4 stages x 12.8 KB), not by registers or occupancy. The consumers' thread
+// layout is the one of rope_kv_int8_kernel (every thread gets two query heads and one key or value
+// head of a Granite row). The arithmetic, and so every output bit, is that of rope_kv_int8_kernel.
 constexpr int kBulkStages = 4;
-constexpr int kBulkAhead = kBulkStages - 1;
-constexpr int kBulkThreads = 128;                    // 16 heads per pass, 8 lanes each
-constexpr int kBulkHeadsPerPass = kBulkThreads / 8;  // thread (g, j) owns heads g, g + 16, g + 32, ...
+constexpr int kBulkConsumers = 128;                    // 16 heads per pass, 8 lanes each
+constexpr int kBulkThreads = kBulkConsumers + 32;      // + the producer warp
+constexpr int kBulkHeadsPerPass = kBulkConsumers / 8;  // thread (g, j) owns heads g, g + 16, g + 32, ...
 
 struct RowMeta {
   int pos, kv_row, ok, pad;
 };
 
-__global__ void __launch_bounds__(kBulkThreads) rope_kv_bulk_kernel(const RopeKvParams p,
+// Bounded wait that also gives up when another thread of the CTA already has.
+__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kMbarWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (i > 64) __nanosleep(64);
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__global__ void __launch_bounds__(kBulkThreads, 4) rope_kv_bulk_kernel(const RopeKvParams p,
                                                                     unsigned int* status) {
-  pdl_begin();
   extern __shared__ __align__(128) unsigned char smem[];
   const int heads_total = p.Hq + 2 * p.Hk;
   const uint32_t act_bytes = static_cast<uint32_t>(heads_total) * kD * 2u;
   const uint32_t tbl_bytes = (kD / 2) * 4u;  // one table row
   const uint32_t stage_bytes = act_bytes + 2u * tbl_bytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(kBulkStages) * stage_bytes);
-  RowMeta* meta = reinterpret_cast<RowMeta*>(full + kBulkStages);
+  uint64_t* empty = full + kBulkStages;
+  RowMeta* meta = reinterpret_cast<RowMeta*>(empty + kBulkStages);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + kBulkStages);
   const int t = threadIdx.x;
-  const int g = t >> 3, j = t & 7;
-  const unsigned gmask = 0xffu << (t & 24);
   const long long n_local = (p.rows - static_cast<long long>(blockIdx.x) + gridDim.x - 1) / gridDim.x;
 
+  // the barriers live in shared memory: they are set up while the kernel before this one drains
   if (t == 0) {
-    for (int s = 0; s < kBulkStages; ++s) mbar_init(full + s, 1);
+    for (int s = 0; s < kBulkStages; ++s) mbar_init(full + s, 1), mbar_init(empty + s, kBulkConsumers / 32);
+    *abort_flag = 0;
     mbar_init_fence();
   }
+  pdl_begin();
   __syncthreads();
 
-  auto issue = [&](long long i) {  // elected thread only
-    const int r = static_cast<int>(blockIdx.x + i * static_cast<long long>(gridDim.x));
-    const int s = static_cast<int>(i % kBulkStages);
-    int pos, kv_row, ok = 1;
-    if (p.mode == kRunOfPositions) {
-      pos = p.base_pos + r;
-      kv_row = p.d_pt != nullptr ? __ldg(p.d_pt + pos) : pos;
-    } else if (p.mode == kPerRowArrays) {
-      pos = __ldg(p.pos_rows + r);
-      kv_row = __ldg(p.kv_rows + r);
-      if (pos < 0 || pos >= p.max_pos || kv_row < 0 || kv_row >= p.stride) ok = 0;  // row is skipped
-    } else {
-      pos = p.mr->pos[r];
-      const int slot = p.mr->tree ? p.mr->slot[r] : pos;
-      kv_row = p.mr->pt[r][slot];
-    }
-    meta[s].pos = pos, meta[s].kv_row = kv_row, meta[s].ok = ok;
-    unsigned char* stage = smem + static_cast<size_t>(s) * stage_bytes;
-    if (!ok) {  // nothing to copy: one plain arrival completes the phase
-      mbar_arrive_expect_tx(full + s, 0);
-      return;
-    }
-    const bool tables = p.cos_tbl != nullptr;
-    mbar_arrive_expect_tx(full + s, act_bytes + (tables ? 2u * tbl_bytes : 0u));
-    const uint32_t qb = static_cast<uint32_t>(p.Hq) * kD * 2u, kb = static_cast<uint32_t>(p.Hk) * kD * 2u;
-    if (p.q != nullptr && p.k == p.q + static_cast<size_t>(p.Hq) * kD &&
-        p.v == p.k + static_cast<size_t>(p.Hk) * kD && p.pitch_q == p.pitch_k && p.pitch_k == p.pitch_v) {
-      bulk_load(stage, p.q + static_cast<size_t>(r) * p.pitch_q, act_bytes, full + s);  // token-major row
-    } else {
-      if (qb != 0u) bulk_load(stage, p.q + static_cast<size_t>(r) * p.pitch_q, qb, full + s);
-      bulk_load(stage + qb, p.k + static_cast<size_t>(r) * p.pitch_k, kb, full + s);
-      bulk_load(stage + qb + kb, p.v + static_cast<size_t>(r) * p.pitch_v, kb, full + s);
-    }
-    if (tables) {
-      bulk_load(stage + act_bytes, p.cos_tbl + static_cast<size_t>(pos) * (kD / 2), tbl_bytes, full + s);
-      bulk_load(stage + act_bytes + tbl_bytes, p.sin_tbl + static_cast<size_t>(pos) * (kD / 2), tbl_bytes,
-                full + s);
-    }
-  };
-  if (t == 0)
-    for (long long i = 0; i < kBulkAhead && i < n_local; ++i) issue(i);
-  long long issued_until = kBulkAhead < n_local ? kBulkAhead : n_local;  // meaningful in thread 0
-
-  bool failed = false;
-  for (long long i = 0; i < n_local; ++i) {
-    const int s = static_cast<int>(i % kBulkStages);
-    const uint32_t parity = static_cast<uint32_t>((i / kBulkStages) & 1);
-    const bool landed = mbar_wait_bounded(full + s, parity);
-    // One barrier per row: it makes the verdict CTA-wide, and it also tells the elected thread
-    // that every thread is done reading the stage of row i - 1, which is the one it refills next.
-    if (__syncthreads_or(!landed)) {
-      failed = true;
-      break;
-    }
-    if (t == 0 && i + kBulkAhead < n_local) {
-      issue(i + kBulkAhead);
-      issued_until = i + kBulkAhead + 1;
-    }
-    const RowMeta m = meta[s];
-    if (!m.ok) continue;
-    const int r = static_cast<int>(blockIdx.x + i * static_cast<long long>(gridDim.x));
-    const unsigned char* stage = smem + static_cast<size_t>(s) * stage_bytes;
-    float c[8], sn[8];
-    if (p.cos_tbl != nullptr) {
-      const float4* cp = reinterpret_cast<const float4*>(stage + act_bytes) + 2 * j;
-      const float4* sp = reinterpret_cast<const float4*>(stage + act_bytes + tbl_bytes) + 2 * j;
-      const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
-      c[0] = c0.x, c[1] = c0.y, c[2] = c0.z, c[3] = c0.w, c[4] = c1.x, c[5] = c1.y, c[6] = c1.z, c[7] = c1.w;
-      sn[0] = s0.x, sn[1] = s0.y, sn[2] = s0.z, sn[3] = s0.w, sn[4] = s1.x, sn[5] = s1.y, sn[6] = s1.z, sn[7] = s1.w;
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) c[e] = 1.0f, sn[e] = 0.0f;
-    }
-#pragma unroll
-    for (int k = 0; k < kMaxHeadsPerThread; ++k) {
-      const int head = g + k * kBulkHeadsPerPass;
-      if (head >= heads_total) break;
-      const bool is_q = head < p.Hq;
-      const bool is_k = !is_q && head < p.Hq + p.Hk;
-      const uint4* src = reinterpret_cast<const uint4*>(stage + static_cast<size_t>(head) * kD * 2);
-      float lo[8], hi[8];
-      unpack8(src[j], lo);
-      unpack8(src[8 + j], hi);
-      if (is_q || (is_k && p.rotate_k)) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float a, b;
-          rope_pair(lo[e], hi[e], c[e], sn[e], a, b);
-          lo[e] = a, hi[e] = b;
+  if (t >= kBulkConsumers) {
+    // ---- producer ----------------------------------------------------------------------------
+    if (t != kBulkConsumers) return;
+    auto where = [&](long long i, int& pos, int& kv_row, int& ok) {
+      const int r = static_cast<int>(blockIdx.x + i * static_cast<long long>(gridDim.x));
+      ok = 1;
+      if (p.mode == kRunOfPositions) {
+        pos = p.base_pos + r;
+        kv_row = p.d_pt != nullptr ? __ldg(p.d_pt + pos) : pos;
+      } else if (p.mode == kPerRowArrays) {
+        pos = __ldg(p.pos_rows + r);
+        kv_row = __ldg(p.kv_rows + r);
+      } else {
+        pos = p.mr->pos[r];
+        const int slot = p.mr->tree ? p.mr->slot[r] : pos;
+        kv_row = p.mr->pt[r][slot];
+      }
+    };
+    int pos = 0, kv_row = 0, ok = 1;
+    if (n_local > 0) where(0, pos, kv_row, ok);
+    long long issued = 0;
+    bool good = true;
+    for (long long i = 0; i < n_local; ++i) {
+      const int s = static_cast<int>(i % kBulkStages);
+      int npos = 0, nkv = 0, nok = 1;
+      if (i + 1 < n_local) where(i + 1, npos, nkv, nok);  // in flight while this row is issued
+      if (!(good = mbar_wait_or_abort(empty + s, static_cast<uint32_t>(((i / kBulkStages) & 1) ^ 1), abort_flag))) break;
+      const int r = static_cast<int>(blockIdx.x + i * static_cast<long long>(gridDim.x));
+      // a bad index skips the row instead of touching memory outside the tables or the pool
+      if (p.mode == kPerRowArrays && (pos < 0 || pos >= p.max_pos || kv_row < 0 || kv_row >= p.stride)) ok = 0;
+      meta[s].pos = pos, meta[s].kv_row = kv_row, meta[s].ok = ok;
+      unsigned char* stage = smem + static_cast<size_t>(s) * stage_bytes;
+      if (!ok) {  // nothing to copy: one plain arrival completes the phase
+        mbar_arrive_expect_tx(full + s, 0);
+      } else {
+        const bool tables = p.cos_tbl != nullptr;
+        mbar_arrive_expect_tx(full + s, act_bytes + (tables ? 2u * tbl_bytes : 0u));
+        const uint32_t qb = static_cast<uint32_t>(p.Hq) * kD * 2u, kb = static_cast<uint32_t>(p.Hk) * kD * 2u;
+        if (p.q != nullptr && p.k == p.q + static_cast<size_t>(p.Hq) * kD &&
+            p.v == p.k + static_cast<size_t>(p.Hk) * kD && p.pitch_q == p.pitch_k && p.pitch_k == p.pitch_v) {
+          bulk_load(stage, p.q + static_cast<size_t>(r) * p.pitch_q, act_bytes, full + s);  // token-major row
+        } else {
+          if (qb != 0u) bulk_load(stage, p.q + static_cast<size_t>(r) * p.pitch_q, qb, full + s);
+          bulk_load(stage + qb, p.k + static_cast<size_t>(r) * p.pitch_k, kb, full + s);
+          bulk_load(stage + qb + kb, p.v + static_cast<size_t>(r) * p.pitch_v, kb, full + s);
+        }
+        if (tables) {
+          bulk_load(stage + act_bytes, p.cos_tbl + static_cast<size_t>(pos) * (kD / 2), tbl_bytes, full + s);
+          bulk_load(stage + act_bytes + tbl_bytes, p.sin_tbl + static_cast<size_t>(pos) * (kD / 2), tbl_bytes,
+                    full + s);
         }
       }
-      if (is_q) {
-        uint4* dst = reinterpret_cast<uint4*>(p.q_rot + (static_cast<size_t>(r) * p.Hq + head) * kD);
-        st_stream(dst + j, pack8(lo));
-        st_stream(dst + 8 + j, pack8(hi));
-        continue;
-      }
-      if (is_k && p.rotate_k && p.k_from_bf16) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) lo[e] = round_bf16(lo[e]), hi[e] = round_bf16(hi[e]);
-      }
-      float amax = 0.0f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fmaxf(fabsf(lo[e]), fabsf(hi[e])));
-      amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
-      amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 4));
-      const Kv8Scale sc = kv8_scale(amax);
-      const int hkv = is_k ? head - p.Hq : head - p.Hq - p.Hk;
-      const size_t srow = static_cast<size_t>(hkv) * p.stride + m.kv_row;
-      int8_t* cache = (is_k ? p.cache_k : p.cache_v) + srow * kD;
-      if (j == 0) (is_k ? p.k_scale : p.v_scale)[srow] = sc.s;
-      const uint2 cl = kv8_quant8(lo, sc), ch = kv8_quant8(hi, sc);
-      st_stream(reinterpret_cast<uint2*>(cache) + j, cl);
-      st_stream(reinterpret_cast<uint2*>(cache) + 8 + j, ch);
+      issued = i + 1;
+      pos = npos, kv_row = nkv, ok = nok;
     }
+    if (!good) {
+      // A stage never came back, or a consumer gave up. Record it and give every copy issued so far one
+      // more bounded chance to land, so that none is in flight towards this CTA's shared memory at exit.
+      atomicOr(status, kStatusRopeWaitTimeout);
+      for (long long i = issued > kBulkStages ? issued - kBulkStages : 0; i < issued; ++i)
+        (void)mbar_wait_bounded(full + (i % kBulkStages), static_cast<uint32_t>((i / kBulkStages) & 1));
+    } else {
+      // normal path: the consumers hand the last stages back only after reading them, i.e. after
+      // their copies landed; wait for that so that no copy outlives the CTA's shared memory
+      for (long long i = n_local > kBulkStages ? n_local - kBulkStages : 0; i < n_local; ++i)
+        if (!mbar_wait_or_abort(empty + (i % kBulkStages), static_cast<uint32_t>((i / kBulkStages) & 1), abort_flag)) {
+          atomicOr(status, kStatusRopeWaitTimeout);
+          break;
+        }
+    }
+    return;
   }
-  if (failed && t == 0) {
-    // A copy never signalled. Record it and give every copy issued so far one more bounded
-    // chance to land, so that none is in flight towards this CTA's shared memory at exit.
-    atomicOr(status, kStatusRopeWaitTimeout);
-    for (long long i = 0; i < issued_until; ++i)
-      (void)mbar_wait_bounded(full + (i % kBulkStages), static_cast<uint32_t>((i / kBulkStages) & 1));
+
+  // ---- consumers -------------------------------------------------------------------------------
+  const int g = t >> 3, j = t & 7, lane = t & 31;
+  const unsigned gmask = 0xffu << (t & 24);
+  for (long long i = 0; i < n_local; ++i) {
+    const int s = static_cast<int>(i % kBulkStages);
+    if (!mbar_wait_or_abort(full + s, static_cast<uint32_t>((i / kBulkStages) & 1), abort_flag)) {
+      if (lane == 0) atomicOr(status, kStatusRopeWaitTimeout);
+      return;
+    }
+    const RowMeta m = meta[s];
+    if (m.ok) {
+      const int r = static_cast<int>(blockIdx.x + i * static_cast<long long>(gridDim.x));
+      const unsigned char* stage = smem + static_cast<size_t>(s) * stage_bytes;
+      float c[8], sn[8];
+      if (p.cos_tbl != nullptr) {
+        const float4* cp = reinterpret_cast<const float4*>(stage + act_bytes) + 2 * j;
+        const float4* sp = reinterpret_cast<const float4*>(stage + act_bytes + tbl_bytes) + 2 * j;
+        const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+        c[0] = c0.x, c[1] = c0.y, c[2] = c0.z, c[3] = c0.w, c[4] = c1.x, c[5] = c1.y, c[6] = c1.z, c[7] = c1.w;
+        sn[0] = s0.x, sn[1] = s0.y, sn[2] = s0.z, sn[3] = s0.w, sn[4] = s1.x, sn[5] = s1.y, sn[6] = s1.z, sn[7] = s1.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) c[e] = 1.0f, sn[e] = 0.0f;
+      }
+#pragma unroll
+      for (int k = 0; k < kMaxHeadsPerThread; ++k) {
+        const int head = g + k * kBulkHeadsPerPass;
+        if (head >= heads_total) break;
+        const bool is_q = head < p.Hq;
+        const bool is_k = !is_q && head < p.Hq + p.Hk;
+        const uint4* src = reinterpret_cast<const uint4*>(stage + static_cast<size_t>(head) * kD * 2);
+        float lo[8], hi[8];
+        unpack8(src[j], lo);
+        unpack8(src[8 + j], hi);
+        if (is_q || (is_k && p.rotate_k)) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float a, b;
+            rope_pair(lo[e], hi[e], c[e], sn[e], a, b);
+            lo[e] = a, hi[e] = b;
+          }
+        }
+        if (is_q) {
+          uint4* dst = reinterpret_cast<uint4*>(p.q_rot + (static_cast<size_t>(r) * p.Hq + head) * kD);
+          st_stream(dst + j, pack8(lo));
+          st_stream(dst + 8 + j, pack8(hi));
+          continue;
+        }
+        if (is_k && p.rotate_k && p.k_from_bf16) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) lo[e] = round_bf16(lo[e]), hi[e] = round_bf16(hi[e]);
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fmaxf(fabsf(lo[e]), fabsf(hi[e])));
+        amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 4));
+        const Kv8Scale sc = kv8_scale(amax);
+        const int hkv = is_k ? head - p.Hq : head - p.Hq - p.Hk;
+        const size_t srow = static_cast<size_t>(hkv) * p.stride + m.kv_row;
+        int8_t* cache = (is_k ? p.cache_k : p.cache_v) + srow * kD;
+        if (j == 0) (is_k ? p.k_scale : p.v_scale)[srow] = sc.s;
+        const uint2 cl = kv8_quant8(lo, sc), ch = kv8_quant8(hi, sc);
+        st_stream(reinterpret_cast<uint2*>(cache) + j, cl);
+        st_stream(reinterpret_cast<uint2*>(cache) + 8 + j, ch);
+      }
+    }
+    // the warp is done reading the stage: it goes back to the producer
+    __syncwarp();
+    if (lane == 0) mbar_arrive_local(empty + s);
   }
 }
 
@@ -399,18 +437,18 @@ int launch_rope_kv(const char* fn, RopeKvParams& p) {
   const bool want_bulk = !(env != nullptr && env[0] == '0');
   unsigned int* status = want_bulk ? device_status_ptr() : nullptr;
   const size_t stage_bytes = static_cast<size_t>(heads_total) * kD * 2 + 2 * (kD / 2) * 4;
-  const size_t smem = kBulkStages * stage_bytes + kBulkStages * (sizeof(uint64_t) + sizeof(RowMeta));
+  const size_t smem = kBulkStages * stage_bytes + kBulkStages * (2 * sizeof(uint64_t) + sizeof(RowMeta)) + 16;
   const bool aligned = aligned16(p.q) && aligned16(p.k) && aligned16(p.v) && aligned16(p.cos_tbl) &&
                        aligned16(p.sin_tbl) && (p.pitch_q * 2) % 16 == 0 && (p.pitch_k * 2) % 16 == 0 &&
                        (p.pitch_v * 2) % 16 == 0;
   if (status != nullptr && aligned && heads_total <= kMaxHeadsPerThread * kBulkHeadsPerPass && smem <= 100 * 1024) {
-    static bool attr_set[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    static std::atomic<bool> attr_set[64];  // per device; relaxed: setting the attribute twice is harmless
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(fn, "cannot identify the current device");
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_relaxed)) {
       G4_CUDA_TRY(fn, cudaFuncSetAttribute(rope_kv_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            100 * 1024));
-      attr_set[dev] = true;
+      attr_set[dev].store(true, std::memory_order_relaxed);
     }
     const int per_sm = static_cast<int>(std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / smem)));
     const unsigned grid = static_cast<unsigned>(std::min<long long>(p.rows, static_cast<long long>(sm_count()) * per_sm));
