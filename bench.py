@@ -1074,6 +1074,45 @@ def _run_e2e_bound(seq, rows, device, steps, s, glue, torch):
     return ms, h2d, d2h, steps
 
 
+def prefill_attention_only(rows, launches, local_rank):
+    """The causal attention of one prefill chunk over an int8 pool of 16-token pages in permuted
+    order, `launches` times after three warm-up launches: the small case a profiler capture runs."""
+    import torch
+    import granite4_b200  # noqa: F401
+    from granite4_b200 import glue, kernels as k
+    s = glue.GraniteShapes()
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    g = torch.Generator(device=device).manual_seed(1234)
+    stride = max(16384, (rows + 15) // 16 * 16)
+    ck = torch.randint(-127, 128, (s.kv_heads, stride, s.head_dim), generator=g, device=device, dtype=torch.int8)
+    cv = torch.randint(-127, 128, (s.kv_heads, stride, s.head_dim), generator=g, device=device, dtype=torch.int8)
+    ksc = torch.rand(s.kv_heads, stride, generator=g, device=device) * 0.02 + 0.005
+    vsc = torch.rand(s.kv_heads, stride, generator=g, device=device) * 0.02 + 0.005
+    pages = torch.randperm(stride // 16, generator=g, device=device)
+    table = (pages.repeat_interleave(16) * 16 + torch.arange(stride, device=device) % 16).to(torch.int32)
+    q = torch.randn(rows, s.q_heads * s.head_dim, generator=g, device=device).to(torch.bfloat16)
+    out = torch.empty_like(q)
+
+    def run():
+        return k.prefill_attention_int8(q, 1.0 / 128, s.q_heads, s.kv_heads, s.head_dim, 0, stride, out, ck, cv, ksc, vsc,
+                                        pt=table)
+    for _ in range(3):
+        assert run() == 0
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    a.record()
+    for _ in range(launches):
+        run()
+    b.record()
+    torch.cuda.synchronize(device)
+    us = a.elapsed_time(b) / launches * 1e3
+    flops = 4.0 * s.head_dim * s.q_heads * rows * (rows + 1) / 2
+    from granite4_b200 import capi
+    return {"prefill_attention_rows": rows, "mean_us": us, "tflops": flops / (us * 1e-6) / 1e12,
+            "device_status": capi.lib().device_status()}
+
+
 def timed_step(seq, op_events, stream):
     """GlueSequence.run() with an event pair around every op (for the per-op durations)."""
     import torch
@@ -1098,6 +1137,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--sweep-only", action="store_true", help="only the sweep (short profiler captures)")
+    ap.add_argument("--prefill-attention-only", type=int, metavar="ROWS", default=0,
+                    help="only the causal prefill attention of a chunk of ROWS rows, a few launches (profiler captures)")
     ap.add_argument("--traffic-from-ncu", metavar="CSV", help="convert a profiler launch list; no benchmark")
     ap.add_argument("--traffic-rows", type=int, default=8192, help="token rows of that capture")
     args = ap.parse_args()
@@ -1111,6 +1152,9 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} needs one process per GPU: launch with "
                          f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {args.gpus} "
                          f"--master-addr 127.0.0.1 --master-port <port> bench.py --gpus {args.gpus} ...")
+    if args.prefill_attention_only:
+        print(json.dumps(prefill_attention_only(args.prefill_attention_only, max(args.steps, 1), local_rank)))
+        return
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
     else:
