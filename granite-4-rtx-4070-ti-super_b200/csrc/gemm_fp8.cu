@@ -34,6 +34,7 @@
 #include <cstdlib>
 #include <map>
 #include <mutex>
+#include <utility>
 
 #include "../../include/granite4_b200.h"
 #include "g4_host.h"
@@ -734,6 +735,291 @@ gemm_fp8_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   }
 }
 
+// ---- at most 16 rows: the weights as the M operand ---------------------------------------------------
+// A decode or verify step multiplies 1 .. 16 rows by every weight matrix: the GEMM is one pass over W,
+// and an MMA whose M side is the (mostly empty) activation tile gets through too few weight bytes per
+// instruction to keep up with an SM's share of HBM. Here the operands change sides: D^T = W A^T, so
+// one MMA (M 128 weight rows, N 16 activation rows, K 32) consumes 4 KB of weights, and the
+// accumulator is 128 tensor-memory lanes (output columns) by 16 columns (output rows).
+//
+// A unit is 128 weight rows times a slice of K; the grid is one CTA per unit and is not persistent.
+// The CTA is small (a 90 KB ring, 32 columns of tensor memory) so that two are resident per SM: while
+// one drains its accumulator the other streams, and under programmatic dependent launch the CTAs of
+// the next GEMM on the stream move in and fetch their first weight blocks while this one finishes.
+//
+// The slices of one tile are the CTAs of one thread-block cluster, and their partial sums meet in
+// distributed shared memory as a reduce-scatter: rank o owns a chunk of the tile's 128 columns; the
+// epilogue thread of every other rank that holds one of those columns stores its partial sums into
+// rank o's receive buffer and arrives (release, cluster scope) on rank o's mbarrier; the owner's
+// thread for the column waits for that barrier (acquire), adds the partials in rank order - its own
+// from registers in its place - and runs the epilogue. No workspace in global memory, no atomics,
+// the same order of additions every time, and no cluster-wide barrier on the way out: the only one
+// is at the start (every CTA is running and its barriers exist before anyone writes to it), where
+// it overlaps the first loads.
+//
+// Roles: warp 0, lanes 0 .. 4: lane s owns ring stage s (k-blocks s, s + 5, ...): arms its barrier and
+// issues the two TMA loads, the first W block before the wait on the kernel ahead of this one on the
+// stream; warp 1: tensor-memory allocation, one thread issues the MMAs; warps 2-5: accumulator ->
+// registers, exchange, epilogue. Every mbarrier wait is bounded as in the other forms.
+constexpr int kDecStages = 5, kDecRows = 16;
+constexpr uint32_t kDecWBytes = kBM * kBK, kDecABytes = kDecRows * kBK, kDecStageBytes = kDecWBytes + kDecABytes;
+constexpr uint32_t kDecTmemCols = 32;
+constexpr int kDecMaxSplits = 8;  // the portable cluster size
+constexpr uint32_t kDecRecvBytes = 10240;
+constexpr size_t kDecSmemBytes = 1024 + size_t(kDecStages) * kDecStageBytes + kDecRecvBytes + 256;
+struct DecRing {
+  uint64_t full[kDecStages], empty[kDecStages], acc_full, red_full;
+  uint32_t tmem_base;
+  int abort;
+};
+
+// Columns of a tile owned by one rank of a cluster of `splits`: a multiple of 8, so that an owner's
+// bf16 row segment starts on a 16-byte boundary. (splits - 1) * 4 row groups * chunk * 16 bytes fit
+// in kDecRecvBytes for every splits <= 8.
+__host__ __device__ constexpr int dec_chunk(int splits) { return ((kBM + splits - 1) / splits + 7) / 8 * 8; }
+static_assert(7 * 4 * dec_chunk(8) * 16 <= int(kDecRecvBytes) && 5 * 4 * dec_chunk(6) * 16 <= int(kDecRecvBytes) &&
+                  4 * 4 * dec_chunk(5) * 16 <= int(kDecRecvBytes) && 3 * 4 * dec_chunk(4) * 16 <= int(kDecRecvBytes) &&
+                  2 * 4 * dec_chunk(3) * 16 <= int(kDecRecvBytes) && 6 * 4 * dec_chunk(7) * 16 <= int(kDecRecvBytes) &&
+                  1 * 4 * dec_chunk(2) * 16 <= int(kDecRecvBytes),
+              "the receive buffer holds every rank's partial sums of the owned columns");
+
+__device__ __forceinline__ bool dec_wait(uint64_t* bar, uint32_t parity, DecRing* ring, unsigned int* status) {
+  volatile int* ab = &ring->abort;
+  for (uint32_t i = 0; i < kMbarWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*ab) return false;
+    if (i > 256) __nanosleep(64);
+  }
+  *ab = 1;
+  if (status != nullptr) atomicOr(status, kStatusGemmWaitTimeout);
+  return false;
+}
+// The same wait with acquire semantics at cluster scope: what the arriving threads of other CTAs
+// stored into this CTA's shared memory before their arrival is visible after it.
+__device__ __forceinline__ bool dec_wait_cluster(uint64_t* bar, uint32_t parity, DecRing* ring, unsigned int* status) {
+  volatile int* ab = &ring->abort;
+  for (uint32_t i = 0; i < kMbarWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (*ab) return false;
+    if (i > 256) __nanosleep(64);
+  }
+  *ab = 1;
+  if (status != nullptr) atomicOr(status, kStatusGemmWaitTimeout);
+  return false;
+}
+
+// 32 lanes x 16 consecutive 32-bit columns of tensor memory: thread t of the warp gets lane (base lane + t).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+gemm_fp8_decode_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                       const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw);
+  uint8_t* recv_ptr = tiles_ptr + size_t(kDecStages) * kDecStageBytes;
+  DecRing* ring = reinterpret_cast<DecRing*>(recv_ptr + kDecRecvBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int splits = p.splits;
+  const uint32_t rank = splits > 1 ? cluster_rank() : 0u;  // the slice of K
+  const int tile = int(blockIdx.x) / splits;
+  const int kblocks = (p.K + kBK - 1) / kBK;
+  const int kb0 = int(rank) * p.kb_per, kb1 = min(kblocks, kb0 + p.kb_per);
+  const int chunk = dec_chunk(splits);
+  const int owned = max(0, min(chunk, kBM - int(rank) * chunk));  // columns of the tile this rank finishes
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    for (int s = 0; s < kDecStages; ++s) mbar_init(&ring->full[s], 1), mbar_init(&ring->empty[s], 1);
+    mbar_init(&ring->acc_full, 1);
+    mbar_init(&ring->red_full, uint32_t(max(1, (splits - 1) * owned)));  // one arrival per partial column
+    ring->abort = 0;
+    mbar_init_fence();
+    fence_async_smem();
+  }
+  if (warp == 1) tmem_alloc<false>(smem_u32(&ring->tmem_base), kDecTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ring->tmem_base;
+  // Split arrival on the cluster barrier: "this CTA runs and its barriers exist". Every thread waits
+  // for it once, the epilogue threads just before they write to a peer, by when it is long complete.
+  if (splits > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+
+  // The kernel after this one may move in as CTAs of this one retire. Only the threads that read
+  // what the kernel ahead wrote (activations, their scale, the residual) or that write wait for it.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane < kDecStages) {
+      const uint32_t dst = tiles_addr + uint32_t(lane) * kDecStageBytes, bar = smem_u32(&ring->full[lane]);
+      int kb = kb0 + lane;
+      const bool any = kb < kb1;
+      if (any) {  // first use of the stage: it is empty; W is a constant of the model
+        mbar_arrive_expect_tx(&ring->full[lane], kDecStageBytes);
+        tma_load_2d<false>(dst, &map_w, kb * kBK, tile * kBM, bar);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (any) tma_load_2d<false>(dst + kDecWBytes, &map_a, kb * kBK, 0, bar);
+      uint32_t round = 1;
+      for (kb += kDecStages; kb < kb1; kb += kDecStages, ++round) {
+        if (!dec_wait(&ring->empty[lane], (round & 1u) ^ 1u, ring, p.status)) break;
+        mbar_arrive_expect_tx(&ring->full[lane], kDecStageBytes);
+        tma_load_2d<false>(dst, &map_w, kb * kBK, tile * kBM, bar);
+        tma_load_2d<false>(dst + kDecWBytes, &map_a, kb * kBK, 0, bar);
+      }
+    }
+    __syncwarp();
+    if (splits > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // f32 accumulator, e4m3 x e4m3, both operands K-major, N 16, M 128
+      constexpr uint32_t idesc = (1u << 4) | (uint32_t(kDecRows >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
+        const uint32_t s = it % kDecStages, ph = (it / kDecStages) & 1u;
+        if (!(ok = dec_wait(&ring->full[s], ph, ring, p.status))) break;
+        tc_fence_after();
+        const uint32_t w_addr = tiles_addr + s * kDecStageBytes;
+        const uint64_t w_desc = smem_desc_k128(w_addr), a_desc = smem_desc_k128(w_addr + kDecWBytes);
+#pragma unroll
+        for (int k = 0; k < kBK / 32; ++k)
+          mma_f8<false>(tmem_base, w_desc + uint64_t(2 * k), a_desc + uint64_t(2 * k), idesc, (it | uint32_t(k)) != 0u);
+        mma_commit<false>(smem_u32(&ring->empty[s]));
+      }
+      if (ok) mma_commit<false>(smem_u32(&ring->acc_full));
+    }
+    __syncwarp();
+    if (splits > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  } else {
+    const int et = (warp & 3) * 32 + lane;  // the tensor-memory lane this thread reads = the tile's column
+    const int n = tile * kBM + et;
+    const int groups = (p.M + 3) / 4;       // float4 groups of rows that carry data
+    const int owner = et / chunk;           // the rank that finishes this column
+    const bool mine = owner == int(rank);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // what the epilogue needs from global memory, requested before the accumulator is complete
+    float sc = 0.0f;
+    uint16_t resid[kDecRows];
+    if (mine && n < p.N) {
+      sc = (p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f) * seg_scale(p, n);
+      if (p.out_kind == GRANITE4_GEMM_OUT_RESIDUAL) {
+#pragma unroll
+        for (int j = 0; j < kDecRows; ++j)
+          if (j < p.M) resid[j] = p.residual[size_t(j) * p.ldc + n];  // may alias the output: plain loads
+      }
+    }
+    bool ok = dec_wait(&ring->acc_full, 0u, ring, p.status);
+    tc_fence_after();
+    __syncwarp();
+    uint32_t v[kDecRows];
+    tmem_ld16(tmem_base + (uint32_t((warp & 3) * 32) << 16), v);
+    tmem_ld_wait();
+    tc_fence_before();
+    if (splits > 1) {
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every CTA of the cluster runs
+      const int local = et - owner * chunk;  // column within the owner's chunk
+      if (!mine) {
+        // slot of this rank among the owner's senders: ranks in order, the owner itself left out
+        const uint32_t slot = rank < uint32_t(owner) ? rank : rank - 1u;
+        const uint32_t base = cluster_addr(smem_u32(recv_ptr), uint32_t(owner));
+#pragma unroll
+        for (int g = 0; g < kDecRows / 4; ++g) {
+          if (g < groups) {
+            const uint32_t dst = base + (((slot * (kDecRows / 4) + uint32_t(g)) * uint32_t(chunk) + uint32_t(local)) << 4);
+            asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[4 * g]),
+                         "r"(v[4 * g + 1]), "r"(v[4 * g + 2]), "r"(v[4 * g + 3])
+                         : "memory");
+          }
+        }
+        asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
+                         cluster_addr(smem_u32(&ring->red_full), uint32_t(owner)))
+                     : "memory");
+      } else {
+        ok = ok && dec_wait_cluster(&ring->red_full, 0u, ring, p.status);
+        const float4* red = reinterpret_cast<const float4*>(recv_ptr);
+        float acc[kDecRows];
+#pragma unroll
+        for (int j = 0; j < kDecRows; ++j) acc[j] = 0.0f;
+        bool first = true;
+        for (int r = 0; r < splits; ++r) {  // rank order; this rank's own partial comes from its registers
+          const int slot = r < int(rank) ? r : r - 1;
+#pragma unroll
+          for (int g = 0; g < kDecRows / 4; ++g) {
+            if (g < groups) {
+              float4 x;
+              if (r == int(rank))
+                x = make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]), __uint_as_float(v[4 * g + 2]),
+                                __uint_as_float(v[4 * g + 3]));
+              else
+                x = red[(size_t(slot) * (kDecRows / 4) + g) * chunk + local];
+              if (first) {
+                acc[4 * g] = x.x, acc[4 * g + 1] = x.y, acc[4 * g + 2] = x.z, acc[4 * g + 3] = x.w;
+              } else {
+                acc[4 * g] = __fadd_rn(acc[4 * g], x.x), acc[4 * g + 1] = __fadd_rn(acc[4 * g + 1], x.y);
+                acc[4 * g + 2] = __fadd_rn(acc[4 * g + 2], x.z), acc[4 * g + 3] = __fadd_rn(acc[4 * g + 3], x.w);
+              }
+            }
+          }
+          first = false;
+        }
+#pragma unroll
+        for (int j = 0; j < kDecRows; ++j) v[j] = __float_as_uint(acc[j]);
+      }
+    }
+    if (mine && ok && n < p.N) {
+#pragma unroll
+      for (int j = 0; j < kDecRows; ++j) {
+        if (j < p.M) {
+          const size_t off = size_t(j) * p.ldc + n;
+          float y = sc * __uint_as_float(v[j]);
+          if (p.out_kind == GRANITE4_GEMM_OUT_F32) {
+            p.out_f32[off] = y;
+          } else {
+            if (p.out_kind == GRANITE4_GEMM_OUT_RESIDUAL) y = __fadd_rn(bf16_to_f32(resid[j]), __fmul_rn(p.resid_scale, y));
+            p.out_bf16[off] = uint16_t(f32_to_bf16_bits(y));
+          }
+        }
+      }
+    }
+  }
+
+  // A CTA leaves when its own part is done: senders have nothing more to receive (a rank that owns
+  // no columns gets no stores), owners have seen every arrival on red_full.
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (ring->abort) {  // give copies and MMAs already issued a bounded time to land
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<false>(tmem_base, kDecTmemCols);
+  }
+}
+
 // ---- host ---------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -925,6 +1211,78 @@ int launch_stream(const char* fn, const uint8_t* d_a, long long lda, const uint8
   return 0;
 }
 
+bool decode_form_enabled() {
+  const char* v = std::getenv("G4_GEMM_DECODE");  // G4_GEMM_DECODE=0: at most 16 rows take the older forms
+  return !(v != nullptr && v[0] == '0');
+}
+
+// Slices of K for the 16-row form. A unit costs about 4 us whatever its size (first bytes from HBM,
+// the hand-over of the partial sums, the epilogue), and a CTA with a 90 KB ring streams ~45 B/ns, so
+// few large units are better than many small ones as long as every SM has one: measured at one row,
+// tiles x slices of about 1.3 per SM is the best plan for all five projection shapes of the model
+// (1 slice for the gate|up and lm_head shapes, 4 for QKV, 6 for O and down; clusters of 7 or 8 lose
+// to the scheduling of large clusters what they gain in balance). At least four k-blocks per slice.
+// G4_GEMM_DECODE_SPLITS forces a count (measurements).
+struct DecodePlan {
+  int splits, kb_per;
+};
+DecodePlan plan_decode(int N, int K, int sms) {
+  const int tiles = (N + kBM - 1) / kBM, kblocks = (K + kBK - 1) / kBK;
+  int s = (13 * (sms > 0 ? sms : 1) / 10 + tiles - 1) / tiles;
+  if (s > 6) s = 6;
+  if (const char* v = std::getenv("G4_GEMM_DECODE_SPLITS"); v != nullptr && std::atoi(v) > 0) s = std::atoi(v);
+  if (s > kblocks / 4) s = kblocks / 4;
+  if (s > kDecMaxSplits) s = kDecMaxSplits;
+  if (s < 1) s = 1;
+  const int per = (kblocks + s - 1) / s;
+  return DecodePlan{(kblocks + per - 1) / per, per};
+}
+
+// Launches the 16-row form; 1 when the device cannot co-schedule a cluster of the planned size (the
+// caller then takes another form), 0 launched, -1 failed.
+int launch_decode(const char* fn, const uint8_t* d_a, long long lda, const uint8_t* d_w, GemmParams p) {
+  const DecodePlan pl = plan_decode(p.N, p.K, sm_count());
+  p.splits = pl.splits, p.kb_per = pl.kb_per;
+  static std::mutex mu;
+  static std::map<int, cudaError_t> done;
+  static std::map<std::pair<int, int>, bool> fits;
+  int dev = 0;
+  G4_CUDA_TRY(fn, cudaGetDevice(&dev));
+  const int tiles = (p.N + kBM - 1) / kBM;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(unsigned(tiles) * unsigned(p.splits));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kDecSmemBytes;
+  cfg.stream = current_stream();
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = unsigned(p.splits), attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.find(dev) == done.end())
+      done[dev] = cudaFuncSetAttribute(gemm_fp8_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(kDecSmemBytes));
+    G4_CUDA_TRY(fn, done[dev]);
+    const auto key = std::make_pair(dev, p.splits);
+    if (fits.find(key) == fits.end()) {
+      int n = 0;
+      cfg.numAttrs = 1;
+      fits[key] = cudaOccupancyMaxActiveClusters(&n, gemm_fp8_decode_kernel, &cfg) == cudaSuccess && n >= 1;
+      (void)cudaGetLastError();
+    }
+    if (!fits[key]) return 1;
+  }
+  CUtensorMap map_a, map_w;
+  if (!make_map(&map_a, d_a, p.M, p.K, lda, kDecRows) || !make_map(&map_w, d_w, p.N, p.K, p.K, kBM))
+    return fail(fn, "the tensor map could not be encoded");
+  cfg.numAttrs = pdl_enabled() ? 2u : 1u;
+  G4_CUDA_TRY(fn, cudaLaunchKernelEx(&cfg, gemm_fp8_decode_kernel, map_a, map_w, p));
+  return 0;
+}
+
 // Encodes the two tensor maps of form C and launches it over min(units, SMs) CTAs (CTA pairs).
 template <class C>
 int launch(const char* fn, const uint8_t* d_a, long long lda, const uint8_t* d_w, const GemmParams& p) {
@@ -960,6 +1318,7 @@ int launch(const char* fn, const uint8_t* d_a, long long lda, const uint8_t* d_w
 
 extern "C" long long granite4_gemm_fp8_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M <= kDecRows && decode_form_enabled()) return 0;  // partial sums go through a cluster's shared memory
   if (M > 2 && stream_enabled()) return 0;  // the stream form needs none
   return static_cast<long long>(plan_split(M, N, K, sm_count()).bytes);
 }
@@ -1007,6 +1366,10 @@ extern "C" int granite4_kernel_gemm_fp8(int out_kind, const uint8_t* d_a, long l
     p.swiglu_i = N / 2, p.amax_slot = ep->d_out_scale_amax;
     if (!amax_prezeroed()) G4_CUDA_TRY(fn, cudaMemsetAsync(p.amax_slot, 0, 2 * sizeof(float), current_stream()));
     if (M <= kBM) return launch<CfgWide>(fn, d_a, lda, d_w, p);  // no split of K under this epilogue
+  }
+  if (M <= kDecRows && decode_form_enabled()) {
+    const int rc = launch_decode(fn, d_a, lda, d_w, p);
+    if (rc <= 0) return rc;
   }
   if (M <= kBM) {
     // A stream of the weights. Measured per layer of four projections (one CUDA graph): the split of

@@ -1841,20 +1841,27 @@ def test_gemm_fp8_rejects_bad_arguments(K):
     assert K.gemm_fp8(a[:0], w, out[:0]) == 0                              # no rows: nothing to do
 
 
-@pytest.mark.parametrize("stream", ["1", "0"])
+@pytest.mark.parametrize("form", ["decode", "stream", "split"])
 @pytest.mark.parametrize("M,N,Kd", [(1, 6144, 4096), (16, 4096, 1536), (5, 1000, 4096 + 64), (8, 520, 12800),
-                                    (2, 4096, 4096), (40, 1000, 2048), (128, 6144, 1024), (40, 520, 4096 + 64)])
-def test_gemm_fp8_decode_rows_split_k_is_deterministic_and_reusable(K, port, monkeypatch, M, N, Kd, stream):
-    """At most 128 rows, both ways of streaming the weights. stream = 1: full-K tiles of a planned
-    width (3-D TMA boxes where K is a multiple of 128; one and two rows still split K). stream = 0:
-    256-column tiles, and up to 16 rows K split over CTAs that add their partial sums in a fixed
-    order through the workspace, which is handed from call to call without being cleared again."""
-    monkeypatch.setenv("G4_GEMM_STREAM", stream)
+                                    (2, 4096, 4096), (40, 1000, 2048), (128, 6144, 1024), (40, 520, 4096 + 64),
+                                    (3, 25600, 4096), (16, 100, 256), (7, 4096, 12800)])
+def test_gemm_fp8_decode_rows_split_k_is_deterministic_and_reusable(K, port, monkeypatch, M, N, Kd, form):
+    """At most 128 rows, every way of streaming the weights. decode (the default): up to 16 rows with
+    the weights as the M operand, K sliced over the CTAs of a cluster that hand their partial sums to
+    rank 0 through distributed shared memory (no workspace); more rows as in stream. stream: full-K
+    tiles of a planned width (3-D TMA boxes where K is a multiple of 128; one and two rows split K
+    through the workspace). split: 256-column tiles, and up to 16 rows K split over CTAs that add their
+    partial sums in a fixed order through the workspace, which is handed from call to call without
+    being cleared again."""
+    monkeypatch.setenv("G4_GEMM_DECODE", "1" if form == "decode" else "0")
+    monkeypatch.setenv("G4_GEMM_STREAM", "0" if form == "split" else "1")
     rng = np.random.default_rng(N + Kd)
     a, w = _codes(rng, (M, Kd)), _codes(rng, (N, Kd))
     res = rand_bf16(M, (M, N))
     ws = K.gemm_fp8_workspace(M, N, Kd, DEV)
-    assert ws is not None or M > (2 if stream == "1" else 16)  # no workspace is wanted where no form would use one
+    # no workspace is wanted where no form would use one
+    assert ws is None or (form == "stream" and M <= 2) or (form == "split" and M <= 16)
+    assert ws is not None or form == "decode" or M > 2 or N * Kd < 2 ** 20
     exact, mag = _gemm_f64(a, w, 0.3, (0.01,), (), N)
     a_scale = torch.tensor([0.3, 0.0], device=DEV)
     f32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
