@@ -849,7 +849,7 @@ def small_shapes_and_embed(seq, rows, device, stream):
     # so let the clocks come back before the latency-sized measurements
     torch.cuda.synchronize()
     time.sleep(1.0)
-    for n in (1, 8):
+    for n in (1, 8, 16):
         outs = {name: torch.empty(n, N, dtype=torch.bfloat16, device=device) for name, N, _ in proj}
         wsp = {name: k.gemm_fp8_workspace(n, N, Kd, device) for name, N, Kd in proj}
 
@@ -1113,6 +1113,39 @@ def prefill_attention_only(rows, launches, local_rank):
             "device_status": capi.lib().device_status()}
 
 
+def decode_gemm_only(shape, launches, local_rank):
+    """One decode-size FP8 GEMM (shape "N,K,rows": weight rows, depth, activation rows) over three
+    rotated weight matrices, `launches` times after six warm-up launches: the small case a profiler
+    capture of the 16-row form runs."""
+    import torch
+    import granite4_b200  # noqa: F401
+    from granite4_b200 import capi, kernels as k
+    N, Kd, rows = (int(x) for x in shape.split(","))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    g = torch.Generator(device=device).manual_seed(1234)
+
+    def codes(r, c):
+        return (torch.randn(r, c, generator=g, device=device) * (448.0 / 5.0)).to(torch.float8_e4m3fn).view(torch.uint8)
+    ws = [codes(N, Kd) for _ in range(3)]
+    a = codes(max(rows, 1), Kd)
+    a_sc = torch.tensor([5.0 / 448.0, 5.0], device=device)
+    out = torch.empty(rows, N, dtype=torch.bfloat16, device=device)
+    wsp = k.gemm_fp8_workspace(rows, N, Kd, device)
+    for i in range(6):
+        assert k.gemm_fp8(a, ws[i % 3], out, a_scale=a_sc, w_scales=(0.01,), workspace=wsp) == 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    e0.record()
+    for i in range(launches):
+        k.gemm_fp8(a, ws[i % 3], out, a_scale=a_sc, w_scales=(0.01,), workspace=wsp)
+    e1.record()
+    torch.cuda.synchronize(device)
+    us = e0.elapsed_time(e1) / launches * 1e3
+    return {"decode_gemm": {"N": N, "K": Kd, "rows": rows}, "mean_us_eager": us, "weight_gbs": N * Kd / (us * 1e-6) / 1e9,
+            "device_status": capi.lib().device_status()}
+
+
 def timed_step(seq, op_events, stream):
     """GlueSequence.run() with an event pair around every op (for the per-op durations)."""
     import torch
@@ -1139,6 +1172,8 @@ def main():
     ap.add_argument("--sweep-only", action="store_true", help="only the sweep (short profiler captures)")
     ap.add_argument("--prefill-attention-only", type=int, metavar="ROWS", default=0,
                     help="only the causal prefill attention of a chunk of ROWS rows, a few launches (profiler captures)")
+    ap.add_argument("--decode-gemm-only", metavar="N,K,ROWS", default="",
+                    help="only one decode-size FP8 GEMM of that shape, --steps launches (a small profiler case)")
     ap.add_argument("--traffic-from-ncu", metavar="CSV", help="convert a profiler launch list; no benchmark")
     ap.add_argument("--traffic-rows", type=int, default=8192, help="token rows of that capture")
     args = ap.parse_args()
@@ -1154,6 +1189,9 @@ def main():
                          f"--master-addr 127.0.0.1 --master-port <port> bench.py --gpus {args.gpus} ...")
     if args.prefill_attention_only:
         print(json.dumps(prefill_attention_only(args.prefill_attention_only, max(args.steps, 1), local_rank)))
+        return
+    if args.decode_gemm_only:
+        print(json.dumps(decode_gemm_only(args.decode_gemm_only, max(args.steps, 1), local_rank)))
         return
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
