@@ -244,27 +244,24 @@ __device__ __forceinline__ void rope_pair(float a, float b, float c, float s, fl
 // the bf16 result is the neighbouring value (the stated tolerance is 1 bf16
 // ulp; the reference's own device kernels are tested to the same bound against
 // this host formula).
-// For g below about -87.3 the sum 1 + e^-g passes 2^126 and its flushed reciprocal
-// is zero, while the host still divides by a finite number until expf(-g)
-// overflows at -g = 88.7228...: there the host's quotient is a normal float of
-// magnitude ~1e-36. Those few gate values (three bf16 values: -87.5, -88, -88.5)
-// take swiglu_tail, which forms g * 2^(64 - t) * 2^-64 with every factor in the
-// normal range; below the overflow point both sides give g / inf = -0.
-static __device__ __noinline__ float swiglu_tail(float g, float t, float u) {
-  if (g < -88.72283f) return __fmul_rn(__fmul_rn(g, 0.0f), u);
-  float r;
-  const float s = __fsub_rn(64.0f, t);
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(s));
-  return __fmul_rn(__fmul_rn(__fmul_rn(g, r), 0x1p-64f), u);
-}
+// For g below about -87.3 the sum d = 1 + e^-g passes 2^126, where the flushed
+// reciprocal would be zero, while the host still divides by a finite number until
+// expf(-g) overflows at -g = 88.7228... (there its quotient is a normal float of
+// magnitude ~1e-36; three bf16 gates fall in that window: -87.5, -88, -88.5).
+// The reciprocal is therefore taken of d / 4 - exact scaling, and d / 4 <= 2^126 for
+// every finite d - and the factor 1/4 applied to the product afterwards: the same
+// mantissas as g * rcp(d) * u wherever that is in range (the unit's result depends
+// on the exponent only through its sign flip), the host's quotient in the window,
+// and g * 0 = -0 once e^-g overflows to infinity, as on the host. No test, no branch:
+// two multiplications by a power of two per element. (g * r is four times the
+// result and overflows for |g| above 8.5e37, which no gate of a network reaches.)
 __device__ __forceinline__ float swiglu(float g, float u) {
   float e, r;
   const float t = __fmul_rn(g, -1.4426950408889634f);
-  if (__builtin_expect(t > 126.0f, 0)) return swiglu_tail(g, t, u);
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
-  const float d = __fadd_rn(1.0f, e);
+  const float d = __fmul_rn(__fadd_rn(1.0f, e), 0.25f);
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
-  return __fmul_rn(__fmul_rn(g, r), u);
+  return __fmul_rn(__fmul_rn(__fmul_rn(g, r), 0.25f), u);
 }
 
 // ---- memory helpers -----------------------------------------------------------

@@ -1992,6 +1992,31 @@ def test_whole_layer_forward_glue_gemms_and_attention(K, port):
     t.close()
 
 
+def test_gemm_fp8_fused_swiglu_epilogue_with_gates_beyond_the_fast_range(K, port):
+    """Gate sums of a few hundred in magnitude, so that the epilogue meets gates in the window
+    -88.72 .. -87.34 (where 1 + e^-g is beyond 2^126 and the host still divides by a finite number),
+    gates below it (-0 on the host) and large positive gates, against the host form applied to the same
+    GEMM's f32 output."""
+    M, I, Kd = 300, 640, 512
+    rng = np.random.default_rng(99)
+    a, w = _codes(rng, (M, Kd)), _codes(rng, (2 * I, Kd))
+    w[(w & 0x7F) > 0x50] = 0x41
+    a_scale = torch.tensor([0.6 / Kd ** 0.5, 0.0], device=DEV)
+    ws = (0.4, 0.02)
+    gu = torch.empty(M, 2 * I, dtype=torch.float32, device=DEV)
+    assert K.gemm_fp8(dev(a), dev(w), gu, a_scale=a_scale, w_scales=ws, segs=(I,)) == 0
+    act = torch.zeros(M, I, dtype=torch.int16, device=DEV)
+    slot = torch.zeros(2, dtype=torch.float32, device=DEV)
+    assert K.gemm_fp8(dev(a), dev(w), act, a_scale=a_scale, w_scales=ws, segs=(I,), swiglu_scale_amax=slot) == 0
+    g_h = host(gu)
+    gate = g_h[:, :I]
+    assert (gate < -88.8).sum() > 100 and ((gate > -88.7) & (gate < -87.4)).sum() > 10 and (gate > 50).sum() > 100
+    want = port.swiglu(np.ascontiguousarray(gate), np.ascontiguousarray(g_h[:, I:]))
+    got = host(act)
+    assert bf16_ulp_distance(got, want).max() <= 1
+    assert float(host(slot)[1]) == float(np.abs(_bf16_to_f32_np(got)).max())
+
+
 @pytest.mark.parametrize("M,I,Kd", [(300, 640, 512), (100, 200, 256), (1000, 1536, 1024), (9, 128, 128)])
 def test_gemm_fp8_fused_swiglu_epilogue_and_one_sweep_encode(K, port, M, I, Kd):
     """gate|up projection with SwiGLU folded into the epilogue (pair form, single form, ragged I):
