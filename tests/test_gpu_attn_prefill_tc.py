@@ -5,7 +5,8 @@ Oracle: the reference's golden bf16 pipeline (engine/src/kernel_math.h:265-331) 
 pool, one row at a time. Tolerances as for every attention kernel here: 0.03 absolute against that
 pipeline (engine/tests/test_kernels.cu:2055), 0.01 against an unrounded float64 evaluation.
 Random pools with random per-row scales, permuted page tables, chunks that start at position 0 and
-chunks that continue a prefix, row counts that are and are not multiples of the 64-row CTA tile.
+chunks that continue a prefix, row counts that are and are not multiples of the 64-row CTA tile,
+prefixes that are and are not multiples of the 128-position cache tile.
 """
 import numpy as np
 import pytest
@@ -107,9 +108,10 @@ def test_tensor_core_form_against_the_oracle_and_the_mma_sync_form(K, port, monk
 
 
 def test_peaked_softmax_rescales_the_accumulator(K, monkeypatch):
-    """Queries of magnitude ~60: logits spread over some +-25 binary orders, so the running maximum
-    jumps by more than 2^8 several times along a prefix and the accumulator is rescaled in tensor
-    memory; a few keys are made dominant late in the prefix. At these magnitudes the golden
+    """Queries of magnitude ~60: logits spread over some +-25 binary orders, so that along a prefix
+    the exponentials against the running maximum leave f16's range several times (a half tile's sum
+    reaches 2^12): the maximum is then taken anew and the accumulator rescaled in tensor memory; a
+    few keys are made dominant late in the prefix. At these magnitudes the golden
     pipeline's own bf16 rounding of the logits is the larger error, so the yardsticks are the
     unrounded float64 evaluation and the mma.sync form."""
     rows, stride = 192, 512
