@@ -800,7 +800,8 @@ def small_shapes_and_embed(seq, rows, device, stream):
     bf16_burst, bf16_sust = float(mp.get("bf16_tflops", 1590.0)), float(mp.get("bf16_tflops_sustained", 1400.0))
 
     def fp8_codes(r, c):
-        return (torch.randn(r, c, generator=g, device=device) * (448.0 / 5.0)).to(torch.float8_e4m3fn).view(torch.uint8)
+        # (clamped: e4m3 has no infinity, a value past 448 would become a NaN code)
+        return (torch.randn(r, c, generator=g, device=device) * (448.0 / 5.0)).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
     H, I, QKV = s.hidden, s.intermediate, (s.q_heads + 2 * s.kv_heads) * s.head_dim
     proj = (("qkv", QKV, H), ("o", H, H), ("gate_up", 2 * I, H), ("down", H, I))
     wsets = [{name: fp8_codes(N, Kd) for name, N, Kd in proj} for _ in range(2)]
@@ -1126,7 +1127,8 @@ def decode_gemm_only(shape, launches, local_rank):
     g = torch.Generator(device=device).manual_seed(1234)
 
     def codes(r, c):
-        return (torch.randn(r, c, generator=g, device=device) * (448.0 / 5.0)).to(torch.float8_e4m3fn).view(torch.uint8)
+        # (clamped: e4m3 has no infinity, a value past 448 would become a NaN code)
+        return (torch.randn(r, c, generator=g, device=device) * (448.0 / 5.0)).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
     ws = [codes(N, Kd) for _ in range(3)]
     a = codes(max(rows, 1), Kd)
     a_sc = torch.tensor([5.0 / 448.0, 5.0], device=device)

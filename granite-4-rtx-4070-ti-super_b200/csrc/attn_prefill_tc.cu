@@ -7,39 +7,38 @@
 // (engine/src/attention_gpu.h:18-19).
 //
 // A CTA owns 64 consecutive query positions of one kv head as TWO row tiles of 128 MMA rows
-// (32 positions x the 4 query heads of the group), and walks the cache in tiles of 128 positions.
+// (32 positions x the 4 query heads of the group), and walks the cache in tiles of 64 positions.
 // Both contractions of a tile are tcgen05.mma instructions with f16 operands and f32 accumulators
-// in tensor memory (all 512 columns: S and O of both row tiles):
-//   S_t = Q_t K^T   M 128, N 128, K 128  (8 instructions of K 16; Q and K from shared memory)
-//   O_t += P_t V    M 128, N 128, K 64 per half tile of 64 positions (4 instructions; P from TENSOR
-//                   MEMORY, where the softmax wrote it over the first 32 columns of the 64 logits it
-//                   came from; V from shared memory as an N-major operand)
-// so that one K / V tile, converted from int8 ONCE, serves 256 query rows. An MMA occupies the tensor
-// pipe for about the same time whatever its N up to 64 columns, and for 64 cycles at 128, so the S
-// tile is as wide as tensor memory allows.
+// in tensor memory:
+//   S_t = Q_t K^T   M 128, N 64, K 128   (8 instructions of K 16; Q and K from shared memory),
+//                   two S buffers per row tile
+//   O_t += P_t V    M 128, N 128, K 64   (4 instructions; P from TENSOR MEMORY, where the softmax
+//                   wrote it over the S buffer it came from; V from shared memory as an N-major
+//                   operand)
+// so that one K / V tile, converted from int8 ONCE, serves 256 query rows.
 //
 // Roles by warp (14 warps; every hand-over is an mbarrier, every wait on one is bounded):
-//   warp 0      producer: looks 32 positions at a time up in the page table and fetches their raw
+//   warp 0      producer: looks the tile's 64 positions up in the page table and fetches their raw
 //               K and V code rows with bulk asynchronous copies (TMA engine, cp.async.bulk into this
 //               CTA's own shared memory, no multicast; one 2 KB copy per 16-token page where the
 //               rows are consecutive, else 128 bytes per row) and their scales with 4-byte
 //               cp.async, into a three-stage ring;
 //   warp 1      allocates the tensor memory; one thread issues every MMA and commits them to the
-//               barriers of whoever waits for the result: per tile and row tile, P V of the first
-//               half as soon as its P is written, P V of the second half likewise, directly followed
-//               by that row tile's S for the next tile, which overwrites the buffer the P V reads
-//               (MMAs execute in issue order, so no barrier is needed between them);
+//               barriers of whoever waits for the result: per tile, first S of the NEXT tile for both
+//               row tiles (into the S buffer that tile j - 1 used), then P V of this tile for each
+//               row tile as soon as its P is written. The tensor cores thus work on tile j + 1's
+//               logits while the softmax of tile j runs; an S overwrites the buffer a P V of two
+//               tiles ago read, and MMAs execute in issue order, so no barrier is needed between them;
 //   warps 4-7   softmax of row tile 0, warps 8-11 of row tile 1: a thread owns one row (its
-//               tensor-memory lane): per half tile it reads its 64 logits (tcgen05.ld), applies the
-//               column factor (K scale x softmax scale) minus the running maximum in one FMA and the
-//               causal mask, exponentiates, sums, and writes the probabilities as f16 pairs back over
-//               the logits (tcgen05.st). This common sweep does not look for a new maximum: a sum
-//               below 2^12 proves every term fits f16. Only otherwise (and in a row's first tile) is
-//               the half tile's maximum taken, O rescaled in tensor memory (after the P V before it
-//               is known complete) and the sweep repeated; the final division uses the same maximum
-//               as every sum, so the result does not depend on when the maximum moved;
+//               tensor-memory lane): reads its 64 logits (tcgen05.ld), applies the column factor
+//               (K scale x softmax scale) and the causal mask, keeps the running maximum and sum,
+//               and writes the probabilities as f16 pairs back over the logits (tcgen05.st). The
+//               accumulator O is rescaled in tensor memory only when a tile's maximum exceeds the
+//               running one by more than 2^12 (the final division uses the same maximum, so the
+//               result does not depend on when the rescale happens), and only then does a tile
+//               wait for the previous P V;
 //   warps 2-3, 12-13  converters: int8 codes -> f16, written as 128-byte-swizzled tiles
-//               ([position][64 dims] twice), two buffers: K as the exact codes, K-major for
+//               ([position][64 dims] twice), three buffers: K as the exact codes, K-major for
 //               S = Q K^T; V as code x scale and, the same byte layout, N-major for P V.
 // The K scale multiplies the logit in f32, so K's operand holds the codes exactly; Q is scaled by
 // one power of two per CTA into f16's range. Arithmetic against the reference's golden pipeline
@@ -68,16 +67,15 @@ constexpr int kD = 128;      // head dim
 constexpr int kQPos = 32;    // query positions per row tile (x 4 heads = 128 MMA rows)
 constexpr int kRowTiles = 2;
 constexpr int kCtaPos = kQPos * kRowTiles;  // 64 query positions per CTA
-constexpr int kTN = 128;     // cache positions per tile
-constexpr int kHalf = 64;    // positions per half tile: the unit of the softmax and of a P V group
-constexpr int kRawPos = 32;  // positions per raw stage
+constexpr int kTN = 64;      // cache positions per tile
 constexpr int kThreads = 448;  // 14 warps: four on two of the SM's sub-partitions, so 128 registers per thread
-constexpr int kBufs = 2;  // converted K / V buffers
+constexpr int kBufs = 3;  // converted K / V buffers
 constexpr int kRaw = 3;   // raw stages
 
 constexpr uint32_t kQTileBytes = 128 * kD * 2;     // 32768: two 64-dim halves of [128 rows][128 bytes]
-constexpr uint32_t kKvTileBytes = kTN * kD * 2;    // 32768: two 64-dim halves of [128 positions][128 bytes]
-constexpr uint32_t kRawBytes = kRawPos * kD;       // 4096 per matrix and stage
+constexpr uint32_t kKvTileBytes = kTN * kD * 2;    // 16384: two 64-dim halves of [64 positions][128 bytes]
+constexpr uint32_t kPTileBytes = 128 * kTN * 2;    // 16384: [128 rows][128 bytes]
+constexpr uint32_t kRawBytes = kTN * kD;           // 8192 per matrix and stage
 
 struct TcSmem {
   // swizzled operand tiles first: each sits on a 1024-byte boundary
@@ -86,11 +84,10 @@ struct TcSmem {
   uint8_t v16[kBufs][kKvTileBytes];
   uint8_t raw_k[kRaw][kRawBytes];
   uint8_t raw_v[kRaw][kRawBytes];
-  float raw_ks[kRaw][kRawPos], raw_vs[kRaw][kRawPos];  // scales of the raw stages
+  float raw_ks[kRaw][kTN], raw_vs[kRaw][kTN];  // scales of the raw stages
   float cs[kBufs][kTN];  // per converted K tile: K scale x softmax scale x log2(e) x the power of two taken out of Q
   uint64_t raw_full[kRaw], raw_empty[kRaw], kv_full[kBufs], kv_empty[kBufs];
-  // per row tile: S of a tile complete; per row tile and half tile: P written / that half's P V complete
-  uint64_t s_full[kRowTiles], p_full[kRowTiles][2], pv_done[kRowTiles][2];
+  uint64_t s_full[kRowTiles][2], p_full[kRowTiles][2], pv_done[kRowTiles][2];
   uint64_t q_ready;
   uint32_t q_amax;  // max |q| over the CTA's rows, as float bits
   uint32_t tmem_base;
@@ -113,14 +110,13 @@ struct TcParams {
   float scale_log2;
 };
 
-// tensor-memory columns: S[t] 128 each (the logits of a tile; the f16 probabilities of half tile h go
-// over its columns 64 h .. 64 h + 31), then O[t] 128 each
+// tensor-memory columns: S[t][buffer] 64 each, then O[t] 128 each
 constexpr uint32_t kTmemCols = 512;
-__device__ __forceinline__ uint32_t s_col(int t) { return uint32_t(t * kTN); }
+__device__ __forceinline__ uint32_t s_col(int t, int sb) { return uint32_t((t * 2 + sb) * kTN); }
 __device__ __forceinline__ uint32_t o_col(int t) { return uint32_t(256 + t * kD); }
 
 // Instruction descriptors (kind::f16): f32 accumulator, f16 x f16, M 128.
-constexpr uint32_t kIdescS = (1u << 4) | (uint32_t(kTN >> 3) << 17) | (uint32_t(128 >> 4) << 24);             // N 128, both K-major
+constexpr uint32_t kIdescS = (1u << 4) | (uint32_t(kTN >> 3) << 17) | (uint32_t(128 >> 4) << 24);             // N 64, both K-major
 constexpr uint32_t kIdescPV = (1u << 4) | (1u << 16) | (uint32_t(kD >> 3) << 17) | (uint32_t(128 >> 4) << 24);  // N 128, B N-major
 
 // P V with P in tensor memory: D (+)= A (tensor memory: lane = row, a 32-bit column = two
@@ -241,8 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
   const int row0 = blk * kCtaPos;                           // first chunk row of this CTA
   const int nrows = min(kCtaPos, p.rows - row0);            // its live rows
   const int kv_end = p.base_pos + row0 + nrows;             // cache positions [0, kv_end) are needed
-  const int n_kv = (kv_end + kTN - 1) / kTN;                // tiles of 128 positions
-  const int n_raw = n_kv * (kTN / kRawPos);                 // raw stages of 32 positions
+  const int n_kv = (kv_end + kTN - 1) / kTN;
   const size_t head_row0 = static_cast<size_t>(hkv) * p.stride;
 
   if (threadIdx.x == 0) {
@@ -255,8 +250,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
       mbar_init(&sm->kv_empty[i], 1);
     }
     for (int t = 0; t < kRowTiles; ++t) {
-      mbar_init(&sm->s_full[t], 1);
-      for (int i = 0; i < 2; ++i) mbar_init(&sm->pv_done[t][i], 1), mbar_init(&sm->p_full[t][i], 4);
+      // one barrier of each kind per S buffer: the warps of a row tile may be a tile apart, never two
+      for (int i = 0; i < 2; ++i)
+        mbar_init(&sm->s_full[t][i], 1), mbar_init(&sm->pv_done[t][i], 1), mbar_init(&sm->p_full[t][i], 4);
     }
     mbar_init(&sm->q_ready, 8);
     sm->abort = 0;
@@ -272,27 +268,32 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
 
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------
-    // a raw stage is 32 positions: lane l fetches position l of it
-    auto row_of = [&](int r) {
-      const int pa = min(r * kRawPos + lane, kv_end - 1);  // past the end: a row that is masked anyway
-      const int a = p.pt != nullptr ? __ldg(p.pt + pa) : pa;
-      return min(max(a, 0), static_cast<int>(p.stride) - 1);
+    // lane l fetches positions l and l + 32 of every tile
+    auto rows_of = [&](int j, int& a, int& b) {
+      const int pa = min(j * kTN + lane, kv_end - 1), pb = min(j * kTN + 32 + lane, kv_end - 1);  // past the end: a row that is masked anyway
+      a = p.pt != nullptr ? __ldg(p.pt + pa) : pa;
+      b = p.pt != nullptr ? __ldg(p.pt + pb) : pb;
+      a = min(max(a, 0), static_cast<int>(p.stride) - 1), b = min(max(b, 0), static_cast<int>(p.stride) - 1);
     };
-    int ra = row_of(0), na = n_raw > 1 ? row_of(1) : 0;  // a table entry is read two stages ahead
-    for (int r = 0; r < n_raw; ++r) {
-      const int s = r % kRaw;
-      if (!wait_tc(&sm->raw_empty[s], ((r / kRaw) & 1) ^ 1, sm, p.status)) break;
+    int ra, rb, na = 0, nb = 0;  // this tile's rows and the next tile's: a table entry is read two tiles ahead
+    rows_of(0, ra, rb);
+    if (n_kv > 1) rows_of(1, na, nb);
+    for (int j = 0; j < n_kv; ++j) {
+      const int s = j % kRaw;
+      if (!wait_tc(&sm->raw_empty[s], ((j / kRaw) & 1) ^ 1, sm, p.status)) break;
       if (lane == 0) mbar_arrive_expect_tx(&sm->raw_full[s], 2u * kRawBytes);
       __syncwarp();
       // A group of 16 consecutive positions usually is one page of the pool, i.e. 16 consecutive pool
       // rows: one 2 KB copy per matrix then replaces 16 copies of 128 bytes (the copy engine takes a
-      // few dozen cycles per request whatever its size). Lanes 0-15 / 16-31 hold groups 0 / 1.
-      const int first = __shfl_sync(0xffffffffu, ra, lane & 16);
-      const unsigned run = __ballot_sync(0xffffffffu, ra == first + (lane & 15));
+      // few dozen cycles per request whatever its size). Lanes 0-15 / 16-31 hold groups 0 / 1 in ra and
+      // groups 2 / 3 in rb.
+      const int first_a = __shfl_sync(0xffffffffu, ra, lane & 16), first_b = __shfl_sync(0xffffffffu, rb, lane & 16);
+      const unsigned run_a = __ballot_sync(0xffffffffu, ra == first_a + (lane & 15));
+      const unsigned run_b = __ballot_sync(0xffffffffu, rb == first_b + (lane & 15));
       const unsigned mine = 0xffffu << (lane & 16);
-      const bool page = (run & mine) == mine;
-      const size_t oa = (head_row0 + ra) * kD;
-      if (page) {
+      const bool page_a = (run_a & mine) == mine, page_b = (run_b & mine) == mine;
+      const size_t oa = (head_row0 + ra) * kD, ob = (head_row0 + rb) * kD;
+      if (page_a) {
         if ((lane & 15) == 0) {
           bulk_load(sm->raw_k[s] + lane * kD, p.ck + oa, 16 * kD, &sm->raw_full[s]);
           bulk_load(sm->raw_v[s] + lane * kD, p.cv + oa, 16 * kD, &sm->raw_full[s]);
@@ -301,70 +302,69 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
         bulk_load(sm->raw_k[s] + lane * kD, p.ck + oa, kD, &sm->raw_full[s]);
         bulk_load(sm->raw_v[s] + lane * kD, p.cv + oa, kD, &sm->raw_full[s]);
       }
+      if (page_b) {
+        if ((lane & 15) == 0) {
+          bulk_load(sm->raw_k[s] + (32 + lane) * kD, p.ck + ob, 16 * kD, &sm->raw_full[s]);
+          bulk_load(sm->raw_v[s] + (32 + lane) * kD, p.cv + ob, 16 * kD, &sm->raw_full[s]);
+        }
+      } else {
+        bulk_load(sm->raw_k[s] + (32 + lane) * kD, p.ck + ob, kD, &sm->raw_full[s]);
+        bulk_load(sm->raw_v[s] + (32 + lane) * kD, p.cv + ob, kD, &sm->raw_full[s]);
+      }
       cp_async4(&sm->raw_ks[s][lane], p.ks + head_row0 + ra);
+      cp_async4(&sm->raw_ks[s][32 + lane], p.ks + head_row0 + rb);
       cp_async4(&sm->raw_vs[s][lane], p.vs + head_row0 + ra);
+      cp_async4(&sm->raw_vs[s][32 + lane], p.vs + head_row0 + rb);
       cp_async_arrive_noinc(&sm->raw_full[s]);
-      ra = na;
-      if (r + 2 < n_raw) na = row_of(r + 2);
+      ra = na, rb = nb;
+      if (j + 2 < n_kv) rows_of(j + 2, na, nb);
     }
   } else if (warp == 1) {
     // ---- MMA issue ----------------------------------------------------------------------------
-    // One thread issues every MMA; it is the busiest thread of the CTA, and an MMA costs it about
-    // the same whatever its shape, so the shapes are as large as tensor memory allows (S: N 128) and
-    // its instruction count per MMA is kept at the minimum: the descriptors of Q are formed once,
-    // those of a tile's K and V once per tile (both row tiles use them), four MMAs per asm statement.
+    // One thread issues every MMA; it is the busiest thread of the CTA (29 MMAs and commits per
+    // tile), so its instruction count per MMA is kept at the minimum: the descriptors of Q are
+    // formed once, those of a tile's K and V once per tile (both row tiles use them), and four MMAs
+    // go out per asm statement.
     if (lane == 0) {
       bool ok = wait_tc(&sm->q_ready, 0, sm, p.status);
       const uint32_t q_lo = (smem_u32(sm->q16[0]) >> 4) | (1u << 16), k_lo = (smem_u32(sm->k16[0]) >> 4) | (1u << 16);
-      const uint32_t v_lo = (smem_u32(sm->v16[0]) >> 4) | ((kKvTileBytes / 2 >> 4) << 16);  // 64-dim halves 16 KB apart
+      const uint32_t v_lo = (smem_u32(sm->v16[0]) >> 4) | ((kKvTileBytes / 2 >> 4) << 16);  // 64-dim halves 8 KB apart
       uint64_t qd[kRowTiles][8];
 #pragma unroll
       for (int t = 0; t < kRowTiles; ++t)
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // 16 dims = 32 bytes per instruction; dims 64.. in the second half tile
           qd[t][kk] = desc_of(q_lo + ((t * kQTileBytes + (kk >> 2) * (kQTileBytes / 2) + (kk & 3) * 32) >> 4));
-      uint32_t kbase = 0;  // low descriptor word of the K tile of the S being issued
-      auto issue_s = [&](int t) {
+      auto issue_s = [&](int j) {
+        const int b = j % kBufs, sb = j & 1;
+        if (!(ok = ok && wait_tc(&sm->kv_full[b], (j / kBufs) & 1, sm, p.status))) return;
+        tc_fence_after();
         uint64_t kd[8];
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) kd[kk] = desc_of(kbase + (((kk >> 2) * (kKvTileBytes / 2) + (kk & 3) * 32) >> 4));
-        mma4_ss(tmem_base + s_col(t), qd[t][0], kd[0], qd[t][1], kd[1], qd[t][2], kd[2], qd[t][3], kd[3], kIdescS, 0u);
-        mma4_ss(tmem_base + s_col(t), qd[t][4], kd[4], qd[t][5], kd[5], qd[t][6], kd[6], qd[t][7], kd[7], kIdescS, 1u);
-        mma_commit<false>(smem_u32(&sm->s_full[t]));
-      };
-      if (ok && (ok = wait_tc(&sm->kv_full[0], 0, sm, p.status))) {
-        tc_fence_after();
-        kbase = k_lo;
-        issue_s(0);
-        issue_s(1);
-      }
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int b = j & 1;
-        const uint32_t vbase = v_lo + ((b * kKvTileBytes) >> 4);
-        for (int t = 0; t < kRowTiles && ok; ++t) {
+        for (int kk = 0; kk < 8; ++kk)
+          kd[kk] = desc_of(k_lo + ((b * kKvTileBytes + (kk >> 2) * (kKvTileBytes / 2) + (kk & 3) * 32) >> 4));
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            // 16 positions per instruction: 8 columns of P, two 8-row groups of V (2 KB)
-            if (!(ok = ok && wait_tc(&sm->p_full[t][h], j & 1, sm, p.status))) break;
-            tc_fence_after();
-            const uint32_t vb = vbase + ((h * 4 * 2048) >> 4);
-            mma4_ts(tmem_base + o_col(t), tmem_base + s_col(t) + h * kHalf, desc_of(vb), desc_of(vb + (2048 >> 4)),
-                    desc_of(vb + (4096 >> 4)), desc_of(vb + (6144 >> 4)), kIdescPV, (j > 0 || h > 0) ? 1u : 0u);
-            mma_commit<false>(smem_u32(&sm->pv_done[t][h]));
-          }
-          if (!ok) break;
-          if (t == kRowTiles - 1) mma_commit<false>(smem_u32(&sm->kv_empty[b]));  // every MMA that reads tile j is issued
-          // this row tile's S of the next tile follows its P V directly: it overwrites the buffer that
-          // P V reads, and MMAs execute in issue order
-          if (j + 1 < n_kv) {
-            if (t == 0) {
-              if (!(ok = wait_tc(&sm->kv_full[b ^ 1], ((j + 1) >> 1) & 1, sm, p.status))) break;
-              tc_fence_after();
-              kbase = k_lo + (((b ^ 1) * kKvTileBytes) >> 4);
-            }
-            issue_s(t);
-          }
+        for (int t = 0; t < kRowTiles; ++t) {
+          mma4_ss(tmem_base + s_col(t, sb), qd[t][0], kd[0], qd[t][1], kd[1], qd[t][2], kd[2], qd[t][3], kd[3], kIdescS, 0u);
+          mma4_ss(tmem_base + s_col(t, sb), qd[t][4], kd[4], qd[t][5], kd[5], qd[t][6], kd[6], qd[t][7], kd[7], kIdescS, 1u);
+          mma_commit<false>(smem_u32(&sm->s_full[t][sb]));
         }
+      };
+      if (ok) issue_s(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) issue_s(j + 1);
+        const int b = j % kBufs, sb = j & 1;
+        uint64_t vd[4];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // 16 positions per instruction: 8 columns of P, two 8-row groups of V
+          vd[kk] = desc_of(v_lo + ((b * kKvTileBytes + kk * 2048) >> 4));
+        for (int t = 0; t < kRowTiles && ok; ++t) {
+          if (!(ok = wait_tc(&sm->p_full[t][sb], (j >> 1) & 1, sm, p.status))) break;
+          tc_fence_after();
+          mma4_ts(tmem_base + o_col(t), tmem_base + s_col(t, sb), vd[0], vd[1], vd[2], vd[3], kIdescPV, j > 0 ? 1u : 0u);
+          mma_commit<false>(smem_u32(&sm->pv_done[t][sb]));
+        }
+        if (ok) mma_commit<false>(smem_u32(&sm->kv_empty[b]));
       }
     }
   } else if (warp < 4 || warp >= 12) {
@@ -375,45 +375,46 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
     bool okc = wait_tc(&sm->q_ready, 0, sm, p.status);
     const float col_scale = p.scale_log2 * q_up_factor(sm->q_amax);
     for (int j = 0; j < n_kv && okc; ++j) {
-      const int b = j & 1;
-      if (!wait_tc(&sm->kv_empty[b], ((j >> 1) & 1) ^ 1, sm, p.status)) break;
-      for (int q = 0; q < kTN / kRawPos && okc; ++q) {
-        const int r = j * (kTN / kRawPos) + q, s = r % kRaw;
-        if (!(okc = wait_tc(&sm->raw_full[s], (r / kRaw) & 1, sm, p.status))) break;
-        // unit u = (row, piece of 16 codes): a quarter warp reads one whole raw row; its stores land in
-        // eight different 16-byte columns (the lanes of the second half tile write their two chunks in
-        // the other order)
-        uint4 rk[2], rv[2];
+      const int s = j % kRaw, b = j % kBufs;
+      if (!wait_tc(&sm->raw_full[s], (j / kRaw) & 1, sm, p.status)) break;
+      if (!wait_tc(&sm->kv_empty[b], ((j / kBufs) & 1) ^ 1, sm, p.status)) break;
+      // unit u = (row, piece of 16 codes): a quarter warp reads one whole raw row; its stores land in
+      // eight different 16-byte columns (the lanes of the second half tile write their two chunks in
+      // the other order)
+      uint4 raw[4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          rk[i] = *reinterpret_cast<const uint4*>(sm->raw_k[s] + (i * 128 + c) * 16);
-          rv[i] = *reinterpret_cast<const uint4*>(sm->raw_v[s] + (i * 128 + c) * 16);
-        }
+      for (int i = 0; i < 4; ++i) raw[i] = *reinterpret_cast<const uint4*>(sm->raw_k[s] + (i * 128 + c) * 16);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int u = i * 128 + c, row = u >> 3, piece = u & 7;
-          const int half = piece >> 2, ch = (piece & 3) * 2, flip = half;
-          const int trow = q * kRawPos + row;  // row of the 128-position tile
-          uint4 lo, hi;
-          codes16_to_half(rk[i], lo, hi);
-          uint8_t* kt = sm->k16[b] + half * (kKvTileBytes / 2);
-          *reinterpret_cast<uint4*>(kt + sw128(trow, ch + flip)) = flip ? hi : lo;
-          *reinterpret_cast<uint4*>(kt + sw128(trow, ch + 1 - flip)) = flip ? lo : hi;
-          codes16_to_half(rv[i], lo, hi);
-          const __half2 sv = __float2half2_rn(sm->raw_vs[s][row]);  // V = code x scale, rounded to f16
-          mul8(lo, sv), mul8(hi, sv);
-          uint8_t* vt = sm->v16[b] + half * (kKvTileBytes / 2);
-          *reinterpret_cast<uint4*>(vt + sw128(trow, ch + flip)) = flip ? hi : lo;
-          *reinterpret_cast<uint4*>(vt + sw128(trow, ch + 1 - flip)) = flip ? lo : hi;
-        }
-        if (c < kRawPos) sm->cs[b][q * kRawPos + c] = sm->raw_ks[s][c] * col_scale;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm->raw_empty[s]));
+      for (int i = 0; i < 4; ++i) {
+        const int u = i * 128 + c, row = u >> 3, piece = u & 7;
+        const int half = piece >> 2, ch = (piece & 3) * 2, flip = half;
+        uint4 lo, hi;
+        codes16_to_half(raw[i], lo, hi);
+        uint8_t* kt = sm->k16[b] + half * (kKvTileBytes / 2);
+        *reinterpret_cast<uint4*>(kt + sw128(row, ch + flip)) = flip ? hi : lo;
+        *reinterpret_cast<uint4*>(kt + sw128(row, ch + 1 - flip)) = flip ? lo : hi;
       }
-      if (!okc) break;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) raw[i] = *reinterpret_cast<const uint4*>(sm->raw_v[s] + (i * 128 + c) * 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int u = i * 128 + c, row = u >> 3, piece = u & 7;
+        const int half = piece >> 2, ch = (piece & 3) * 2, flip = half;
+        uint4 lo, hi;
+        codes16_to_half(raw[i], lo, hi);
+        const __half2 sv = __float2half2_rn(sm->raw_vs[s][row]);  // V = code x scale, rounded to f16
+        mul8(lo, sv), mul8(hi, sv);
+        uint8_t* vt = sm->v16[b] + half * (kKvTileBytes / 2);
+        *reinterpret_cast<uint4*>(vt + sw128(row, ch + flip)) = flip ? hi : lo;
+        *reinterpret_cast<uint4*>(vt + sw128(row, ch + 1 - flip)) = flip ? lo : hi;
+      }
+      if (c < kTN) sm->cs[b][c] = sm->raw_ks[s][c] * col_scale;
       fence_async_smem();  // the tiles are read by the tensor cores (async proxy)
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm->kv_full[b]));
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&sm->kv_full[b]));
+        mbar_arrive(smem_u32(&sm->raw_empty[s]));
+      }
     }
   } else {
     // ---- softmax (warps 4-11): row tile t, tensor-memory lane = MMA row = (head hl, position pl) -----------------
@@ -460,114 +461,90 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const TcPa
     // finite maximum: all its logits are masked and it never looks for one.
     float m_run = live ? -INFINITY : 0.0f, l_run = 0.0f;
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const int b = j & 1;
-      if (!(ok = wait_tc(&sm->s_full[t], j & 1, sm, p.status))) break;
+    for (int j = 0; j < n_kv; ++j) {
+      const int sb = j & 1, b = j % kBufs;
+      if (!(ok = wait_tc(&sm->s_full[t][sb], (j >> 1) & 1, sm, p.status))) break;
       tc_fence_after();
+      const int kv0 = j * kTN;
+      const uint32_t s_addr = lane_addr + s_col(t, sb);
+      // only a tile that reaches past the warp's first position needs the causal mask (warp-uniform)
+      const bool masked = !all_live || kv0 + kTN - 1 > pos_first;
+      const float4* cs4 = reinterpret_cast<const float4*>(sm->cs[b]);
+      // One sweep over the row's 64 logits computes the probabilities against the maximum the row has
+      // had so far, and the tile's own maximum on the side. The running maximum is replaced only when
+      // a tile exceeds it by more than 2^12 (always so in the first tile): then O and the sum are
+      // rescaled and the sweep is repeated against the new maximum. Probabilities therefore stay below
+      // 2^12, inside f16, and the final division uses the same maximum as every sum, so the result
+      // does not depend on when the maximum moved.
+      uint32_t pk[32];
+      float l_tile = 0.0f;
 #pragma unroll 1
-      for (int h = 0; h < 2 && ok; ++h) {  // the tile's two halves of 64 positions, each with its own P V group
-        const int kv0 = j * kTN + h * kHalf;
-        const uint32_t s_addr = lane_addr + s_col(t) + h * kHalf;
-        // only a half tile that reaches past the warp's first position needs the causal mask (warp-uniform)
-        const bool masked = !all_live || kv0 + kHalf - 1 > pos_first;
-        const float4* cs4 = reinterpret_cast<const float4*>(sm->cs[b] + h * kHalf);
-        // The common sweep over the row's 64 logits only exponentiates against the maximum the row has
-        // had so far (one FMA, one ex2, one add and half a conversion per logit) and does not look for
-        // a new maximum. It is valid while every probability stays inside f16, which the sum shows: a
-        // sum below 2^12 has no term above 2^12. Otherwise (and in a row's first tile, where there is
-        // no maximum yet) a second kind of sweep finds the half tile's maximum, the running maximum
-        // moves up to it, O and the sum are rescaled, and the common sweep is repeated - every term is
-        // then at most 1. The final division uses the same maximum as every sum, so the result does
-        // not depend on when the maximum moved.
-        uint32_t pk[32];
-        float l_tile = 0.0f;
-        bool need_max = m_run == -INFINITY;
-#pragma unroll 1
-        for (int attempt = 0; attempt < 2; ++attempt) {
-          uint32_t v2[2][32];  // both halves of the 64 logits are requested before the first is waited for
-          tmem_ld32(s_addr, v2[0]);
-          tmem_ld32(s_addr + 32, v2[1]);
-          tmem_ld_wait();
-          if (__any_sync(0xffffffffu, need_max)) {
-            float m_tile = -INFINITY;
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        const float base = m_run == -INFINITY ? 0.0f : m_run;
+        float m_tile = -INFINITY;
+        l_tile = 0.0f;
+        uint32_t v2[2][32];  // both halves of the row are requested before the first is waited for
+        tmem_ld32(s_addr, v2[0]);
+        tmem_ld32(s_addr + 32, v2[1]);
+        tmem_ld_wait();
 #pragma unroll
-            for (int hc = 0; hc < 2; ++hc) {
+        for (int hc = 0; hc < 2; ++hc) {
+          const uint32_t(&v)[32] = v2[hc];
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                const float4 c4 = cs4[hc * 8 + (i >> 2)];
-                float y[4] = {__uint_as_float(v2[hc][i]) * c4.x, __uint_as_float(v2[hc][i + 1]) * c4.y,
-                              __uint_as_float(v2[hc][i + 2]) * c4.z, __uint_as_float(v2[hc][i + 3]) * c4.w};
-                if (masked) {
+          for (int i = 0; i < 32; i += 4) {
+            const float4 c4 = cs4[hc * 8 + (i >> 2)];
+            float y[4] = {__uint_as_float(v[i]) * c4.x, __uint_as_float(v[i + 1]) * c4.y, __uint_as_float(v[i + 2]) * c4.z,
+                          __uint_as_float(v[i + 3]) * c4.w};
+            if (masked) {
 #pragma unroll
-                  for (int e = 0; e < 4; ++e)
-                    if (kv0 + hc * 32 + i + e > pos) y[e] = -INFINITY;
-                }
-                m_tile = fmaxf(fmaxf(m_tile, fmaxf(y[0], y[1])), fmaxf(y[2], y[3]));
-              }
+              for (int e = 0; e < 4; ++e)
+                if (kv0 + hc * 32 + i + e > pos) y[e] = -INFINITY;
             }
-            const float m_new = fmaxf(m_run, m_tile);
-            const float corr = (m_new > m_run && m_run > -INFINITY) ? ex2_approx(m_run - m_new) : 1.0f;
-            l_run *= corr;
-            m_run = m_new;
-            if (j > 0 || h > 0) {
-              // O has to shrink: it is complete (and nobody adds to it) once the P V group issued before
-              // this one is done - the other half of this tile, or the second half of the tile before.
-              // That barrier completes once per tile and cannot run ahead of this warp (the next
-              // completion needs this warp's P), so its parity names the phase.
-              const int ph = h == 1 ? 0 : 1, pj = h == 1 ? j : j - 1;
-              if (!(ok = wait_tc(&sm->pv_done[t][ph], pj & 1, sm, p.status))) break;
-              tc_fence_after();
-#pragma unroll 1
-              for (int oc = 0; oc < 4; ++oc) {
-                uint32_t v[32];
-                tmem_ld32(lane_addr + o_col(t) + oc * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                tmem_st32(lane_addr + o_col(t) + oc * 32, v);
-              }
-            }
-            need_max = false;
+            m_tile = fmaxf(fmaxf(m_tile, fmaxf(y[0], y[1])), fmaxf(y[2], y[3]));
+            const float p0 = ex2_approx(y[0] - base), p1 = ex2_approx(y[1] - base), p2 = ex2_approx(y[2] - base),
+                        p3 = ex2_approx(y[3] - base);
+            l_tile += (p0 + p1) + (p2 + p3);
+            const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+            pk[hc * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&h01);
+            pk[hc * 16 + (i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&h23);
           }
-          const float nbase = m_run == -INFINITY ? 0.0f : -m_run;
-          l_tile = 0.0f;
-#pragma unroll
-          for (int hc = 0; hc < 2; ++hc) {
-            const uint32_t(&v)[32] = v2[hc];
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const float4 c4 = cs4[hc * 8 + (i >> 2)];
-              float y[4] = {fmaf(__uint_as_float(v[i]), c4.x, nbase), fmaf(__uint_as_float(v[i + 1]), c4.y, nbase),
-                            fmaf(__uint_as_float(v[i + 2]), c4.z, nbase), fmaf(__uint_as_float(v[i + 3]), c4.w, nbase)};
-              if (masked) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  if (kv0 + hc * 32 + i + e > pos) y[e] = -INFINITY;
-              }
-              const float p0 = ex2_approx(y[0]), p1 = ex2_approx(y[1]), p2 = ex2_approx(y[2]), p3 = ex2_approx(y[3]);
-              l_tile += (p0 + p1) + (p2 + p3);
-              const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
-              pk[hc * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&h01);
-              pk[hc * 16 + (i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&h23);
-            }
-          }
-          need_max = !(l_tile < 4096.0f);  // a term may have left f16's range (or the sum is not a number)
-          if (attempt == 1 || !__any_sync(0xffffffffu, need_max)) break;
         }
-        if (!ok) break;
-        l_run += l_tile;
-        // The probabilities go over the first 32 columns of the 64 logits they came from; nothing else
-        // reads or writes those columns until this half's P V, and the S of the next tile is issued
-        // after that P V.
-        tmem_st32(s_addr, pk);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[t][h]));
+        const bool grow = m_tile > m_run + 12.0f;  // also true for the first live logits (m_run = -inf)
+        if (attempt == 1 || !__any_sync(0xffffffffu, grow)) break;
+        const float m_new = grow ? m_tile : m_run;
+        const float corr = (grow && m_run > -INFINITY) ? ex2_approx(m_run - m_new) : 1.0f;
+        l_run *= corr;
+        m_run = m_new;
+        if (j > 0) {
+          // O has to shrink: it is complete (and nobody adds to it) once the previous tile's P V is done
+          if (!(ok = wait_tc(&sm->pv_done[t][(j - 1) & 1], ((j - 1) >> 1) & 1, sm, p.status))) break;
+          tc_fence_after();
+#pragma unroll 1
+          for (int oc = 0; oc < 4; ++oc) {
+            uint32_t v[32];
+            tmem_ld32(lane_addr + o_col(t) + oc * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+            tmem_st32(lane_addr + o_col(t) + oc * 32, v);
+          }
+        }
       }
+      if (!ok) break;
+      l_run += l_tile;
+      // The probabilities go over the first 32 columns of the logits they came from. That buffer last
+      // held P of tile j - 2, and S of tile j, issued after that tile's P V, has completed: MMAs
+      // complete in issue order, so nothing reads the old P any more and no wait is needed here.
+      // (P V completions of even and odd tiles are counted on two barriers, so that a thread which
+      // has not looked at them for a tile or two still reads the right phase when it has to.)
+      tmem_st32(s_addr, pk);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[t][sb]));
     }
     // ---- the finished row: O / l -> bf16
-    if (ok && n_kv > 0) ok = wait_tc(&sm->pv_done[t][1], (n_kv - 1) & 1, sm, p.status);
+    if (ok && n_kv > 0) ok = wait_tc(&sm->pv_done[t][(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, sm, p.status);
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;

@@ -5,8 +5,7 @@ Oracle: the reference's golden bf16 pipeline (engine/src/kernel_math.h:265-331) 
 pool, one row at a time. Tolerances as for every attention kernel here: 0.03 absolute against that
 pipeline (engine/tests/test_kernels.cu:2055), 0.01 against an unrounded float64 evaluation.
 Random pools with random per-row scales, permuted page tables, chunks that start at position 0 and
-chunks that continue a prefix, row counts that are and are not multiples of the 64-row CTA tile,
-prefixes that are and are not multiples of the 128-position cache tile.
+chunks that continue a prefix, row counts that are and are not multiples of the 64-row CTA tile.
 """
 import numpy as np
 import pytest
@@ -109,9 +108,8 @@ def test_tensor_core_form_against_the_oracle_and_the_mma_sync_form(K, port, monk
 
 def test_peaked_softmax_rescales_the_accumulator(K, monkeypatch):
     """Queries of magnitude ~60: logits spread over some +-25 binary orders, so that along a prefix
-    the exponentials against the running maximum leave f16's range several times (a half tile's sum
-    reaches 2^12): the maximum is then taken anew and the accumulator rescaled in tensor memory; a
-    few keys are made dominant late in the prefix. At these magnitudes the golden
+    the running maximum jumps by more than 2^12 several times: the accumulator is then rescaled in
+    tensor memory; a few keys are made dominant late in the prefix. At these magnitudes the golden
     pipeline's own bf16 rounding of the logits is the larger error, so the yardsticks are the
     unrounded float64 evaluation and the mma.sync form."""
     rows, stride = 192, 512
@@ -129,3 +127,21 @@ def test_peaked_softmax_rescales_the_accumulator(K, monkeypatch):
     tbl = np.arange(stride, dtype=np.int32)
     exact = f64_rows(qb[sel], (ck, cv, ks, vs), [tbl] * len(sel), sel.astype(np.int32))
     assert close(f32_of(got[sel]).reshape(len(sel), Hq, D), exact, 0.02)
+
+
+def test_a_query_head_that_is_not_a_number_stays_in_its_rows(K):
+    """One head of one query row is NaN: that row and head come out NaN, every other output is what it
+    is without the NaN to a bf16 step (rows do not share softmax state), and no wait runs out."""
+    rows, stride = 200, 512
+    pl = pool(11, stride)
+    rng = np.random.default_rng(12)
+    q = bf16_bits(rng.standard_normal((rows, Hq * D)))
+    clean = run(K, q, pl, 0, stride, None)
+    q2 = q.copy()
+    q2[70, 5 * D:6 * D] = 0x7FC0
+    got = run(K, q2, pl, 0, stride, None).reshape(rows, Hq, D)
+    clean = clean.reshape(rows, Hq, D)
+    assert (got[70, 5] & 0x7FFF > 0x7F80).all()
+    keep = np.ones((rows, Hq), bool)
+    keep[70, 5] = False
+    assert close(f32_of(got[keep]), f32_of(clean[keep]), 0.0)  # (when a maximum moves may differ within the warp)
