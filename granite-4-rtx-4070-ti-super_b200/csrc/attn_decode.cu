@@ -83,6 +83,7 @@ struct AttnParams {
   long long stride;
   int splits, split_len, max_len;
   float scale_log2;  // scale * log2(e)
+  int early;         // every CTA of the grid is resident at once: the kernel after this one may be staged right away
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -210,6 +211,9 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
 template <int NT, bool EXT>
 __global__ void __launch_bounds__(kWarps * 32, NT == 1 ? kCtasPerSmT : kCtasPerSm)
     attn_decode_t_kernel(const AttnParams p) {
+  // (a decode-size grid fits the device in one wave, so CTAs of the next kernel that are staged early
+  // take nothing from CTAs of this one that are still to start)
+  if (p.early) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   pdl_begin();
   extern __shared__ __align__(128) unsigned char s_dyn[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -714,6 +718,7 @@ int attn_launch(const char* fn, const uint16_t* d_q, const int8_t* d_cache_k, co
     }
   }
   const dim3 grid(static_cast<unsigned>(s.splits), static_cast<unsigned>(Hk), static_cast<unsigned>(s.groups));
+  p.early = static_cast<long long>(s.splits) * Hk * s.groups <= 3ll * sm_count() ? 1 : 0;
   const bool ext = r.window > 0 || r.d_row_tail != nullptr;
   if (rows_per_group <= 2) {
     if (ext) G4_LAUNCH_PDL(fn, (attn_decode_t_kernel<1, true>), grid, dim3(kWarps * 32), kAttnSmemBytesT, st, p);

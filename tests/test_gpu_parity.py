@@ -1887,6 +1887,29 @@ def test_gemm_fp8_decode_rows_split_k_is_deterministic_and_reusable(K, port, mon
                 (np.abs(_bf16_to_f32_np(host(out)) - _bf16_to_f32_np(want)) <= 4e-4 * mag)).all()
 
 
+def test_gemm_fp8_split_workspace_is_left_clean_and_must_be_zero(K, monkeypatch):
+    """The contract of the split-K workspace: zero before the first use, left clean by every call that
+    returns 0 with device status 0 (so it is handed from call to call), and to be zeroed again by the
+    caller if it was ever dirtied - a workspace filled with other bytes and zeroed gives the right
+    result, and the counters at its head read zero after every call."""
+    monkeypatch.setenv("G4_GEMM_DECODE", "0")
+    monkeypatch.setenv("G4_GEMM_STREAM", "0")
+    M, N, Kd = 2, 4096, 4096
+    rng = np.random.default_rng(5)
+    a, w = _codes(rng, (M, Kd)), _codes(rng, (N, Kd))
+    ws = K.gemm_fp8_workspace(M, N, Kd, DEV)
+    assert ws is not None
+    exact, mag = _gemm_f64(a, w, 0.3, (0.01,), (), N)
+    a_scale = torch.tensor([0.3, 0.0], device=DEV)
+    f32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ws.fill_(0xAB)   # a workspace that held something else ...
+    ws.zero_()       # ... is zeroed again by its owner before the library sees it
+    for _ in range(2):
+        assert K.gemm_fp8(dev(a), dev(w), f32, a_scale=a_scale, w_scales=(0.01,), workspace=ws) == 0
+        assert (np.abs(host(f32) - exact) <= 1e-5 * mag + 1e-12).all()
+        assert int(ws[:64].to(torch.int32).sum()) == 0  # the tile counters are back at zero
+
+
 def test_gemm_fp8_pair_and_single_forms_agree(K, monkeypatch):
     """The CTA-pair form (cta_group::2 MMAs) and the single-CTA form add the same products in the
     same order."""
