@@ -1731,7 +1731,8 @@ def test_gemm_fp8_golden_fixture(K):
 
 
 @pytest.mark.parametrize("M,N,Kd,lda,ldc", [(200, 520, 384, 384, 520), (129, 257, 144, 160, 264), (1, 8, 16, 16, 8),
-                                            (77, 250, 96, 96, 251)])
+                                            (77, 250, 96, 96, 251), (5, 250, 96, 96, 251), (16, 520, 1536, 1600, 528),
+                                            (3, 129, 4096, 4096, 136)])
 def test_gemm_fp8_matches_oracle(K, port, M, N, Kd, lda, ldc):
     rng = np.random.default_rng(M * 1000 + N)
     a_full, w = _codes(rng, (M, lda)), _codes(rng, (N, Kd))
