@@ -1911,6 +1911,41 @@ def test_gemm_fp8_split_workspace_is_left_clean_and_must_be_zero(K, monkeypatch)
         assert int(ws[:64].to(torch.int32).sum()) == 0  # the tile counters are back at zero
 
 
+def test_gemm_fp8_decode_form_chain_replayed_from_a_cuda_graph(K):
+    """Three dependent 16-row GEMMs (cluster launches with programmatic dependent launch between them),
+    the last one adding into its own residual, captured into a CUDA graph and replayed: the same bits
+    as the eager calls, replay after replay."""
+    rng = np.random.default_rng(8)
+    M, H, N1 = 4, 4096, 1024
+    a = dev(_codes(rng, (M, H)))
+    w1, w2, w3 = dev(_codes(rng, (N1, H))), dev(_codes(rng, (H, H))), dev(_codes(rng, (N1, H)))
+    sc = torch.tensor([0.3, 0.0], device=DEV)
+    res0 = dev(rand_bf16(9, (M, N1)))
+
+    def chain(o1, o2, o3):
+        assert K.gemm_fp8(a, w1, o1, a_scale=sc, w_scales=(0.01,)) == 0
+        assert K.gemm_fp8(a, w2, o2, a_scale=sc, w_scales=(0.01,)) == 0
+        assert K.gemm_fp8(a, w3, o3, a_scale=sc, w_scales=(0.01,), residual=o3, resid_scale=0.22) == 0
+    e1, e2 = empty_bf16(M, N1), empty_bf16(M, H)
+    e3 = res0.clone()
+    chain(e1, e2, e3)
+    torch.cuda.synchronize()
+    g1, g2, g3 = empty_bf16(M, N1), empty_bf16(M, H), res0.clone()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        chain(g1, g2, g3)  # warm: attributes and cluster queries happen outside capture
+        g3.copy_(res0)
+        st.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            chain(g1, g2, g3)
+        for _ in range(2):
+            g3.copy_(res0)
+            graph.replay()
+            st.synchronize()
+            assert (host(g1) == host(e1)).all() and (host(g2) == host(e2)).all() and (host(g3) == host(e3)).all()
+
+
 def test_gemm_fp8_pair_and_single_forms_agree(K, monkeypatch):
     """The CTA-pair form (cta_group::2 MMAs) and the single-CTA form add the same products in the
     same order."""
