@@ -666,11 +666,15 @@ int granite4_prefill_attention_int8(const uint16_t* d_q_rot, float scale, int Hq
  * granite4_kernel_fp8_encode_with_amax turns a into FP8 codes in one sweep;
  * the 4 I bytes per row of gate|up output never exist.
  * Needs K % 16 == 0, lda % 16 == 0, 16-byte aligned A and W; any M >= 0, any N.
- * d_ws / ws_bytes, as the ws / ws_bytes of prefill_gemm: with one or two rows a
+ * d_ws / ws_bytes, as the ws / ws_bytes of prefill_gemm: with a few rows a
  * GEMM has too few output tiles to occupy the card and splits K across CTAs,
  * which add their partial sums in a fixed order (the result does not depend on
- * scheduling). granite4_gemm_fp8_workspace_bytes(M, N, K) is the size that
- * allows the planned split (0: none wanted, e.g. from three rows on); the buffer must be zeroed once
+ * scheduling). Up to 16 rows the slices of a tile are the CTAs of one
+ * thread-block cluster and exchange their sums through its shared memory: no
+ * workspace is wanted. The older forms (selected by G4_GEMM_DECODE=0 in the
+ * environment, or where the device cannot co-schedule the cluster) split
+ * through d_ws. granite4_gemm_fp8_workspace_bytes(M, N, K) is the size that
+ * allows the planned split (0: none wanted); the buffer must be zeroed once
  * before its first use (every call leaves its first bytes, the tile counters,
  * zero again) and belongs to one call at a time. The counters return to zero
  * only when a call runs to completion: after granite4_b200_device_status
